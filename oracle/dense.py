@@ -1,0 +1,44 @@
+"""Dense goldens: Matmul-AllReduce, AllGather-Matmul, Matmul-ReduceScatter.
+
+Test infrastructure only (see package docstring).
+"""
+import torch
+
+
+def matmul_fp32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """fp32-accumulated product of low-precision operands.
+
+    Follows examples/utils/gen_data.py:45-53 (`torch.matmul(a.to(float32),
+    b.to(float32))`)."""
+    return torch.matmul(a.to(torch.float32), b.to(torch.float32))
+
+
+def golden_matmul_allreduce(a_list, b_list) -> torch.Tensor:
+    """D = sum_r A_r @ B_r, fp32, identical on every rank.
+
+    examples/utils/gen_data.py:66-70 (sum over ranks of the per-rank product)."""
+    out = matmul_fp32(a_list[0], b_list[0])
+    for a, b in zip(a_list[1:], b_list[1:]):
+        out = out + matmul_fp32(a, b)
+    return out
+
+
+def golden_matmul_reduce_scatter(a_list, b_list):
+    """Per-rank row block of the all-reduced product.
+
+    examples/utils/gen_data.py:66-70 builds the summed [M,N] golden; the
+    operator writes rank r's rows [r*M/R,(r+1)*M/R) at byte offset r*size
+    (examples/matmul_reduce_scatter/matmul_reduce_scatter_host.h:70)."""
+    full = golden_matmul_allreduce(a_list, b_list)
+    r = len(a_list)
+    m = full.shape[0] // r
+    return [full[i * m:(i + 1) * m].contiguous() for i in range(r)]
+
+
+def golden_allgather_matmul(a_list, b_list):
+    """C_r = cat(A_0..A_{R-1}) @ B_r, fp32, one output per rank.
+
+    examples/utils/gen_data_allgather_matmul.py:54-64 (per-rank distinct A and
+    B); examples/utils/gen_data.py:63-65 is the same-B special case."""
+    gathered = torch.cat([a.to(torch.float32) for a in a_list], dim=0)
+    return [torch.matmul(gathered, b.to(torch.float32)) for b in b_list]

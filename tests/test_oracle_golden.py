@@ -1,0 +1,189 @@
+"""The CPU oracle against fixtures produced by the reference's own Python golden
+code (tests/golden/make_golden.py) and against the reference's known-answer
+vectors.  CPU only."""
+import os
+
+import numpy as np
+import torch
+
+from oracle import dense, moe, mxquant, swizzle, verify
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+# ---------------------------------------------------------------- MX quant --
+def test_mx_e4m3_rne_bit_exact(golden_dir):
+    f = _load(golden_dir, "mx_quant.npz")
+    codes, scale, deq = mxquant.quantize_mx_e4m3(f["x"], "rne")
+    assert np.array_equal(codes, f["native_codes"])
+    assert np.array_equal(scale, f["native_scale"])
+    assert np.array_equal(deq, f["native_dequant"])
+
+
+def test_mx_e4m3_lut_bit_exact(golden_dir):
+    f = _load(golden_dir, "mx_quant.npz")
+    codes, scale, deq = mxquant.quantize_mx_e4m3(f["x"], "lut")
+    assert np.array_equal(codes, f["lut_codes"])
+    assert np.array_equal(scale, f["lut_scale"])
+    assert np.array_equal(deq, f["lut_dequant"])
+    # the two backends differ only on exact ties
+    assert (f["lut_codes"] != f["native_codes"]).sum() > 0
+
+
+def test_mx_e4m3_axis0_bit_exact(golden_dir):
+    f = _load(golden_dir, "mx_quant.npz")
+    for backend, mode in (("native", "rne"), ("lut", "lut")):
+        codes, scale, _ = mxquant.quantize_mx_e4m3_axis0(f["axis0_x"], mode)
+        assert np.array_equal(codes, f[f"{backend}_axis0_codes"])
+        assert np.array_equal(scale, f[f"{backend}_axis0_scale"])
+
+
+def test_mx_edge_cases(golden_dir):
+    f = _load(golden_dir, "mx_quant.npz")
+    _, scale, _ = mxquant.quantize_mx_e4m3(f["x"], "rne")
+    assert (scale[0, :5] == 127).all()            # all-zero blocks -> exp 0
+    assert scale[1, 0] == 127                     # amax < 1e-12 -> exp 0
+    assert scale[2, 0] == 127                     # 2^-120 is below 1e-12 too -> exp 0
+    x = np.full((1, 32), 2.0 ** -30, dtype=np.float32)
+    assert mxquant.quantize_mx_e4m3(x)[1][0, 0] == 127 - 30 - 8
+    assert (scale[:, 5] == 127).all()             # odd block count padded with 1.0
+
+
+def test_mx_e2m1_bit_exact(golden_dir):
+    f = _load(golden_dir, "mx_quant.npz")
+    idx, packed, scale, deq = mxquant.quantize_mx_e2m1(f["fp4_x"])
+    assert np.array_equal(idx, f["fp4_idx"])
+    assert np.array_equal(packed, f["fp4_packed"])
+    assert np.array_equal(scale, f["fp4_scale"])
+    assert np.array_equal(deq, f["fp4_dequant"])
+
+
+def test_e4m3_rne_matches_torch_cast_everywhere():
+    allc = np.arange(256, dtype=np.uint8)
+    vals = mxquant.e4m3_to_f32(allc)
+    finite = vals[np.isfinite(vals)]
+    mids = np.sort(np.unique(finite))
+    probe = np.concatenate([mids, (mids[:-1] + mids[1:]) / 2, np.nextafter(((mids[:-1] + mids[1:]) / 2).astype(np.float32), np.float32(1e9)),
+                            np.nextafter(((mids[:-1] + mids[1:]) / 2).astype(np.float32), np.float32(-1e9))]).astype(np.float32)
+    ref = torch.from_numpy(probe).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(mxquant.f32_to_e4m3_rne(probe), ref)
+
+
+def test_bf16_round_trip():
+    x = (np.random.default_rng(0).standard_normal(4096) * 100).astype(np.float32)
+    ref = torch.from_numpy(x).to(torch.bfloat16).view(torch.uint16).numpy()
+    assert np.array_equal(mxquant.f32_to_bf16_bits(x), ref)
+
+
+# ------------------------------------------------------------------- dense --
+def test_dense_goldens(golden_dir):
+    f = _load(golden_dir, "dense.npz")
+    a = [torch.from_numpy(f[f"mmar_a{r}"]) for r in range(2)]
+    b = [torch.from_numpy(f[f"mmar_b{r}"]) for r in range(2)]
+    assert np.array_equal(dense.golden_matmul_allreduce(a, b).numpy(), f["mmar_golden"])
+    rs = dense.golden_matmul_reduce_scatter(a, b)
+    assert np.array_equal(torch.cat(rs).numpy(), f["mmar_golden"])
+    a = [torch.from_numpy(f[f"agmm_a{r}"]).view(torch.bfloat16) for r in range(2)]
+    b = [torch.from_numpy(f[f"agmm_b{r}"]).view(torch.bfloat16) for r in range(2)]
+    for r, g in enumerate(dense.golden_allgather_matmul(a, b)):
+        assert np.array_equal(g.numpy(), f[f"agmm_golden{r}"])
+
+
+def test_verifier_decisions(golden_dir):
+    f = _load(golden_dir, "verify.npz")
+    golden = torch.from_numpy(f["golden"])
+    for dt, k, name, act, ok in zip(f["dtypes"], f["ks"], f["names"], f["actual"], f["ok"]):
+        dtype = {"bfloat16": torch.bfloat16, "float16": torch.float16}[str(dt)]
+        got, _, _ = verify.reference_check(torch.from_numpy(act).to(dtype), golden, int(k))
+        assert got == bool(ok), (dt, k, name)
+
+
+# ---------------------------------------------------------------- swizzle --
+def test_comm_swizzle_tables(golden_dir):
+    f = _load(golden_dir, "comm_swizzle.npz")
+    for ci, (gr, gc, gk, sr, sc, direction, det) in enumerate(f["configs"]):
+        table = f[f"table{ci}"]
+        for i, (data, rank) in enumerate(table):
+            row, col, rk = swizzle.block_comm_swizzle_coord(gr, gc, gk, sr, sc, i, int(direction), bool(det))
+            assert (row * gc + col, rk) == (data, rank), (ci, i)
+
+
+def test_comm_swizzle_worked_example():
+    # docs/comm_swizzle/comm_swizzle_algorithm.md:87-95, gridShape=(2,2,4), coreSplit=(2,2)
+    want = [(0, 0, 0), (0, 1, 1), (0, 0, 2), (0, 1, 3)]
+    assert [swizzle.comm_swizzle_coord(2, 2, 4, 2, 2, i) for i in range(4)] == want
+
+
+def test_matrix_swizzle_is_a_serpentine_permutation():
+    for rows, cols, off in ((5, 3, 2), (8, 16, 7), (1, 9, 7), (9, 1, 3)):
+        seen = [swizzle.matrix_swizzle_coord(rows, cols, i, off) for i in range(rows * cols)]
+        assert sorted(seen) == [(r, c) for r in range(rows) for c in range(cols)]
+    # first group walks columns forward, second group backward
+    assert swizzle.matrix_swizzle_coord(4, 3, 0, 2) == (0, 0)
+    assert swizzle.matrix_swizzle_coord(4, 3, 6, 2) == (2, 2)
+
+
+def test_alltoallv_gmm_scheduler_known_answer():
+    # tests/comm_block_scheduler_alltoallv_gmm/test_comm_block_scheduler_alltoallv_gmm.cpp:94-101
+    expected = [1, 3, 0, 0, 42, 1, 1, 4, 4, 0, 0, 4, 0, 10, 2, 3]
+    t = np.arange(1, 33)
+    got = []
+    prev, loops, offs = moe.set_comm_core(t, 2, 4, 2, 1, 3)
+    got += [1, 3, 0, 0, prev, loops, offs[0], offs[1]]
+    prev, loops, offs = moe.set_comm_core(t, 2, 4, 2, 4, 6)
+    got += [4, prev, loops, offs[0]]
+    prev, loops, offs = moe.set_comm_core(t, 2, 4, 2, 0, 3)
+    got += [0, prev, loops, offs[1]]
+    assert got == expected
+    cs = moe.cumsum_mm(t, 2, 4, 2)
+    assert cs.tolist() == [[5, 6], [18, 20], [39, 42], [68, 72]]
+
+
+# -------------------------------------------------------------------- MoE --
+def test_moe_subfunctions(golden_dir):
+    f = _load(golden_dir, "moe.npz")
+    ep, epr, top_k = 3, 2, 2
+    srcs, counts, routed = [], [], []
+    for r in range(ep):
+        s, c = moe.moe_init_routing(f[f"sub_idx{r}"], ep * epr)
+        assert np.array_equal(s, f[f"sub_rowidx{r}"])
+        assert np.array_equal(c, f[f"sub_tokens{r}"])
+        rt = moe.permute_rows(f[f"sub_x{r}"], s, top_k)
+        assert np.array_equal(rt, f[f"sub_routed{r}"])
+        srcs.append(s); counts.append(c); routed.append(rt)
+    recv, blocks = moe.alltoallv_dispatch(routed, np.stack(counts), ep, epr)
+    for r in range(ep):
+        assert np.array_equal(recv[r], f[f"sub_recv{r}"])
+        assert blocks[r] == f[f"sub_blocks{r}"].tolist()
+    back = moe.alltoallv_combine(recv, np.stack(counts), ep, epr)
+    for r in range(ep):
+        assert np.array_equal(back[r], f[f"sub_back{r}"])
+        assert np.array_equal(back[r], routed[r])          # dispatch then combine is the identity
+        ref = moe.unpermute_reference_cpu(back[r], srcs[r], f[f"sub_probs{r}"])
+        assert np.array_equal(ref, f[f"sub_combine{r}"])
+        mine = moe.unpermute_fp32(back[r], moe.expanded_row_idx_src_to_dst(srcs[r]), f[f"sub_probs{r}"])
+        assert np.allclose(mine, ref, rtol=2 ** -6, atol=2 ** -6)
+    assert np.array_equal(moe.swiglu_bf16(f["swiglu_in"]), f["swiglu_out"])
+
+
+def test_moe_full_pipeline(golden_dir):
+    f = _load(golden_dir, "moe.npz")
+    m, k, n, top_k, e_num, ep = [int(v) for v in f["e2e_shape"]]
+    epr = e_num // ep
+    xs = [mxquant.bf16_bits_to_f32(f[f"e2e_x{r}"]).reshape(m, k) for r in range(ep)]
+    outs, inter = moe.dispatch_ffn_combine(
+        xs, [f[f"e2e_idx{r}"] for r in range(ep)], [f[f"e2e_probs{r}"] for r in range(ep)],
+        [f[f"e2e_w1q{r}"] for r in range(ep)], [f[f"e2e_w1s{r}"] for r in range(ep)],
+        [f[f"e2e_w2q{r}"] for r in range(ep)], [f[f"e2e_w2s{r}"] for r in range(ep)],
+        ep, epr, return_intermediates=True)
+    for r in range(ep):
+        assert np.array_equal(inter["sorted_src"][r], f[f"e2e_rowidx{r}"])
+        # GEMM2 output rows (bf16) before the combine all-to-all: bit-exact
+        assert np.array_equal(mxquant.f32_to_bf16_bits(inter["gmm2"][r]).reshape(-1), f[f"e2e_gmm2{r}"].reshape(-1))
+        assert np.array_equal(mxquant.f32_to_bf16_bits(inter["back"][r]).reshape(-1), f[f"e2e_back{r}"].reshape(-1))
+        ref = mxquant.bf16_bits_to_f32(f[f"e2e_out{r}"]).reshape(m, k)
+        # final weighted sum: fp32 accumulate (device definition) vs the reference's bf16 CPU fallback
+        err = np.abs(outs[r] - ref) / np.maximum(1.0, np.abs(ref))
+        assert err.max() <= 2 ** -6
