@@ -1,0 +1,211 @@
+// extern "C" surface (include/catccos_b200.h).
+#include "../../include/catccos_b200.h"
+
+#include "dense_ops.h"
+#include "ptx.cuh"
+#include "symm_heap.h"
+
+using namespace cb;
+
+namespace {
+
+__global__ void wait_unset_flag_kernel(const uint32_t *flag, uint32_t expected, uint64_t timeout_ns, int *status) {
+    __shared__ int abort_flag;
+    abort_flag = 0;
+    WaitCtl ctl;
+    ctl.abort_smem = &abort_flag;
+    ctl.status = status;
+    ctl.deadline_ns = globaltimer_ns() + timeout_ns;
+    ctl.rank = 0;
+    wait_flag_ge(flag, expected, ctl, W_TEST, 0);
+}
+
+int dense_op_of(int32_t commType) {
+    switch (commType) {
+        case CATCCOS_MATMUL_ALLREDUCE: return OP_MMAR;
+        case CATCCOS_ALLGATHER_MATMUL:
+        case CATCCOS_ASCEND950_ALLGATHER_MATMUL: return OP_AGMM;
+        case CATCCOS_MATMUL_REDUCE_SCATTER:
+        case CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER: return OP_MMRS;
+        default: return -1;
+    }
+}
+
+int check_tiling(const CocTilingParams *tiling) {
+    Team *t = team();
+    if (!t) {
+        set_error("symmetric heap not initialised (call catccos_shmem_init first)");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    if (!tiling) {
+        set_error("tiling is NULL");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (tiling->rankSize != 0 && static_cast<int>(tiling->rankSize) != t->n_pes) {
+        set_error("tiling.rankSize (%u) differs from the number of PEs (%d)", tiling->rankSize, t->n_pes);
+        return CATCCOS_ERR_INVALID;
+    }
+    return CATCCOS_OK;
+}
+
+int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
+                     uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    if (!params) {
+        set_error("params is NULL");
+        return CATCCOS_ERR_INVALID;
+    }
+    Team *t = team();
+    const int want = t->emulated ? t->n_pes : 1;
+    if (n_params != want) {
+        set_error(t->emulated ? "emulated PEs: use catccos_launch_emulated with one parameter block per PE"
+                              : "catccos_launch_emulated needs catccos_shmem_init_emulated");
+        return CATCCOS_ERR_INVALID;
+    }
+    DenseArgs args[kMaxRanks];
+    for (int i = 0; i < n_params; ++i) args[i] = {params[i].ptrA, params[i].ptrB, params[i].ptrC};
+    return launch_dense(op, dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric,
+                        static_cast<int>(tiling->m), static_cast<int>(tiling->n), static_cast<int>(tiling->k),
+                        static_cast<int>(transA), static_cast<int>(transB));
+}
+
+}  // namespace
+
+extern "C" {
+
+int catccos_shmem_init(int32_t my_pe, int32_t n_pes, uint64_t local_mem_size, const char *ip_port) {
+    return team_init(my_pe, n_pes, local_mem_size, ip_port);
+}
+int catccos_shmem_init_emulated(int32_t n_pes, uint64_t local_mem_size) {
+    return team_init_emulated(n_pes, local_mem_size);
+}
+int catccos_shmem_finalize(void) { return team_finalize(); }
+void *catccos_shmem_malloc(size_t bytes) { return team_malloc(bytes); }
+void catccos_shmem_free(void *ptr) {
+    if (ptr) team_free(ptr);
+}
+void *catccos_shmem_ptr(const void *ptr, int32_t pe) { return team_ptr(ptr, pe); }
+int32_t catccos_shmem_my_pe(void) { return team() ? team()->my_pe : -1; }
+int32_t catccos_shmem_n_pes(void) { return team() ? team()->n_pes : 0; }
+int catccos_shmem_barrier_all(void) {
+    if (!team()) {
+        set_error("symmetric heap not initialised");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        set_error("cudaDeviceSynchronize failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return team_host_barrier();
+}
+
+const char *catccos_last_error(void) { return last_error(); }
+
+int catccos_last_status(int32_t *words8) {
+    if (!team()) {
+        set_error("symmetric heap not initialised");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        set_error("cudaDeviceSynchronize failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    int w[ST_WORDS];
+    int rc = team_read_status(w);
+    if (rc) return rc;
+    if (words8)
+        for (int i = 0; i < ST_WORDS; ++i) words8[i] = w[i];
+    if (w[ST_CODE] != 0) {
+        set_error("device wait ran out: code=%d site=%d rank=%d index=%d expected=%d seen=%d", w[ST_CODE], w[ST_WHERE],
+                  w[ST_RANK], w[ST_INDEX], w[ST_EXPECTED], w[ST_SEEN]);
+        return CATCCOS_ERR_DEVICE_WAIT;
+    }
+    return CATCCOS_OK;
+}
+int catccos_reset_status(void) { return team_reset_status(); }
+
+int catccos_debug_wait_unset_flag(void *stream, uint32_t timeout_ms) {
+    Team *t = team();
+    if (!t) {
+        set_error("symmetric heap not initialised");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    // the last word of the flag region is never written by any operator
+    const uint32_t *flag = reinterpret_cast<const uint32_t *>(t->base[t->my_pe]) + (kFlagWords - 1);
+    wait_unset_flag_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+        flag, 0x7fffffffu, static_cast<uint64_t>(timeout_ms) * 1000000ull, t->status_dev);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
+    (void)dataType;
+    if (!tiling) return 0;
+    const int world = tiling->rankSize ? static_cast<int>(tiling->rankSize) : (team() ? team()->n_pes : 1);
+    const int op = dense_op_of(commType);
+    if (op >= 0)
+        return dense_symmetric_bytes(op, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
+                                     static_cast<int>(tiling->k));
+    return 0;
+}
+size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
+    (void)commType;
+    (void)dataType;
+    (void)tiling;
+    return 0;   // the dense operators keep everything in the symmetric region
+}
+
+#define DENSE_LAUNCH(name, op, dtype)                                                                          \
+    int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
+             uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
+        (void)fftsAddr;                                                                                          \
+        (void)workspace;                                                                                         \
+        return launch_dense_abi(op, dtype, stream, blockNum, params, 1, symmetric, tiling, transA, transB);      \
+    }
+DENSE_LAUNCH(LaunchMatmulAllReduceFP16, OP_MMAR, CATCCOS_FP16)
+DENSE_LAUNCH(LaunchMatmulAllReduceBF16, OP_MMAR, CATCCOS_BF16)
+DENSE_LAUNCH(LaunchAllGatherMatmulFP16, OP_AGMM, CATCCOS_FP16)
+DENSE_LAUNCH(LaunchAllGatherMatmulBF16, OP_AGMM, CATCCOS_BF16)
+DENSE_LAUNCH(LaunchMatmulReduceScatterFP16, OP_MMRS, CATCCOS_FP16)
+DENSE_LAUNCH(LaunchMatmulReduceScatterBF16, OP_MMRS, CATCCOS_BF16)
+DENSE_LAUNCH(LaunchAscend950AllGatherMatmulFP16, OP_AGMM, CATCCOS_FP16)
+DENSE_LAUNCH(LaunchAscend950AllGatherMatmulBF16, OP_AGMM, CATCCOS_BF16)
+DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterFP16, OP_MMRS, CATCCOS_FP16)
+DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16, OP_MMRS, CATCCOS_BF16)
+
+int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum, uint64_t fftsAddr,
+                   CatccosKernelParams *params, uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling,
+                   uint32_t transA, uint32_t transB) {
+    (void)fftsAddr;
+    (void)workspace;
+    const int op = dense_op_of(commType);
+    if (op >= 0 && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_dense_abi(op, dataType, stream, blockNum, params, 1, symmetric, tiling, transA, transB);
+    set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
+    return CATCCOS_ERR_INVALID;
+}
+
+int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum,
+                            CatccosKernelParams *params, uint8_t **workspaces, uint8_t *symmetric,
+                            CocTilingParams *tiling, uint32_t transA, uint32_t transB) {
+    (void)workspaces;
+    Team *t = team();
+    if (!t || !t->emulated) {
+        set_error("catccos_launch_emulated needs catccos_shmem_init_emulated");
+        return t ? CATCCOS_ERR_INVALID : CATCCOS_ERR_NOT_INIT;
+    }
+    const int op = dense_op_of(commType);
+    if (op >= 0 && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_dense_abi(op, dataType, stream, blockNum, params, t->n_pes, symmetric, tiling, transA, transB);
+    set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
+    return CATCCOS_ERR_INVALID;
+}
+
+}  // extern "C"

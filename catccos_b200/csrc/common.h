@@ -1,0 +1,52 @@
+// Shared host/device definitions of the fused GEMM + collective kernels.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace cb {
+
+constexpr int kMaxRanks = 8;
+
+// Flag region: the first kFlagBytes of every PE's symmetric heap.  32-bit words,
+// zeroed once at heap creation; every flag has a single writer that stores the
+// launch epoch (monotonic across all operators), readers wait for >= epoch.
+constexpr size_t kFlagBytes = 4u << 20;
+constexpr uint32_t kFlagWords = kFlagBytes / 4;
+constexpr uint32_t kFlagEntered = 0;      // entered[src PE]            (kMaxRanks words)
+constexpr uint32_t kFlagBarrier = 16;     // host-visible barrier words (kMaxRanks words)
+constexpr uint32_t kFlagOpBase = 64;      // per-operator flags start here
+
+enum FusedOp : int { OP_AGMM = 0, OP_MMRS = 1, OP_MMAR = 2 };
+
+// GEMM tile of the dense (f16/bf16) kernel.
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kAStageBytes = BM * BK * 2;   // 16 KiB
+constexpr int kBStageBytes = BN * BK * 2;   // 32 KiB
+constexpr int kGemmThreads = 256;           // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 comm
+constexpr int kGemmSmemBytes = kStages * (kAStageBytes + kBStageBytes) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kAgSubChunks = 4;             // an all-gather chunk (BM rows) is pushed as 4 units of 32 rows
+
+struct alignas(64) RankArgs {
+    CUtensorMap tmA;    // A as passed by the caller: [rows, K], K innermost, box {BK, BM}
+    CUtensorMap tmAg;   // AG-MM: gathered A [R*m, K] in this PE's symmetric region
+    CUtensorMap tmB;    // transB=1: [N, K] box {BK, BN};  transB=0: [K, N] box {64 (n), BK (k)}
+    const void *A;      // raw pointers of the same operands
+    void *C;
+};
+
+struct FusedParams {
+    RankArgs ranks[kMaxRanks];        // indexed by LOCAL rank (1 entry per process; R entries when emulating)
+    uint8_t *heap_base[kMaxRanks];    // VA (in this process) of every PE's symmetric heap
+    uint64_t symm_off;                // byte offset of the operator's data region inside the heap
+    int world, rank_base, n_local, ctas_per_rank;
+    int M, N, K;                      // AG-MM: M = rows held by one rank; MM-RS / MM-AR: M = total rows
+    uint32_t epoch;
+    uint64_t timeout_ns;
+    int *status;                      // cb::StatusWord[ST_WORDS], device memory
+};
+
+struct Team;   // symmetric heap + peers (symm_heap.cu)
+
+}  // namespace cb

@@ -1,0 +1,196 @@
+// Host launchers of the f16/bf16 fused kernels: tensor maps, shape checks, launch.
+#include "dense_ops.h"
+
+#include <string.h>
+
+#include "gemm_fused.cuh"
+#include "ptx.cuh"
+
+namespace cb {
+
+static int encode_2d(const DriverApi *api, CUtensorMap *tm, CUtensorMapDataType dt, const void *base, uint64_t inner,
+                     uint64_t outer, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = api->TensorMapEncodeTiled(tm, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        const char *s = nullptr;
+        api->GetErrorString(r, &s);
+        set_error("cuTensorMapEncodeTiled failed: %s (base=%p inner=%llu outer=%llu stride=%llu box=%ux%u)",
+                  s ? s : "?", base, (unsigned long long)inner, (unsigned long long)outer,
+                  (unsigned long long)row_stride_bytes, box_inner, box_outer);
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+template <int OP, typename T, bool B_MN>
+static int launch_kernel(const FusedParams &p, int grid, bool cooperative, cudaStream_t stream) {
+    auto kern = fused_gemm_kernel<OP, T, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+    if (e != cudaSuccess) {
+        set_error("cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    if (cooperative) {
+        // several emulated ranks wait on one another inside one launch: co-residency must be guaranteed
+        void *args[] = {const_cast<FusedParams *>(&p)};
+        e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
+                                        kGemmSmemBytes, stream);
+    } else {
+        kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(p);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        set_error("kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+template <int OP, typename T>
+static int launch_b(const FusedParams &p, int grid, bool coop, cudaStream_t s, bool b_mn) {
+    return b_mn ? launch_kernel<OP, T, true>(p, grid, coop, s) : launch_kernel<OP, T, false>(p, grid, coop, s);
+}
+template <int OP>
+static int launch_t(const FusedParams &p, int grid, bool coop, cudaStream_t s, bool bf16, bool b_mn) {
+    return bf16 ? launch_b<OP, __nv_bfloat16>(p, grid, coop, s, b_mn) : launch_b<OP, __half>(p, grid, coop, s, b_mn);
+}
+
+size_t dense_symmetric_bytes(int op, int world, int m, int n, int k) {
+    const size_t es = 2;
+    if (world <= 1) return 0;
+    switch (op) {
+        case OP_AGMM: return static_cast<size_t>(world) * m * k * es;
+        case OP_MMRS: return static_cast<size_t>(m) * n * es;
+        case OP_MMAR: {
+            const size_t mr = (m + world - 1) / world;
+            return 2 * static_cast<size_t>(world) * mr * n * es;
+        }
+    }
+    return 0;
+}
+
+int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, const DenseArgs *args, void *symmetric,
+                 int m, int n, int k, int trans_a, int trans_b) {
+    Team *t = team();
+    if (!t) {
+        set_error("symmetric heap not initialised (call catccos_shmem_init first)");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    std::string why;
+    const DriverApi *api = driver_api(&why);
+    if (!api) {
+        set_error("CUDA driver unavailable: %s", why.c_str());
+        return CATCCOS_ERR_CUDA;
+    }
+    if (op != OP_AGMM && op != OP_MMRS && op != OP_MMAR) {
+        set_error("unknown dense operator %d", op);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (dtype != 1 && dtype != 27) {
+        set_error("dense operators take FP16 (1) or BF16 (27), got %d", dtype);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (trans_a != 0) {
+        set_error("transA=1 is not supported");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (m <= 0 || n <= 0 || k <= 0 || (k % 8) != 0 || (n % 8) != 0) {
+        set_error("unsupported shape m=%d n=%d k=%d (n and k must be positive multiples of 8)", m, n, k);
+        return CATCCOS_ERR_INVALID;
+    }
+    const int R = t->n_pes;
+    if (op == OP_MMRS && (m % R) != 0) {
+        set_error("matmul_reduce_scatter needs m (%d) divisible by the world size (%d)", m, R);
+        return CATCCOS_ERR_INVALID;
+    }
+    const int n_local = t->emulated ? R : 1;
+    const int nt = (n + BN - 1) / BN;
+    const size_t need = dense_symmetric_bytes(op, R, m, n, k);
+    uint64_t symm_off = 0;
+    if (R > 1) {
+        uint8_t *sp = static_cast<uint8_t *>(symmetric);
+        uint8_t *b = t->base[t->my_pe];
+        if (sp == nullptr || sp < b + kFlagBytes || sp + need > b + t->heap_bytes) {
+            set_error("symmetric buffer %p (+%zu bytes) is not inside the symmetric heap", symmetric, need);
+            return CATCCOS_ERR_INVALID;
+        }
+        symm_off = static_cast<uint64_t>(sp - b);
+        if (symm_off % 1024 != 0) {
+            set_error("symmetric buffer must be 1024-byte aligned");
+            return CATCCOS_ERR_INVALID;
+        }
+        size_t flags = 0;
+        if (op == OP_AGMM) flags = static_cast<size_t>(R) * ((m + BM - 1) / BM) * kAgSubChunks;
+        if (op == OP_MMRS) flags = static_cast<size_t>(R) * ((m / R + BM - 1) / BM) * nt;
+        if (op == OP_MMAR) flags = 2 * static_cast<size_t>(R) * (((m + R - 1) / R + BM - 1) / BM) * nt;
+        if (kFlagOpBase + flags > kFlagWords) {
+            set_error("shape needs %zu flags, the flag region holds %u", flags, kFlagWords - kFlagOpBase);
+            return CATCCOS_ERR_INVALID;
+        }
+    }
+
+    FusedParams p;
+    memset(&p, 0, sizeof(p));
+    const CUtensorMapDataType dt = dtype == 27 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int a_rows = m;   // rows of the caller's A in every operator
+    for (int l = 0; l < n_local; ++l) {
+        const DenseArgs &a = args[l];
+        if (!a.A || !a.B || !a.C || (reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
+            (reinterpret_cast<uintptr_t>(a.C) & 15)) {
+            set_error("A, B and C must be non-null and 16-byte aligned");
+            return CATCCOS_ERR_INVALID;
+        }
+        RankArgs &ra = p.ranks[l];
+        int rc = encode_2d(api, &ra.tmA, dt, a.A, k, a_rows, static_cast<uint64_t>(k) * 2, BK, BM);
+        if (rc) return rc;
+        if (trans_b) {
+            rc = encode_2d(api, &ra.tmB, dt, a.B, k, n, static_cast<uint64_t>(k) * 2, BK, BN);
+        } else {
+            rc = encode_2d(api, &ra.tmB, dt, a.B, n, k, static_cast<uint64_t>(n) * 2, 64, BK);
+        }
+        if (rc) return rc;
+        if (op == OP_AGMM && R > 1) {
+            const int pe = t->emulated ? l : t->my_pe;
+            rc = encode_2d(api, &ra.tmAg, dt, t->base[pe] + symm_off, k, static_cast<uint64_t>(R) * m,
+                           static_cast<uint64_t>(k) * 2, BK, BM);
+            if (rc) return rc;
+        } else {
+            ra.tmAg = ra.tmA;
+        }
+        ra.A = a.A;
+        ra.C = a.C;
+    }
+    for (int pe = 0; pe < R; ++pe) p.heap_base[pe] = t->base[pe];
+    p.symm_off = symm_off;
+    p.world = R;
+    p.rank_base = t->emulated ? 0 : t->my_pe;
+    p.n_local = n_local;
+    int per_rank = t->num_sms / n_local;
+    if (block_num > 0 && static_cast<int>(block_num) < per_rank) per_rank = static_cast<int>(block_num);
+    if (per_rank < 1) per_rank = 1;
+    p.ctas_per_rank = per_rank;
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.epoch = ++t->epoch;
+    p.timeout_ns = t->timeout_ns;
+    p.status = t->status_dev;
+
+    const int grid = per_rank * n_local;
+    const bool coop = n_local > 1;
+    const bool bf16 = dtype == 27;
+    const bool b_mn = trans_b == 0;
+    switch (op) {
+        case OP_AGMM: return launch_t<OP_AGMM>(p, grid, coop, stream, bf16, b_mn);
+        case OP_MMRS: return launch_t<OP_MMRS>(p, grid, coop, stream, bf16, b_mn);
+        default: return launch_t<OP_MMAR>(p, grid, coop, stream, bf16, b_mn);
+    }
+}
+
+}  // namespace cb

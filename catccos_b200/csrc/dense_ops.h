@@ -1,0 +1,23 @@
+// Host entry points of the f16/bf16 fused operators.
+#pragma once
+#include "common.h"
+#include "symm_heap.h"
+
+namespace cb {
+
+struct DenseArgs {
+    const void *A;   // [m, k] row-major
+    const void *B;   // transB=0: [k, n] row-major;  transB=1: [n, k] row-major
+    void *C;         // AG-MM: [R*m, n];  MM-RS: [m/R, n];  MM-AR: [m, n]
+};
+
+// Bytes of the caller's symmetric buffer the operator uses (0 for a single rank).
+size_t dense_symmetric_bytes(int op, int world, int m, int n, int k);
+
+// args: one entry per LOCAL rank (1 normally; the world size when all ranks are emulated on one GPU).
+// m, n, k carry the reference's meaning per operator (AG-MM: m = rows held by one rank; MM-RS and
+// MM-AR: m = rows of the full product).  Asynchronous on `stream`.
+int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, const DenseArgs *args, void *symmetric,
+                 int m, int n, int k, int trans_a, int trans_b);
+
+}  // namespace cb

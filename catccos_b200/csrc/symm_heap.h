@@ -1,0 +1,80 @@
+// Symmetric heap over cuMem VMM: every PE owns one physical allocation, exports it as a POSIX
+// file descriptor, and maps every peer's allocation into its own address space (NVLink P2P).
+// Replaces the ACLSHMEM heap the reference initialises with set_attr()/aclshmemx_init_attr()
+// (utils/shmem_init.h:16-39) and the shmem_malloc/shmem_ptr/shmem_free calls of its drivers
+// (examples/matmul_allreduce/main.cpp:122-135,173-178).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/catccos_b200.h"   // error codes
+#include "common.h"
+
+namespace cb {
+
+// Driver entry points, resolved at run time through the CUDA runtime so that the library loads
+// on machines without a driver (build and symbol checks) and needs no link against libcuda.
+struct DriverApi {
+    CUresult (*MemCreate)(CUmemGenericAllocationHandle *, size_t, const CUmemAllocationProp *, unsigned long long);
+    CUresult (*MemRelease)(CUmemGenericAllocationHandle);
+    CUresult (*MemAddressReserve)(CUdeviceptr *, size_t, size_t, CUdeviceptr, unsigned long long);
+    CUresult (*MemAddressFree)(CUdeviceptr, size_t);
+    CUresult (*MemMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long);
+    CUresult (*MemUnmap)(CUdeviceptr, size_t);
+    CUresult (*MemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc *, size_t);
+    CUresult (*MemExportToShareableHandle)(void *, CUmemGenericAllocationHandle, CUmemAllocationHandleType,
+                                           unsigned long long);
+    CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle *, void *, CUmemAllocationHandleType);
+    CUresult (*MemGetAllocationGranularity)(size_t *, const CUmemAllocationProp *, CUmemAllocationGranularity_flags);
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                     const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                     CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                     CUtensorMapFloatOOBfill);
+    CUresult (*GetErrorString)(CUresult, const char **);
+    bool loaded = false;
+};
+// Returns nullptr (and sets *why) when no driver is available.
+const DriverApi *driver_api(std::string *why = nullptr);
+
+
+struct Team {
+    int my_pe = 0;
+    int n_pes = 1;
+    bool emulated = false;         // all PEs are regions on the current device of this process
+    int device = 0;
+    int num_sms = 0;
+    size_t heap_bytes = 0;         // per PE, flag region included
+    size_t bump = kFlagBytes;      // next free byte of the (symmetric) bump allocator
+    std::vector<size_t> alloc_stack;   // offsets of live allocations, in order
+    uint8_t *base[kMaxRanks] = {};
+    CUmemGenericAllocationHandle handles[kMaxRanks] = {};
+    uint32_t epoch = 0;            // launches so far; identical on all PEs by collective-call order
+    int *status_dev = nullptr;     // StatusWord[ST_WORDS]
+    uint64_t timeout_ns = 10ull * 1000 * 1000 * 1000;
+    // host rendezvous
+    int sock = -1;
+    std::string sock_prefix;
+    uint32_t barrier_seq = 0;
+    struct Pending { int type; int from; uint32_t seq; int fd; };
+    std::vector<Pending> pending;
+};
+
+Team *team();                       // the process-wide team, nullptr before init
+int team_init(int my_pe, int n_pes, uint64_t local_mem_size, const char *ip_port);
+int team_init_emulated(int n_pes, uint64_t local_mem_size);
+int team_finalize();
+void *team_malloc(size_t bytes);    // collective: same offset on every PE; nullptr when exhausted
+int team_free(void *p);             // stack discipline: frees p and everything allocated after it
+int team_host_barrier();
+void *team_ptr(const void *local, int pe);
+int team_read_status(int *out_words /* ST_WORDS */);
+int team_reset_status();
+const char *last_error();
+void set_error(const char *fmt, ...);
+
+}  // namespace cb

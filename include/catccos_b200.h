@@ -1,0 +1,162 @@
+/*
+ * C-ABI of the B200 implementation of the fused compute-communication operators.
+ *
+ * Plain C: pointers and sizes only.  Every function returns 0 on success or one of the
+ * CATCCOS_ERR_* codes; catccos_last_error() gives the message of the last failure on the calling
+ * thread.  Device pointers are ordinary CUDA device pointers of the calling process; `symmetric`
+ * pointers come from catccos_shmem_malloc().  One process per GPU, one rank ("PE") per process;
+ * all ranks call the collective entry points with the same shapes in the same order (the
+ * reference's rule too: nothing checks it).
+ *
+ * Each declaration names the reference interface it replaces (paths relative to the reference
+ * project root).
+ */
+#ifndef CATCCOS_B200_H
+#define CATCCOS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define CATCCOS_API __attribute__((visibility("default")))
+#else
+#define CATCCOS_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    CATCCOS_OK = 0,
+    CATCCOS_ERR_INVALID = 1,     /* bad argument, unsupported shape or layout */
+    CATCCOS_ERR_NOT_INIT = 2,    /* catccos_shmem_init has not been called */
+    CATCCOS_ERR_CUDA = 3,        /* a CUDA call failed, or no driver/GPU is present */
+    CATCCOS_ERR_BOOTSTRAP = 4,   /* rendezvous with the peer processes failed or timed out */
+    CATCCOS_ERR_NOMEM = 5,
+    CATCCOS_ERR_DEVICE_WAIT = 6  /* a device-side wait ran out: see catccos_last_status */
+};
+
+/* utils/info.h:95-114 — same 17 fields, same order. */
+typedef struct CocTilingParams {
+    uint32_t m, k, n;
+    uint32_t transA, transB;
+    uint32_t m0, k0, n0;
+    uint32_t commTileM, commInterval, commNpuSplit, commDataSplit, commBlockM;
+    uint32_t rankSize, epSize, expertNum, topK;
+} CocTilingParams;
+
+/* utils/info.h:123-167 (KernelParams) without the C++ members.  customPtrs order per operator is
+ * the reference's: MXFP8 AllGather-Matmul {aScale, bScale}; MoE {b2, expertIdx, probs, bScale, b2Scale}. */
+typedef struct CatccosKernelParams {
+    uint8_t *ptrA;
+    uint8_t *ptrB;
+    uint8_t *ptrC;
+    uint8_t **customPtrs;
+    uint32_t customCount;
+} CatccosKernelParams;
+
+/* utils/info.h:46-93: values of CocCommType / CocDataType used by this library. */
+enum {
+    CATCCOS_MATMUL_ALLREDUCE = 0,
+    CATCCOS_ALLGATHER_MATMUL = 1,
+    CATCCOS_ASCEND950_ALLGATHER_MATMUL = 2,
+    CATCCOS_MATMUL_REDUCE_SCATTER = 3,
+    CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER = 4,
+    CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = 18,
+    CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL = 22,
+    CATCCOS_MX_QUANT_ALLGATHER = 24,
+    CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25,
+    CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27,
+    CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE = 32
+};
+enum { CATCCOS_FP16 = 1, CATCCOS_INT8 = 2, CATCCOS_BF16 = 27, CATCCOS_FP8E4M3FN = 36 };
+
+/* ------------------------------------------------------------------ symmetric heap ---- */
+
+/* Replaces set_attr() + aclshmemx_init_attr() (utils/shmem_init.h:16-39,
+ * examples/matmul_allreduce/main.cpp:122-125).  Collective.  Creates this PE's heap of
+ * `local_mem_size` bytes on the current CUDA device, exchanges it with the peers found through
+ * `ip_port` (any string shared by the job, e.g. "tcp://127.0.0.1:8788"; an empty string is
+ * CATCCOS_ERR_INVALID as in set_attr) and maps every peer's heap over NVLink. */
+CATCCOS_API int catccos_shmem_init(int32_t my_pe, int32_t n_pes, uint64_t local_mem_size, const char *ip_port);
+
+/* Test/development mode with no counterpart in the reference: all `n_pes` PEs are regions on the
+ * current device of this one process; the launch functions then take one parameter block per PE
+ * (catccos_launch_emulated) and run all ranks inside one cooperative launch. */
+CATCCOS_API int catccos_shmem_init_emulated(int32_t n_pes, uint64_t local_mem_size);
+
+/* shmem_finalize() (examples/matmul_allreduce/main.cpp:178). Collective. */
+CATCCOS_API int catccos_shmem_finalize(void);
+/* shmem_malloc() / aclshmem_calloc() (main.cpp:135; tests/dynamic_tiling/main.cpp:291): collective,
+ * same offset on every PE, 1024-byte aligned; NULL when the heap is exhausted.  Not zero-filled
+ * (the kernels need no zeroed data region). */
+CATCCOS_API void *catccos_shmem_malloc(size_t bytes);
+/* shmem_free(): allocations are released in reverse order of allocation (stack discipline). */
+CATCCOS_API void catccos_shmem_free(void *ptr);
+/* shmem_ptr(p, pe): address in this process of PE `pe`'s copy of symmetric address `p`. */
+CATCCOS_API void *catccos_shmem_ptr(const void *ptr, int32_t pe);
+CATCCOS_API int32_t catccos_shmem_my_pe(void);   /* shmem_my_pe() */
+CATCCOS_API int32_t catccos_shmem_n_pes(void);   /* shmem_n_pes() */
+/* aclshmem_barrier_all() (examples/ascend950_dispatch_ffn_combine/main.cpp:217-219): host barrier
+ * of all PEs after synchronising the device. */
+CATCCOS_API int catccos_shmem_barrier_all(void);
+
+/* ----------------------------------------------------------------------- diagnostics ---- */
+CATCCOS_API const char *catccos_last_error(void);
+/* Synchronises the device and copies the 8 status words {code, wait site, rank, flag index,
+ * expected, seen, -, -}.  Returns CATCCOS_ERR_DEVICE_WAIT when code != 0.  (The reference has no
+ * return codes from kernels and unbounded device waits: utils/utils.h:26-40,
+ * include/catccos/arch/cross_rank_sync.hpp:88-97.) */
+CATCCOS_API int catccos_last_status(int32_t *words8);
+CATCCOS_API int catccos_reset_status(void);
+/* Bounded-wait self test: one thread waits `timeout_ms` for a flag nothing sets, then reports
+ * through the status words.  Leaves the context usable. */
+CATCCOS_API int catccos_debug_wait_unset_flag(void *stream, uint32_t timeout_ms);
+
+/* Bytes of the `symmetric` buffer an operator carves for itself (the reference sizes it as one
+ * fixed SHMEM_BUFF_BYTES allocation, utils/info.h:35). */
+CATCCOS_API size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling);
+/* GetWorkspaceSize() of the operator classes (utils/catccos_operator.h:39). */
+CATCCOS_API size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling);
+
+/* ------------------------------------------------------------------ kernel launchers ---- */
+/* tests/dynamic_tiling/include/launch_map.h:15-16 — KernelFuncPtr
+ *   void (*)(void *stream, uint32_t blockNum, uint64_t fftsAddr, KernelParams &, uint8_t *workspace,
+ *            uint8_t *symmetric, CocTilingParams &, uint32_t transA, uint32_t transB)
+ * with the two references turned into pointers and an int status returned.  `stream` is a
+ * cudaStream_t.  `blockNum` > 0 caps the number of SMs used (0 = all); `fftsAddr` is ignored.
+ * Asynchronous on `stream`.  Shapes come from `tiling` (m, k, n, rankSize). */
+#define CATCCOS_DECLARE_LAUNCH(name)                                                                   \
+    CATCCOS_API int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params,          \
+             uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB)
+
+/* tests/dynamic_tiling/impl/kernel_fp16.cpp / kernel_bf16.cpp:72,121,221 */
+CATCCOS_DECLARE_LAUNCH(LaunchMatmulAllReduceFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchMatmulAllReduceBF16);
+CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulBF16);
+CATCCOS_DECLARE_LAUNCH(LaunchMatmulReduceScatterFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchMatmulReduceScatterBF16);
+/* tests/dynamic_tiling/include/launch_map.h:85-88 (same loops on the newer NPU) */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllGatherMatmulFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllGatherMatmulBF16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16);
+
+/* KernelDispatcher::GetKernelFunc(commType, dataType) + call (launch_map.h:31-39,
+ * tests/dynamic_tiling/main.cpp:351-368): CATCCOS_ERR_INVALID when the pair is not registered. */
+CATCCOS_API int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum, uint64_t fftsAddr,
+                   CatccosKernelParams *params, uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling,
+                   uint32_t transA, uint32_t transB);
+
+/* Emulated-PE form of catccos_launch (see catccos_shmem_init_emulated): `params` and `workspaces`
+ * are arrays with one entry per PE. */
+CATCCOS_API int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum,
+                            CatccosKernelParams *params, uint8_t **workspaces, uint8_t *symmetric,
+                            CocTilingParams *tiling, uint32_t transA, uint32_t transB);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CATCCOS_B200_H */
