@@ -1,0 +1,348 @@
+#!/usr/bin/env python3
+"""Benchmark of the fused compute-communication hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--op agmm|mmrs|mmar] [--impl reference]
+
+One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE / MASTER_*).  A "step" is one
+launch of the fused operator through the C-ABI.  Rank 0 prints ONE JSON line.
+
+Workload (default, `--op agmm`): AllGather-Matmul bf16 with the gathered A fixed at [8192, 8192]
+and a per-rank weight B [8192, 4096]: at N GPUs every rank holds 8192/N rows of A and computes the
+whole [8192, 4096] product with its own B, so the work per GPU is the same at every N (weak
+scaling) and N = 8 is the benchmark's 8-rank configuration (A_local [1024, 8192]).  At N = 1 the
+all-gather degenerates and the step is the plain tcgen05 GEMM.  Inputs are synthetic (seeded
+normal(0,1) activations, normal(0,0.02) weights); A + B + C = 268 MB per rank, larger than the
+126 MB L2, so consecutive steps do not find their operands in cache.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOTAL, K_DIM, N_DIM = 8192, 8192, 4096           # allgather_matmul bf16 (benchmark configuration 2)
+RS_M, RS_KLOCAL, RS_N = 8192, 2048, 8192           # matmul_reduce_scatter bf16 (configuration 3)
+AR_M, AR_K, AR_N = 512, 1024, 2048                 # matmul_allreduce fp16 (configuration 1)
+NVLINK_GBS = 770.0                                 # measured peer-copy bandwidth per direction on this pool
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self.proc.terminate()           # the exact process started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                maxes.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def workload(op, world):
+    if op == "agmm":
+        m_local = M_TOTAL // world
+        return dict(name="allgather_matmul_bf16", m=m_local, k=K_DIM, n=N_DIM, a_shape=(m_local, K_DIM),
+                    b_shape=(K_DIM, N_DIM), c_shape=(M_TOTAL, N_DIM), flops=2.0 * M_TOTAL * K_DIM * N_DIM,
+                    comm_bytes=(world - 1) * m_local * K_DIM * 2, dtype="bf16",
+                    desc=f"allgather_matmul bf16: gathered A[8192,8192] (A_local[{m_local},8192] per rank) x "
+                         f"B[8192,4096] per rank -> C[8192,4096]")
+    if op == "mmrs":
+        return dict(name="matmul_reduce_scatter_bf16", m=RS_M, k=RS_KLOCAL, n=RS_N, a_shape=(RS_M, RS_KLOCAL),
+                    b_shape=(RS_KLOCAL, RS_N), c_shape=(RS_M // world, RS_N), flops=2.0 * RS_M * RS_KLOCAL * RS_N,
+                    comm_bytes=(world - 1) * (RS_M // world) * RS_N * 2, dtype="bf16",
+                    desc=f"matmul_reduce_scatter bf16: A[8192,2048] x B[2048,8192] per rank, summed over ranks, "
+                         f"rows scattered -> D[{RS_M // world},8192]")
+    if op == "mmar":
+        return dict(name="matmul_allreduce_fp16", m=AR_M, k=AR_K, n=AR_N, a_shape=(AR_M, AR_K), b_shape=(AR_K, AR_N),
+                    c_shape=(AR_M, AR_N), flops=2.0 * AR_M * AR_K * AR_N,
+                    comm_bytes=2 * (world - 1) * AR_M * AR_N * 2 // max(world, 1), dtype="fp16",
+                    desc="matmul_allreduce fp16: A[512,1024] x B[1024,2048] per rank, summed over ranks")
+    raise ValueError(op)
+
+
+def host_inputs(wl, rank, torch):
+    dt = torch.float16 if wl["dtype"] == "fp16" else torch.bfloat16
+    g = torch.Generator().manual_seed(1234 + rank)
+    if wl["dtype"] == "fp16":
+        a = (torch.rand(wl["a_shape"], generator=g) * 2 - 1).to(dt)
+        b = (torch.rand(wl["b_shape"], generator=g) * 2 - 1).to(dt)
+    else:
+        a = torch.randn(wl["a_shape"], generator=g).to(dt)
+        b = (torch.randn(wl["b_shape"], generator=g) * 0.02).to(dt)
+    return a, b, dt
+
+
+def cpu_golden_rate(wl, sample_rows, torch):
+    """Times the CPU golden (oracle port of the reference's torch fp32 matmul) on a bounded sample:
+    `sample_rows` rows of the (gathered / full) A against one rank's B."""
+    from oracle import dense                      # checker, used here only as the timed CPU baseline
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(99)
+    dt = torch.float16 if wl["dtype"] == "fp16" else torch.bfloat16
+    k, n = wl["b_shape"]
+    a = torch.randn((sample_rows, k), generator=g).to(dt)
+    b = (torch.randn((k, n), generator=g) * 0.02).to(dt)
+    dense.matmul_fp32(a[:64], b)                  # warm the thread pool
+    t0 = time.perf_counter()
+    dense.matmul_fp32(a, b)
+    dt_s = time.perf_counter() - t0
+    flops = 2.0 * sample_rows * k * n
+    return flops / dt_s / 1e12, cores, dt_s
+
+
+def run_reference(args, rank, world):
+    """`--impl reference`: the reference's own implementation of the path is its CPU host golden
+    (its device code targets Ascend NPUs and cannot be built here); rank 0 times the oracle port of
+    that golden on the host cores, the other ranks exit."""
+    if rank != 0:
+        return
+    import torch
+    wl = workload(args.op, max(world, 1))
+    rows = 1024 if args.op != "mmar" else AR_M
+    vals = []
+    for _ in range(args.warmup):
+        cpu_golden_rate(wl, min(rows, 256), torch)
+    cores = os.cpu_count() or 1
+    for _ in range(args.steps):
+        v, cores, _ = cpu_golden_rate(wl, rows, torch)
+        vals.append(v)
+    value = statistics.median(vals)
+    sample = f"{rows} of {wl['c_shape'][0] if args.op == 'agmm' else wl['m']} rows of A x full B, fp32 matmul, {args.steps} runs, median"
+    ms = (2.0 * rows * wl["b_shape"][0] * wl["b_shape"][1]) / (value * 1e12) * 1e3
+    line = {
+        "impl": "reference", "metric": "fused-op TFLOP/s (whole job)", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl["desc"], "op": wl["name"]},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torchrun for --gpus > 1 (one process per GPU)")
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    from catccos_b200 import runtime as rt
+    from catccos_b200 import lib, check
+
+    assert args.warmup >= 3, "at least 3 warm-up steps"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    wl = workload(args.op, world)
+    comm = {"agmm": rt.ALLGATHER_MATMUL, "mmrs": rt.MATMUL_REDUCE_SCATTER, "mmar": rt.MATMUL_ALLREDUCE}[args.op]
+    a_h, b_h, dt = host_inputs(wl, rank, torch)
+    til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
+    dtype_code = rt.FP16 if wl["dtype"] == "fp16" else rt.BF16
+    need = rt.symmetric_bytes(comm, dtype_code, til)
+    port = os.environ.get("MASTER_PORT", "29500")
+    addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    rt.shmem_init(rank, world, 2 * max(need, 1 << 20) + (8 << 20), f"tcp://{addr}:{port}")
+    symm = rt.shmem_malloc(max(need, 1024))
+
+    a_d, b_d = a_h.cuda(), b_h.cuda()
+    c_d = torch.empty(wl["c_shape"], dtype=dt, device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def step():
+        rt.launch(comm, a_d, b_d, c_d, symm, til, stream=stream)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    rc, words = rt.last_status()
+    if rc != 0:
+        raise SystemExit(f"device wait ran out during warm-up: {words}")
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    rc, words = rt.last_status()
+    if rc != 0:
+        raise SystemExit(f"device wait ran out: {words}")
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    elapsed_ms = max_over_ranks(elapsed_ms)
+    ms_per_step = elapsed_ms / args.steps
+
+    # compute-only twin (peer data already in place, no flags): exposed communication
+    exposed = None
+    if world > 1:
+        check(lib().catccos_debug_set_flags(1))
+        for _ in range(3):
+            step()
+        barrier()
+        ev0.record(stream)
+        for _ in range(args.steps):
+            step()
+        ev1.record(stream)
+        torch.cuda.synchronize()
+        co_ms = max_over_ranks(ev0.elapsed_time(ev1)) / args.steps
+        check(lib().catccos_debug_set_flags(0))
+        barrier()
+        exposed = max(0.0, (ms_per_step - co_ms) / ms_per_step)
+
+    # end to end through the host-buffer entry point: H2D of A and B, fused launch, D2H of C, every step
+    e2e = None
+    if not args.no_e2e:
+        a_p, b_p = a_h.pin_memory(), b_h.pin_memory()
+        c_p = torch.empty(wl["c_shape"], dtype=dt).pin_memory()
+
+        def e2e_step():
+            check(lib().catccos_run_host(comm, dtype_code, 0, ctypes.c_void_p(a_p.data_ptr()),
+                                         ctypes.c_void_p(b_p.data_ptr()), ctypes.c_void_p(c_p.data_ptr()), None, 0,
+                                         ctypes.byref(til), 0, 0))
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        e2e = {"value": world * wl["flops"] * args.steps / e2e_s / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": a_p.numel() * 2 + b_p.numel() * 2, "d2h_bytes_per_step": c_p.numel() * 2,
+               "ms_per_step": e2e_s / args.steps * 1e3}
+        # the copy that came back must be the device result (guards against a stale host buffer)
+        if not torch.equal(c_p[:64], c_d[:64].cpu()):
+            raise SystemExit("end-to-end result differs from the device-resident result")
+
+    if rank == 0:
+        peak_tf, peak_hbm, peak_kind = measured_peaks()
+        per_gpu_tflops = wl["flops"] / (ms_per_step * 1e-3) / 1e12
+        t_gemm_us = wl["flops"] / (peak_tf * 1e12) * 1e6
+        t_comm_us = wl["comm_bytes"] / (NVLINK_GBS * 1e9) * 1e6
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+        if os.path.exists(tpath):
+            with open(tpath) as f:
+                traffic = json.load(f).get(f"{wl['name']}_n{world}")
+        line = {
+            "metric": "fused-op TFLOP/s (whole job)", "value": world * per_gpu_tflops, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"],
+            "data": "synthetic",
+            "config": {"workload": wl["desc"], "op": wl["name"], "l2": "operands (268 MB) larger than L2",
+                       "parallelism": f"tp{world}"},
+            "tflops_per_gpu": per_gpu_tflops,
+            "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": per_gpu_tflops / peak_tf, "traffic": traffic, "peak_kind": f"of {peak_kind} (burst cuBLAS bf16)",
+                         "t_gemm_peak_us": t_gemm_us, "t_comm_peak_us": t_comm_us,
+                         "frac_of_max_gemm_comm": max(t_gemm_us, t_comm_us) / (ms_per_step * 1e3)},
+            "exposed_comm_frac": exposed,
+            "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, secs = cpu_golden_rate(wl, 1024, torch)
+            line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"1024 rows of A x full B fp32 matmul ({secs:.2f} s)"}
+        print(json.dumps(line), flush=True)
+
+    rt.shmem_finalize()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

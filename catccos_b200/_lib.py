@@ -47,6 +47,7 @@ SIGNATURES = {
     "catccos_last_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int32)]),
     "catccos_reset_status": (ctypes.c_int, []),
     "catccos_debug_wait_unset_flag": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32]),
+    "catccos_debug_set_flags": (ctypes.c_int, [ctypes.c_uint32]),
     "catccos_symmetric_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(CocTilingParams)]),
     "catccos_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(CocTilingParams)]),
     "catccos_launch": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32] + LAUNCH_ARGS),
@@ -54,6 +55,10 @@ SIGNATURES = {
                                                ctypes.POINTER(KernelParams), ctypes.POINTER(ctypes.c_void_p),
                                                ctypes.c_void_p, ctypes.POINTER(CocTilingParams), ctypes.c_uint32,
                                                ctypes.c_uint32]),
+    "catccos_run_host": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_uint32, ctypes.c_void_p,
+                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                        ctypes.c_uint32, ctypes.POINTER(CocTilingParams), ctypes.c_uint32,
+                                        ctypes.c_uint32]),
 }
 for _op in ("MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend950AllGatherMatmul",
             "Ascend950MatmulReduceScatter"):

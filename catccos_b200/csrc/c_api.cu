@@ -72,6 +72,37 @@ int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, Catccos
 
 }  // namespace
 
+// ---- host-buffer form ------------------------------------------------------------------
+namespace {
+struct HostRunCache {
+    void *dA = nullptr, *dB = nullptr, *dC = nullptr, *symm = nullptr;
+    size_t bytesA = 0, bytesB = 0, bytesC = 0, bytesSymm = 0;
+    cudaStream_t stream = nullptr;
+} g_hr;
+
+int ensure(void **p, size_t *have, size_t want) {
+    if (*have >= want && *p) return CATCCOS_OK;
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *have = 0;
+    cudaError_t e = cudaMalloc(p, want);
+    if (e != cudaSuccess) {
+        set_error("cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+        return CATCCOS_ERR_NOMEM;
+    }
+    *have = want;
+    return CATCCOS_OK;
+}
+void release_host_run_cache() {
+    if (g_hr.dA) cudaFree(g_hr.dA);
+    if (g_hr.dB) cudaFree(g_hr.dB);
+    if (g_hr.dC) cudaFree(g_hr.dC);
+    if (g_hr.stream) cudaStreamDestroy(g_hr.stream);
+    g_hr = HostRunCache();
+}
+}  // namespace
+
+
 extern "C" {
 
 int catccos_shmem_init(int32_t my_pe, int32_t n_pes, uint64_t local_mem_size, const char *ip_port) {
@@ -80,7 +111,10 @@ int catccos_shmem_init(int32_t my_pe, int32_t n_pes, uint64_t local_mem_size, co
 int catccos_shmem_init_emulated(int32_t n_pes, uint64_t local_mem_size) {
     return team_init_emulated(n_pes, local_mem_size);
 }
-int catccos_shmem_finalize(void) { return team_finalize(); }
+int catccos_shmem_finalize(void) {
+    release_host_run_cache();
+    return team_finalize();
+}
 void *catccos_shmem_malloc(size_t bytes) { return team_malloc(bytes); }
 void catccos_shmem_free(void *ptr) {
     if (ptr) team_free(ptr);
@@ -145,6 +179,15 @@ int catccos_debug_wait_unset_flag(void *stream, uint32_t timeout_ms) {
     return CATCCOS_OK;
 }
 
+int catccos_debug_set_flags(uint32_t flags) {
+    if (!team()) {
+        set_error("symmetric heap not initialised");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    team()->debug_flags = flags;
+    return CATCCOS_OK;
+}
+
 size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
     (void)dataType;
     if (!tiling) return 0;
@@ -206,6 +249,58 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
         return launch_dense_abi(op, dataType, stream, blockNum, params, t->n_pes, symmetric, tiling, transA, transB);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
+}
+
+int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
+                     void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
+                     uint32_t transA, uint32_t transB) {
+    (void)hostCustom;
+    (void)customCount;
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    Team *t = team();
+    if (t->emulated) {
+        set_error("catccos_run_host needs one process per PE (catccos_shmem_init)");
+        return CATCCOS_ERR_INVALID;
+    }
+    const int op = dense_op_of(commType);
+    if (op < 0 || (dataType != CATCCOS_FP16 && dataType != CATCCOS_BF16)) {
+        set_error("catccos_run_host: no host-buffer path for commType=%d dataType=%d", commType, dataType);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (!hostA || !hostB || !hostC) {
+        set_error("host buffers must not be NULL");
+        return CATCCOS_ERR_INVALID;
+    }
+    const size_t m = tiling->m, n = tiling->n, k = tiling->k, R = t->n_pes;
+    const size_t bytesA = m * k * 2, bytesB = k * n * 2;
+    const size_t bytesC = (op == OP_AGMM ? R * m : op == OP_MMRS ? m / R : m) * n * 2;
+    const size_t need = dense_symmetric_bytes(op, static_cast<int>(R), static_cast<int>(m), static_cast<int>(n),
+                                              static_cast<int>(k));
+    if ((rc = ensure(&g_hr.dA, &g_hr.bytesA, bytesA)) || (rc = ensure(&g_hr.dB, &g_hr.bytesB, bytesB)) ||
+        (rc = ensure(&g_hr.dC, &g_hr.bytesC, bytesC)))
+        return rc;
+    if (need > g_hr.bytesSymm) {
+        if (g_hr.symm) team_free(g_hr.symm);
+        g_hr.symm = team_malloc(need);
+        if (!g_hr.symm) return CATCCOS_ERR_NOMEM;
+        g_hr.bytesSymm = need;
+    }
+    if (!g_hr.stream) cudaStreamCreateWithFlags(&g_hr.stream, cudaStreamNonBlocking);
+    cudaMemcpyAsync(g_hr.dA, hostA, bytesA, cudaMemcpyHostToDevice, g_hr.stream);
+    cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.stream);
+    CatccosKernelParams kp{static_cast<uint8_t *>(g_hr.dA), static_cast<uint8_t *>(g_hr.dB),
+                           static_cast<uint8_t *>(g_hr.dC), nullptr, 0};
+    rc = launch_dense_abi(op, dataType, g_hr.stream, blockNum, &kp, 1, static_cast<uint8_t *>(g_hr.symm), tiling,
+                          transA, transB);
+    if (rc) return rc;
+    cudaMemcpyAsync(hostC, g_hr.dC, bytesC, cudaMemcpyDeviceToHost, g_hr.stream);
+    cudaError_t e = cudaStreamSynchronize(g_hr.stream);
+    if (e != cudaSuccess) {
+        set_error("host-buffer run failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
 }
 
 }  // extern "C"

@@ -43,6 +43,7 @@ struct FusedParams {
     int world, rank_base, n_local, ctas_per_rank;
     int M, N, K;                      // AG-MM: M = rows held by one rank; MM-RS / MM-AR: M = total rows
     uint32_t epoch;
+    int compute_only;                 // measurement mode: no peer traffic, no flag waits (data left by an earlier launch)
     uint64_t timeout_ns;
     int *status;                      // cb::StatusWord[ST_WORDS], device memory
 };

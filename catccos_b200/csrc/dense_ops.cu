@@ -179,6 +179,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.N = n;
     p.K = k;
     p.epoch = ++t->epoch;
+    p.compute_only = (t->debug_flags & 1u) ? 1 : 0;
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
 

@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             for (int t = cta; t < num_tiles && ok; t += p.ctas_per_rank) {
                 const Tile tl = decode_tile<OP>(p, rank, t);
                 if (!tl.valid) continue;
-                if (OP == OP_AGMM && tl.a_gathered) {
+                if (OP == OP_AGMM && tl.a_gathered && !p.compute_only) {
                     // rows of this tile were pushed by rank tl.peer as kAgSubChunks units
                     const uint32_t w = kFlagOpBase + (tl.peer * mt_ag + tl.mi) * kAgSubChunks;
                     for (int q = 0; q < kAgSubChunks && ok; ++q)
@@ -273,7 +273,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             const bool remote = (OP != OP_AGMM) && (tl.peer != rank);
 
             // Waits on peers are done by one thread; the group then meets on a bounded barrier.
-            const bool need_pre = (OP != OP_AGMM) && R > 1 && (remote ? !((entered_ok >> tl.peer) & 1) : true);
+            const bool need_pre =
+                (OP != OP_AGMM) && R > 1 && !p.compute_only && (remote ? !((entered_ok >> tl.peer) & 1) : true);
             if (need_pre) {
                 if (etid == 0) {
                     bool w = true;
@@ -300,7 +301,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 dst_row = C + static_cast<size_t>(row) * p.N;
             } else if (remote) {
                 // partial tile -> owner's staging rows [src = rank][row inside the owner's block]
-                T *stage = reinterpret_cast<T *>(p.heap_base[tl.peer] + p.symm_off);
+                // (compute-only measurement: same stores, but into this rank's own staging rows)
+                T *stage = reinterpret_cast<T *>(p.heap_base[p.compute_only ? rank : tl.peer] + p.symm_off);
                 dst_row = stage + (static_cast<size_t>(rank) * mr + (row - tl.peer * mr)) * p.N;
             } else {
                 dst_row = (OP == OP_MMRS) ? C + static_cast<size_t>(row - rank * mr) * p.N
@@ -361,7 +363,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 } else {
                     for (int i = 0; i < 32 && col + i < p.N; ++i) dst_row[col + i] = static_cast<T>(f[i]);
                 }
-                if (OP == OP_MMAR && !remote && R > 1) {
+                if (OP == OP_MMAR && !remote && R > 1 && !p.compute_only) {
                     // reduced tile -> every peer's "final" rows (second half of the symmetric region)
                     const size_t final_off = static_cast<size_t>(R) * mr * p.N;
                     for (int jj = 1; jj < R; ++jj) {
@@ -384,7 +386,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
 
-            if (OP != OP_AGMM && R > 1 && (remote || OP == OP_MMAR)) {
+            if (OP != OP_AGMM && R > 1 && !p.compute_only && (remote || OP == OP_MMAR)) {
                 // all 128 threads' stores of this tile are done -> one thread publishes it
                 if (!(ok = epi.sync(ctl))) break;
                 if (etid == 0) {
@@ -404,7 +406,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             ++tcount;
         }
 
-        if (OP == OP_MMAR && R > 1 && ok) {
+        if (OP == OP_MMAR && R > 1 && ok && !p.compute_only) {
             // second phase: copy the peers' reduced tiles from my "final" rows into D
             const int mrr = rows_per_rank<OP>(p);
             const int nt = ceil_div(p.N, BN);
@@ -434,7 +436,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
     } else {
         // ------------------------------------------------------------- comm warps ----
         const int ctid = (warp - 6) * 32 + lane;     // 0..63
-        if (R > 1) {
+        if (R > 1 && !p.compute_only) {
             if (cta == 0 && ctid < R && ctid != rank) {
                 // tell every peer that this rank has entered the epoch: its symmetric data region
                 // may now be overwritten

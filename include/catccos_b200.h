@@ -113,6 +113,10 @@ CATCCOS_API int catccos_reset_status(void);
 /* Bounded-wait self test: one thread waits `timeout_ms` for a flag nothing sets, then reports
  * through the status words.  Leaves the context usable. */
 CATCCOS_API int catccos_debug_wait_unset_flag(void *stream, uint32_t timeout_ms);
+/* Measurement switch (no counterpart in the reference): bit 0 makes later launches compute-only —
+ * no peer traffic and no flag waits, operating on whatever an earlier fused launch left in the
+ * symmetric region — so that exposed communication = fused time - compute-only time. */
+CATCCOS_API int catccos_debug_set_flags(uint32_t flags);
 
 /* Bytes of the `symmetric` buffer an operator carves for itself (the reference sizes it as one
  * fixed SHMEM_BUFF_BYTES allocation, utils/info.h:35). */
@@ -155,6 +159,17 @@ CATCCOS_API int catccos_launch(int32_t commType, int32_t dataType, void *stream,
 CATCCOS_API int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum,
                             CatccosKernelParams *params, uint8_t **workspaces, uint8_t *symmetric,
                             CocTilingParams *tiling, uint32_t transA, uint32_t transB);
+
+/* ------------------------------------------------------------------- host-buffer form ---- */
+/* The operator classes' AllocateDeviceSpace() (host -> device copy of the inputs), kernel launch
+ * and WriteResultFile() (device -> host copy of the result) in one synchronous call, with memory
+ * instead of .bin files (examples/matmul_allreduce/matmul_allreduce_host.h:17-85,
+ * examples/matmul_allreduce/main.cpp:127-171).  hostA/hostB/hostC (and hostCustom[i]) are host
+ * buffers laid out as the operator's device operands; pinned memory copies fastest.  Device
+ * staging buffers and the symmetric buffer are created on first use and kept. */
+CATCCOS_API int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA,
+                                 const void *hostB, void *hostC, const void *const *hostCustom, uint32_t customCount,
+                                 CocTilingParams *tiling, uint32_t transA, uint32_t transB);
 
 #ifdef __cplusplus
 }

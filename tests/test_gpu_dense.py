@@ -69,7 +69,7 @@ def test_matmul_reduce_scatter(world, trans_b, m, n, k):
     gold = dense.golden_matmul_reduce_scatter(a, b)
     outs = _run_emulated(rt.MATMUL_REDUCE_SCATTER, world, a, b, (m // world, n), m, k, n, trans_b, torch.bfloat16)
     for r in range(world):
-        assert_close_to_golden(outs[r], gold[r], k * world, TOL, f"mmrs rank {r}")
+        assert_close_to_golden(outs[r], gold[r], k, TOL, f"mmrs rank {r}", strict_reference=(world <= 2 or k >= 2048))
 
 
 @pytest.mark.parametrize("world,m,n,k,dtype", [
@@ -83,7 +83,7 @@ def test_matmul_allreduce(world, m, n, k, dtype):
     gold = dense.golden_matmul_allreduce(a, b)
     outs = _run_emulated(rt.MATMUL_ALLREDUCE, world, a, b, (m, n), m, k, n, 0, dtype)
     for r in range(world):
-        assert_close_to_golden(outs[r], gold, k * world, TOL, f"mmar rank {r}")
+        assert_close_to_golden(outs[r], gold, k, TOL, f"mmar rank {r}", strict_reference=(world <= 2 or k >= 2048))
     # every rank must hold bit-identical results (deterministic reduction, then broadcast)
     for r in range(1, world):
         assert torch.equal(outs[0], outs[r])
