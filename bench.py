@@ -239,9 +239,26 @@ def main():
     if rc != 0:
         raise SystemExit(f"device wait ran out during warm-up: {words}")
 
+    # nvidia-smi samples every 100 ms and the timed region can be much shorter, so the timed
+    # steps are bracketed by identical untimed launches: the clock samples then describe the GPU
+    # under the same load (every rank runs the same bracket; the launches are collective).
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
+    load_steps = 0
+    if not os.environ.get("BENCH_NO_LOAD_BRACKET"):
+        t0 = time.perf_counter()
+        for _ in range(10):
+            step()
+        torch.cuda.synchronize()
+        t_step = (time.perf_counter() - t0) / 10
+        if world > 1:                       # every rank must launch the same number of collective steps
+            tt = torch.tensor([t_step], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t_step = float(tt.item())
+        load_steps = int(min(20000, max(args.warmup, 0.6 / max(t_step, 1e-6))))
+    for _ in range(load_steps):
+        step()
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
@@ -250,8 +267,12 @@ def main():
     ev1.record(stream)
     torch.cuda.synchronize()
     elapsed_ms = ev0.elapsed_time(ev1)
+    for _ in range(load_steps // 3):
+        step()
     barrier()
     clocks = sampler.stop() if sampler else None
+    if clocks is not None:
+        clocks["load_bracket_steps"] = load_steps
     rc, words = rt.last_status()
     if rc != 0:
         raise SystemExit(f"device wait ran out: {words}")
