@@ -25,7 +25,9 @@ constexpr int kStages = 4;
 constexpr int kAStageBytes = BM * BK * 2;   // 16 KiB
 constexpr int kBStageBytes = BN * BK * 2;   // 32 KiB
 constexpr int kGemmThreads = 256;           // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 comm
-constexpr int kGemmSmemBytes = kStages * (kAStageBytes + kBStageBytes) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kPushPieceBytes = 16 * 1024; // all-gather push: shared-memory staging piece (two of them)
+constexpr int kGemmSmemBytes =
+    kStages * (kAStageBytes + kBStageBytes) + 2 * kPushPieceBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int kAgSubChunks = 4;             // an all-gather chunk (BM rows) is pushed as 4 units of 32 rows
 
 struct alignas(64) RankArgs {

@@ -23,11 +23,10 @@ struct GemmSmem {
     uint64_t tmem_empty[2];
     uint64_t drain;
     uint64_t epi_bar;    // 128 epilogue threads
-    uint64_t comm_bar;   // 64 comm threads
+    uint64_t push_bar[2];   // all-gather push: bulk loads into the two staging pieces
     uint32_t tmem_base;
     int abort_flag;
     int epi_ok;
-    int comm_ok;
 };
 
 // Bounded barrier among a fixed group of threads (an mbarrier instead of bar.sync so that a
@@ -112,7 +111,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
     uint8_t *smem_b = smem + kStages * kAStageBytes;
-    GemmSmem *sh = reinterpret_cast<GemmSmem *>(smem + kStages * (kAStageBytes + kBStageBytes));
+    uint8_t *smem_push = smem + kStages * (kAStageBytes + kBStageBytes);
+    GemmSmem *sh = reinterpret_cast<GemmSmem *>(smem_push + 2 * kPushPieceBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -135,10 +135,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
         }
         mbar_init(&sh->drain, 1);
         mbar_init(&sh->epi_bar, 128);
-        mbar_init(&sh->comm_bar, 64);
+        mbar_init(&sh->push_bar[0], 1);
+        mbar_init(&sh->push_bar[1], 1);
         sh->abort_flag = 0;
         sh->epi_ok = 1;
-        sh->comm_ok = 1;
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
@@ -443,15 +443,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 fence_sys();
                 st_release_sys(flag_ptr(p, ctid, kFlagEntered + rank), p.epoch);
             }
-            if (OP == OP_AGMM) {
-                // push my rows to every peer's gathered region, destination rank-1 first (it consumes
-                // my rows first), in units of 32 rows; one flag per unit
+            if (OP == OP_AGMM && ctid == 0) {
+                // Push my rows into every peer's gathered region with bulk copies (global -> shared ->
+                // peer global), destination rank-1 first (it consumes my rows first), in units of 32
+                // rows with one flag per unit.  One thread drives the copy engine; two 16 KiB pieces
+                // are in flight.
                 const int units_per_dest = mt_ag * kAgSubChunks;
                 const int total = (R - 1) * units_per_dest;
                 const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
                 bool ok = true;
                 uint32_t entered_ok = 0;
-                GroupSync cs{&sh->comm_bar, 0};
+                uint32_t piece = 0;      // pieces issued so far (buffer = piece & 1, phase = (piece >> 1) & 1)
                 for (int u = cta; u < total && ok; u += p.ctas_per_rank) {
                     const int jj = u / units_per_dest;              // 0 -> rank-1, 1 -> rank-2, ...
                     const int d = (rank + R - 1 - jj) % R;
@@ -460,36 +462,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                     const int r0 = chunk * BM + sub * (BM / kAgSubChunks);
                     const int r1 = min(p.M, r0 + BM / kAgSubChunks);
                     if (!((entered_ok >> d) & 1)) {
-                        if (ctid == 0 &&
-                            !wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d))
-                            *reinterpret_cast<volatile int *>(&sh->comm_ok) = 0;
-                        if (!(ok = cs.sync(ctl))) break;
-                        if (!(ok = (*reinterpret_cast<volatile int *>(&sh->comm_ok) != 0))) break;
+                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d)))
+                            break;
                         entered_ok |= 1u << d;
                     }
                     if (r1 > r0) {
-                        const uint4 *src =
-                            reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(ra.A) + r0 * row_bytes);
-                        uint4 *dst = reinterpret_cast<uint4 *>(p.heap_base[d] + p.symm_off +
-                                                               (static_cast<size_t>(rank) * p.M + r0) * row_bytes);
-                        const size_t nvec = (r1 - r0) * row_bytes / 16;
-                        size_t i = ctid;
-                        for (; i + 7 * 64 < nvec; i += 8 * 64) {
-                            uint4 tmp[8];
-#pragma unroll
-                            for (int g = 0; g < 8; ++g) tmp[g] = __ldg(src + i + g * 64);
-#pragma unroll
-                            for (int g = 0; g < 8; ++g) dst[i + g * 64] = tmp[g];
+                        const uint8_t *src = static_cast<const uint8_t *>(ra.A) + r0 * row_bytes;
+                        uint8_t *dst = p.heap_base[d] + p.symm_off + (static_cast<size_t>(rank) * p.M + r0) * row_bytes;
+                        const size_t bytes = (r1 - r0) * row_bytes;
+                        for (size_t off = 0; off < bytes && ok; off += kPushPieceBytes, ++piece) {
+                            const uint32_t len = static_cast<uint32_t>(min(static_cast<size_t>(kPushPieceBytes), bytes - off));
+                            const uint32_t b = piece & 1;
+                            bulk_wait_read<1>();     // the store that last used this piece has read it
+                            mbar_expect_tx(&sh->push_bar[b], len);
+                            bulk_load(smem_push + b * kPushPieceBytes, src + off, len, &sh->push_bar[b]);
+                            if (!(ok = mbar_wait(&sh->push_bar[b], (piece >> 1) & 1, ctl, W_DRAIN))) break;
+                            bulk_store(dst + off, smem_push + b * kPushPieceBytes, len);
+                            bulk_commit();
                         }
-                        for (; i < nvec; i += 64) dst[i] = __ldg(src + i);
                     }
-                    if (!(ok = cs.sync(ctl))) break;
-                    if (ctid == 0) {
-                        fence_sys();
-                        st_release_sys(flag_ptr(p, d, kFlagOpBase + (rank * mt_ag + chunk) * kAgSubChunks + sub),
-                                       p.epoch);
-                    }
+                    if (!ok) break;
+                    bulk_wait<0>();          // every piece of the unit has been written to the peer
+                    fence_proxy_async();
+                    fence_sys();
+                    st_release_sys(flag_ptr(p, d, kFlagOpBase + (rank * mt_ag + chunk) * kAgSubChunks + sub), p.epoch);
                 }
+                bulk_wait<0>();
             }
         }
     }
