@@ -48,6 +48,7 @@ SIGNATURES = {
     "catccos_reset_status": (ctypes.c_int, []),
     "catccos_debug_wait_unset_flag": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32]),
     "catccos_debug_set_flags": (ctypes.c_int, [ctypes.c_uint32]),
+    "catccos_debug_set_trace": (ctypes.c_int, [ctypes.c_void_p]),
     "catccos_symmetric_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(CocTilingParams)]),
     "catccos_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(CocTilingParams)]),
     "catccos_launch": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32] + LAUNCH_ARGS),

@@ -188,6 +188,15 @@ int catccos_debug_set_flags(uint32_t flags) {
     return CATCCOS_OK;
 }
 
+int catccos_debug_set_trace(void *device_buf) {
+    if (!team()) {
+        set_error("symmetric heap not initialised");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    team()->trace_dev = static_cast<unsigned long long *>(device_buf);
+    return CATCCOS_OK;
+}
+
 size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
     (void)dataType;
     if (!tiling) return 0;

@@ -48,6 +48,21 @@ struct FusedParams {
     int compute_only;                 // measurement mode: no peer traffic, no flag waits (data left by an earlier launch)
     uint64_t timeout_ns;
     int *status;                      // cb::StatusWord[ST_WORDS], device memory
+    unsigned long long *trace;        // optional: kTraceSlots %globaltimer stamps per CTA (nullptr = off)
+};
+
+// Per-CTA trace slots (nanoseconds of %globaltimer).
+enum TraceSlot : int {
+    TR_START = 0, TR_END = 1,
+    TR_PROD_WAIT_FIRST = 2,   // producer: when the first wait for pushed rows began
+    TR_PROD_WAIT_NS = 3,      // producer: total time spent waiting for pushed rows
+    TR_PUSH_BEGIN = 4, TR_PUSH_END = 5,
+    TR_EPI_WAIT_NS = 6,       // epilogue: total time waiting for peers (entered / partial tiles)
+    TR_EPI_STORE_NS = 7,      // epilogue: total time draining accumulators (TMEM -> memory)
+    TR_MMA_WAIT_TMEM_NS = 8,  // MMA warp: total time waiting for a free accumulator
+    TR_MMA_WAIT_SMEM_NS = 9,  // MMA warp: total time waiting for operands in shared memory
+    TR_TILES = 10,
+    kTraceSlots = 16
 };
 
 struct Team;   // symmetric heap + peers (symm_heap.cu)

@@ -182,6 +182,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.compute_only = (t->debug_flags & 1u) ? 1 : 0;
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
+    p.trace = t->trace_dev;
 
     const int grid = per_rank * n_local;
     const bool coop = n_local > 1;

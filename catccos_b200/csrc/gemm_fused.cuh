@@ -101,6 +101,11 @@ __device__ __forceinline__ Tile decode_tile(const FusedParams &p, int rank, int 
     return tl;
 }
 
+#define CB_TRACE(slot, value)                                                     \
+    do {                                                                          \
+        if (p.trace) p.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + (slot)] = (value); \
+    } while (0)
+
 __device__ __forceinline__ uint32_t *flag_ptr(const FusedParams &p, int pe, uint32_t word) {
     return reinterpret_cast<uint32_t *>(p.heap_base[pe]) + word;
 }
@@ -160,22 +165,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
     ctl.rank = rank;
 
     const int mt_ag = ceil_div(p.M, BM);   // AG-MM: chunks per source rank
+    if (threadIdx.x == 0) CB_TRACE(TR_START, globaltimer_ns());
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer ----
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            uint64_t prod_wait_ns = 0;
             for (int t = cta; t < num_tiles && ok; t += p.ctas_per_rank) {
                 const Tile tl = decode_tile<OP>(p, rank, t);
                 if (!tl.valid) continue;
                 if (OP == OP_AGMM && tl.a_gathered && !p.compute_only) {
                     // rows of this tile were pushed by rank tl.peer as kAgSubChunks units
                     const uint32_t w = kFlagOpBase + (tl.peer * mt_ag + tl.mi) * kAgSubChunks;
+                    const uint64_t tw0 = p.trace ? globaltimer_ns() : 0;
                     for (int q = 0; q < kAgSubChunks && ok; ++q)
                         ok = wait_flag_ge(flag_ptr(p, rank, w + q), p.epoch, ctl, W_AG_CHUNK, w + q);
                     if (!ok) break;
                     fence_proxy_async();
+                    if (p.trace) {
+                        if (prod_wait_ns == 0) CB_TRACE(TR_PROD_WAIT_FIRST, tw0);
+                        prod_wait_ns += globaltimer_ns() - tw0 + 1;
+                    }
                 }
                 const CUtensorMap *tma = (OP == OP_AGMM && tl.a_gathered) ? &ra.tmAg : &ra.tmA;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
@@ -194,6 +206,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                     }
                 }
             }
+            CB_TRACE(TR_PROD_WAIT_NS, prod_wait_ns);
             if (!ok) {
                 // Aborting: loads already issued still land in shared memory; wait for them (bounded).
                 for (uint32_t back = 1; back <= kStages && back <= it; ++back) {
@@ -212,16 +225,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             constexpr uint32_t idesc = make_idesc_f16(fmt, BM, BN, 0, B_MN ? 1 : 0);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
+            uint64_t mma_wait_tmem = 0, mma_wait_smem = 0;
             for (int t = cta; t < num_tiles && ok; t += p.ctas_per_rank) {
                 const Tile tl = decode_tile<OP>(p, rank, t);
                 if (!tl.valid) continue;
                 const uint32_t acc = tcount & 1;
+                const uint64_t tm0 = p.trace ? globaltimer_ns() : 0;
                 if (!(ok = mbar_wait(&sh->tmem_empty[acc], ((tcount >> 1) & 1) ^ 1, ctl, W_TMEM_EMPTY))) break;
+                if (p.trace) mma_wait_tmem += globaltimer_ns() - tm0;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % kStages;
+                    const uint64_t ts0 = p.trace ? globaltimer_ns() : 0;
                     if (!(ok = mbar_wait(&sh->full[s], (it / kStages) & 1, ctl, W_MBAR_FULL))) break;
+                    if (p.trace) mma_wait_smem += globaltimer_ns() - ts0;
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + s * kAStageBytes);
                     const uint32_t b_addr = smem_u32(smem_b + s * kBStageBytes);
@@ -241,6 +259,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 umma_commit(&sh->tmem_full[acc]);
                 ++tcount;
             }
+            CB_TRACE(TR_MMA_WAIT_TMEM_NS, mma_wait_tmem);
+            CB_TRACE(TR_MMA_WAIT_SMEM_NS, mma_wait_smem);
+            CB_TRACE(TR_TILES, tcount);
             if (!ok) {
                 umma_commit(&sh->drain);
                 const uint64_t t0 = globaltimer_ns();
@@ -258,6 +279,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
         uint32_t entered_ok = 0;                // bitmap of peers known to have entered this epoch
         bool ok = true;
         GroupSync epi{&sh->epi_bar, 0};
+        uint64_t epi_wait_ns = 0, epi_store_ns = 0;
         const int mr = (OP == OP_AGMM) ? 0 : rows_per_rank<OP>(p);
         const int per = tiles_per_peer<OP>(p);
         T *const C = reinterpret_cast<T *>(ra.C);
@@ -276,6 +298,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             const bool need_pre =
                 (OP != OP_AGMM) && R > 1 && !p.compute_only && (remote ? !((entered_ok >> tl.peer) & 1) : true);
             if (need_pre) {
+                const uint64_t tp0 = p.trace ? globaltimer_ns() : 0;
                 if (etid == 0) {
                     bool w = true;
                     if (remote) {
@@ -294,6 +317,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 if (!(ok = epi.sync(ctl))) break;
                 if (!(ok = (*reinterpret_cast<volatile int *>(&sh->epi_ok) != 0))) break;
                 if (remote) entered_ok |= 1u << tl.peer;
+                if (p.trace) epi_wait_ns += globaltimer_ns() - tp0;
             }
 
             T *dst_row = nullptr;        // where this thread's row of the tile goes
@@ -310,18 +334,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             }
             const T *my_stage = (OP != OP_AGMM) ? reinterpret_cast<const T *>(p.heap_base[rank] + p.symm_off) : nullptr;
 
+            // MM-RS / MM-AR: every output row segment (128 columns = 256 B) is staged in this thread's
+            // private shared-memory row and leaves as one bulk copy, so that a peer receives full
+            // 128-byte lines instead of 16-byte fragments.  AG-MM writes its (local) rows directly.
+            constexpr bool kStaged = (OP != OP_AGMM);
+            uint8_t *my_row_smem = smem_push + row_in_tile * 256;
+            const uint64_t te0 = p.trace ? globaltimer_ns() : 0;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
+                if (kStaged && (c & 3) == 0) bulk_wait_read<0>();   // my staging row is free again
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
                 tmem_ld_wait();
                 const int col = tl.n0 + c * 32;
-                if (!row_ok || col >= p.N) continue;
+                const bool live = row_ok && col < p.N;
+                if (!kStaged && !live) continue;
                 float f[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
                 const bool full_vec = col + 32 <= p.N;
-                if (OP != OP_AGMM && !remote && R > 1) {
+                if (OP != OP_AGMM && !remote && R > 1 && live) {
                     // deterministic reduction: partials added in rank order, own fp32 accumulator in its slot
                     float accv[32];
 #pragma unroll
@@ -345,7 +377,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                                     }
                                 }
                             } else {
-                                for (int i = 0; i < 32 && col + i < p.N; ++i) accv[i] += static_cast<float>(src[i]);
+                                // N is a multiple of 8: the ragged edge is made of whole 8-element groups
+                                for (int g = 0; g < 4 && col + g * 8 < p.N; ++g) {
+                                    const uint4 u = *reinterpret_cast<const uint4 *>(src + g * 8);
+                                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                                    for (int h = 0; h < 4; ++h) {
+                                        const float2 x = Pack2<T>::unpack(w4[h]);
+                                        accv[g * 8 + h * 2] += x.x;
+                                        accv[g * 8 + h * 2 + 1] += x.y;
+                                    }
+                                }
                             }
                         }
                     }
@@ -355,39 +397,48 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) pk[i] = Pack2<T>::pack(f[2 * i], f[2 * i + 1]);
-                if (full_vec) {
+                if (!kStaged) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g)
-                        *reinterpret_cast<uint4 *>(dst_row + col + g * 8) =
-                            make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                        if (col + g * 8 < p.N)
+                            *reinterpret_cast<uint4 *>(dst_row + col + g * 8) =
+                                make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
                 } else {
-                    for (int i = 0; i < 32 && col + i < p.N; ++i) dst_row[col + i] = static_cast<T>(f[i]);
-                }
-                if (OP == OP_MMAR && !remote && R > 1 && !p.compute_only) {
-                    // reduced tile -> every peer's "final" rows (second half of the symmetric region)
-                    const size_t final_off = static_cast<size_t>(R) * mr * p.N;
-                    for (int jj = 1; jj < R; ++jj) {
-                        const int d = (rank + jj) % R;
-                        T *fin = reinterpret_cast<T *>(p.heap_base[d] + p.symm_off) + final_off +
-                                 static_cast<size_t>(row) * p.N + col;
-                        if (full_vec) {
 #pragma unroll
-                            for (int g = 0; g < 4; ++g)
-                                *reinterpret_cast<uint4 *>(fin + g * 8) =
-                                    make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-                        } else {
-                            for (int i = 0; i < 32 && col + i < p.N; ++i) fin[i] = static_cast<T>(f[i]);
+                    for (int g = 0; g < 4; ++g)
+                        *reinterpret_cast<uint4 *>(my_row_smem + (c & 3) * 64 + g * 16) =
+                            make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                    if ((c & 3) == 3) {
+                        fence_proxy_async();    // my shared-memory writes -> visible to the copy engine
+                        const int colh = tl.n0 + (c >> 2) * 128;
+                        if (row_ok && colh < p.N) {
+                            const uint32_t len = static_cast<uint32_t>(min(128, p.N - colh)) * sizeof(T);
+                            bulk_store(dst_row + colh, my_row_smem, len);
+                            if (OP == OP_MMAR && !remote && R > 1 && !p.compute_only) {
+                                // reduced rows -> every peer's "final" rows (second half of the symmetric region)
+                                const size_t final_off = static_cast<size_t>(R) * mr * p.N;
+                                for (int jj = 1; jj < R; ++jj) {
+                                    const int d = (rank + jj) % R;
+                                    T *fin = reinterpret_cast<T *>(p.heap_base[d] + p.symm_off) + final_off +
+                                             static_cast<size_t>(row) * p.N + colh;
+                                    bulk_store(fin, my_row_smem, len);
+                                }
+                            }
+                            bulk_commit();
                         }
                     }
                 }
             }
+            if (p.trace) epi_store_ns += globaltimer_ns() - te0;
             // accumulator drained: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
 
             if (OP != OP_AGMM && R > 1 && !p.compute_only && (remote || OP == OP_MMAR)) {
-                // all 128 threads' stores of this tile are done -> one thread publishes it
+                // every thread's rows have been written to the peer(s) -> one thread publishes the tile
+                bulk_wait<0>();
+                fence_proxy_async();
                 if (!(ok = epi.sync(ctl))) break;
                 if (etid == 0) {
                     fence_sys();
@@ -406,6 +457,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             ++tcount;
         }
 
+        if (OP != OP_AGMM) bulk_wait<0>();     // my staging row must outlive the copies that read it
+        if (etid == 0) {
+            CB_TRACE(TR_EPI_WAIT_NS, epi_wait_ns);
+            CB_TRACE(TR_EPI_STORE_NS, epi_store_ns);
+        }
         if (OP == OP_MMAR && R > 1 && ok && !p.compute_only) {
             // second phase: copy the peers' reduced tiles from my "final" rows into D
             const int mrr = rows_per_rank<OP>(p);
@@ -454,6 +510,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 bool ok = true;
                 uint32_t entered_ok = 0;
                 uint32_t piece = 0;      // pieces issued so far (buffer = piece & 1, phase = (piece >> 1) & 1)
+                CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
                 for (int u = cta; u < total && ok; u += p.ctas_per_rank) {
                     const int jj = u / units_per_dest;              // 0 -> rank-1, 1 -> rank-2, ...
                     const int d = (rank + R - 1 - jj) % R;
@@ -488,6 +545,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                     st_release_sys(flag_ptr(p, d, kFlagOpBase + (rank * mt_ag + chunk) * kAgSubChunks + sub), p.epoch);
                 }
                 bulk_wait<0>();
+                CB_TRACE(TR_PUSH_END, globaltimer_ns());
             }
         }
     }
@@ -499,6 +557,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
+    if (threadIdx.x == 0) CB_TRACE(TR_END, globaltimer_ns());
 }
 
 }  // namespace cb

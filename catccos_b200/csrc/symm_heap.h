@@ -56,6 +56,7 @@ struct Team {
     uint32_t epoch = 0;            // launches so far; identical on all PEs by collective-call order
     int *status_dev = nullptr;     // StatusWord[ST_WORDS]
     uint64_t timeout_ns = 10ull * 1000 * 1000 * 1000;
+    unsigned long long *trace_dev = nullptr;   // optional per-CTA trace buffer (catccos_debug_set_trace)
     uint32_t debug_flags = 0;      // bit 0: compute-only launches (exposed-communication measurement)
     // host rendezvous
     int sock = -1;

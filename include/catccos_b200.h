@@ -117,6 +117,11 @@ CATCCOS_API int catccos_debug_wait_unset_flag(void *stream, uint32_t timeout_ms)
  * no peer traffic and no flag waits, operating on whatever an earlier fused launch left in the
  * symmetric region — so that exposed communication = fused time - compute-only time. */
 CATCCOS_API int catccos_debug_set_flags(uint32_t flags);
+/* Device-side tracing, the counterpart of the reference's AscendTimer (tools/AscendTimerDevice.hpp,
+ * include/catccos/dgemm/device/device_dgemm.hpp:61-117): `device_buf` (device memory, at least
+ * 16 * 8 bytes per CTA of the largest grid, zeroed by the caller) receives per-CTA %globaltimer
+ * stamps and accumulated wait times of later launches; NULL switches tracing off. */
+CATCCOS_API int catccos_debug_set_trace(void *device_buf);
 
 /* Bytes of the `symmetric` buffer an operator carves for itself (the reference sizes it as one
  * fixed SHMEM_BUFF_BYTES allocation, utils/info.h:35). */
