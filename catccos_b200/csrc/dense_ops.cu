@@ -1,6 +1,7 @@
 // Host launchers of the f16/bf16 fused kernels: tensor maps, shape checks, launch.
 #include "dense_ops.h"
 
+#include <stdlib.h>
 #include <string.h>
 
 #include "gemm_fused.cuh"
@@ -174,7 +175,19 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     int per_rank = t->num_sms / n_local;
     if (block_num > 0 && static_cast<int>(block_num) < per_rank) per_rank = static_cast<int>(block_num);
     if (per_rank < 1) per_rank = 1;
+    if (R > 1 && per_rank < 2) {
+        set_error("fused operators need at least 2 CTAs per rank (blockNum=%u)", block_num);
+        return CATCCOS_ERR_INVALID;
+    }
     p.ctas_per_rank = per_rank;
+    p.push_ctas = 0;
+    if (op == OP_AGMM && R > 1) {
+        int pc = 6;
+        if (const char *e = getenv("CATCCOS_PUSH_CTAS")) pc = atoi(e);
+        if (pc > per_rank / 4) pc = per_rank / 4;
+        if (pc < 1) pc = 1;
+        p.push_ctas = pc;
+    }
     p.M = m;
     p.N = n;
     p.K = k;

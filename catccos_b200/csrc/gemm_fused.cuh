@@ -23,7 +23,7 @@ struct GemmSmem {
     uint64_t tmem_empty[2];
     uint64_t drain;
     uint64_t epi_bar;    // 128 epilogue threads
-    uint64_t push_bar[2];   // all-gather push: bulk loads into the two staging pieces
+    uint64_t push_bar[kPushLanes];   // pusher CTA: one per lane (bulk load landed)
     uint32_t tmem_base;
     int abort_flag;
     int epi_ok;
@@ -127,6 +127,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
     const int R = p.world;
     const RankArgs &ra = p.ranks[lrank];
     const int num_tiles = R * tiles_per_peer<OP>(p);
+    // AG-MM with peers: the last push_ctas CTAs do no GEMM; the others share the tiles
+    const int gemm_ctas = p.ctas_per_rank - ((OP == OP_AGMM && R > 1 && !p.compute_only) ? p.push_ctas : 0);
+    const bool is_pusher = cta >= gemm_ctas;
     const int kblocks = ceil_div(p.K, BK);
 
     if (threadIdx.x == 0) {
@@ -140,8 +143,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
         }
         mbar_init(&sh->drain, 1);
         mbar_init(&sh->epi_bar, 128);
-        mbar_init(&sh->push_bar[0], 1);
-        mbar_init(&sh->push_bar[1], 1);
+        for (int l = 0; l < kPushLanes; ++l) mbar_init(&sh->push_bar[l], 1);
         sh->abort_flag = 0;
         sh->epi_ok = 1;
         mbar_init_fence();
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             uint32_t it = 0;
             bool ok = true;
             uint64_t prod_wait_ns = 0;
-            for (int t = cta; t < num_tiles && ok; t += p.ctas_per_rank) {
+            for (int t = cta; t < num_tiles && ok && !is_pusher; t += gemm_ctas) {
                 const Tile tl = decode_tile<OP>(p, rank, t);
                 if (!tl.valid) continue;
                 if (OP == OP_AGMM && tl.a_gathered && !p.compute_only) {
@@ -226,7 +228,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             uint64_t mma_wait_tmem = 0, mma_wait_smem = 0;
-            for (int t = cta; t < num_tiles && ok; t += p.ctas_per_rank) {
+            for (int t = cta; t < num_tiles && ok && !is_pusher; t += gemm_ctas) {
                 const Tile tl = decode_tile<OP>(p, rank, t);
                 if (!tl.valid) continue;
                 const uint32_t acc = tcount & 1;
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
         const int mr = (OP == OP_AGMM) ? 0 : rows_per_rank<OP>(p);
         const int per = tiles_per_peer<OP>(p);
         T *const C = reinterpret_cast<T *>(ra.C);
-        for (int t = cta; t < num_tiles && ok; t += p.ctas_per_rank) {
+        for (int t = cta; t < num_tiles && ok && !is_pusher; t += gemm_ctas) {
             const Tile tl = decode_tile<OP>(p, rank, t);
             if (!tl.valid) continue;
             const uint32_t acc = tcount & 1;
@@ -345,54 +347,46 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 if (kStaged && (c & 3) == 0) bulk_wait_read<0>();   // my staging row is free again
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
-                tmem_ld_wait();
                 const int col = tl.n0 + c * 32;
                 const bool live = row_ok && col < p.N;
+                const bool reduce = (OP != OP_AGMM) && !remote && R > 1 && live;
+                // own rows: fetch every peer's partial of this chunk while the accumulator is on its way
+                uint4 part[kMaxRanks][4];
+                if (reduce) {
+#pragma unroll
+                    for (int s = 0; s < kMaxRanks; ++s) {
+                        if (s < R && s != rank) {
+                            const T *src = my_stage + (static_cast<size_t>(s) * mr + (row - rank * mr)) * p.N + col;
+#pragma unroll
+                            for (int g = 0; g < 4; ++g)
+                                part[s][g] = (col + g * 8 < p.N) ? *reinterpret_cast<const uint4 *>(src + g * 8)
+                                                                 : make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                }
+                tmem_ld_wait();
                 if (!kStaged && !live) continue;
                 float f[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-                const bool full_vec = col + 32 <= p.N;
-                if (OP != OP_AGMM && !remote && R > 1 && live) {
-                    // deterministic reduction: partials added in rank order, own fp32 accumulator in its slot
-                    float accv[32];
+                if (reduce) {
+                    // fixed summation order (own fp32 accumulator, then the peers' partials by rank):
+                    // every output element has one owner, so results are reproducible run to run
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) accv[i] = 0.f;
-                    for (int s = 0; s < R; ++s) {
-                        if (s == rank) {
+                    for (int s = 0; s < kMaxRanks; ++s) {
+                        if (s < R && s != rank) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) accv[i] += f[i];
-                        } else {
-                            const T *src = my_stage + (static_cast<size_t>(s) * mr + (row - rank * mr)) * p.N + col;
-                            if (full_vec) {
+                            for (int g = 0; g < 4; ++g) {
+                                const uint32_t w4[4] = {part[s][g].x, part[s][g].y, part[s][g].z, part[s][g].w};
 #pragma unroll
-                                for (int g = 0; g < 4; ++g) {
-                                    const uint4 u = *reinterpret_cast<const uint4 *>(src + g * 8);
-                                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                                    for (int h = 0; h < 4; ++h) {
-                                        const float2 x = Pack2<T>::unpack(w4[h]);
-                                        accv[g * 8 + h * 2] += x.x;
-                                        accv[g * 8 + h * 2 + 1] += x.y;
-                                    }
-                                }
-                            } else {
-                                // N is a multiple of 8: the ragged edge is made of whole 8-element groups
-                                for (int g = 0; g < 4 && col + g * 8 < p.N; ++g) {
-                                    const uint4 u = *reinterpret_cast<const uint4 *>(src + g * 8);
-                                    const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                                    for (int h = 0; h < 4; ++h) {
-                                        const float2 x = Pack2<T>::unpack(w4[h]);
-                                        accv[g * 8 + h * 2] += x.x;
-                                        accv[g * 8 + h * 2 + 1] += x.y;
-                                    }
+                                for (int h = 0; h < 4; ++h) {
+                                    const float2 x = Pack2<T>::unpack(w4[h]);
+                                    f[g * 8 + h * 2] += x.x;
+                                    f[g * 8 + h * 2 + 1] += x.y;
                                 }
                             }
                         }
                     }
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) f[i] = accv[i];
                 }
                 uint32_t pk[16];
 #pragma unroll
@@ -499,19 +493,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 fence_sys();
                 st_release_sys(flag_ptr(p, ctid, kFlagEntered + rank), p.epoch);
             }
-            if (OP == OP_AGMM && ctid == 0) {
-                // Push my rows into every peer's gathered region with bulk copies (global -> shared ->
-                // peer global), destination rank-1 first (it consumes my rows first), in units of 32
-                // rows with one flag per unit.  One thread drives the copy engine; two 16 KiB pieces
-                // are in flight.
+            if (OP == OP_AGMM && is_pusher && ctid < kPushLanes) {
+                // Pusher CTA: moves my rows into every peer's gathered region with bulk copies
+                // (global -> shared -> peer global), destination rank-1 first (it consumes my rows
+                // first), in units of 32 rows with one flag per unit.  Each of the kPushLanes threads
+                // owns a 16 KiB staging piece (the GEMM stage area is free in this CTA) and whole
+                // units, so a unit's flag has a single writer.  Keeping this traffic on dedicated SMs
+                // keeps NVLink back-pressure away from the SMs that feed tensor cores.
                 const int units_per_dest = mt_ag * kAgSubChunks;
                 const int total = (R - 1) * units_per_dest;
                 const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
+                const int lane_id = (cta - gemm_ctas) * kPushLanes + ctid;
+                const int n_lanes = p.push_ctas * kPushLanes;
+                uint8_t *buf = smem + ctid * kPushPieceBytes;
+                uint64_t *bar = &sh->push_bar[ctid];
                 bool ok = true;
                 uint32_t entered_ok = 0;
-                uint32_t piece = 0;      // pieces issued so far (buffer = piece & 1, phase = (piece >> 1) & 1)
-                CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
-                for (int u = cta; u < total && ok; u += p.ctas_per_rank) {
+                uint32_t piece = 0;
+                if (ctid == 0) CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
+                for (int u = lane_id; u < total && ok; u += n_lanes) {
                     const int jj = u / units_per_dest;              // 0 -> rank-1, 1 -> rank-2, ...
                     const int d = (rank + R - 1 - jj) % R;
                     const int cu = u - jj * units_per_dest;
@@ -529,12 +529,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                         const size_t bytes = (r1 - r0) * row_bytes;
                         for (size_t off = 0; off < bytes && ok; off += kPushPieceBytes, ++piece) {
                             const uint32_t len = static_cast<uint32_t>(min(static_cast<size_t>(kPushPieceBytes), bytes - off));
-                            const uint32_t b = piece & 1;
-                            bulk_wait_read<1>();     // the store that last used this piece has read it
-                            mbar_expect_tx(&sh->push_bar[b], len);
-                            bulk_load(smem_push + b * kPushPieceBytes, src + off, len, &sh->push_bar[b]);
-                            if (!(ok = mbar_wait(&sh->push_bar[b], (piece >> 1) & 1, ctl, W_DRAIN))) break;
-                            bulk_store(dst + off, smem_push + b * kPushPieceBytes, len);
+                            bulk_wait_read<0>();     // my previous store has read the piece
+                            mbar_expect_tx(bar, len);
+                            bulk_load(buf, src + off, len, bar);
+                            if (!(ok = mbar_wait(bar, piece & 1, ctl, W_DRAIN))) break;
+                            bulk_store(dst + off, buf, len);
                             bulk_commit();
                         }
                     }
@@ -545,7 +544,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                     st_release_sys(flag_ptr(p, d, kFlagOpBase + (rank * mt_ag + chunk) * kAgSubChunks + sub), p.epoch);
                 }
                 bulk_wait<0>();
-                CB_TRACE(TR_PUSH_END, globaltimer_ns());
+                if (ctid == 0) CB_TRACE(TR_PUSH_END, globaltimer_ns());
             }
         }
     }

@@ -80,7 +80,11 @@ def test_matmul_reduce_scatter(world, trans_b, m, n, k):
 ])
 def test_matmul_allreduce(world, m, n, k, dtype):
     rt = _rt()
-    a, b = inputs.matmul_allreduce_inputs(world, m, k, n, dtype)
+    if dtype == torch.float16:
+        a, b = inputs.matmul_allreduce_inputs(world, m, k, n, dtype)
+    else:
+        # bf16 partials carry 8 bits: use the activation x weight magnitudes of the bf16 configurations
+        a, b = inputs.matmul_reduce_scatter_inputs(world, m, k, n, dtype)
     partials = [dense.matmul_fp32(x, y) for x, y in zip(a, b)]
     outs = _run_emulated(rt.MATMUL_ALLREDUCE, world, a, b, (m, n), m, k, n, 0, dtype)
     for r in range(world):
