@@ -26,10 +26,11 @@ constexpr int kAStageBytes = BM * BK * 2;   // 16 KiB
 constexpr int kBStageBytes = BN * BK * 2;   // 32 KiB
 constexpr int kGemmThreads = 256;           // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 comm
 constexpr int kPushPieceBytes = 16 * 1024; // all-gather push: one staging piece per pusher lane
-constexpr int kPushLanes = 12;             // pusher lanes (threads with a piece in flight) per pusher CTA
+constexpr int kPushLanes = 12;             // lanes (threads with a piece in flight) of a dedicated pusher CTA
+constexpr int kPushLanesShared = 2;        // lanes of a CTA that also runs the GEMM (staging next to the stages)
 constexpr int kGemmSmemBytes =
     kStages * (kAStageBytes + kBStageBytes) + 2 * kPushPieceBytes + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int kAgSubChunks = 4;             // an all-gather chunk (BM rows) is pushed as 4 units of 32 rows
+constexpr int kAgSubChunks = 8;             // an all-gather chunk (BM rows) is pushed as 8 units of 16 rows
 
 struct alignas(64) RankArgs {
     CUtensorMap tmA;    // A as passed by the caller: [rows, K], K innermost, box {BK, BM}
@@ -44,7 +45,8 @@ struct FusedParams {
     uint8_t *heap_base[kMaxRanks];    // VA (in this process) of every PE's symmetric heap
     uint64_t symm_off;                // byte offset of the operator's data region inside the heap
     int world, rank_base, n_local, ctas_per_rank;
-    int push_ctas;                    // AG-MM: the last push_ctas CTAs of a rank only move all-gather traffic
+    int push_ctas;                    // AG-MM: > 0: the last push_ctas CTAs of a rank only move all-gather traffic;
+                                      // 0: every CTA pushes from its comm warp next to its GEMM tiles
     int M, N, K;                      // AG-MM: M = rows held by one rank; MM-RS / MM-AR: M = total rows
     uint32_t epoch;
     int compute_only;                 // measurement mode: no peer traffic, no flag waits (data left by an earlier launch)

@@ -182,10 +182,11 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.ctas_per_rank = per_rank;
     p.push_ctas = 0;
     if (op == OP_AGMM && R > 1) {
-        int pc = 6;
+        // 0 (default): every CTA pushes next to its GEMM tiles; N > 0: N CTAs only push
+        int pc = 0;
         if (const char *e = getenv("CATCCOS_PUSH_CTAS")) pc = atoi(e);
         if (pc > per_rank / 4) pc = per_rank / 4;
-        if (pc < 1) pc = 1;
+        if (pc < 0) pc = 0;
         p.push_ctas = pc;
     }
     p.M = m;

@@ -493,19 +493,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 fence_sys();
                 st_release_sys(flag_ptr(p, ctid, kFlagEntered + rank), p.epoch);
             }
-            if (OP == OP_AGMM && is_pusher && ctid < kPushLanes) {
-                // Pusher CTA: moves my rows into every peer's gathered region with bulk copies
+            const bool dedicated = p.push_ctas > 0;
+            const int my_lanes = dedicated ? kPushLanes : kPushLanesShared;
+            if (OP == OP_AGMM && (is_pusher || !dedicated) && ctid < my_lanes) {
+                // All-gather push: my rows go into every peer's gathered region with bulk copies
                 // (global -> shared -> peer global), destination rank-1 first (it consumes my rows
-                // first), in units of 32 rows with one flag per unit.  Each of the kPushLanes threads
-                // owns a 16 KiB staging piece (the GEMM stage area is free in this CTA) and whole
-                // units, so a unit's flag has a single writer.  Keeping this traffic on dedicated SMs
-                // keeps NVLink back-pressure away from the SMs that feed tensor cores.
+                // first), in units of BM/kAgSubChunks rows with one flag per unit.  Every pushing
+                // thread ("lane") owns a 16 KiB staging piece and whole units, so a unit's flag has a
+                // single writer.  Default: each GEMM CTA pushes with two lanes of its comm warp
+                // (staging next to the GEMM stages); optionally a few CTAs are dedicated to pushing
+                // with 12 lanes each (the GEMM stage area is free there).
                 const int units_per_dest = mt_ag * kAgSubChunks;
                 const int total = (R - 1) * units_per_dest;
                 const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
-                const int lane_id = (cta - gemm_ctas) * kPushLanes + ctid;
-                const int n_lanes = p.push_ctas * kPushLanes;
-                uint8_t *buf = smem + ctid * kPushPieceBytes;
+                const int lane_id = (dedicated ? (cta - gemm_ctas) : cta) * my_lanes + ctid;
+                const int n_lanes = (dedicated ? p.push_ctas : p.ctas_per_rank) * my_lanes;
+                uint8_t *buf = (dedicated ? smem : smem_push) + ctid * kPushPieceBytes;
                 uint64_t *bar = &sh->push_bar[ctid];
                 bool ok = true;
                 uint32_t entered_ok = 0;
