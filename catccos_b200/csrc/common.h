@@ -25,11 +25,12 @@ constexpr int kStages = 4;
 constexpr int kAStageBytes = BM * BK * 2;   // 16 KiB
 constexpr int kBStageBytes = BN * BK * 2;   // 32 KiB
 constexpr int kGemmThreads = 256;           // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 comm
-constexpr int kPushPieceBytes = 16 * 1024; // all-gather push: one staging piece per pusher lane
-constexpr int kPushLanes = 12;             // lanes (threads with a piece in flight) of a dedicated pusher CTA
-constexpr int kPushLanesShared = 2;        // lanes of a CTA that also runs the GEMM (staging next to the stages)
+constexpr int kPushPieceBytes = 8 * 1024;  // all-gather push: one staging piece per pusher lane
+constexpr int kPushLanes = 24;             // lanes (threads with a piece in flight) of a dedicated pusher CTA
+constexpr int kSideSmemBytes = 32 * 1024;  // next to the GEMM stages: push staging (AG-MM) or epilogue row staging
+constexpr int kPushLanesShared = kSideSmemBytes / kPushPieceBytes;   // lanes of a CTA that also runs the GEMM
 constexpr int kGemmSmemBytes =
-    kStages * (kAStageBytes + kBStageBytes) + 2 * kPushPieceBytes + 1024 /*align*/ + 256 /*barriers*/;
+    kStages * (kAStageBytes + kBStageBytes) + kSideSmemBytes + 1024 /*align*/ + 512 /*barriers*/;
 constexpr int kAgSubChunks = 8;             // an all-gather chunk (BM rows) is pushed as 8 units of 16 rows
 
 struct alignas(64) RankArgs {

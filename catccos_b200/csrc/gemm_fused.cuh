@@ -117,7 +117,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
     uint8_t *smem_a = smem;
     uint8_t *smem_b = smem + kStages * kAStageBytes;
     uint8_t *smem_push = smem + kStages * (kAStageBytes + kBStageBytes);
-    GemmSmem *sh = reinterpret_cast<GemmSmem *>(smem_push + 2 * kPushPieceBytes);
+    GemmSmem *sh = reinterpret_cast<GemmSmem *>(smem_push + kSideSmemBytes);
+    static_assert(sizeof(GemmSmem) <= 512, "barrier block outgrew its budget");
+    static_assert(kPushLanes * kPushPieceBytes <= kStages * (kAStageBytes + kBStageBytes), "pusher staging");
+    static_assert(BM * 256 <= kSideSmemBytes, "epilogue row staging");
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
