@@ -60,6 +60,11 @@ SIGNATURES = {
                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
                                         ctypes.c_uint32, ctypes.POINTER(CocTilingParams), ctypes.c_uint32,
                                         ctypes.c_uint32]),
+    "catccos_gemm_no_alloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int32,
+                                             ctypes.c_uint32, ctypes.c_uint32]),
+    "catccos_gemm_no_alloc_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_uint64),
+                                                    ctypes.c_uint32]),
 }
 for _op in ("MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend950AllGatherMatmul",
             "Ascend950MatmulReduceScatter"):
