@@ -60,6 +60,9 @@ SIGNATURES = {
                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
                                         ctypes.c_uint32, ctypes.POINTER(CocTilingParams), ctypes.c_uint32,
                                         ctypes.c_uint32]),
+    "catccos_mx_quant": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32]),
+    "catccos_sf_atoms_bytes": (ctypes.c_size_t, [ctypes.c_uint32, ctypes.c_uint32]),
     "catccos_gemm_no_alloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                              ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_int32,
                                              ctypes.c_uint32, ctypes.c_uint32]),
@@ -70,6 +73,10 @@ for _op in ("MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend
             "Ascend950MatmulReduceScatter"):
     for _dt in ("FP16", "BF16"):
         SIGNATURES[f"Launch{_op}{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
+
+
+for _dt in ("FP16", "BF16"):
+    SIGNATURES[f"LaunchAscend950Fp8MxAllGatherMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
 
 
 def load():

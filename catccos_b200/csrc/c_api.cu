@@ -2,6 +2,8 @@
 #include "../../include/catccos_b200.h"
 
 #include "dense_ops.h"
+#include "mx_ops.h"
+#include "mx_quant.h"
 #include "ptx.cuh"
 #include "symm_heap.h"
 
@@ -70,7 +72,44 @@ int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, Catccos
                         static_cast<int>(transA), static_cast<int>(transB));
 }
 
+int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
+                     uint8_t **workspaces, uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA,
+                     uint32_t transB) {
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    Team *t = team();
+    const int want = t->emulated ? t->n_pes : 1;
+    if (!params || n_params != want || !workspaces) {
+        set_error("MXFP8 AllGather-Matmul: one parameter block and one workspace per local PE are required");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (transA) {
+        set_error("transA=1 is not supported");
+        return CATCCOS_ERR_INVALID;
+    }
+    MxAgArgs args[kMaxRanks];
+    for (int i = 0; i < n_params; ++i) {
+        if (params[i].customCount < 2 || !params[i].customPtrs) {
+            set_error("MXFP8 AllGather-Matmul expects customPtrs = {aScale, bScale}");
+            return CATCCOS_ERR_INVALID;
+        }
+        args[i] = {params[i].ptrA, params[i].ptrB, params[i].ptrC, params[i].customPtrs[0], params[i].customPtrs[1],
+                   workspaces[i]};
+    }
+    return launch_mx_allgather_matmul(dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric,
+                                      static_cast<int>(tiling->m), static_cast<int>(tiling->n),
+                                      static_cast<int>(tiling->k), static_cast<int>(transB));
+}
+
 }  // namespace
+
+int catccos_mx_quant(void *stream, const void *inputBf16, uint8_t *codes, uint8_t *scales, uint8_t *sfAtoms,
+                     uint32_t rows, uint32_t k) {
+    const int nb = static_cast<int>(k / 32);
+    return mx_quant_launch(static_cast<cudaStream_t>(stream), inputBf16, static_cast<int>(rows), static_cast<int>(k),
+                           codes, k, scales, (nb + 1) / 2 * 2, sfAtoms);
+}
+size_t catccos_sf_atoms_bytes(uint32_t rows, uint32_t k) { return sf_atoms_bytes(static_cast<int>(rows), static_cast<int>(k)); }
 
 // ---- host-buffer form ------------------------------------------------------------------
 namespace {
@@ -205,12 +244,16 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     if (op >= 0)
         return dense_symmetric_bytes(op, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
+    if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
+        return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
+                                     static_cast<int>(tiling->k));
     return 0;
 }
 size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
-    (void)commType;
     (void)dataType;
-    (void)tiling;
+    if (tiling && commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
+        return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
+                                     static_cast<int>(tiling->k));
     return 0;   // the dense operators keep everything in the symmetric region
 }
 
@@ -232,14 +275,24 @@ DENSE_LAUNCH(LaunchAscend950AllGatherMatmulBF16, OP_AGMM, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterFP16, OP_MMRS, CATCCOS_FP16)
 DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16, OP_MMRS, CATCCOS_BF16)
 
+#define MXAG_LAUNCH(name, dtype)                                                                               \
+    int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
+             uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
+        (void)fftsAddr;                                                                                          \
+        return launch_mx_ag_abi(dtype, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB); \
+    }
+MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16, CATCCOS_FP16)
+MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16, CATCCOS_BF16)
+
 int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum, uint64_t fftsAddr,
                    CatccosKernelParams *params, uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling,
                    uint32_t transA, uint32_t transB) {
     (void)fftsAddr;
-    (void)workspace;
     const int op = dense_op_of(commType);
     if (op >= 0 && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_dense_abi(op, dataType, stream, blockNum, params, 1, symmetric, tiling, transA, transB);
+    if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }
@@ -247,7 +300,6 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
 int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum,
                             CatccosKernelParams *params, uint8_t **workspaces, uint8_t *symmetric,
                             CocTilingParams *tiling, uint32_t transA, uint32_t transB) {
-    (void)workspaces;
     Team *t = team();
     if (!t || !t->emulated) {
         set_error("catccos_launch_emulated needs catccos_shmem_init_emulated");
@@ -256,6 +308,9 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
     const int op = dense_op_of(commType);
     if (op >= 0 && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_dense_abi(op, dataType, stream, blockNum, params, t->n_pes, symmetric, tiling, transA, transB);
+    if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_ag_abi(dataType, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
+                                transB);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }

@@ -1,0 +1,163 @@
+// Host launcher of the MXFP8 AllGather-Matmul.
+#include "mx_ops.h"
+
+#include <string.h>
+
+#include "mx_gemm.cuh"
+#include "mx_quant.h"
+
+namespace cb {
+
+static int encode_u8(const DriverApi *api, CUtensorMap *tm, const void *base, uint64_t inner, uint64_t outer,
+                     uint32_t box_inner, uint32_t box_outer) {
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = api->TensorMapEncodeTiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides,
+                                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (u8) failed: %d (base=%p inner=%llu outer=%llu)", static_cast<int>(r), base,
+                  (unsigned long long)inner, (unsigned long long)outer);
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+size_t mx_ag_symmetric_bytes(int world, int m, int n, int k) {
+    (void)n;
+    if (world <= 1) return 0;
+    const size_t data = align_up(static_cast<size_t>(world) * m * k, 1024);
+    return data + static_cast<size_t>(world) * sf_atoms_bytes(m, k);
+}
+
+size_t mx_ag_workspace_bytes(int m, int n, int k) {
+    return align_up(sf_atoms_bytes(m, k), 1024) + align_up(sf_atoms_bytes(n, k), 1024);
+}
+
+template <typename TOut, bool B_MN>
+static int launch_k(const MxParams &p, int grid, bool coop, cudaStream_t stream) {
+    auto kern = mx_allgather_gemm_kernel<TOut, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxSmemBytes);
+    if (e == cudaSuccess) {
+        if (coop) {
+            void *args[] = {const_cast<MxParams *>(&p)};
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
+                                            kMxSmemBytes, stream);
+        } else {
+            kern<<<grid, kGemmThreads, kMxSmemBytes, stream>>>(p);
+            e = cudaGetLastError();
+        }
+    }
+    if (e != cudaSuccess) {
+        set_error("MX kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t block_num, const MxAgArgs *args,
+                               void *symmetric, int m, int n, int k, int trans_b) {
+    Team *t = team();
+    if (!t) {
+        set_error("symmetric heap not initialised (call catccos_shmem_init first)");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    std::string why;
+    const DriverApi *api = driver_api(&why);
+    if (!api) {
+        set_error("CUDA driver unavailable: %s", why.c_str());
+        return CATCCOS_ERR_CUDA;
+    }
+    if (out_dtype != 1 && out_dtype != 27) {
+        set_error("MXFP8 AllGather-Matmul writes FP16 (1) or BF16 (27), got %d", out_dtype);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (m <= 0 || n <= 0 || k <= 0 || (k % 32) != 0 || (n % 16) != 0) {
+        set_error("unsupported shape m=%d n=%d k=%d (k multiple of 32, n multiple of 16)", m, n, k);
+        return CATCCOS_ERR_INVALID;
+    }
+    const int R = t->n_pes;
+    const int n_local = t->emulated ? R : 1;
+    const int mt = (m + BM - 1) / BM;
+    const size_t need = mx_ag_symmetric_bytes(R, m, n, k);
+    uint64_t symm_off = 0, sf_off = 0;
+    if (R > 1) {
+        uint8_t *sp = static_cast<uint8_t *>(symmetric);
+        uint8_t *b = t->base[t->my_pe];
+        if (sp == nullptr || sp < b + kFlagBytes || sp + need > b + t->heap_bytes || ((sp - b) % 1024) != 0) {
+            set_error("symmetric buffer %p (+%zu bytes) is not a 1024-aligned range of the symmetric heap", symmetric, need);
+            return CATCCOS_ERR_INVALID;
+        }
+        symm_off = static_cast<uint64_t>(sp - b);
+        sf_off = symm_off + align_up(static_cast<size_t>(R) * m * k, 1024);
+        if (kFlagOpBase + static_cast<size_t>(R) * mt * kMxFlagsPerChunk > kFlagWords) {
+            set_error("shape needs more flags than the flag region holds");
+            return CATCCOS_ERR_INVALID;
+        }
+    }
+    MxParams p;
+    memset(&p, 0, sizeof(p));
+    const int kblocks = k / 32;
+    const int a_ld = (kblocks + 1) / 2 * 2;
+    for (int l = 0; l < n_local; ++l) {
+        const MxAgArgs &a = args[l];
+        if (!a.A || !a.B || !a.C || !a.a_scale || !a.b_scale || !a.workspace ||
+            (reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
+            (reinterpret_cast<uintptr_t>(a.C) & 15) || (reinterpret_cast<uintptr_t>(a.workspace) & 15)) {
+            set_error("A, B, C, both scale tensors and the workspace must be non-null (16-byte aligned data)");
+            return CATCCOS_ERR_INVALID;
+        }
+        uint8_t *sfa = a.workspace;
+        uint8_t *sfb = a.workspace + align_up(sf_atoms_bytes(m, k), 1024);
+        int rc = sf_to_atoms_launch(stream, a.a_scale, 0, m, kblocks, a_ld, sfa);
+        if (rc) return rc;
+        rc = trans_b ? sf_to_atoms_launch(stream, a.b_scale, 0, n, kblocks, a_ld, sfb)
+                     : sf_to_atoms_launch(stream, a.b_scale, 1, n, kblocks, 0, sfb);
+        if (rc) return rc;
+        MxRankArgs &ra = p.ranks[l];
+        if ((rc = encode_u8(api, &ra.tmA, a.A, k, m, MX_BK, BM))) return rc;
+        rc = trans_b ? encode_u8(api, &ra.tmB, a.B, k, n, MX_BK, BN) : encode_u8(api, &ra.tmB, a.B, n, k, 128, MX_BK);
+        if (rc) return rc;
+        if (R > 1) {
+            const int pe = t->emulated ? l : t->my_pe;
+            if ((rc = encode_u8(api, &ra.tmAg, t->base[pe] + symm_off, k, static_cast<uint64_t>(R) * m, MX_BK, BM)))
+                return rc;
+        } else {
+            ra.tmAg = ra.tmA;
+        }
+        ra.A = a.A;
+        ra.sfa = sfa;
+        ra.sfb = sfb;
+        ra.C = a.C;
+    }
+    for (int pe = 0; pe < R; ++pe) p.heap_base[pe] = t->base[pe];
+    p.symm_off = symm_off;
+    p.sf_off = sf_off;
+    p.world = R;
+    p.rank_base = t->emulated ? 0 : t->my_pe;
+    p.n_local = n_local;
+    int per_rank = t->num_sms / n_local;
+    if (block_num > 0 && static_cast<int>(block_num) < per_rank) per_rank = static_cast<int>(block_num);
+    if (per_rank < 1) per_rank = 1;
+    p.ctas_per_rank = per_rank;
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.epoch = ++t->epoch;
+    p.compute_only = (t->debug_flags & 1u) ? 1 : 0;
+    p.timeout_ns = t->timeout_ns;
+    p.status = t->status_dev;
+    p.trace = t->trace_dev;
+    const int grid = per_rank * n_local;
+    const bool coop = n_local > 1;
+    const bool b_mn = trans_b == 0;
+    if (out_dtype == 27)
+        return b_mn ? launch_k<__nv_bfloat16, true>(p, grid, coop, stream) : launch_k<__nv_bfloat16, false>(p, grid, coop, stream);
+    return b_mn ? launch_k<__half, true>(p, grid, coop, stream) : launch_k<__half, false>(p, grid, coop, stream);
+}
+
+}  // namespace cb

@@ -1,0 +1,24 @@
+// Host entry points of the MXFP8 operators.
+#pragma once
+#include "common.h"
+#include "symm_heap.h"
+
+namespace cb {
+
+struct MxAgArgs {
+    const uint8_t *A;        // e4m3 [m, k]
+    const uint8_t *B;        // e4m3: transB=0 [k, n]; transB=1 [n, k]
+    void *C;                 // 16-bit [R*m, n]
+    const uint8_t *a_scale;  // E8M0 [m, even(k/32)]  (reference layout [m, k/64, 2])
+    const uint8_t *b_scale;  // transB=0: [k/64, n, 2];  transB=1: [n, even(k/32)]
+    uint8_t *workspace;      // mx_ag_workspace_bytes() bytes of device memory
+};
+
+size_t mx_ag_symmetric_bytes(int world, int m, int n, int k);
+size_t mx_ag_workspace_bytes(int m, int n, int k);
+
+// AllGather-Matmul on MXFP8 operands; out_dtype 1 = fp16, 27 = bf16.  m = rows held by one rank.
+int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t block_num, const MxAgArgs *args,
+                               void *symmetric, int m, int n, int k, int trans_b);
+
+}  // namespace cb

@@ -1,0 +1,188 @@
+// MX block quantisation (bf16 -> e4m3 codes + E8M0 scale per 32 along K): HBM-bound kernels.
+//
+// Follows the reference's host golden bit for bit (examples/utils/gen_mx_quant_allgather_data.py:
+// 168-189, 255-313 with the round-to-nearest-even cast of gen_data_moe.py:482-493), which is also
+// what the reference's device code does (include/catccos/comm/block/comm_block_mx_quant.hpp:413-663)
+// except for blocks whose largest magnitude is below 1e-12, where the golden's rule (scale 1.0) wins.
+#include "mx_quant.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "ptx.cuh"
+
+namespace cb {
+
+namespace {
+
+__device__ __forceinline__ uint32_t bf16_abs_max(const uint4 &v) {
+    // largest |bits| of the 8 bf16 values (integer order == magnitude order; NaN sorts above Inf)
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m = max(m, w[i] & 0x7FFFu);
+        m = max(m, (w[i] >> 16) & 0x7FFFu);
+    }
+    return m;
+}
+
+// scale byte and the exact reciprocal 2^-exp for a block whose largest |bf16 bits| is amax_bits
+__device__ __forceinline__ void block_scale(uint32_t amax_bits, uint32_t *scale_byte, float *inv_scale) {
+    const float amax = __uint_as_float(amax_bits << 16);
+    // `amax < 1e-12` is false for NaN, as in the golden
+    if (amax < 1e-12f) {
+        *scale_byte = 127u;
+        *inv_scale = 1.0f;
+        return;
+    }
+    const uint32_t e = (amax_bits >> 7) & 0xFFu;     // biased exponent; floor(log2(amax)) = e - 127
+    *scale_byte = e - 8u;                            // (e - 127 - emax) + 127 with emax = 8; e >= 87 here
+    *inv_scale = __uint_as_float((262u - e) << 23);  // 2^-(e - 135)
+}
+
+__device__ __forceinline__ uint32_t to_e4m3(float x) {
+    // round-to-nearest-even, saturating at +-448; NaN keeps its sign (0x7F / 0xFF) as torch's cast does
+    if (x != x) return 0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u);
+    return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ uint2 quantise8(const uint4 &v, float inv_scale) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t c[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        c[2 * i] = to_e4m3(__uint_as_float(w[i] << 16) * inv_scale);
+        c[2 * i + 1] = to_e4m3(__uint_as_float(w[i] & 0xFFFF0000u) * inv_scale);
+    }
+    uint2 r;
+    r.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+    r.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+    return r;
+}
+
+// offset of (row, kb) inside the tcgen05 scale-factor atoms: atoms of 128 rows x 4 k-blocks
+__device__ __host__ __forceinline__ size_t sf_atom_offset(uint32_t row, uint32_t kb, uint32_t kb4_count) {
+    return (static_cast<size_t>(row >> 7) * kb4_count + (kb >> 2)) * 512 + (row & 31u) * 16 + ((row >> 5) & 3u) * 4 +
+           (kb & 3u);
+}
+
+// One thread quantises 8 consecutive values; 4 neighbouring threads share a 32-value block.
+// codes: [rows, k] bytes (row stride code_ld).  scales_rm: optional [rows, scale_ld] bytes.
+// sf_atoms: optional tcgen05 atom layout.  Rows are addressed through optional gather / scatter
+// lists: src_row = src_rows ? src_rows[r] : r, dst_row likewise (used by the MoE quant-scatter).
+__global__ void __launch_bounds__(256) mx_quant_kernel(const uint4 *__restrict__ in, int rows, int k, uint8_t *codes,
+                                                       size_t code_ld, uint8_t *scales_rm, int scale_ld,
+                                                       uint8_t *sf_atoms, int kb4_count) {
+    const int vec_per_row = k >> 3;                  // k % 32 == 0
+    const size_t total = static_cast<size_t>(rows) * vec_per_row;
+    const int nblocks = k >> 5;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / vec_per_row);
+        const int vcol = static_cast<int>(i - static_cast<size_t>(row) * vec_per_row);
+        const uint4 v = __ldg(in + i);
+        uint32_t am = bf16_abs_max(v);
+        const uint32_t lanes = __activemask();   // the 4 lanes of a block are always active together (k % 32 == 0)
+        am = max(am, __shfl_xor_sync(lanes, am, 1));
+        am = max(am, __shfl_xor_sync(lanes, am, 2));
+        uint32_t sb;
+        float inv;
+        block_scale(am, &sb, &inv);
+        const uint2 q = quantise8(v, inv);
+        *reinterpret_cast<uint2 *>(codes + static_cast<size_t>(row) * code_ld + vcol * 8) = q;
+        if ((vcol & 3) == 0) {
+            const int kb = vcol >> 2;
+            if (scales_rm) {
+                scales_rm[static_cast<size_t>(row) * scale_ld + kb] = static_cast<uint8_t>(sb);
+                if (kb == nblocks - 1 && (nblocks & 1)) scales_rm[static_cast<size_t>(row) * scale_ld + kb + 1] = 127;
+            }
+            if (sf_atoms) sf_atoms[sf_atom_offset(row, kb, kb4_count)] = static_cast<uint8_t>(sb);
+        }
+    }
+}
+
+// scale bytes in one of the operator layouts -> tcgen05 atoms (pad positions keep the 127 = 1.0 fill)
+//   kind 0: [rows, ld] row-major (activations, transposed weights)
+//   kind 1: [kblocks/2, rows, 2]  (weights of a [K, N] operand: reference layout [K/64, N, 2])
+__global__ void sf_to_atoms_kernel(const uint8_t *__restrict__ src, int kind, int rows, int kblocks, int ld,
+                                   uint8_t *atoms, int kb4_count) {
+    const size_t total = static_cast<size_t>(rows) * kblocks;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint32_t row = static_cast<uint32_t>(i / kblocks);
+        const uint32_t kb = static_cast<uint32_t>(i - static_cast<size_t>(row) * kblocks);
+        uint8_t v;
+        if (kind == 0)
+            v = src[static_cast<size_t>(row) * ld + kb];
+        else
+            v = src[(static_cast<size_t>(kb >> 1) * rows + row) * 2 + (kb & 1u)];
+        atoms[sf_atom_offset(row, kb, kb4_count)] = v;
+    }
+}
+
+}  // namespace
+
+size_t sf_atoms_bytes(int rows, int k) {
+    const size_t row_tiles = (static_cast<size_t>(rows) + 127) / 128;
+    const size_t kb4 = (static_cast<size_t>(k) + 127) / 128;
+    return row_tiles * kb4 * 512;
+}
+
+static int grid_for(size_t work_items, int threads) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    size_t blocks = (work_items + threads - 1) / threads;
+    const size_t cap = static_cast<size_t>(sms) * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return static_cast<int>(blocks);
+}
+
+int mx_quant_launch(cudaStream_t stream, const void *in_bf16, int rows, int k, uint8_t *codes, size_t code_ld,
+                    uint8_t *scales_rm, int scale_ld, uint8_t *sf_atoms) {
+    if (rows <= 0 || k <= 0 || (k % 32) != 0) {
+        set_error("MX quantisation needs rows > 0 and k a positive multiple of 32 (rows=%d k=%d)", rows, k);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (!in_bf16 || !codes || (reinterpret_cast<uintptr_t>(in_bf16) & 15) || (reinterpret_cast<uintptr_t>(codes) & 7) ||
+        (code_ld & 7)) {
+        set_error("MX quantisation: input must be 16-byte aligned, codes 8-byte aligned with a row stride multiple of 8");
+        return CATCCOS_ERR_INVALID;
+    }
+    const int kb4 = (k + 127) / 128;
+    if (sf_atoms) {
+        cudaError_t e = cudaMemsetAsync(sf_atoms, 127, sf_atoms_bytes(rows, k), stream);
+        if (e != cudaSuccess) {
+            set_error("cudaMemsetAsync failed: %s", cudaGetErrorString(e));
+            return CATCCOS_ERR_CUDA;
+        }
+    }
+    const size_t vecs = static_cast<size_t>(rows) * (k / 8);
+    mx_quant_kernel<<<grid_for(vecs, 256), 256, 0, stream>>>(static_cast<const uint4 *>(in_bf16), rows, k, codes, code_ld,
+                                                            scales_rm, scale_ld, sf_atoms, kb4);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("mx_quant_kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+int sf_to_atoms_launch(cudaStream_t stream, const uint8_t *src, int kind, int rows, int kblocks, int ld, uint8_t *atoms) {
+    const int k = kblocks * 32;
+    cudaError_t e = cudaMemsetAsync(atoms, 127, sf_atoms_bytes(rows, k), stream);
+    if (e == cudaSuccess) {
+        const size_t total = static_cast<size_t>(rows) * kblocks;
+        sf_to_atoms_kernel<<<grid_for(total, 256), 256, 0, stream>>>(src, kind, rows, kblocks, ld, atoms, (k + 127) / 128);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        set_error("scale re-layout failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+}  // namespace cb

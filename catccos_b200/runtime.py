@@ -77,7 +77,7 @@ def last_status():
 
 
 def launch(comm_type, a, b, c, symmetric, til, trans_a=0, trans_b=0, block_num=0, stream=None, dtype=None,
-           custom=()):
+           custom=(), workspace=None):
     """One rank per process: catccos_launch (KernelDispatcher::GetKernelFunc + call)."""
     kp = KernelParams()
     kp.ptrA, kp.ptrB, kp.ptrC = a.data_ptr(), b.data_ptr(), c.data_ptr()
@@ -87,12 +87,13 @@ def launch(comm_type, a, b, c, symmetric, til, trans_a=0, trans_b=0, block_num=0
         kp.customPtrs = ctypes.cast(arr, ctypes.POINTER(ctypes.c_void_p))
         kp.customCount = len(custom)
     dt = dtype if dtype is not None else _DTYPE[a.dtype]
-    check(lib().catccos_launch(comm_type, dt, _stream_ptr(stream), block_num, 0, ctypes.byref(kp), None,
+    ws = ctypes.c_void_p(workspace.data_ptr()) if workspace is not None else None
+    check(lib().catccos_launch(comm_type, dt, _stream_ptr(stream), block_num, 0, ctypes.byref(kp), ws,
                                ctypes.c_void_p(symmetric), ctypes.byref(til), trans_a, trans_b))
 
 
 def launch_emulated(comm_type, a_list, b_list, c_list, symmetric, til, trans_a=0, trans_b=0, block_num=0,
-                    stream=None, dtype=None, custom_lists=None):
+                    stream=None, dtype=None, custom_lists=None, workspaces=None):
     """All ranks in one cooperative launch (needs shmem_init_emulated)."""
     n = len(a_list)
     kps = (KernelParams * n)()
@@ -105,5 +106,8 @@ def launch_emulated(comm_type, a_list, b_list, c_list, symmetric, til, trans_a=0
             kps[i].customPtrs = ctypes.cast(arr, ctypes.POINTER(ctypes.c_void_p))
             kps[i].customCount = len(custom_lists[i])
     dt = dtype if dtype is not None else _DTYPE[a_list[0].dtype]
-    check(lib().catccos_launch_emulated(comm_type, dt, _stream_ptr(stream), block_num, kps, None,
+    ws = None
+    if workspaces is not None:
+        ws = (ctypes.c_void_p * n)(*[w.data_ptr() for w in workspaces])
+    check(lib().catccos_launch_emulated(comm_type, dt, _stream_ptr(stream), block_num, kps, ws,
                                         ctypes.c_void_p(symmetric), ctypes.byref(til), trans_a, trans_b))

@@ -153,6 +153,14 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllGatherMatmulBF16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16);
 
+/* tests/dynamic_tiling/impl/kernel_fp16_ascend950.cpp:274 (MxAllGatherMatmulTla,
+ * include/catccos/dgemm/kernel/mx_allgather_matmul.hpp:27-428): ptrA/ptrB = e4m3 operands,
+ * customPtrs = {aScale [m, k/64, 2], bScale (transB=0: [k/64, n, 2]; transB=1: [n, k/64, 2])} E8M0 bytes,
+ * `workspace` = catccos_workspace_bytes() bytes.  The data type names the 16-bit OUTPUT type (the
+ * reference writes fp16, examples/ascend950_fp8_mx_allgather_matmul/..._host.h:33; BF16 is added). */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16);
+
 /* KernelDispatcher::GetKernelFunc(commType, dataType) + call (launch_map.h:31-39,
  * tests/dynamic_tiling/main.cpp:351-368): CATCCOS_ERR_INVALID when the pair is not registered. */
 CATCCOS_API int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum, uint64_t fftsAddr,
@@ -175,6 +183,18 @@ CATCCOS_API int catccos_launch_emulated(int32_t commType, int32_t dataType, void
 CATCCOS_API int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA,
                                  const void *hostB, void *hostC, const void *const *hostCustom, uint32_t customCount,
                                  CocTilingParams *tiling, uint32_t transA, uint32_t transB);
+
+/* ------------------------------------------------------------------ MX quantisation ---- */
+/* CommBlockMxQuant::ComputeMxQuant (include/catccos/comm/block/comm_block_mx_quant.hpp:413-663) on
+ * a whole [rows, k] bf16 matrix: e4m3 codes [rows, k] and one E8M0 scale byte per 32 values along k,
+ * written as [rows, even(k/32)] bytes (odd counts padded with 127 = 1.0), bit-identical to the
+ * reference's host golden (examples/utils/gen_mx_quant_allgather_data.py:168-189,255-313 with the
+ * round-to-nearest-even cast).  k must be a multiple of 32.  `sfAtoms` (optional, may be NULL)
+ * additionally receives the scales in the tcgen05 scale-factor layout that the MX GEMM kernels read
+ * (catccos_sf_atoms_bytes bytes).  Asynchronous on `stream`; needs no symmetric heap. */
+CATCCOS_API int catccos_mx_quant(void *stream, const void *inputBf16, uint8_t *codes, uint8_t *scales, uint8_t *sfAtoms,
+                                 uint32_t rows, uint32_t k);
+CATCCOS_API size_t catccos_sf_atoms_bytes(uint32_t rows, uint32_t k);
 
 /* ------------------------------------------------------------- allocation-free GEMM ---- */
 /* No counterpart in the reference.  For callers that cannot allocate device memory where they

@@ -42,3 +42,19 @@ def golden_allgather_matmul(a_list, b_list):
     B); examples/utils/gen_data.py:63-65 is the same-B special case."""
     gathered = torch.cat([a.to(torch.float32) for a in a_list], dim=0)
     return [torch.matmul(gathered, b.to(torch.float32)) for b in b_list]
+
+
+def golden_mx_allgather_matmul(a_codes_list, a_scales_list, b_codes_list, b_scales_list):
+    """MXFP8 AllGather-Matmul golden: C_r = cat_s(dequant(A_s)) @ dequant(B_r) in fp32.
+
+    examples/utils/gen_data_fp8_mx_allgather_matmul.py:645-669 (`matmul(allgathered_a, b_fp32)` on
+    the dequantised operands).  a_codes: uint8 [m,k] with scales [m, >=k/32]; b_codes: uint8 [k,n]
+    with scales [>=k/32, n] (blocks of 32 along k for both operands)."""
+    import numpy as np
+    from . import mxquant
+    a = np.concatenate([mxquant.dequant_mx_e4m3(c, s) for c, s in zip(a_codes_list, a_scales_list)], axis=0)
+    outs = []
+    for bc, bs in zip(b_codes_list, b_scales_list):
+        b = mxquant.dequant_mx_e4m3(np.ascontiguousarray(bc.T), np.ascontiguousarray(bs.T)).T
+        outs.append(torch.matmul(torch.from_numpy(a), torch.from_numpy(np.ascontiguousarray(b))))
+    return outs
