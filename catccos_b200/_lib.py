@@ -40,6 +40,7 @@ SIGNATURES = {
     "catccos_shmem_malloc": (ctypes.c_void_p, [ctypes.c_size_t]),
     "catccos_shmem_free": (None, [ctypes.c_void_p]),
     "catccos_shmem_ptr": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_int32]),
+    "catccos_shmem_get_host": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_size_t]),
     "catccos_shmem_my_pe": (ctypes.c_int32, []),
     "catccos_shmem_n_pes": (ctypes.c_int32, []),
     "catccos_shmem_barrier_all": (ctypes.c_int, []),
@@ -77,6 +78,9 @@ for _op in ("MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend
 
 for _dt in ("FP16", "BF16"):
     SIGNATURES[f"LaunchAscend950Fp8MxAllGatherMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
+
+
+SIGNATURES["LaunchAscend950DispatchFFNCombineBF16"] = (ctypes.c_int, LAUNCH_ARGS)
 
 
 def load():

@@ -2,6 +2,7 @@
 #include "../../include/catccos_b200.h"
 
 #include "dense_ops.h"
+#include "moe_ops.h"
 #include "mx_ops.h"
 #include "mx_quant.h"
 #include "ptx.cuh"
@@ -101,6 +102,36 @@ int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelPa
                                       static_cast<int>(tiling->k), static_cast<int>(transB));
 }
 
+int launch_moe_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params, uint8_t **workspaces,
+                   uint8_t *symmetric, CocTilingParams *tiling) {
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    Team *t = team();
+    const int want = t->emulated ? t->n_pes : 1;
+    if (!params || n_params != want || !workspaces) {
+        set_error("dispatch_ffn_combine: one parameter block and one workspace per local PE are required");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (tiling->epSize != 0 && static_cast<int>(tiling->epSize) != t->n_pes) {
+        set_error("tiling.epSize (%u) must equal the number of PEs (%d)", tiling->epSize, t->n_pes);
+        return CATCCOS_ERR_INVALID;
+    }
+    MoeArgs args[kMaxRanks];
+    for (int i = 0; i < n_params; ++i) {
+        if (params[i].customCount < 5 || !params[i].customPtrs) {
+            set_error("dispatch_ffn_combine expects customPtrs = {b2, expertIdx, probs, bScale, b2Scale}");
+            return CATCCOS_ERR_INVALID;
+        }
+        uint8_t **c = params[i].customPtrs;
+        args[i] = {params[i].ptrA, params[i].ptrB, params[i].ptrC, c[0], reinterpret_cast<const int *>(c[1]),
+                   reinterpret_cast<const float *>(c[2]), c[3], c[4], workspaces[i]};
+    }
+    return launch_moe_dispatch_ffn_combine(static_cast<cudaStream_t>(stream), blockNum, args, symmetric,
+                                           static_cast<int>(tiling->m), static_cast<int>(tiling->k),
+                                           static_cast<int>(tiling->n), static_cast<int>(tiling->topK),
+                                           static_cast<int>(tiling->expertNum));
+}
+
 }  // namespace
 
 int catccos_mx_quant(void *stream, const void *inputBf16, uint8_t *codes, uint8_t *scales, uint8_t *sfAtoms,
@@ -159,6 +190,20 @@ void catccos_shmem_free(void *ptr) {
     if (ptr) team_free(ptr);
 }
 void *catccos_shmem_ptr(const void *ptr, int32_t pe) { return team_ptr(ptr, pe); }
+int catccos_shmem_get_host(void *hostDst, const void *ptr, int32_t pe, size_t bytes) {
+    void *src = team_ptr(ptr, pe);
+    if (!src || !hostDst) {
+        set_error("catccos_shmem_get_host: bad pointer or PE");
+        return CATCCOS_ERR_INVALID;
+    }
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(hostDst, src, bytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        set_error("catccos_shmem_get_host failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
 int32_t catccos_shmem_my_pe(void) { return team() ? team()->my_pe : -1; }
 int32_t catccos_shmem_n_pes(void) { return team() ? team()->n_pes : 0; }
 int catccos_shmem_barrier_all(void) {
@@ -247,6 +292,10 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
         return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
+    if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0)
+        return moe_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->k),
+                                   static_cast<int>(tiling->n), static_cast<int>(tiling->topK),
+                                   static_cast<int>(tiling->expertNum));
     return 0;
 }
 size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
@@ -254,6 +303,12 @@ size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTili
     if (tiling && commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
         return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
+    if (tiling && commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0) {
+        const int world = tiling->rankSize ? static_cast<int>(tiling->rankSize) : (team() ? team()->n_pes : 1);
+        return moe_workspace_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->k),
+                                   static_cast<int>(tiling->n), static_cast<int>(tiling->topK),
+                                   static_cast<int>(tiling->expertNum));
+    }
     return 0;   // the dense operators keep everything in the symmetric region
 }
 
@@ -284,6 +339,15 @@ DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16, OP_MMRS, CATCCOS_BF16)
 MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16, CATCCOS_FP16)
 MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16, CATCCOS_BF16)
 
+int LaunchAscend950DispatchFFNCombineBF16(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params,
+                                          uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA,
+                                          uint32_t transB) {
+    (void)fftsAddr;
+    (void)transA;
+    (void)transB;
+    return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
+}
+
 int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t blockNum, uint64_t fftsAddr,
                    CatccosKernelParams *params, uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling,
                    uint32_t transA, uint32_t transB) {
@@ -293,6 +357,8 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
         return launch_dense_abi(op, dataType, stream, blockNum, params, 1, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
+    if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
+        return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }
@@ -311,6 +377,8 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
                                 transB);
+    if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
+        return launch_moe_abi(stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }

@@ -1,0 +1,437 @@
+// MoE helper kernels: routing (stable counting sort + count exchange + offset tables),
+// quantise-and-dispatch, and the weighted un-permute.
+//
+// Reference semantics:
+//   routing      examples/aux_ops/moe_init_routing_v2/moe_init_routing_v2.h:54-241 (stable sort by expert,
+//                expandedRowIdx src -> dst, tokens per expert); golden examples/utils/gen_data_moe.py:48-57
+//   count gather examples/aux_ops/allgather_kernel_with_flag.h:24-155
+//   offsets      include/catccos/comm/block/comm_block_scheduler_alltoallv_gmm.hpp:72-78,131-159 (prevSum, cumsumMM)
+//   dispatch     include/catccos/comm/block/comm_block_mx_quant.hpp:318-369 (quantise once, scatter to top-k slots)
+//                and include/catccos/dgemm/kernel/ascend950_alltoall_gmm.hpp:419-471 (receive order:
+//                local expert major, source rank minor)
+//   un-permute   examples/aux_ops/moe_token_unpermute/moe_token_unpermute.h:234-278
+#include "moe_ops.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "ptx.cuh"
+
+namespace cb {
+
+namespace {
+
+__device__ __forceinline__ uint32_t *mflag(const MoeParams &p, int pe, uint32_t word) {
+    return reinterpret_cast<uint32_t *>(p.heap_base[pe]) + word;
+}
+
+// ------------------------------------------------------------------------------ routing ----
+// One CTA (1024 threads) per rank.  Stable counting sort with warp-private counters: warp w owns
+// the w-th contiguous slice of the flattened [m, topK] expert ids, walks it 32 ids at a time and
+// ranks equal ids inside a step with __match_any_sync, so equal experts keep their index order.
+__global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
+    extern __shared__ int smem_i[];
+    const int E = p.experts;
+    int *cnt = smem_i;                    // [32][E]
+    int *scan = smem_i + 32 * E;          // [E] totals, then exclusive prefix
+    int *seg_all = scan + E;              // [E] receive segment base of every expert on its owner
+    __shared__ int abort_flag;
+    __shared__ int seg_end_all[kMaxRanks];
+
+    const int lrank = blockIdx.x;
+    const int rank = p.rank_base + lrank;
+    const int R = p.world;
+    const int EL = p.experts_per_rank;
+    const MoeRankArgs &ra = p.ranks[lrank];
+    MoeMeta *meta = ra.meta;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int total = p.m * p.top_k;
+
+    if (tid == 0) abort_flag = 0;
+    for (int i = tid; i < 32 * E; i += blockDim.x) cnt[i] = 0;
+    if (tid < 4) meta->done_counter[tid] = 0;
+    if (tid == 0) meta->overflow = 0;
+    // this rank's symmetric data regions may be overwritten from now on
+    if (tid < R && tid != rank) {
+        fence_sys();
+        st_release_sys(mflag(p, tid, kFlagEntered + rank), p.epoch);
+    }
+    __syncthreads();
+
+    const int chunk = ((total + 31) / 32 + 31) / 32 * 32;
+    const int begin = warp * chunk;
+    const int end = min(total, begin + chunk);
+    for (int base = begin; base < end; base += 32) {
+        const int i = base + lane;
+        const bool valid = i < end;
+        const int key = valid ? ra.expert_idx[i] : -1 - lane;
+        const unsigned mask = __match_any_sync(0xffffffffu, key);
+        if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
+        __syncwarp();
+    }
+    __syncthreads();
+    if (tid < E) {
+        int tot = 0;
+        for (int w = 0; w < 32; ++w) tot += cnt[w * E + tid];
+        scan[tid] = tot;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = scan[e];
+            scan[e] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    int my_count = 0;
+    if (tid < E) {
+        // counters -> first destination row of (warp, expert)
+        int run = scan[tid];
+        for (int w = 0; w < 32; ++w) {
+            const int c = cnt[w * E + tid];
+            cnt[w * E + tid] = run;
+            run += c;
+        }
+        my_count = run - scan[tid];
+    }
+    __syncthreads();
+    for (int base = begin; base < end; base += 32) {
+        const int i = base + lane;
+        const bool valid = i < end;
+        const int key = valid ? ra.expert_idx[i] : -1 - lane;
+        const unsigned mask = __match_any_sync(0xffffffffu, key);
+        const int rnk = __popc(mask & ((1u << lane) - 1u));
+        int dst = 0;
+        if (valid) dst = cnt[warp * E + key] + rnk;
+        __syncwarp();
+        if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
+        __syncwarp();
+        if (valid) ra.expanded_row_idx[i] = dst;
+    }
+
+    // ---- tokens-per-expert to every rank (the count all-gather), then the offset tables ----
+    if (tid < E) {
+        for (int pe = 0; pe < R; ++pe) {
+            int *dstc = reinterpret_cast<int *>(p.heap_base[pe] + p.lay.counts_off);
+            dstc[rank * E + tid] = my_count;
+        }
+    }
+    __syncthreads();
+    if (tid < R) {
+        fence_sys();
+        st_release_sys(mflag(p, tid, kMoeFlagCounts + rank), p.epoch);
+    }
+    WaitCtl ctl;
+    ctl.abort_smem = &abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+    if (tid < R) wait_flag_ge(mflag(p, rank, kMoeFlagCounts + tid), p.epoch, ctl, W_MOE_COUNTS, tid);
+    __syncthreads();
+    if (abort_flag) return;
+
+    const int *counts = reinterpret_cast<const int *>(p.heap_base[rank] + p.lay.counts_off);
+    for (int i = tid; i < R * E; i += blockDim.x) meta->counts_all[i / E][i % E] = counts[i];
+    if (tid < R) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            meta->prefix_all[tid][e] = run;
+            run += counts[tid * E + e];
+        }
+    }
+    // receive layout of every owner: local-expert segments start on multiples of 128 rows
+    if (tid < R) {
+        int run = 0;
+        for (int le = 0; le < EL; ++le) {
+            const int e = tid * EL + le;
+            int rows = 0;
+            for (int r = 0; r < R; ++r) rows += counts[r * E + e];
+            seg_all[e] = run;
+            run += (rows + 127) / 128 * 128;
+        }
+        seg_end_all[tid] = run;
+    }
+    __syncthreads();
+    if (tid < E) {
+        int before = 0;
+        for (int r = 0; r < rank; ++r) before += counts[r * E + tid];
+        meta->dest_base[tid] = seg_all[tid] + before;
+    }
+    if (tid < EL) {
+        const int e = rank * EL + tid;
+        int run = 0;
+        for (int r = 0; r < R; ++r) {
+            meta->cum_src[r][tid] = run;
+            run += counts[r * E + e];
+        }
+        meta->cum_src[R][tid] = run;
+        meta->seg_rows[tid] = run;
+        meta->seg_base[tid] = seg_all[e];
+    }
+    if (tid == 0) {
+        meta->seg_base[EL] = seg_end_all[rank];
+        int tiles = 0, rows = 0;
+        for (int le = 0; le < EL; ++le) {
+            int r2 = 0;
+            for (int r = 0; r < R; ++r) r2 += counts[r * E + rank * EL + le];
+            meta->tile_prefix[le] = tiles;
+            tiles += (r2 + 127) / 128;
+            rows += r2;
+        }
+        meta->tile_prefix[EL] = tiles;
+        meta->total_rows = rows;
+        int over = 0;
+        for (int o = 0; o < R; ++o)
+            if (seg_end_all[o] > p.lay.rows_cap) over = 1;
+        if (over) {
+            meta->overflow = 1;
+            if (atomicCAS(p.status + ST_CODE, 0, 4) == 0) {   // 4: receive capacity exceeded
+                p.status[ST_WHERE] = W_MOE_ROWS;
+                p.status[ST_RANK] = rank;
+                p.status[ST_EXPECTED] = p.lay.rows_cap;
+                p.status[ST_SEEN] = seg_end_all[rank];
+            }
+        }
+    }
+}
+
+// -------------------------------------------------------------------- quantise + dispatch ----
+__device__ __forceinline__ uint32_t abs_max8(const uint4 &v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m = max(m, w[i] & 0x7FFFu);
+        m = max(m, (w[i] >> 16) & 0x7FFFu);
+    }
+    return m;
+}
+__device__ __forceinline__ uint32_t cvt_e4m3(float x) {
+    if (x != x) return 0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u);
+    return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+
+constexpr int kDispWarps = 8;
+constexpr int kMaxTopK = 16;
+
+// One warp per token: the row is quantised once and written to each of its top-k destination rows
+// (codes as 256-byte warp-wide stores, the row's scale bytes as 8-byte stores from shared memory).
+__global__ void __launch_bounds__(kDispWarps * 32) moe_quant_dispatch_kernel(const MoeParams p) {
+    __shared__ __align__(16) uint8_t s_scale[kDispWarps][1024];
+    __shared__ int abort_flag;
+    const int lrank = blockIdx.x / p.ctas_per_rank;
+    const int cta = blockIdx.x - lrank * p.ctas_per_rank;
+    const int rank = p.rank_base + lrank;
+    const int R = p.world;
+    const MoeRankArgs &ra = p.ranks[lrank];
+    const MoeMeta *meta = ra.meta;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) abort_flag = 0;
+    __syncthreads();
+    WaitCtl ctl;
+    ctl.abort_smem = &abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+    // every owner must have entered this epoch before its receive rows are overwritten
+    if (threadIdx.x < R && threadIdx.x != rank)
+        wait_flag_ge(mflag(p, rank, kFlagEntered + threadIdx.x), p.epoch, ctl, W_ENTERED, threadIdx.x);
+    __syncthreads();
+    const bool skip = abort_flag || meta->overflow;
+
+    const int K = p.K, EL = p.experts_per_rank, topk = p.top_k;
+    const int vec_per_row = K >> 3;
+    const int sld = p.lay.scale_ld;
+    if (!skip) {
+        for (int t = cta * kDispWarps + warp; t < p.m; t += p.ctas_per_rank * kDispWarps) {
+            // lane k < topK resolves destination k
+            unsigned long long my_codes = 0, my_scales = 0;
+            if (lane < topk) {
+                const int e = ra.expert_idx[t * topk + lane];
+                const int d = ra.expanded_row_idx[t * topk + lane];
+                const int row = meta->dest_base[e] + (d - meta->prefix_all[rank][e]);
+                const int o = e / EL;
+                my_codes = reinterpret_cast<unsigned long long>(p.heap_base[o] + p.lay.recv_codes_off +
+                                                                static_cast<size_t>(row) * K);
+                my_scales = reinterpret_cast<unsigned long long>(p.heap_base[o] + p.lay.recv_scale_off +
+                                                                 static_cast<size_t>(row) * sld);
+            }
+            const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(ra.x) +
+                                                               static_cast<size_t>(t) * K);
+            for (int v = lane; v < vec_per_row; v += 32) {
+                const uint4 x = __ldg(src + v);
+                uint32_t am = abs_max8(x);
+                am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
+                am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
+                const float amax = __uint_as_float(am << 16);
+                uint32_t sb = 127u;
+                float inv = 1.0f;
+                if (!(amax < 1e-12f)) {
+                    const uint32_t e8 = (am >> 7) & 0xFFu;
+                    sb = e8 - 8u;
+                    inv = __uint_as_float((262u - e8) << 23);
+                }
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+                uint32_t c[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    c[2 * i] = cvt_e4m3(__uint_as_float(w[i] << 16) * inv);
+                    c[2 * i + 1] = cvt_e4m3(__uint_as_float(w[i] & 0xFFFF0000u) * inv);
+                }
+                uint2 q;
+                q.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+                q.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+                if ((v & 3) == 0) s_scale[warp][v >> 2] = static_cast<uint8_t>(sb);
+                for (int k = 0; k < topk; ++k) {
+                    uint8_t *dst = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, my_codes, k));
+                    *reinterpret_cast<uint2 *>(dst + static_cast<size_t>(v) * 8) = q;
+                }
+            }
+            // K % 256 == 0: vec_per_row is a multiple of 32, all lanes ran the same number of iterations
+            __syncwarp();
+            for (int k = 0; k < topk; ++k) {
+                uint8_t *dst = reinterpret_cast<uint8_t *>(__shfl_sync(0xffffffffu, my_scales, k));
+                for (int j = lane; j < sld / 8; j += 32)
+                    *reinterpret_cast<uint2 *>(dst + j * 8) = *reinterpret_cast<const uint2 *>(&s_scale[warp][j * 8]);
+            }
+            __syncwarp();
+        }
+    }
+    // last CTA of this rank publishes "my rows are in place" to every owner
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(&ra.meta->done_counter[0], 1u);
+        if (prev == static_cast<unsigned>(p.ctas_per_rank) - 1u) {
+            fence_sys();
+            for (int o = 0; o < R; ++o) st_release_sys(mflag(p, o, kMoeFlagDispatch + rank), p.epoch);
+        }
+    }
+}
+
+// -------------------------------------------------------------------------- un-permute ----
+// out[t] = bf16_rne( sum_k fp32(combine[idx[t,k]]) * prob[t,k] ), products and sums rounded
+// separately (no fused multiply-add) in k order.
+__global__ void __launch_bounds__(256) moe_unpermute_kernel(const MoeParams p) {
+    __shared__ int abort_flag;
+    const int lrank = blockIdx.x / p.ctas_per_rank;
+    const int cta = blockIdx.x - lrank * p.ctas_per_rank;
+    const int rank = p.rank_base + lrank;
+    const int R = p.world;
+    const MoeRankArgs &ra = p.ranks[lrank];
+    if (threadIdx.x == 0) abort_flag = 0;
+    __syncthreads();
+    WaitCtl ctl;
+    ctl.abort_smem = &abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+    if (threadIdx.x < R) wait_flag_ge(mflag(p, rank, kMoeFlagCombine + threadIdx.x), p.epoch, ctl, W_MOE_COMBINE, threadIdx.x);
+    __syncthreads();
+    if (abort_flag || ra.meta->overflow) return;
+    const int K = p.K, topk = p.top_k;
+    const int vec_per_row = K >> 3;
+    const __nv_bfloat16 *comb = reinterpret_cast<const __nv_bfloat16 *>(p.heap_base[rank] + p.lay.combine_off);
+    const size_t total = static_cast<size_t>(p.m) * vec_per_row;
+    for (size_t i = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(p.ctas_per_rank) * blockDim.x) {
+        const int t = static_cast<int>(i / vec_per_row);
+        const int v = static_cast<int>(i - static_cast<size_t>(t) * vec_per_row);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int k = 0; k < topk; ++k) {
+            const int row = ra.expanded_row_idx[t * topk + k];
+            const float w = ra.probs[t * topk + k];
+            const uint4 x = *reinterpret_cast<const uint4 *>(comb + static_cast<size_t>(row) * K + v * 8);
+            const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(xs[j] << 16), w));
+                acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(xs[j] & 0xFFFF0000u), w));
+            }
+        }
+        uint4 o;
+        o.x = Pack2<__nv_bfloat16>::pack(acc[0], acc[1]);
+        o.y = Pack2<__nv_bfloat16>::pack(acc[2], acc[3]);
+        o.z = Pack2<__nv_bfloat16>::pack(acc[4], acc[5]);
+        o.w = Pack2<__nv_bfloat16>::pack(acc[6], acc[7]);
+        *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(ra.out) + static_cast<size_t>(t) * K + v * 8) = o;
+    }
+}
+
+// One CTA per rank: returns once every rank's dispatch rows have landed in my receive buffer.
+__global__ void moe_wait_dispatch_kernel(const MoeParams p) {
+    __shared__ int abort_flag;
+    const int rank = p.rank_base + blockIdx.x;
+    if (threadIdx.x == 0) abort_flag = 0;
+    __syncthreads();
+    WaitCtl ctl;
+    ctl.abort_smem = &abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+    if (threadIdx.x < p.world)
+        wait_flag_ge(mflag(p, rank, kMoeFlagDispatch + threadIdx.x), p.epoch, ctl, W_MOE_ROWS, threadIdx.x);
+}
+
+}  // namespace
+
+int moe_launch_wait_dispatch(const MoeParams &p, cudaStream_t stream) {
+    moe_wait_dispatch_kernel<<<p.n_local, 32, 0, stream>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("moe_wait_dispatch_kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+int moe_launch_route(const MoeParams &p, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(34) * p.experts * sizeof(int);
+    cudaError_t e = cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e == cudaSuccess) {
+        if (p.n_local > 1) {
+            void *args[] = {const_cast<MoeParams *>(&p)};
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(moe_route_kernel), dim3(p.n_local), dim3(1024), args,
+                                            smem, stream);
+        } else {
+            moe_route_kernel<<<1, 1024, smem, stream>>>(p);
+            e = cudaGetLastError();
+        }
+    }
+    if (e != cudaSuccess) {
+        set_error("moe_route_kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+template <typename K>
+static int launch_grid(K kern, const MoeParams &p, int threads, cudaStream_t stream, const char *name) {
+    cudaError_t e;
+    const int grid = p.ctas_per_rank * p.n_local;
+    if (p.n_local > 1) {
+        void *args[] = {const_cast<MoeParams *>(&p)};
+        e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(threads), args, 0, stream);
+    } else {
+        kern<<<grid, threads, 0, stream>>>(p);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        set_error("%s launch failed: %s", name, cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+int moe_launch_dispatch(const MoeParams &p, cudaStream_t stream) {
+    return launch_grid(moe_quant_dispatch_kernel, p, kDispWarps * 32, stream, "moe_quant_dispatch_kernel");
+}
+int moe_launch_unpermute(const MoeParams &p, cudaStream_t stream) {
+    return launch_grid(moe_unpermute_kernel, p, 256, stream, "moe_unpermute_kernel");
+}
+
+}  // namespace cb

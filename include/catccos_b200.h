@@ -98,6 +98,9 @@ CATCCOS_API void catccos_shmem_free(void *ptr);
 CATCCOS_API void *catccos_shmem_ptr(const void *ptr, int32_t pe);
 CATCCOS_API int32_t catccos_shmem_my_pe(void);   /* shmem_my_pe() */
 CATCCOS_API int32_t catccos_shmem_n_pes(void);   /* shmem_n_pes() */
+/* Host-side get (the role of aclshmem_getmem on the host): synchronises the device and copies `bytes`
+ * bytes of PE `pe`'s copy of symmetric address `ptr` into host memory. */
+CATCCOS_API int catccos_shmem_get_host(void *hostDst, const void *ptr, int32_t pe, size_t bytes);
 /* aclshmem_barrier_all() (examples/ascend950_dispatch_ffn_combine/main.cpp:217-219): host barrier
  * of all PEs after synchronising the device. */
 CATCCOS_API int catccos_shmem_barrier_all(void);
@@ -160,6 +163,16 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16);
  * reference writes fp16, examples/ascend950_fp8_mx_allgather_matmul/..._host.h:33; BF16 is added). */
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16);
+
+/* The MoE operator: DispatchFFNCombine<...>(fftsAddr, gmA, gmB, gmBScale, gmB2, gmB2Scale, gmD, gmExpertIdx,
+ * gmProbs, gmWorkSpace, gmSymmetric, CocTilingParams, ...) (examples/ascend950_dispatch_ffn_combine/
+ * ascend950_dispatch_ffn_combine_device.h:617-718), with the operands in the operator class's KernelParams
+ * order (ascend950_dispatch_ffn_combine_host.h:121-122, main.cpp:210-214): ptrA = tokens bf16 [m, k],
+ * ptrB = up/gate weights e4m3 [E/R, n, k], ptrC = output bf16 [m, k], customPtrs = {b2 e4m3 [E/R, k, n/2],
+ * expertIdx int32 [m, topK], probs fp32 [m, topK], bScale E8M0 [E/R, n, k/32], b2Scale E8M0 [E/R, k, n/64]}.
+ * tiling: m, k, n, topK, expertNum, epSize (= rankSize).  k % 256 == 0 and n % 512 == 0 as in the reference.
+ * `workspace` = catccos_workspace_bytes() bytes, 256-byte aligned. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950DispatchFFNCombineBF16);
 
 /* KernelDispatcher::GetKernelFunc(commType, dataType) + call (launch_map.h:31-39,
  * tests/dynamic_tiling/main.cpp:351-368): CATCCOS_ERR_INVALID when the pair is not registered. */
