@@ -54,6 +54,65 @@ def main():
         rc, words = rt.last_status()
         assert rc == 0, words
         check(f"mmar#{rep}", e, gold)
+    # MXFP8 AllGather-Matmul (scale atoms and data pushed to the peers)
+    from oracle import mxquant, moe
+    import numpy as np
+    import ctypes
+    from catccos_b200 import lib
+    m, k, n = 256, 512, 384
+    ac, asc, bc, bsc = [], [], [], []
+    for r in range(world):
+        g = torch.Generator().manual_seed(70 + r)
+        act = torch.randn((m, k), generator=g).to(torch.bfloat16).to(torch.float32).numpy()
+        w = (torch.randn((k, n), generator=g) * 0.02).to(torch.bfloat16).to(torch.float32).numpy()
+        c, s_, _ = mxquant.quantize_mx_e4m3(act, "rne"); ac.append(c); asc.append(s_)
+        c, s_, _ = mxquant.quantize_mx_e4m3_axis0(w, "rne"); bc.append(c); bsc.append(s_)
+    gold = dense.golden_mx_allgather_matmul(ac, asc, [bc[rank]], [bsc[rank]])[0]
+    til = rt.tiling(m, k, n, world)
+    ws_bytes = lib().catccos_workspace_bytes(rt.FP8_MX_ALLGATHER_MATMUL, rt.BF16, ctypes.byref(til))
+    wsp = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    bs_dev = np.ascontiguousarray(bsc[rank].reshape(bsc[rank].shape[0] // 2, 2, n).transpose(0, 2, 1))
+    c = torch.full((world * m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for rep in range(2):
+        rt.launch(rt.FP8_MX_ALLGATHER_MATMUL, torch.from_numpy(ac[rank]).cuda(), torch.from_numpy(bc[rank]).cuda(), c, symm, til,
+                  dtype=rt.BF16, custom=[torch.from_numpy(asc[rank]).cuda(), torch.from_numpy(bs_dev).cuda()], workspace=wsp)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    check("mx_agmm", c, gold, 2e-2)
+
+    # MoE dispatch -> FFN -> combine
+    m, k, n, top_k, experts = 160, 512, 1024, 4, 4 * world
+    epr = experts // world
+    xs, idxs, probs, w1q, w1s, w2q, w2s = [], [], [], [], [], [], []
+    for r in range(world):
+        xs.append(inputs.bf16_as_f32(inputs.normal((m, k), torch.bfloat16, 10 + r)))
+        ids, pr = inputs.zipf_topk_routing(m, experts, top_k, 100 + r)
+        idxs.append(ids); probs.append(pr)
+        q1, s1, q2, s2 = [], [], [], []
+        for e in range(epr):
+            w1 = inputs.bf16_as_f32(inputs.normal((k, n), torch.bfloat16, 1000 + r * 64 + e, 0.02))
+            w2 = inputs.bf16_as_f32(inputs.normal((n // 2, k), torch.bfloat16, 5000 + r * 64 + e, 0.02))
+            cc, ss, _ = mxquant.quantize_mx_e4m3_axis0(w1, "rne")
+            q1.append(np.ascontiguousarray(cc.T)); s1.append(np.ascontiguousarray(ss[:k // 32].T))
+            cc, ss, _ = mxquant.quantize_mx_e4m3_axis0(w2, "rne")
+            q2.append(np.ascontiguousarray(cc.T)); s2.append(np.ascontiguousarray(ss[:(n // 2) // 32].T))
+        w1q.append(np.stack(q1)); w1s.append(np.stack(s1)); w2q.append(np.stack(q2)); w2s.append(np.stack(s2))
+    gold = moe.dispatch_ffn_combine(xs, idxs, probs, w1q, w1s, w2q, w2s, world, epr)[rank]
+    til = rt.tiling(m, k, n, world, topK=top_k, expertNum=experts, epSize=world)
+    need = rt.symmetric_bytes(rt.DISPATCH_FFN_COMBINE, rt.BF16, til)
+    assert need <= (200 << 20), need
+    ws_bytes = lib().catccos_workspace_bytes(rt.DISPATCH_FFN_COMBINE, rt.BF16, ctypes.byref(til))
+    wsp = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    out = torch.full((m, k), float("nan"), dtype=torch.bfloat16, device="cuda")
+    t = lambda a: torch.from_numpy(a).cuda()
+    for rep in range(2):
+        rt.launch(rt.DISPATCH_FFN_COMBINE, t(xs[rank]).to(torch.bfloat16), t(w1q[rank]), out, symm, til, dtype=rt.BF16,
+                  custom=[t(w2q[rank]), t(idxs[rank].astype(np.int32)), t(probs[rank].astype(np.float32)), t(w1s[rank]),
+                          t(w2s[rank])], workspace=wsp)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    check("moe", out, torch.from_numpy(gold), 2e-2)
+
     rt.shmem_finalize()
     if failures:
         print(f"[rank {rank}] FAILED {failures}", flush=True)
