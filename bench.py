@@ -29,6 +29,8 @@ sys.path.insert(0, ROOT)
 M_TOTAL, K_DIM, N_DIM = 8192, 8192, 4096           # allgather_matmul bf16 (benchmark configuration 2)
 RS_M, RS_KLOCAL, RS_N = 8192, 2048, 8192           # matmul_reduce_scatter bf16 (configuration 3)
 AR_M, AR_K, AR_N = 512, 1024, 2048                 # matmul_allreduce fp16 (configuration 1)
+MX_M_TOTAL, MX_K, MX_N = 16384, 7168, 4096         # MXFP8 allgather_matmul (configuration 4)
+MOE_M, MOE_K, MOE_N, MOE_TOPK = 4096, 7168, 4096, 8  # MoE (configuration 5), 32 experts per rank
 NVLINK_GBS = 770.0                                 # measured peer-copy bandwidth per direction on this pool
 
 
@@ -115,6 +117,25 @@ def workload(op, world):
                     c_shape=(AR_M, AR_N), flops=2.0 * AR_M * AR_K * AR_N,
                     comm_bytes=2 * (world - 1) * AR_M * AR_N * 2 // max(world, 1), dtype="fp16",
                     desc="matmul_allreduce fp16: A[512,1024] x B[1024,2048] per rank, summed over ranks")
+    if op == "mxag":
+        m_local = MX_M_TOTAL // world
+        return dict(name="mxfp8_allgather_matmul", m=m_local, k=MX_K, n=MX_N, c_shape=(MX_M_TOTAL, MX_N),
+                    flops=2.0 * MX_M_TOTAL * MX_K * MX_N, comm_bytes=(world - 1) * m_local * (MX_K + MX_K // 32),
+                    dtype="mxfp8", peak_scale=2.0,
+                    desc=f"MXFP8 allgather_matmul: activations [{m_local},7168] bf16 per rank quantised to e4m3 + E8M0/32 "
+                         f"(inside the step), gathered [16384,7168] x W[7168,4096] e4m3 -> bf16 [16384,4096]")
+    if op == "moe":
+        experts = 32 * world
+        return dict(name="moe_dispatch_ffn_combine", m=MOE_M, k=MOE_K, n=MOE_N, top_k=MOE_TOPK, experts=experts,
+                    flops=float(MOE_M * MOE_TOPK) * (2.0 * MOE_K * MOE_N + 2.0 * (MOE_N // 2) * MOE_K),
+                    comm_bytes=int((world - 1) / max(world, 1) * MOE_M * MOE_TOPK * (MOE_K + MOE_K // 32 + 2 * MOE_K)),
+                    dtype="mxfp8", peak_scale=2.0, c_shape=(MOE_M, MOE_K),
+                    desc=f"MoE dispatch->GMM->SwiGLU->GMM->combine: 4096 tokens/rank, hidden 7168, {experts} experts "
+                         f"(32/rank), FFN 2048, top-8 Zipf(1.1) routing, MXFP8 weights")
+    if op == "quant":
+        return dict(name="mx_quant_e4m3", m=MX_M_TOTAL, k=MX_K, n=0, c_shape=(MX_M_TOTAL, MX_K), flops=0.0, comm_bytes=0,
+                    dtype="u8", hbm_bytes=MX_M_TOTAL * MX_K * (2 + 1 + 1.0 / 32),
+                    desc="MX quantisation bf16 [16384,7168] -> e4m3 + E8M0 per 32 (HBM-bound)")
     raise ValueError(op)
 
 
@@ -186,7 +207,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar"])
+    ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar", "mxag", "moe", "quant"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -218,22 +239,106 @@ def main():
         torch.cuda.synchronize()
 
     wl = workload(args.op, world)
-    comm = {"agmm": rt.ALLGATHER_MATMUL, "mmrs": rt.MATMUL_REDUCE_SCATTER, "mmar": rt.MATMUL_ALLREDUCE}[args.op]
-    a_h, b_h, dt = host_inputs(wl, rank, torch)
-    til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
-    dtype_code = rt.FP16 if wl["dtype"] == "fp16" else rt.BF16
-    need = rt.symmetric_bytes(comm, dtype_code, til)
     port = os.environ.get("MASTER_PORT", "29500")
     addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
-    rt.shmem_init(rank, world, 2 * max(need, 1 << 20) + (8 << 20), f"tcp://{addr}:{port}")
-    symm = rt.shmem_malloc(max(need, 1024))
-
-    a_d, b_d = a_h.cuda(), b_h.cuda()
-    c_d = torch.empty(wl["c_shape"], dtype=dt, device="cuda")
     stream = torch.cuda.current_stream()
+    sptr = ctypes.c_void_p(stream.cuda_stream)
+    dense_op = args.op in ("agmm", "mmrs", "mmar")
+    a_h = b_h = None
+    if dense_op:
+        comm = {"agmm": rt.ALLGATHER_MATMUL, "mmrs": rt.MATMUL_REDUCE_SCATTER, "mmar": rt.MATMUL_ALLREDUCE}[args.op]
+        a_h, b_h, dt = host_inputs(wl, rank, torch)
+        til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
+        dtype_code = rt.FP16 if wl["dtype"] == "fp16" else rt.BF16
+        need = rt.symmetric_bytes(comm, dtype_code, til)
+        rt.shmem_init(rank, world, 2 * max(need, 1 << 20) + (8 << 20), f"tcp://{addr}:{port}")
+        symm = rt.shmem_malloc(max(need, 1024))
+        a_d, b_d = a_h.cuda(), b_h.cuda()
+        c_d = torch.empty(wl["c_shape"], dtype=dt, device="cuda")
 
-    def step():
-        rt.launch(comm, a_d, b_d, c_d, symm, til, stream=stream)
+        def step():
+            rt.launch(comm, a_d, b_d, c_d, symm, til, stream=stream)
+        launches_per_step = 1
+    else:
+        gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
+
+        def quant_rows(x_bf16):
+            rows, kk = x_bf16.shape
+            codes = torch.empty((rows, kk), dtype=torch.uint8, device="cuda")
+            scales = torch.empty((rows, (kk // 32 + 1) // 2 * 2), dtype=torch.uint8, device="cuda")
+            check(lib().catccos_mx_quant(sptr, ctypes.c_void_p(x_bf16.data_ptr()), ctypes.c_void_p(codes.data_ptr()),
+                                         ctypes.c_void_p(scales.data_ptr()), None, rows, kk))
+            return codes, scales
+        if args.op == "quant":
+            rt.shmem_init(rank, world, 1 << 20, f"tcp://{addr}:{port}")
+            x = torch.randn((wl["m"], wl["k"]), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+            q_codes = torch.empty((wl["m"], wl["k"]), dtype=torch.uint8, device="cuda")
+            q_scales = torch.empty((wl["m"], wl["k"] // 32), dtype=torch.uint8, device="cuda")
+
+            def step():
+                check(lib().catccos_mx_quant(sptr, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(q_codes.data_ptr()),
+                                             ctypes.c_void_p(q_scales.data_ptr()), None, wl["m"], wl["k"]))
+            launches_per_step = 1
+        elif args.op == "mxag":
+            comm = rt.FP8_MX_ALLGATHER_MATMUL
+            til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
+            need = rt.symmetric_bytes(comm, rt.BF16, til)
+            rt.shmem_init(rank, world, max(need, 1 << 20) + (8 << 20), f"tcp://{addr}:{port}")
+            symm = rt.shmem_malloc(max(need, 1024))
+            act = torch.randn((wl["m"], wl["k"]), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+            w = (torch.randn((wl["k"], wl["n"]), generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+            wq_t, ws_t = quant_rows(w.t().contiguous())                      # quantised along K, [n, k]
+            b_codes = wq_t.t().contiguous()                                  # [k, n]
+            kb = wl["k"] // 32
+            b_scale = ws_t[:, :kb].t().contiguous().reshape(kb // 2, 2, wl["n"]).permute(0, 2, 1).contiguous()
+            a_codes = torch.empty((wl["m"], wl["k"]), dtype=torch.uint8, device="cuda")
+            a_scale = torch.empty((wl["m"], kb), dtype=torch.uint8, device="cuda")
+            c_d = torch.empty(wl["c_shape"], dtype=torch.bfloat16, device="cuda")
+            wsp = torch.zeros(lib().catccos_workspace_bytes(comm, rt.BF16, ctypes.byref(til)), dtype=torch.uint8, device="cuda")
+
+            def step():
+                check(lib().catccos_mx_quant(sptr, ctypes.c_void_p(act.data_ptr()), ctypes.c_void_p(a_codes.data_ptr()),
+                                             ctypes.c_void_p(a_scale.data_ptr()), None, wl["m"], wl["k"]))
+                rt.launch(comm, a_codes, b_codes, c_d, symm, til, stream=stream, dtype=rt.BF16,
+                          custom=[a_scale, b_scale], workspace=wsp)
+            launches_per_step = 4
+        else:   # moe
+            comm = rt.DISPATCH_FFN_COMBINE
+            m, k, n, top_k, experts = wl["m"], wl["k"], wl["n"], wl["top_k"], wl["experts"]
+            el = experts // world
+            til = rt.tiling(m, k, n, world, topK=top_k, expertNum=experts, epSize=world)
+            need = rt.symmetric_bytes(comm, rt.BF16, til)
+            rt.shmem_init(rank, world, need + (8 << 20), f"tcp://{addr}:{port}")
+            symm = rt.shmem_malloc(need)
+            x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+            w1q = torch.empty((el, n, k), dtype=torch.uint8, device="cuda")
+            w1s = torch.empty((el, n, k // 32), dtype=torch.uint8, device="cuda")
+            w2q = torch.empty((el, k, n // 2), dtype=torch.uint8, device="cuda")
+            w2s = torch.empty((el, k, (n // 2) // 32), dtype=torch.uint8, device="cuda")
+            for e in range(el):
+                wt = (torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                cq, cs = quant_rows(wt)
+                w1q[e], w1s[e] = cq, cs[:, :k // 32]
+                wt = (torch.randn((k, n // 2), generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                cq, cs = quant_rows(wt)
+                w2q[e], w2s[e] = cq, cs[:, :(n // 2) // 32]
+            # top-8 routing: softmax(N(0,1) logits + log of a Zipf(1.1) weight per expert), renormalised gate weights
+            logits = torch.randn((m, experts), generator=gen, device="cuda")
+            zipf = torch.arange(1, experts + 1, device="cuda", dtype=torch.float32).pow(-1.1)
+            zipf = zipf / zipf.sum()
+            perm = torch.randperm(experts, generator=torch.Generator().manual_seed(7)).cuda()
+            pr = torch.softmax(logits + torch.log(zipf * experts)[perm], dim=-1)
+            top_p, top_i = torch.topk(pr, top_k, dim=-1)
+            probs = (top_p / top_p.sum(dim=-1, keepdim=True)).float().contiguous()
+            idx = top_i.to(torch.int32).contiguous()
+            c_d = torch.empty((m, k), dtype=torch.bfloat16, device="cuda")
+            wsp = torch.zeros(lib().catccos_workspace_bytes(comm, rt.BF16, ctypes.byref(til)), dtype=torch.uint8, device="cuda")
+            torch.cuda.synchronize()
+
+            def step():
+                rt.launch(comm, x, w1q, c_d, symm, til, stream=stream, dtype=rt.BF16,
+                          custom=[w2q, idx, probs, w1s, w2s], workspace=wsp)
+            launches_per_step = 10
 
     for _ in range(args.warmup):
         step()
@@ -292,7 +397,7 @@ def main():
     # pushes): exposed communication = (fused - compute-only) / fused
     exposed = None
     compute_only_ms = None
-    if world > 1:
+    if world > 1 and args.op in ("agmm", "mmrs", "mmar", "mxag"):
         check(lib().catccos_debug_set_flags(1))
         compute_only_ms, _ = timed_region(False)
         check(lib().catccos_debug_set_flags(0))
@@ -301,7 +406,7 @@ def main():
 
     # end to end through the host-buffer entry point: H2D of A and B, fused launch, D2H of C, every step
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and dense_op:
         a_p, b_p = a_h.pin_memory(), b_h.pin_memory()
         c_p = torch.empty(wl["c_shape"], dtype=dt).pin_memory()
 
@@ -326,34 +431,50 @@ def main():
 
     if rank == 0:
         peak_tf, peak_hbm, peak_kind = measured_peaks(load_steps > 0)
-        per_gpu_tflops = wl["flops"] / (ms_per_step * 1e-3) / 1e12
-        t_gemm_us = wl["flops"] / (peak_tf * 1e12) * 1e6
-        t_comm_us = wl["comm_bytes"] / (NVLINK_GBS * 1e9) * 1e6
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-        if os.path.exists(tpath):
-            with open(tpath) as f:
-                traffic = json.load(f).get(f"{wl['name']}_n{world}")
-        line = {
-            "metric": "fused-op TFLOP/s (whole job)", "value": world * per_gpu_tflops, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"],
-            "data": "synthetic",
-            "config": {"workload": wl["desc"], "op": wl["name"], "l2": "operands (268 MB) larger than L2",
-                       "parallelism": f"tp{world}"},
-            "tflops_per_gpu": per_gpu_tflops,
-            "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak_tf, "unit": "TFLOP/s",
-                         "frac": per_gpu_tflops / peak_tf, "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                         "t_gemm_peak_us": t_gemm_us, "t_comm_peak_us": t_comm_us,
-                         "frac_of_max_gemm_comm": max(t_gemm_us, t_comm_us) / (ms_per_step * 1e3)},
-            "exposed_comm_frac": exposed, "compute_only_ms_per_step": compute_only_ms,
-            "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks,
-        }
-        if world == 1 and not args.no_cpu_baseline:
-            v, cores, secs = cpu_golden_rate(wl, 1024, torch)
-            line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                    "sample": f"1024 rows of A x full B fp32 matmul ({secs:.2f} s)"}
-        print(json.dumps(line), flush=True)
+        if args.op == "quant":
+            gbs = wl["hbm_bytes"] / (ms_per_step * 1e-3) / 1e9
+            line = {
+                "metric": "MX quantisation GB/s (whole job)", "value": world * gbs, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                "config": {"workload": wl["desc"], "op": wl["name"], "l2": "operands (235 MB) larger than L2"},
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak_hbm, "unit": "GB/s", "frac": gbs / peak_hbm,
+                             "traffic": None, "peak_kind": "of measured (STREAM-style copy)"},
+                "e2e": None, "gpu_launches": args.steps * launches_per_step, "clocks": clocks,
+            }
+            print(json.dumps(line), flush=True)
+        else:
+            peak_tf *= wl.get("peak_scale", 1.0)      # fp8 tensor peak taken as twice the measured bf16 figure
+            if wl.get("peak_scale"):
+                peak_kind = "2 x " + peak_kind
+            per_gpu_tflops = wl["flops"] / (ms_per_step * 1e-3) / 1e12
+            t_gemm_us = wl["flops"] / (peak_tf * 1e12) * 1e6
+            t_comm_us = wl["comm_bytes"] / (NVLINK_GBS * 1e9) * 1e6
+            traffic = None
+            tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+            if os.path.exists(tpath):
+                with open(tpath) as f:
+                    traffic = json.load(f).get(f"{wl['name']}_n{world}")
+            line = {
+                "metric": "fused-op TFLOP/s (whole job)", "value": world * per_gpu_tflops, "unit": "TFLOP/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"],
+                "data": "synthetic",
+                "config": {"workload": wl["desc"], "op": wl["name"], "l2": "operands larger than L2 (126 MB)",
+                           "parallelism": f"tp{world}" if args.op != "moe" else f"ep{world}"},
+                "tflops_per_gpu": per_gpu_tflops,
+                "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak_tf, "unit": "TFLOP/s",
+                             "frac": per_gpu_tflops / peak_tf, "traffic": traffic, "peak_kind": f"of {peak_kind}",
+                             "t_gemm_peak_us": t_gemm_us, "t_comm_peak_us": t_comm_us,
+                             "frac_of_max_gemm_comm": max(t_gemm_us, t_comm_us) / (ms_per_step * 1e3)},
+                "exposed_comm_frac": exposed, "compute_only_ms_per_step": compute_only_ms,
+                "e2e": e2e, "gpu_launches": args.steps * launches_per_step, "clocks": clocks,
+            }
+            if world == 1 and not args.no_cpu_baseline and dense_op:
+                v, cores, secs = cpu_golden_rate(wl, 1024, torch)
+                line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                        "sample": f"1024 rows of A x full B fp32 matmul ({secs:.2f} s)"}
+            print(json.dumps(line), flush=True)
 
     rt.shmem_finalize()
     if world > 1:
