@@ -41,6 +41,7 @@ SIGNATURES = {
     "catccos_shmem_free": (None, [ctypes.c_void_p]),
     "catccos_shmem_ptr": (ctypes.c_void_p, [ctypes.c_void_p, ctypes.c_int32]),
     "catccos_shmem_get_host": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_size_t]),
+    "catccos_shmem_put_host": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_size_t]),
     "catccos_shmem_my_pe": (ctypes.c_int32, []),
     "catccos_shmem_n_pes": (ctypes.c_int32, []),
     "catccos_shmem_barrier_all": (ctypes.c_int, []),

@@ -6,6 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcatccos_b200.so")
+DRIVER = os.path.join(HERE, "catccos_run")
 SOURCES = ["symm_heap.cu", "dense_ops.cu", "c_api.cu", "no_alloc.cu", "mx_quant.cu", "mx_ops.cu", "moe_aux.cu", "moe_ops.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
@@ -46,7 +47,22 @@ def build(force=False, verbose=False):
     if force or procs or not os.path.exists(LIB):
         cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-cudart", "static", "-Xcompiler", "-fPIC", "-lpthread", "-ldl", "-lrt"]
         subprocess.check_call(cmd)
+    build_driver(force)
     return LIB
+
+
+def build_driver(force=False):
+    """The C++ host driver (operator registry, file I/O, launch map) on top of the shared library."""
+    src = os.path.join(CSRC, "host", "catccos_run.cpp")
+    inc = os.path.join(os.path.dirname(HERE), "include")
+    deps = [src, LIB] + [os.path.join(inc, "catccos_host", f) for f in os.listdir(os.path.join(inc, "catccos_host"))]
+    deps.append(os.path.join(inc, "catccos_b200.h"))
+    if force or not os.path.exists(DRIVER) or any(os.path.getmtime(d) > os.path.getmtime(DRIVER) for d in deps):
+        cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-I", inc, "-I", os.path.join(cuda, "include"), src, "-o", DRIVER,
+                               "-L", HERE, "-lcatccos_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart",
+                               "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")])
+    return DRIVER
 
 
 if __name__ == "__main__":

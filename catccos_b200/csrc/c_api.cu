@@ -204,6 +204,19 @@ int catccos_shmem_get_host(void *hostDst, const void *ptr, int32_t pe, size_t by
     }
     return CATCCOS_OK;
 }
+int catccos_shmem_put_host(void *ptr, int32_t pe, const void *hostSrc, size_t bytes) {
+    void *dst = team_ptr(ptr, pe);
+    if (!dst || !hostSrc) {
+        set_error("catccos_shmem_put_host: bad pointer or PE");
+        return CATCCOS_ERR_INVALID;
+    }
+    cudaError_t e = cudaMemcpy(dst, hostSrc, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        set_error("catccos_shmem_put_host failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
 int32_t catccos_shmem_my_pe(void) { return team() ? team()->my_pe : -1; }
 int32_t catccos_shmem_n_pes(void) { return team() ? team()->n_pes : 0; }
 int catccos_shmem_barrier_all(void) {

@@ -1,0 +1,118 @@
+// One rank of one fused operator, driven the way the reference's per-example main.cpp and its
+// dynamic-tiling launcher drive it (examples/matmul_allreduce/main.cpp:27-178,
+// tests/dynamic_tiling/main.cpp:200-368): symmetric-heap init, operator from the registry,
+// AllocateDeviceSpace from .bin files, launcher from the (commType, dataType) map, warm-up and
+// timed launches, WriteResultFile.
+//
+//   catccos_run <kernel> <dtype> <rank_size> <rank_id> <ip_port> <m> <n> <k> <data_dir>
+//               [transA transB [topK expertNum [device_id [warmup timed]]]]
+//   kernel: mmar | agmm | a5agmm | mmrs | a5mmrs | a5fp8mxagmm | a5moe     dtype: 1 (fp16) | 27 (bf16)
+//   catccos_run --list        prints the registered operator names
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <iostream>
+#include <string>
+
+#include "catccos_host/launch_map.h"
+#include "catccos_host/operators.h"
+
+int main(int argc, char **argv) {
+    if (argc >= 2 && std::string(argv[1]) == "--list") {
+        for (const auto &n : OperatorRegistry::Instance().Names()) std::cout << n << "\n";
+        return 0;
+    }
+    if (argc < 10) {
+        std::cerr << "usage: catccos_run <kernel> <dtype> <rank_size> <rank_id> <ip_port> <m> <n> <k> <data_dir> "
+                     "[transA transB [topK expertNum [device_id [warmup timed]]]]\n";
+        return 1;
+    }
+    const std::string kernel = argv[1];
+    const CocDataType dtype = static_cast<CocDataType>(std::atoi(argv[2]));
+    const int rankSize = std::atoi(argv[3]), rankId = std::atoi(argv[4]);
+    const std::string ipPort = argv[5];
+    CocTilingParams tiling{};
+    tiling.m = static_cast<uint32_t>(std::atoi(argv[6]));
+    tiling.n = static_cast<uint32_t>(std::atoi(argv[7]));
+    tiling.k = static_cast<uint32_t>(std::atoi(argv[8]));
+    const std::string dataDir = argv[9];
+    tiling.transA = argc > 10 ? std::atoi(argv[10]) : 0;
+    tiling.transB = argc > 11 ? std::atoi(argv[11]) : 0;
+    tiling.topK = argc > 12 ? std::atoi(argv[12]) : 1;
+    tiling.expertNum = argc > 13 ? std::atoi(argv[13]) : 0;
+    const int deviceId = argc > 14 ? std::atoi(argv[14]) : rankId;
+    const int warmUp = argc > 15 ? std::atoi(argv[15]) : 0;
+    const int timed = argc > 16 ? std::atoi(argv[16]) : 1;
+    tiling.m0 = M0;
+    tiling.n0 = N0;
+    tiling.k0 = K0;
+    tiling.rankSize = rankSize;
+    tiling.epSize = rankSize;
+
+    const CocCommType commType = GetCommType(kernel);
+    if (commType == UNKNOWN) {
+        std::cerr << "unknown kernel " << kernel << "\n";
+        return 1;
+    }
+    auto op = OperatorRegistry::Instance().CreateOperator(CommTypeOpNameMap().at(commType));
+    if (!op) {
+        std::cout << "Operator " << CommTypeOpNameMap().at(commType) << " not found!" << std::endl;
+        return -1;
+    }
+    std::cout << "[TEST] input rank_size: " << rankSize << " rank_id: " << rankId << " input_ip: " << ipPort << "\n";
+    CUDA_CHECK(cudaSetDevice(deviceId));
+    cudaStream_t stream = nullptr;
+    CUDA_CHECK(cudaStreamCreate(&stream));
+    if (catccos_shmem_init(rankId, rankSize, SHMEM_MALLOC_MAX_SIZE, ipPort.c_str()) != CATCCOS_OK) {
+        std::cerr << "[ERROR] shmem init failed: " << catccos_last_error() << "\n";
+        return 1;
+    }
+    if (!op->CheckCocTilingParams(rankSize, tiling)) {
+        std::printf("M: %u, K: %u, N: %u coc params check failed!\n", tiling.m, tiling.k, tiling.n);
+        catccos_shmem_finalize();
+        return 1;
+    }
+    const CocCommType actual = op->GetActualKernelType(tiling);
+    KernelParams params;
+    op->AllocateDeviceSpace(params, tiling, rankId, dataDir);
+    const size_t wsBytes = op->GetWorkspaceSize(tiling);
+    uint8_t *workspace = nullptr;
+    if (wsBytes > 0) CUDA_CHECK(cudaMalloc(reinterpret_cast<void **>(&workspace), wsBytes));
+    uint8_t *symmetric = static_cast<uint8_t *>(catccos_shmem_malloc(SHMEM_BUFF_BYTES));
+    const KernelFuncPtr launch = KernelDispatcher::GetKernelFunc(actual, dtype);
+    int rc = 1;
+    if (!symmetric) {
+        std::cerr << "[ERROR] " << catccos_last_error() << "\n";
+    } else if (!launch) {
+        std::cerr << "[ERROR] no kernel registered for (" << actual << ", " << dtype << ")\n";
+    } else {
+        rc = 0;
+        cudaEvent_t e0, e1;
+        CUDA_CHECK(cudaEventCreate(&e0));
+        CUDA_CHECK(cudaEventCreate(&e1));
+        for (int i = 0; i < warmUp + timed && rc == 0; ++i) {
+            if (i == warmUp) CUDA_CHECK(cudaEventRecord(e0, stream));
+            rc = launch(stream, 0, 0, &params, workspace, symmetric, &tiling, tiling.transA, tiling.transB);
+        }
+        CUDA_CHECK(cudaEventRecord(e1, stream));
+        if (rc != 0) std::cerr << "[ERROR] launch failed: " << catccos_last_error() << "\n";
+        int32_t words[8];
+        const int st = catccos_last_status(words);          // synchronises the device
+        if (st != CATCCOS_OK) {
+            std::cerr << "[ERROR] " << catccos_last_error() << "\n";
+            rc = st;
+        } else if (rc == 0) {
+            float ms = 0;
+            CUDA_CHECK(cudaEventElapsedTime(&ms, e0, e1));
+            std::printf("[TEST] %s rank %d: %.3f us per launch (%d timed)\n", kernel.c_str(), rankId, ms * 1e3f / timed, timed);
+            op->WriteResultFile(params, tiling, rankId, dataDir);
+        }
+    }
+    catccos_shmem_barrier_all();
+    FreeDeviceSpace(params);
+    if (workspace) CUDA_CHECK(cudaFree(workspace));
+    if (symmetric) catccos_shmem_free(symmetric);
+    catccos_shmem_finalize();
+    CUDA_CHECK(cudaStreamDestroy(stream));
+    return rc;
+}

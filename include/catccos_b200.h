@@ -101,6 +101,8 @@ CATCCOS_API int32_t catccos_shmem_n_pes(void);   /* shmem_n_pes() */
 /* Host-side get (the role of aclshmem_getmem on the host): synchronises the device and copies `bytes`
  * bytes of PE `pe`'s copy of symmetric address `ptr` into host memory. */
 CATCCOS_API int catccos_shmem_get_host(void *hostDst, const void *ptr, int32_t pe, size_t bytes);
+/* Host-side put (aclshmem_putmem on the host): copies host memory into PE `pe`'s copy of `ptr`. */
+CATCCOS_API int catccos_shmem_put_host(void *ptr, int32_t pe, const void *hostSrc, size_t bytes);
 /* aclshmem_barrier_all() (examples/ascend950_dispatch_ffn_combine/main.cpp:217-219): host barrier
  * of all PEs after synchronising the device. */
 CATCCOS_API int catccos_shmem_barrier_all(void);

@@ -1,0 +1,43 @@
+// (CocCommType, CocDataType) -> launcher, the role of tests/dynamic_tiling/include/launch_map.h:15-59.
+#ifndef CATCCOS_HOST_LAUNCH_MAP_H
+#define CATCCOS_HOST_LAUNCH_MAP_H
+
+#include <unordered_map>
+
+#include "info.h"
+
+// The reference's KernelFuncPtr with references replaced by pointers and an int status.
+using KernelFuncPtr = int (*)(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *, uint8_t *workspace,
+                              uint8_t *symmetric, CocTilingParams *, uint32_t transA, uint32_t transB);
+
+class KernelDispatcher {
+public:
+    static KernelFuncPtr GetKernelFunc(CocCommType commType, CocDataType dataType) {
+        const auto &m = Map();
+        const auto it = m.find(Hash(commType, dataType));
+        return it == m.end() ? nullptr : it->second;
+    }
+
+private:
+    static int Hash(CocCommType c, CocDataType d) { return (static_cast<int>(c) << 8) | static_cast<int>(d); }
+    static const std::unordered_map<int, KernelFuncPtr> &Map() {
+        static const std::unordered_map<int, KernelFuncPtr> m = {
+            {Hash(MATMUL_ALLREDUCE, FP16), &LaunchMatmulAllReduceFP16},
+            {Hash(MATMUL_ALLREDUCE, BF16), &LaunchMatmulAllReduceBF16},
+            {Hash(ALLGATHER_MATMUL, FP16), &LaunchAllGatherMatmulFP16},
+            {Hash(ALLGATHER_MATMUL, BF16), &LaunchAllGatherMatmulBF16},
+            {Hash(MATMUL_REDUCE_SCATTER, FP16), &LaunchMatmulReduceScatterFP16},
+            {Hash(MATMUL_REDUCE_SCATTER, BF16), &LaunchMatmulReduceScatterBF16},
+            {Hash(ASCEND950_ALLGATHER_MATMUL, FP16), &LaunchAscend950AllGatherMatmulFP16},
+            {Hash(ASCEND950_ALLGATHER_MATMUL, BF16), &LaunchAscend950AllGatherMatmulBF16},
+            {Hash(ASCEND950_MATMUL_REDUCE_SCATTER, FP16), &LaunchAscend950MatmulReduceScatterFP16},
+            {Hash(ASCEND950_MATMUL_REDUCE_SCATTER, BF16), &LaunchAscend950MatmulReduceScatterBF16},
+            {Hash(ASCEND950_FP8_MX_ALLGATHER_MATMUL, FP16), &LaunchAscend950Fp8MxAllGatherMatmulFP16},
+            {Hash(ASCEND950_FP8_MX_ALLGATHER_MATMUL, BF16), &LaunchAscend950Fp8MxAllGatherMatmulBF16},
+            {Hash(ASCEND950_DISPATCH_FFN_COMBINE, BF16), &LaunchAscend950DispatchFFNCombineBF16},
+        };
+        return m;
+    }
+};
+
+#endif  // CATCCOS_HOST_LAUNCH_MAP_H

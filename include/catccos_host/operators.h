@@ -1,0 +1,200 @@
+// Host-side operator classes of the fused operators: device buffers from raw .bin files, result
+// files, workspace sizes, tiling checks — the same classes, names and file conventions as the
+// reference's examples/<op>/<op>_host.h, on top of the CUDA runtime and the C-ABI.
+#ifndef CATCCOS_HOST_OPERATORS_H
+#define CATCCOS_HOST_OPERATORS_H
+
+#include <vector>
+
+#include "operator_registry.h"
+
+namespace catccos_host {
+
+// device buffer filled from `path` (or with `fill` repeated when path is empty / unreadable)
+inline uint8_t *DeviceBufferFromFile(const std::string &path, size_t bytes, int fillByte = 0) {
+    uint8_t *dev = nullptr;
+    CUDA_CHECK(cudaMalloc(reinterpret_cast<void **>(&dev), bytes));
+    std::vector<uint8_t> host(bytes, static_cast<uint8_t>(fillByte));
+    if (!path.empty()) ReadFile(path, host.data(), bytes);
+    CUDA_CHECK(cudaMemcpy(dev, host.data(), bytes, cudaMemcpyHostToDevice));
+    return dev;
+}
+inline uint8_t *DeviceZeros(size_t bytes) {
+    uint8_t *dev = nullptr;
+    CUDA_CHECK(cudaMalloc(reinterpret_cast<void **>(&dev), bytes));
+    CUDA_CHECK(cudaMemset(dev, 0, bytes));
+    return dev;
+}
+inline void WriteDeviceBuffer(const std::string &path, const uint8_t *dev, size_t bytes, size_t offset = 0) {
+    std::vector<uint8_t> host(bytes);
+    CUDA_CHECK(cudaMemcpy(host.data(), dev, bytes, cudaMemcpyDeviceToHost));
+    WriteFile(path, host.data(), bytes, offset);
+}
+inline std::string RankFile(const std::string &dir, const std::string &stem, uint32_t rank, const std::string &tail = "") {
+    return dir.empty() ? std::string() : dir + "/" + stem + std::to_string(rank) + tail + ".bin";
+}
+
+// shapes the tcgen05 kernels take: n and k multiples of 8 (16-byte rows for TMA)
+inline bool DenseShapeOk(const CocTilingParams &t) { return t.m > 0 && t.n > 0 && t.k > 0 && t.n % 8 == 0 && t.k % 8 == 0; }
+
+}  // namespace catccos_host
+
+// D = sum_r A_r * B_r on every rank (examples/matmul_allreduce/matmul_allreduce_host.h).
+class MatmulAllReduceOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t aSize = static_cast<size_t>(t.m) * t.k * 2, bSize = static_cast<size_t>(t.k) * t.n * 2;
+        const size_t dSize = static_cast<size_t>(t.m) * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), aSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), bSize), DeviceZeros(dSize));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/output.bin", params.ptrC, static_cast<size_t>(t.m) * t.n * 2);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &) override { return 0; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return MATMUL_ALLREDUCE; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return catccos_host::DenseShapeOk(t) && rankSize >= 1 && rankSize <= MAX_RANK_SIZE &&
+               catccos_symmetric_bytes(MATMUL_ALLREDUCE, FP16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("MatmulAllReduce", MatmulAllReduceOperator);
+
+// C[s*m:(s+1)*m] = A_s * B for all s (examples/allgather_matmul/allgather_matmul_host.h); m = rows per rank.
+class AllGatherMatmulOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t aSize = static_cast<size_t>(t.m) * t.k * 2, bSize = static_cast<size_t>(t.k) * t.n * 2;
+        const size_t cSize = static_cast<size_t>(t.m) * t.rankSize * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), aSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), bSize), DeviceZeros(cSize));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        const size_t cSize = static_cast<size_t>(t.m) * t.rankSize * t.n * 2;
+        // the reference writes one output.bin; per-rank weights give per-rank results, so each rank also
+        // writes output_<rank>.bin
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_" + std::to_string(rankId) + ".bin", params.ptrC, cSize);
+        if (rankId == 0) catccos_host::WriteDeviceBuffer(dataFile + "/output.bin", params.ptrC, cSize);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &) override { return 0; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ALLGATHER_MATMUL; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return catccos_host::DenseShapeOk(t) && rankSize >= 1 && rankSize <= MAX_RANK_SIZE &&
+               catccos_symmetric_bytes(ALLGATHER_MATMUL, BF16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("AllGatherMatmul", AllGatherMatmulOperator);
+class Ascend950AllGatherMatmulOperator : public AllGatherMatmulOperator {
+public:
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_ALLGATHER_MATMUL; }
+};
+REGISTER_OPERATOR("Ascend950AllGatherMatmul", Ascend950AllGatherMatmulOperator);
+
+// D_r = rows r of sum_s A_s * B_s (examples/matmul_reduce_scatter/matmul_reduce_scatter_host.h); m = total rows.
+class MatmulReduceScatterOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t aSize = static_cast<size_t>(t.m) * t.k * 2, bSize = static_cast<size_t>(t.k) * t.n * 2;
+        const size_t cSize = static_cast<size_t>(t.m) / t.rankSize * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), aSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), bSize), DeviceZeros(cSize));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        const size_t cSize = static_cast<size_t>(t.m) / t.rankSize * t.n * 2;
+        catccos_host::WriteDeviceBuffer(dataFile + "/output.bin", params.ptrC, cSize, rankId * cSize);   // offset r*size
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &) override { return 0; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return MATMUL_REDUCE_SCATTER; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return catccos_host::DenseShapeOk(t) && rankSize >= 1 && rankSize <= MAX_RANK_SIZE && t.m % rankSize == 0 &&
+               catccos_symmetric_bytes(MATMUL_REDUCE_SCATTER, BF16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("MatmulReduceScatter", MatmulReduceScatterOperator);
+class Ascend950MatmulReduceScatterOperator : public MatmulReduceScatterOperator {
+public:
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_MATMUL_REDUCE_SCATTER; }
+};
+REGISTER_OPERATOR("Ascend950MatmulReduceScatter", Ascend950MatmulReduceScatterOperator);
+
+// MXFP8 AllGather-Matmul (examples/ascend950_fp8_mx_allgather_matmul/ascend950_fp8_mx_allgather_matmul_host.h):
+// customPtrs = {aScale, bScale}.
+class Ascend950Fp8MxAllGatherMatmulOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t sizeA = static_cast<size_t>(t.m) * t.k, sizeB = static_cast<size_t>(t.k) * t.n;
+        const size_t kb = (static_cast<size_t>(t.k) / 32 + 1) / 2 * 2;
+        const size_t sizeC = static_cast<size_t>(t.m) * t.rankSize * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "input_a_", rankId), sizeA),
+                               DeviceBufferFromFile(RankFile(dataFile, "input_b_", rankId), sizeB), DeviceZeros(sizeC),
+                               DeviceBufferFromFile(RankFile(dataFile, "input_a_scale_", rankId), t.m * kb, 127),
+                               DeviceBufferFromFile(RankFile(dataFile, "input_b_scale_", rankId), t.n * kb, 127));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_" + std::to_string(rankId) + ".bin", params.ptrC,
+                                        static_cast<size_t>(t.m) * t.rankSize * t.n * 2);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &t) override {
+        return catccos_workspace_bytes(ASCEND950_FP8_MX_ALLGATHER_MATMUL, FP16, &t);
+    }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP8_MX_ALLGATHER_MATMUL; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return t.m > 0 && t.k % 32 == 0 && t.n % 16 == 0 && rankSize <= MAX_RANK_SIZE &&
+               catccos_symmetric_bytes(ASCEND950_FP8_MX_ALLGATHER_MATMUL, FP16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950Fp8MxAllGatherMatmul", Ascend950Fp8MxAllGatherMatmulOperator);
+
+// MoE dispatch -> FFN -> combine (examples/ascend950_dispatch_ffn_combine/ascend950_dispatch_ffn_combine_host.h):
+// customPtrs = {b2, expertIdx, probs, bScale, b2Scale}.
+class Ascend950DispatchFFNCombineOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t el = t.expertNum / (t.epSize ? t.epSize : t.rankSize);
+        const size_t aSize = static_cast<size_t>(t.m) * t.k * 2, cSize = aSize;
+        const size_t bSize = el * t.n * t.k, b2Size = el * t.k * (t.n / 2);
+        const size_t bScaleSize = el * t.n * (t.k / 32), b2ScaleSize = el * t.k * (t.n / 2 / 32);
+        const size_t idxSize = static_cast<size_t>(t.m) * t.topK * 4;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "in_routing_matrix_a_", rankId), aSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "in_gmm_matrix_b_", rankId), bSize), DeviceZeros(cSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "in_gmm_matrix_b2_", rankId), b2Size),
+                               DeviceBufferFromFile(RankFile(dataFile, "in_routing_expert_idx_", rankId), idxSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "in_gather_gate_weight_", rankId), idxSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "in_gmm_matrix_b_scale_", rankId), bScaleSize, 127),
+                               DeviceBufferFromFile(RankFile(dataFile, "in_gmm_matrix_b2_scale_", rankId), b2ScaleSize, 127));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_" + std::to_string(rankId) + ".bin", params.ptrC,
+                                        static_cast<size_t>(t.m) * t.k * 2);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &t) override {
+        return catccos_workspace_bytes(ASCEND950_DISPATCH_FFN_COMBINE, BF16, &t);
+    }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_DISPATCH_FFN_COMBINE; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        if (t.k % 256 != 0 || t.n % 512 != 0) {
+            std::fprintf(stderr, "MXFP8 FFN requires K %% 256 == 0 and N %% 512 == 0\n");
+            return false;
+        }
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return t.expertNum > 0 && t.expertNum % rankSize == 0 && t.topK >= 1 && t.topK <= 16 &&
+               catccos_symmetric_bytes(ASCEND950_DISPATCH_FFN_COMBINE, BF16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950DispatchFFNCombine", Ascend950DispatchFFNCombineOperator);
+
+#endif  // CATCCOS_HOST_OPERATORS_H

@@ -1,0 +1,84 @@
+"""The C++ host layer (operator registry, operator classes, launch map, driver binary)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def driver():
+    from catccos_b200 import build as b
+    b.build()
+    return b.DRIVER
+
+
+def test_registry_lists_every_operator_on_the_path(driver):
+    out = subprocess.run([driver, "--list"], capture_output=True, text=True, check=True).stdout.split()
+    assert set(out) == {"MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend950AllGatherMatmul",
+                        "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine"}
+
+
+def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
+    assert subprocess.run([driver], capture_output=True).returncode == 1
+    assert subprocess.run([driver, "nope", "27", "1", "0", "tcp://127.0.0.1:1", "8", "8", "8", str(tmp_path)],
+                          capture_output=True).returncode == 1
+    if not torch.cuda.is_available():
+        r = subprocess.run([driver, "mmar", "1", "1", "0", "tcp://127.0.0.1:1", "128", "256", "64", str(tmp_path)],
+                           capture_output=True, text=True)
+        assert r.returncode != 0 and "shmem init failed" in r.stderr
+
+
+def _write_dense_files(tmp_path, world, a, b, trans_b=False):
+    for r in range(world):
+        av = a[r].view(torch.uint16) if a[r].dtype == torch.bfloat16 else a[r]
+        bm = b[r].t().contiguous() if trans_b else b[r]
+        bv = bm.view(torch.uint16) if bm.dtype == torch.bfloat16 else bm
+        av.numpy().tofile(os.path.join(tmp_path, f"rank_{r}_a.bin"))
+        bv.numpy().tofile(os.path.join(tmp_path, f"rank_{r}_b.bin"))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kernel,dtype", [("mmar", torch.float16), ("agmm", torch.bfloat16), ("mmrs", torch.bfloat16)])
+def test_single_rank_driver_run(driver, tmp_path, kernel, dtype):
+    """rank_size 1 through the whole host path: files -> operator class -> launch map -> result file -> verifier."""
+    from oracle import dense, inputs, verify
+    m, n, k = 384, 520, 256
+    a, b = inputs.allgather_matmul_inputs(1, m, k, n, dtype)
+    _write_dense_files(str(tmp_path), 1, a, b)
+    code = "1" if dtype == torch.float16 else "27"
+    r = subprocess.run([driver, kernel, code, "1", "0", "tcp://127.0.0.1:8788", str(m), str(n), str(k), str(tmp_path),
+                        "0", "0", "1", "0", "0", "2", "3"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    name = "output_0.bin" if kernel == "agmm" else "output.bin"
+    raw = np.fromfile(os.path.join(tmp_path, name), dtype=np.uint16 if dtype == torch.bfloat16 else np.float16)
+    out = torch.from_numpy(raw.reshape(m, n))
+    out = out.view(torch.bfloat16) if dtype == torch.bfloat16 else out
+    gold = dense.matmul_fp32(a[0], b[0])
+    ok, precision, eb = verify.reference_check(out, gold, k)
+    assert ok, (precision, eb)
+
+
+@pytest.mark.gpu
+def test_two_rank_driver_run(driver, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from oracle import dense, inputs, verify
+    world, m, n, k = 2, 256, 512, 256
+    a, b = inputs.allgather_matmul_inputs(world, m, k, n, torch.bfloat16)
+    _write_dense_files(str(tmp_path), world, a, b)
+    port = f"tcp://127.0.0.1:{24000 + os.getpid() % 1000}"
+    procs = [subprocess.Popen([driver, "agmm", "27", "2", str(r), port, str(m), str(n), str(k), str(tmp_path)],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
+    for p in procs:
+        out, _ = p.communicate(timeout=300)
+        assert p.returncode == 0, out
+    gold = dense.golden_allgather_matmul(a, b)
+    for r in range(world):
+        raw = np.fromfile(os.path.join(tmp_path, f"output_{r}.bin"), dtype=np.uint16).reshape(world * m, n)
+        ok, precision, eb = verify.reference_check(torch.from_numpy(raw).view(torch.bfloat16), gold[r], k)
+        assert ok, (r, precision, eb)
