@@ -68,36 +68,62 @@ __device__ __host__ __forceinline__ size_t sf_atom_offset(uint32_t row, uint32_t
 }
 
 // One thread quantises 8 consecutive values; 4 neighbouring threads share a 32-value block.
+// A CTA walks whole rows; every thread keeps kQuantUnroll 16-byte loads in flight.
 // codes: [rows, k] bytes (row stride code_ld).  scales_rm: optional [rows, scale_ld] bytes.
-// sf_atoms: optional tcgen05 atom layout.  Rows are addressed through optional gather / scatter
-// lists: src_row = src_rows ? src_rows[r] : r, dst_row likewise (used by the MoE quant-scatter).
+// sf_atoms: optional tcgen05 atom layout.
+constexpr int kQuantUnroll = 4;
 __global__ void __launch_bounds__(256) mx_quant_kernel(const uint4 *__restrict__ in, int rows, int k, uint8_t *codes,
                                                        size_t code_ld, uint8_t *scales_rm, int scale_ld,
                                                        uint8_t *sf_atoms, int kb4_count) {
-    const int vec_per_row = k >> 3;                  // k % 32 == 0
-    const size_t total = static_cast<size_t>(rows) * vec_per_row;
+    const int vec_per_row = k >> 3;                  // k % 32 == 0, so vec_per_row % 4 == 0
     const int nblocks = k >> 5;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const int row = static_cast<int>(i / vec_per_row);
-        const int vcol = static_cast<int>(i - static_cast<size_t>(row) * vec_per_row);
-        const uint4 v = __ldg(in + i);
-        uint32_t am = bf16_abs_max(v);
-        const uint32_t lanes = __activemask();   // the 4 lanes of a block are always active together (k % 32 == 0)
-        am = max(am, __shfl_xor_sync(lanes, am, 1));
-        am = max(am, __shfl_xor_sync(lanes, am, 2));
-        uint32_t sb;
-        float inv;
-        block_scale(am, &sb, &inv);
-        const uint2 q = quantise8(v, inv);
-        *reinterpret_cast<uint2 *>(codes + static_cast<size_t>(row) * code_ld + vcol * 8) = q;
-        if ((vcol & 3) == 0) {
-            const int kb = vcol >> 2;
-            if (scales_rm) {
-                scales_rm[static_cast<size_t>(row) * scale_ld + kb] = static_cast<uint8_t>(sb);
-                if (kb == nblocks - 1 && (nblocks & 1)) scales_rm[static_cast<size_t>(row) * scale_ld + kb + 1] = 127;
+    const int lane = threadIdx.x & 31;
+    const bool wide_scales = scales_rm && (scale_ld & 7) == 0 && (reinterpret_cast<uintptr_t>(scales_rm) & 7) == 0;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4 *src = in + static_cast<size_t>(row) * vec_per_row;
+        uint8_t *crow = codes + static_cast<size_t>(row) * code_ld;
+        for (int v0 = threadIdx.x; v0 - static_cast<int>(threadIdx.x) < vec_per_row; v0 += 256 * kQuantUnroll) {
+            uint4 x[kQuantUnroll];
+#pragma unroll
+            for (int u = 0; u < kQuantUnroll; ++u) {
+                const int v = v0 + u * 256;
+                x[u] = v < vec_per_row ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
             }
-            if (sf_atoms) sf_atoms[sf_atom_offset(row, kb, kb4_count)] = static_cast<uint8_t>(sb);
+#pragma unroll
+            for (int u = 0; u < kQuantUnroll; ++u) {
+                const int v = v0 + u * 256;
+                // whole warps take this branch together except in a row's last partial warp, whose groups
+                // of 4 lanes (one 32-value block) are still complete
+                if (v - lane >= vec_per_row) continue;
+                const bool live = v < vec_per_row;
+                uint32_t am = bf16_abs_max(x[u]);
+                am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
+                am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
+                uint32_t sb;
+                float inv;
+                block_scale(am, &sb, &inv);
+                if (live) *reinterpret_cast<uint2 *>(crow + v * 8) = quantise8(x[u], inv);
+                const int kb = v >> 2;
+                // the warp's 8 block scales -> lane 0 (one 8-byte store) when the layout allows it
+                uint32_t lo = 0, hi = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    lo |= (__shfl_sync(0xffffffffu, sb, j * 4) & 0xFFu) << (8 * j);
+                    hi |= (__shfl_sync(0xffffffffu, sb, 16 + j * 4) & 0xFFu) << (8 * j);
+                }
+                const bool full_warp = (v - lane) + 32 <= vec_per_row;
+                if (scales_rm) {
+                    if (wide_scales && full_warp) {
+                        if (lane == 0)
+                            *reinterpret_cast<uint2 *>(scales_rm + static_cast<size_t>(row) * scale_ld + kb) = make_uint2(lo, hi);
+                    } else if (live && (v & 3) == 0) {
+                        scales_rm[static_cast<size_t>(row) * scale_ld + kb] = static_cast<uint8_t>(sb);
+                    }
+                    if (live && (v & 3) == 0 && kb == nblocks - 1 && (nblocks & 1))
+                        scales_rm[static_cast<size_t>(row) * scale_ld + kb + 1] = 127;
+                }
+                if (sf_atoms && live && (v & 3) == 0) sf_atoms[sf_atom_offset(row, kb, kb4_count)] = static_cast<uint8_t>(sb);
+            }
         }
     }
 }
@@ -160,7 +186,9 @@ int mx_quant_launch(cudaStream_t stream, const void *in_bf16, int rows, int k, u
         }
     }
     const size_t vecs = static_cast<size_t>(rows) * (k / 8);
-    mx_quant_kernel<<<grid_for(vecs, 256), 256, 0, stream>>>(static_cast<const uint4 *>(in_bf16), rows, k, codes, code_ld,
+    int grid = grid_for(vecs, 256);
+    if (grid > rows) grid = rows;
+    mx_quant_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4 *>(in_bf16), rows, k, codes, code_ld,
                                                             scales_rm, scale_ld, sf_atoms, kb4);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
