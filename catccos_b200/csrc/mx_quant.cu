@@ -17,14 +17,11 @@ namespace {
 
 __device__ __forceinline__ uint32_t bf16_abs_max(const uint4 &v) {
     // largest |bits| of the 8 bf16 values (integer order == magnitude order; NaN sorts above Inf)
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t m = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        m = max(m, w[i] & 0x7FFFu);
-        m = max(m, (w[i] >> 16) & 0x7FFFu);
-    }
-    return m;
+    // two 16-bit magnitudes per word, SIMD-in-word unsigned max
+    const uint32_t m01 = __vmaxu2(v.x & 0x7FFF7FFFu, v.y & 0x7FFF7FFFu);
+    const uint32_t m23 = __vmaxu2(v.z & 0x7FFF7FFFu, v.w & 0x7FFF7FFFu);
+    const uint32_t m = __vmaxu2(m01, m23);
+    return max(m & 0xFFFFu, m >> 16);
 }
 
 // scale byte and the exact reciprocal 2^-exp for a block whose largest |bf16 bits| is amax_bits
@@ -47,17 +44,27 @@ __device__ __forceinline__ uint32_t to_e4m3(float x) {
     return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
 }
 
-__device__ __forceinline__ uint2 quantise8(const uint4 &v, float inv_scale) {
+// `has_nan`: the block holds a NaN (its largest |bits| is above Inf); only then is the per-value NaN
+// handling needed — otherwise two values go through one cvt.rn.satfinite.e4m3x2.f32.
+__device__ __forceinline__ uint2 quantise8(const uint4 &v, float inv_scale, bool has_nan) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t c[8];
+    uint32_t h[4];
+    if (!has_nan) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        c[2 * i] = to_e4m3(__uint_as_float(w[i] << 16) * inv_scale);
-        c[2 * i + 1] = to_e4m3(__uint_as_float(w[i] & 0xFFFF0000u) * inv_scale);
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = make_float2(__uint_as_float(w[i] << 16) * inv_scale,
+                                         __uint_as_float(w[i] & 0xFFFF0000u) * inv_scale);
+            h[i] = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3));   // .x in the low byte
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            h[i] = to_e4m3(__uint_as_float(w[i] << 16) * inv_scale) |
+                   (to_e4m3(__uint_as_float(w[i] & 0xFFFF0000u) * inv_scale) << 8);
     }
     uint2 r;
-    r.x = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
-    r.y = c[4] | (c[5] << 8) | (c[6] << 16) | (c[7] << 24);
+    r.x = h[0] | (h[1] << 16);
+    r.y = h[2] | (h[3] << 16);
     return r;
 }
 
@@ -102,7 +109,7 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const uint4 *__restrict__
                 uint32_t sb;
                 float inv;
                 block_scale(am, &sb, &inv);
-                if (live) *reinterpret_cast<uint2 *>(crow + v * 8) = quantise8(x[u], inv);
+                if (live) *reinterpret_cast<uint2 *>(crow + v * 8) = quantise8(x[u], inv, am > 0x7F80u);
                 const int kb = v >> 2;
                 // the warp's 8 block scales -> lane 0 (one 8-byte store) when the layout allows it
                 uint32_t lo = 0, hi = 0;
