@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "gemm_fused.cuh"
+#include "gemm_pair.cuh"
 #include "ptx.cuh"
 
 namespace cb {
@@ -48,6 +49,28 @@ static int launch_kernel(const FusedParams &p, int grid, bool cooperative, cudaS
     }
     if (e != cudaSuccess) {
         set_error("kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+// CTA-pair (cta_group::2) variant of AllGather-Matmul
+template <typename T, bool B_MN>
+static int launch_pair(const FusedParams &p, int grid, bool cooperative, cudaStream_t stream) {
+    auto kern = pair_agmm_kernel<T, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+    if (e == cudaSuccess) {
+        if (cooperative) {
+            void *args[] = {const_cast<FusedParams *>(&p)};
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
+                                            kPairSmemBytes, stream);
+        } else {
+            kern<<<grid, kGemmThreads, kPairSmemBytes, stream>>>(p);
+            e = cudaGetLastError();
+        }
+    }
+    if (e != cudaSuccess) {
+        set_error("pair kernel launch failed: %s", cudaGetErrorString(e));
         return CATCCOS_ERR_CUDA;
     }
     return CATCCOS_OK;
@@ -136,6 +159,9 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         }
     }
 
+    // AllGather-Matmul runs on CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
+    bool use_pair = (op == OP_AGMM);
+    if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = use_pair && atoi(e) != 0;
     FusedParams p;
     memset(&p, 0, sizeof(p));
     const CUtensorMapDataType dt = dtype == 27 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -151,7 +177,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         int rc = encode_2d(api, &ra.tmA, dt, a.A, k, a_rows, static_cast<uint64_t>(k) * 2, BK, BM);
         if (rc) return rc;
         if (trans_b) {
-            rc = encode_2d(api, &ra.tmB, dt, a.B, k, n, static_cast<uint64_t>(k) * 2, BK, BN);
+            rc = encode_2d(api, &ra.tmB, dt, a.B, k, n, static_cast<uint64_t>(k) * 2, BK, use_pair ? 128 : BN);
         } else {
             rc = encode_2d(api, &ra.tmB, dt, a.B, n, k, static_cast<uint64_t>(n) * 2, 64, BK);
         }
@@ -198,10 +224,21 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.status = t->status_dev;
     p.trace = t->trace_dev;
 
-    const int grid = per_rank * n_local;
     const bool coop = n_local > 1;
     const bool bf16 = dtype == 27;
     const bool b_mn = trans_b == 0;
+    if (use_pair) {
+        if (per_rank < 2) {
+            set_error("the CTA-pair kernel needs at least 2 CTAs per rank");
+            return CATCCOS_ERR_INVALID;
+        }
+        p.ctas_per_rank = per_rank & ~1;
+        p.push_ctas = 0;
+        const int g2 = p.ctas_per_rank * n_local;
+        if (bf16) return b_mn ? launch_pair<__nv_bfloat16, true>(p, g2, coop, stream) : launch_pair<__nv_bfloat16, false>(p, g2, coop, stream);
+        return b_mn ? launch_pair<__half, true>(p, g2, coop, stream) : launch_pair<__half, false>(p, g2, coop, stream);
+    }
+    const int grid = per_rank * n_local;
     switch (op) {
         case OP_AGMM: return launch_t<OP_AGMM>(p, grid, coop, stream, bf16, b_mn);
         case OP_MMRS: return launch_t<OP_MMRS>(p, grid, coop, stream, bf16, b_mn);

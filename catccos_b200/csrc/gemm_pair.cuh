@@ -1,0 +1,304 @@
+// AllGather-Matmul f16/bf16 with CTA pairs (tcgen05 cta_group::2), sm_100a.
+//
+// Two CTAs on neighbouring SMs (a cluster of 2) compute one 256 x 256 tile: each CTA loads its own
+// 128 rows of A and its own 128 columns of B (no multicast) and holds the accumulator of its 128
+// rows in its own TMEM; the leader CTA issues one M=256 MMA per 16 K-elements that reads both
+// CTAs' shared memory.  Per SM and K-step this moves 32 KiB from L2 instead of the 48 KiB of the
+// one-CTA 128 x 256 tile, which is what limits that kernel, and leaves room for 6 pipeline stages.
+// Everything around the main loop (tile order, all-gather push lanes, flags, bounded waits,
+// epilogue) is the one-CTA kernel's.
+#pragma once
+#include <type_traits>
+
+#include "common.h"
+#include "gemm_fused.cuh"
+#include "ptx.cuh"
+
+namespace cb {
+
+constexpr int kPStages = 6;
+constexpr int kPAStage = BM * BK * 2;          // 128 rows of A      : 16 KiB
+constexpr int kPBStage = 128 * BK * 2;         // 128 columns of B   : 16 KiB
+constexpr int kPairSmemBytes = kPStages * (kPAStage + kPBStage) + kSideSmemBytes + 1024 + 512;
+constexpr int BM2 = 2 * BM;                    // rows of a pair's tile
+
+struct PairSmem {
+    uint64_t full[kPStages];        // used in the leader: both CTAs' loads of a stage have landed
+    uint64_t empty[kPStages];       // per CTA: the pair's MMAs have finished reading this stage
+    uint64_t tmem_full[2];          // per CTA: accumulator complete
+    uint64_t tmem_empty[2];         // used in the leader: both CTAs' epilogues have drained the accumulator
+    uint64_t drain;
+    uint64_t push_bar[kPushLanesShared];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <typename T, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    pair_agmm_kernel(const __grid_constant__ FusedParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem + kPStages * kPAStage;
+    uint8_t *smem_push = smem + kPStages * (kPAStage + kPBStage);
+    PairSmem *sh = reinterpret_cast<PairSmem *>(smem_push + kSideSmemBytes);
+    static_assert(sizeof(PairSmem) <= 512, "barrier block outgrew its budget");
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int lrank = blockIdx.x / p.ctas_per_rank;
+    const int cta = blockIdx.x - lrank * p.ctas_per_rank;      // ctas_per_rank is even
+    const int pair = cta >> 1;
+    const int pairs = p.ctas_per_rank >> 1;
+    const uint32_t cr = cluster_ctarank();                      // 0 = leader
+    const int rank = p.rank_base + lrank;
+    const int R = p.world;
+    const RankArgs &ra = p.ranks[lrank];
+    const int mt2 = ceil_div(p.M, BM2);
+    const int nt = ceil_div(p.N, BN);
+    const int per_src = mt2 * nt;
+    const int num_tiles = R * per_src;
+    const int kblocks = ceil_div(p.K, BK);
+    const int mt_ag = ceil_div(p.M, BM);                        // 128-row push chunks per source rank
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPStages; ++s) {
+            mbar_init(&sh->full[s], 2);
+            mbar_init(&sh->empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sh->tmem_full[a], 1);
+            mbar_init(&sh->tmem_empty[a], 8);
+        }
+        mbar_init(&sh->drain, 1);
+        for (int l = 0; l < kPushLanesShared; ++l) mbar_init(&sh->push_bar[l], 1);
+        sh->abort_flag = 0;
+        mbar_init_fence();
+        prefetch_tensormap(&ra.tmA);
+        prefetch_tensormap(&ra.tmB);
+        prefetch_tensormap(&ra.tmAg);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(&sh->tmem_base, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                 // the peer's barriers are initialised before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    WaitCtl ctl;
+    ctl.abort_smem = &sh->abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+    if (threadIdx.x == 0) CB_TRACE(TR_START, globaltimer_ns());
+
+    // tile t -> (source rank s, 256-row tile mi2, column tile ni); own rows first, then rank+1, ...
+    auto decode = [&](int t, int &s, int &mi2, int &ni, bool &gathered) {
+        const int j = t / per_src;
+        const int u = t - j * per_src;
+        s = (rank + j) % R;
+        mi2 = u / nt;
+        ni = u - mi2 * nt;
+        gathered = (j != 0);
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer ----
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += pairs) {
+                int s, mi2, ni;
+                bool gathered;
+                decode(t, s, mi2, ni, gathered);
+                const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;    // this CTA's 128 rows
+                if (gathered && !p.compute_only && row_in_src < p.M) {
+                    const uint32_t w = kFlagOpBase + (s * mt_ag + (row_in_src / BM)) * kAgSubChunks;
+                    for (int q = 0; q < kAgSubChunks && ok; ++q)
+                        ok = wait_flag_ge(flag_ptr(p, rank, w + q), p.epoch, ctl, W_AG_CHUNK, w + q);
+                    if (!ok) break;
+                    fence_proxy_async();
+                }
+                const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
+                const int a_row = (gathered ? s * p.M : 0) + row_in_src;
+                const int n_half = ni * BN + static_cast<int>(cr) * 128;         // this CTA's 128 columns of B
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int st = it % kPStages;
+                    const uint32_t ph = (it / kPStages) & 1;
+                    if (!(ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY))) break;
+                    const uint32_t full_leader = mapa_cluster(smem_u32(&sh->full[st]), 0);
+                    mbar_expect_tx_cluster(full_leader, kPAStage + kPBStage);
+                    tma_load_2d_pair(smem_a + st * kPAStage, tma, full_leader, kb * BK, a_row);
+                    if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            tma_load_2d_pair(smem_b + st * kPBStage + j * (64 * BK * 2), &ra.tmB, full_leader,
+                                             n_half + j * 64, kb * BK);
+                    } else {
+                        tma_load_2d_pair(smem_b + st * kPBStage, &ra.tmB, full_leader, kb * BK, n_half);
+                    }
+                }
+            }
+            if (!ok) {
+                // loads already issued still land in shared memory; give them time (bounded)
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 20000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------- MMA issuer (leader CTA only) ----
+        if (lane == 0 && cr == 0) {
+            constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+            constexpr uint32_t idesc = make_idesc_f16(fmt, BM2, BN, 0, B_MN ? 1 : 0);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += pairs) {
+                const uint32_t acc = tcount & 1;
+                if (!(ok = mbar_wait(&sh->tmem_empty[acc], ((tcount >> 1) & 1) ^ 1, ctl, W_TMEM_EMPTY))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int st = it % kPStages;
+                    if (!(ok = mbar_wait(&sh->full[st], (it / kPStages) & 1, ctl, W_MBAR_FULL))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + st * kPAStage);
+                    const uint32_t b_addr = smem_u32(smem_b + st * kPBStage);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                        const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                                 : make_smem_desc(b_addr + k * 32, 16, 1024);
+                        umma_f16_pair(d_tmem, ad, bd, idesc, (kb | k) != 0);
+                    }
+                    // the stage is free in both CTAs once these MMAs have read it
+                    umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 0));
+                    umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 1));
+                }
+                if (!ok) break;
+                umma_commit_pair(mapa_cluster(smem_u32(&sh->tmem_full[acc]), 0));
+                umma_commit_pair(mapa_cluster(smem_u32(&sh->tmem_full[acc]), 1));
+                ++tcount;
+            }
+            CB_TRACE(TR_TILES, tcount);
+            if (!ok) {
+                umma_commit_pair(mapa_cluster(smem_u32(&sh->drain), 0));
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(&sh->drain, 0)) {
+                    if (globaltimer_ns() - t0 > 2000000ull) break;
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- epilogue ----
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        uint32_t tcount = 0;
+        bool ok = true;
+        T *const C = reinterpret_cast<T *>(ra.C);
+        for (int t = pair; t < num_tiles && ok; t += pairs) {
+            int s, mi2, ni;
+            bool gathered;
+            decode(t, s, mi2, ni, gathered);
+            const uint32_t acc = tcount & 1;
+            if (!(ok = mbar_wait(&sh->tmem_full[acc], (tcount >> 1) & 1, ctl, W_TMEM_FULL))) break;
+            tc_fence_after();
+            const int row = s * p.M + mi2 * BM2 + static_cast<int>(cr) * BM + row_in_tile;
+            const bool row_ok = row < (s + 1) * p.M;
+            T *dst_row = C + static_cast<size_t>(row) * p.N;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                tmem_ld_wait();
+                const int col = ni * BN + c * 32;
+                if (!row_ok || col >= p.N) continue;
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    pk[i] = Pack2<T>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    if (col + g * 8 < p.N)
+                        *reinterpret_cast<uint4 *>(dst_row + col + g * 8) =
+                            make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+            }
+            // accumulator drained: tell the leader's MMA thread (8 warps of the pair arrive)
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty[acc]), 0));
+            ++tcount;
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------------ all-gather push ----
+        const int ctid = lane;
+        if (R > 1 && !p.compute_only) {
+            if (cta == 0 && ctid < R && ctid != rank) {
+                fence_sys();
+                st_release_sys(flag_ptr(p, ctid, kFlagEntered + rank), p.epoch);
+            }
+            if (ctid < kPushLanesShared) {
+                // same units, order and flags as the one-CTA kernel: destination rank-1 first, units of
+                // BM/kAgSubChunks rows, one flag per unit, every lane owns whole units
+                const int units_per_dest = mt_ag * kAgSubChunks;
+                const int total = (R - 1) * units_per_dest;
+                const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
+                const int lane_id = cta * kPushLanesShared + ctid;
+                const int n_lanes = p.ctas_per_rank * kPushLanesShared;
+                uint8_t *buf = smem_push + ctid * kPushPieceBytes;
+                uint64_t *bar = &sh->push_bar[ctid];
+                bool ok = true;
+                uint32_t entered_ok = 0;
+                uint32_t piece = 0;
+                for (int u = lane_id; u < total && ok; u += n_lanes) {
+                    const int jj = u / units_per_dest;
+                    const int d = (rank + R - 1 - jj) % R;
+                    const int cu = u - jj * units_per_dest;
+                    const int chunk = cu / kAgSubChunks, sub = cu % kAgSubChunks;
+                    const int r0 = chunk * BM + sub * (BM / kAgSubChunks);
+                    const int r1 = min(p.M, r0 + BM / kAgSubChunks);
+                    if (!((entered_ok >> d) & 1)) {
+                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d))) break;
+                        entered_ok |= 1u << d;
+                    }
+                    if (r1 > r0) {
+                        const uint8_t *src = static_cast<const uint8_t *>(ra.A) + r0 * row_bytes;
+                        uint8_t *dst = p.heap_base[d] + p.symm_off + (static_cast<size_t>(rank) * p.M + r0) * row_bytes;
+                        const size_t bytes = (r1 - r0) * row_bytes;
+                        for (size_t off = 0; off < bytes && ok; off += kPushPieceBytes, ++piece) {
+                            const uint32_t len = static_cast<uint32_t>(min(static_cast<size_t>(kPushPieceBytes), bytes - off));
+                            bulk_wait_read<0>();
+                            mbar_expect_tx(bar, len);
+                            bulk_load(buf, src + off, len, bar);
+                            if (!(ok = mbar_wait(bar, piece & 1, ctl, W_DRAIN))) break;
+                            bulk_store(dst + off, buf, len);
+                            bulk_commit();
+                        }
+                    }
+                    if (!ok) break;
+                    bulk_wait<0>();
+                    fence_proxy_async();
+                    fence_sys();
+                    st_release_sys(flag_ptr(p, d, kFlagOpBase + (rank * mt_ag + chunk) * kAgSubChunks + sub), p.epoch);
+                }
+                bulk_wait<0>();
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown ----
+    // Neither CTA may leave while the other can still signal its barriers or read its shared memory.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+    if (threadIdx.x == 0) CB_TRACE(TR_END, globaltimer_ns());
+}
+
+}  // namespace cb

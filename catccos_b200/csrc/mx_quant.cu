@@ -112,12 +112,10 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const uint4 *__restrict__
                 if (live) *reinterpret_cast<uint2 *>(crow + v * 8) = quantise8(x[u], inv, am > 0x7F80u);
                 const int kb = v >> 2;
                 // the warp's 8 block scales -> lane 0 (one 8-byte store) when the layout allows it
-                uint32_t lo = 0, hi = 0;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    lo |= (__shfl_sync(0xffffffffu, sb, j * 4) & 0xFFu) << (8 * j);
-                    hi |= (__shfl_sync(0xffffffffu, sb, 16 + j * 4) & 0xFFu) << (8 * j);
-                }
+                // lanes 0,4,...,28 hold the bytes; three shuffles fold them into lane 0
+                uint32_t lo = sb | (__shfl_down_sync(0xffffffffu, sb, 4) << 8);
+                lo |= __shfl_down_sync(0xffffffffu, lo, 8) << 16;
+                const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 16);
                 const bool full_warp = (v - lane) + 32 <= vec_per_row;
                 if (scales_rm) {
                     if (wide_scales && full_warp) {
