@@ -333,6 +333,11 @@ def main():
             idx = top_i.to(torch.int32).contiguous()
             c_d = torch.empty((m, k), dtype=torch.bfloat16, device="cuda")
             wsp = torch.zeros(lib().catccos_workspace_bytes(comm, rt.BF16, ctypes.byref(til)), dtype=torch.uint8, device="cuda")
+            # rows every expert owner receives (explains the max-over-ranks time under skewed routing)
+            owner_rows = torch.bincount((idx.flatten() // el).to(torch.int64), minlength=world).to(torch.float64)
+            if world > 1:
+                dist.all_reduce(owner_rows)
+            moe_imbalance = float(owner_rows.max() / owner_rows.mean())
             torch.cuda.synchronize()
 
             def step():
@@ -470,6 +475,8 @@ def main():
                 "exposed_comm_frac": exposed, "compute_only_ms_per_step": compute_only_ms,
                 "e2e": e2e, "gpu_launches": args.steps * launches_per_step, "clocks": clocks,
             }
+            if args.op == "moe":
+                line["config"]["hottest_rank_rows_over_mean"] = moe_imbalance
             if world == 1 and not args.no_cpu_baseline and dense_op:
                 v, cores, secs = cpu_golden_rate(wl, 1024, torch)
                 line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",

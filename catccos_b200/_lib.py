@@ -82,6 +82,7 @@ for _dt in ("FP16", "BF16"):
 
 
 SIGNATURES["LaunchAscend950DispatchFFNCombineBF16"] = (ctypes.c_int, LAUNCH_ARGS)
+SIGNATURES["LaunchAscend950BF16QuantAllGatherFP8E4M3FN"] = (ctypes.c_int, LAUNCH_ARGS)
 
 
 def load():

@@ -5,6 +5,7 @@
 #include "moe_ops.h"
 #include "mx_ops.h"
 #include "mx_quant.h"
+#include "mxq_allgather.h"
 #include "ptx.cuh"
 #include "symm_heap.h"
 
@@ -130,6 +131,22 @@ int launch_moe_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params,
                                            static_cast<int>(tiling->m), static_cast<int>(tiling->k),
                                            static_cast<int>(tiling->n), static_cast<int>(tiling->topK),
                                            static_cast<int>(tiling->expertNum));
+}
+
+int launch_mxq_ag_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params, uint8_t *symmetric,
+                      CocTilingParams *tiling) {
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    Team *t = team();
+    const int want = t->emulated ? t->n_pes : 1;
+    if (!params || n_params != want) {
+        set_error("MX quant + AllGather: one parameter block per local PE is required");
+        return CATCCOS_ERR_INVALID;
+    }
+    MxqAgArgs args[kMaxRanks];
+    for (int i = 0; i < n_params; ++i) args[i] = {params[i].ptrA, params[i].ptrC, params[i].ptrB};
+    return launch_mx_quant_allgather(static_cast<cudaStream_t>(stream), blockNum, args, symmetric,
+                                     static_cast<int>(tiling->m), static_cast<int>(tiling->n));
 }
 
 }  // namespace
@@ -305,6 +322,8 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
         return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
+    if (commType == CATCCOS_MX_QUANT_ALLGATHER)
+        return mxq_allgather_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n));
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0)
         return moe_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->k),
                                    static_cast<int>(tiling->n), static_cast<int>(tiling->topK),
@@ -352,6 +371,16 @@ DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16, OP_MMRS, CATCCOS_BF16)
 MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16, CATCCOS_FP16)
 MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16, CATCCOS_BF16)
 
+int LaunchAscend950BF16QuantAllGatherFP8E4M3FN(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params,
+                                               uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling,
+                                               uint32_t transA, uint32_t transB) {
+    (void)fftsAddr;
+    (void)workspace;
+    (void)transA;
+    (void)transB;
+    return launch_mxq_ag_abi(stream, blockNum, params, 1, symmetric, tiling);
+}
+
 int LaunchAscend950DispatchFFNCombineBF16(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params,
                                           uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA,
                                           uint32_t transB) {
@@ -372,6 +401,8 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
         return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
+    if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
+        return launch_mxq_ag_abi(stream, blockNum, params, 1, symmetric, tiling);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }
@@ -392,6 +423,8 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
                                 transB);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling);
+    if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
+        return launch_mxq_ag_abi(stream, blockNum, params, t->n_pes, symmetric, tiling);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }

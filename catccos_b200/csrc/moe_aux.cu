@@ -334,31 +334,44 @@ __global__ void __launch_bounds__(256) moe_unpermute_kernel(const MoeParams p) {
     const int K = p.K, topk = p.top_k;
     const int vec_per_row = K >> 3;
     const __nv_bfloat16 *comb = reinterpret_cast<const __nv_bfloat16 *>(p.heap_base[rank] + p.lay.combine_off);
-    const size_t total = static_cast<size_t>(p.m) * vec_per_row;
-    for (size_t i = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<size_t>(p.ctas_per_rank) * blockDim.x) {
-        const int t = static_cast<int>(i / vec_per_row);
-        const int v = static_cast<int>(i - static_cast<size_t>(t) * vec_per_row);
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int k = 0; k < topk; ++k) {
-            const int row = ra.expanded_row_idx[t * topk + k];
-            const float w = ra.probs[t * topk + k];
-            const uint4 x = *reinterpret_cast<const uint4 *>(comb + static_cast<size_t>(row) * K + v * 8);
-            const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(xs[j] << 16), w));
-                acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(xs[j] & 0xFFFF0000u), w));
-            }
+    __shared__ int s_row[kMaxTopK];
+    __shared__ float s_w[kMaxTopK];
+    // one CTA per token at a time; every thread keeps the token's top-k row pieces in flight together
+    for (int t = cta; t < p.m; t += p.ctas_per_rank) {
+        __syncthreads();
+        if (threadIdx.x < topk) {
+            s_row[threadIdx.x] = ra.expanded_row_idx[t * topk + threadIdx.x];
+            s_w[threadIdx.x] = ra.probs[t * topk + threadIdx.x];
         }
-        uint4 o;
-        o.x = Pack2<__nv_bfloat16>::pack(acc[0], acc[1]);
-        o.y = Pack2<__nv_bfloat16>::pack(acc[2], acc[3]);
-        o.z = Pack2<__nv_bfloat16>::pack(acc[4], acc[5]);
-        o.w = Pack2<__nv_bfloat16>::pack(acc[6], acc[7]);
-        *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(ra.out) + static_cast<size_t>(t) * K + v * 8) = o;
+        __syncthreads();
+        for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+            uint4 x[kMaxTopK];
+#pragma unroll
+            for (int k = 0; k < kMaxTopK; ++k)
+                if (k < topk)
+                    x[k] = *reinterpret_cast<const uint4 *>(comb + static_cast<size_t>(s_row[k]) * K + v * 8);
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+            for (int k = 0; k < kMaxTopK; ++k) {
+                if (k < topk) {
+                    const float w = s_w[k];
+                    const uint32_t xs[4] = {x[k].x, x[k].y, x[k].z, x[k].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(__uint_as_float(xs[j] << 16), w));
+                        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(__uint_as_float(xs[j] & 0xFFFF0000u), w));
+                    }
+                }
+            }
+            uint4 o;
+            o.x = Pack2<__nv_bfloat16>::pack(acc[0], acc[1]);
+            o.y = Pack2<__nv_bfloat16>::pack(acc[2], acc[3]);
+            o.z = Pack2<__nv_bfloat16>::pack(acc[4], acc[5]);
+            o.w = Pack2<__nv_bfloat16>::pack(acc[6], acc[7]);
+            *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(ra.out) + static_cast<size_t>(t) * K + v * 8) = o;
+        }
     }
 }
 
@@ -427,11 +440,25 @@ static int launch_grid(K kern, const MoeParams &p, int threads, cudaStream_t str
     return CATCCOS_OK;
 }
 
+// The two HBM-bound kernels wait only for flags of kernels that ran (or run on other GPUs), never
+// for their own CTAs, so they need no co-residency: plain launches with several CTAs per SM.
+template <typename K>
+static int launch_wide(K kern, const MoeParams &p, int threads, int ctas_per_sm, cudaStream_t stream, const char *name) {
+    MoeParams q = p;
+    q.ctas_per_rank = p.ctas_per_rank * ctas_per_sm;
+    kern<<<q.ctas_per_rank * q.n_local, threads, 0, stream>>>(q);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("%s launch failed: %s", name, cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
 int moe_launch_dispatch(const MoeParams &p, cudaStream_t stream) {
-    return launch_grid(moe_quant_dispatch_kernel, p, kDispWarps * 32, stream, "moe_quant_dispatch_kernel");
+    return launch_wide(moe_quant_dispatch_kernel, p, kDispWarps * 32, 4, stream, "moe_quant_dispatch_kernel");
 }
 int moe_launch_unpermute(const MoeParams &p, cudaStream_t stream) {
-    return launch_grid(moe_unpermute_kernel, p, 256, stream, "moe_unpermute_kernel");
+    return launch_wide(moe_unpermute_kernel, p, 256, 6, stream, "moe_unpermute_kernel");
 }
 
 }  // namespace cb

@@ -152,6 +152,52 @@ __global__ void sf_to_atoms_kernel(const uint8_t *__restrict__ src, int kind, in
     }
 }
 
+// Row-major [rows, ld] scale bytes -> atoms through a shared-memory transpose: a CTA takes one
+// 128-row tile and 16 k-block groups (64 scale bytes per row), reads 16-byte pieces of rows and writes
+// whole 16-byte atom lines.  Needs 16-byte aligned rows (ld % 16 == 0).
+__global__ void __launch_bounds__(256) sf_rows_to_atoms_kernel(const uint8_t *__restrict__ src, int rows, int kblocks,
+                                                               int ld, uint8_t *atoms, int kb4_count) {
+    __shared__ __align__(16) uint8_t tile[128][80];
+    const int groups = (kb4_count + 15) / 16;
+    const int row_tiles = (rows + 127) / 128;
+    for (int w = blockIdx.x; w < row_tiles * groups; w += gridDim.x) {
+        const int rt = w / groups, g = w - rt * groups;
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            const int r = idx >> 2, c16 = idx & 3;
+            const int row = rt * 128 + r;
+            const int byte0 = g * 64 + c16 * 16;
+            uint4 v = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+            if (row < rows && byte0 < ld) {
+                v = *reinterpret_cast<const uint4 *>(src + static_cast<size_t>(row) * ld + byte0);
+                // bytes past the last real k-block of the row are padding: neutral scale
+                if (byte0 + 16 > kblocks) {
+                    uint8_t *b = reinterpret_cast<uint8_t *>(&v);
+                    for (int j = 0; j < 16; ++j)
+                        if (byte0 + j >= kblocks) b[j] = 127;
+                }
+            }
+            *reinterpret_cast<uint4 *>(&tile[r][c16 * 16]) = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int o = threadIdx.x + i * 256;
+            const int a = o >> 5, l = o & 31;
+            const int kb4 = g * 16 + a;
+            if (kb4 >= kb4_count) continue;
+            uint4 v;
+            v.x = *reinterpret_cast<const uint32_t *>(&tile[l][a * 4]);
+            v.y = *reinterpret_cast<const uint32_t *>(&tile[l + 32][a * 4]);
+            v.z = *reinterpret_cast<const uint32_t *>(&tile[l + 64][a * 4]);
+            v.w = *reinterpret_cast<const uint32_t *>(&tile[l + 96][a * 4]);
+            *reinterpret_cast<uint4 *>(atoms + (static_cast<size_t>(rt) * kb4_count + kb4) * 512 + l * 16) = v;
+        }
+    }
+}
+
 }  // namespace
 
 size_t sf_atoms_bytes(int rows, int k) {
@@ -205,6 +251,19 @@ int mx_quant_launch(cudaStream_t stream, const void *in_bf16, int rows, int k, u
 
 int sf_to_atoms_launch(cudaStream_t stream, const uint8_t *src, int kind, int rows, int kblocks, int ld, uint8_t *atoms) {
     const int k = kblocks * 32;
+    if (kind == 0 && (ld & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(atoms) & 15) == 0) {
+        // fast path: writes every byte of the atom buffer itself (padding included)
+        const int kb4c = (k + 127) / 128;
+        const size_t work = static_cast<size_t>((rows + 127) / 128) * ((kb4c + 15) / 16);
+        sf_rows_to_atoms_kernel<<<grid_for(work * 256, 256), 256, 0, stream>>>(src, rows, kblocks, ld, atoms, kb4c);
+        cudaError_t e2 = cudaGetLastError();
+        if (e2 != cudaSuccess) {
+            set_error("scale re-layout failed: %s", cudaGetErrorString(e2));
+            return CATCCOS_ERR_CUDA;
+        }
+        return CATCCOS_OK;
+    }
     cudaError_t e = cudaMemsetAsync(atoms, 127, sf_atoms_bytes(rows, k), stream);
     if (e == cudaSuccess) {
         const size_t total = static_cast<size_t>(rows) * kblocks;

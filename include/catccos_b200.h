@@ -166,6 +166,12 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16);
 
+/* MxQuantAllGather (include/catccos/comm/kernel/mx_quant_allgather.hpp:57-288; registered as
+ * REGISTER_KERNEL_FUNC(Ascend950BF16QuantAllGather, MX_QUANT_ALLGATHER, FP8E4M3FN), launch_map.h:91): KernelParams as in
+ * examples/ascend950_mx_quant_allgather/mx_quant_allgather_host.h:48 — ptrA = input bf16 [m, n], ptrB = gathered
+ * E8M0 scales [rankSize*m, even(n/32)], ptrC = gathered e4m3 codes [rankSize*m, n]; tiling m, n (n % 32 == 0). */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950BF16QuantAllGatherFP8E4M3FN);
+
 /* The MoE operator: DispatchFFNCombine<...>(fftsAddr, gmA, gmB, gmBScale, gmB2, gmB2Scale, gmD, gmExpertIdx,
  * gmProbs, gmWorkSpace, gmSymmetric, CocTilingParams, ...) (examples/ascend950_dispatch_ffn_combine/
  * ascend950_dispatch_ffn_combine_device.h:617-718), with the operands in the operator class's KernelParams

@@ -111,3 +111,37 @@ def test_mx_allgather_matmul(world, trans_b, m, n, k, out):
     for r in range(world):
         err = verify.max_rel_err(outs[r], gold[r])
         assert err <= TOL_MX, f"rank {r}: max relative error {err}"
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("m,n", [(128, 256), (200, 7168), (64, 96)])
+def test_mx_quant_allgather_bit_exact(world, m, n):
+    """MxQuantAllGather: every rank ends with all ranks' codes and scales, byte for byte as the golden
+    (the reference compares these outputs bytewise: examples/ascend950_mx_quant_allgather/scripts/run.sh)."""
+    from catccos_b200 import runtime as rt
+    if world > 1 and (m * n) % 16:
+        pytest.skip("rows per rank not a multiple of 16 bytes")
+    xs = [(torch.randn((m, n), generator=torch.Generator().manual_seed(900 + r)) * (0.5 + r)).to(torch.bfloat16)
+          for r in range(world)]
+    gold_c, gold_s = [], []
+    for x in xs:
+        c, s, _ = mxquant.quantize_mx_e4m3(x.to(torch.float32).numpy(), "rne")
+        gold_c.append(c); gold_s.append(s)
+    gold_c, gold_s = np.concatenate(gold_c), np.concatenate(gold_s)
+    sld = gold_s.shape[1]
+    if world > 1 and (m * sld) % 16:
+        pytest.skip("scale rows per rank not a multiple of 16 bytes")
+    til = rt.tiling(m, 1, n, world)
+    need = rt.symmetric_bytes(rt.MX_QUANT_ALLGATHER, rt.FP8E4M3FN, til)
+    with rt.emulated_team(world, max(need, 1 << 20)):
+        symm = rt.shmem_malloc(max(need, 1024))
+        x_d = [dev(x) for x in xs]
+        s_d = [torch.zeros((world * m, sld), dtype=torch.uint8, device="cuda") for _ in range(world)]
+        c_d = [torch.zeros((world * m, n), dtype=torch.uint8, device="cuda") for _ in range(world)]
+        for _ in range(2):
+            rt.launch_emulated(rt.MX_QUANT_ALLGATHER, x_d, s_d, c_d, symm, til, dtype=rt.FP8E4M3FN)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+        for r in range(world):
+            assert np.array_equal(c_d[r].cpu().numpy(), gold_c), f"codes on rank {r}"
+            assert np.array_equal(s_d[r].cpu().numpy(), gold_s), f"scales on rank {r}"
