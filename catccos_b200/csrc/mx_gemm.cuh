@@ -32,7 +32,10 @@ constexpr int kMxFlagsPerChunk = kAgSubChunks + 1;   // data units + one scale-f
 struct alignas(64) MxRankArgs {
     CUtensorMap tmA;        // local activations  [m, K] bytes, box {128, BM}
     CUtensorMap tmAg;       // gathered activations [R*m, K] bytes in this PE's symmetric region
-    CUtensorMap tmB;        // transB=1: [N, K] box {128, BN};  transB=0: [K, N] box {128 (n), 128 (k)}
+    CUtensorMap tmB;        // transB=1: [N, K] box {128, BN} (pair kernel: {128, 128});  transB=0: [K, N] box {128 (n), 128 (k)}
+    CUtensorMap tmSfa;      // pair kernel: scale atoms as rows of 128 u32, box {128, 1}: local activations,
+    CUtensorMap tmSfag;     //              gathered activations (symmetric region),
+    CUtensorMap tmSfb;      //              weights
     const uint8_t *A;       // raw local activations (push source)
     const uint8_t *sfa;     // local scale atoms [ceil(m/128)][ceil(K/128)][512]
     const uint8_t *sfb;     // weight scale atoms [ceil(N/128)][ceil(K/128)][512]

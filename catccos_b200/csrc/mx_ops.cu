@@ -4,6 +4,8 @@
 #include <string.h>
 
 #include "mx_gemm.cuh"
+#include "mx_pair.cuh"
+#include <stdlib.h>
 #include "mx_quant.h"
 
 namespace cb {
@@ -25,6 +27,23 @@ static int encode_u8(const DriverApi *api, CUtensorMap *tm, const void *base, ui
     return CATCCOS_OK;
 }
 
+// scale atoms as a 2-D tensor: rows of 128 u32 (= one 512-byte atom), one atom per load
+static int encode_atoms(const DriverApi *api, CUtensorMap *tm, const void *base, uint64_t n_atoms) {
+    cuuint64_t dims[2] = {128, n_atoms};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, 1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = api->TensorMapEncodeTiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides,
+                                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (scale atoms) failed: %d (base=%p atoms=%llu)", static_cast<int>(r), base,
+                  (unsigned long long)n_atoms);
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 size_t mx_ag_symmetric_bytes(int world, int m, int n, int k) {
@@ -36,6 +55,27 @@ size_t mx_ag_symmetric_bytes(int world, int m, int n, int k) {
 
 size_t mx_ag_workspace_bytes(int m, int n, int k) {
     return align_up(sf_atoms_bytes(m, k), 1024) + align_up(sf_atoms_bytes(n, k), 1024);
+}
+
+template <typename TOut, bool B_MN>
+static int launch_pair_k(const MxParams &p, int grid, bool coop, cudaStream_t stream) {
+    auto kern = mx_pair_agmm_kernel<TOut, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxPairSmemBytes);
+    if (e == cudaSuccess) {
+        if (coop) {
+            void *args[] = {const_cast<MxParams *>(&p)};
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
+                                            kMxPairSmemBytes, stream);
+        } else {
+            kern<<<grid, kGemmThreads, kMxPairSmemBytes, stream>>>(p);
+            e = cudaGetLastError();
+        }
+    }
+    if (e != cudaSuccess) {
+        set_error("MX pair kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
 }
 
 template <typename TOut, bool B_MN>
@@ -99,6 +139,9 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
             return CATCCOS_ERR_INVALID;
         }
     }
+    bool use_pair = true;      // CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
+    if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = atoi(e) != 0;
+    const int kb4 = (k + 127) / 128;
     MxParams p;
     memset(&p, 0, sizeof(p));
     const int kblocks = k / 32;
@@ -120,8 +163,19 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
         if (rc) return rc;
         MxRankArgs &ra = p.ranks[l];
         if ((rc = encode_u8(api, &ra.tmA, a.A, k, m, MX_BK, BM))) return rc;
-        rc = trans_b ? encode_u8(api, &ra.tmB, a.B, k, n, MX_BK, BN) : encode_u8(api, &ra.tmB, a.B, n, k, 128, MX_BK);
+        rc = trans_b ? encode_u8(api, &ra.tmB, a.B, k, n, MX_BK, use_pair ? 128 : BN)
+                     : encode_u8(api, &ra.tmB, a.B, n, k, 128, MX_BK);
         if (rc) return rc;
+        if (use_pair) {
+            if ((rc = encode_atoms(api, &ra.tmSfa, sfa, static_cast<uint64_t>(mt) * kb4))) return rc;
+            if ((rc = encode_atoms(api, &ra.tmSfb, sfb, static_cast<uint64_t>((n + 127) / 128) * kb4))) return rc;
+            const int pe2 = t->emulated ? l : t->my_pe;
+            if (R > 1) {
+                if ((rc = encode_atoms(api, &ra.tmSfag, t->base[pe2] + sf_off, static_cast<uint64_t>(R) * mt * kb4))) return rc;
+            } else {
+                ra.tmSfag = ra.tmSfa;
+            }
+        }
         if (R > 1) {
             const int pe = t->emulated ? l : t->my_pe;
             if ((rc = encode_u8(api, &ra.tmAg, t->base[pe] + symm_off, k, static_cast<uint64_t>(R) * m, MX_BK, BM)))
@@ -152,9 +206,16 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
     p.trace = t->trace_dev;
-    const int grid = per_rank * n_local;
     const bool coop = n_local > 1;
     const bool b_mn = trans_b == 0;
+    if (use_pair && per_rank >= 2) {
+        p.ctas_per_rank = per_rank & ~1;
+        const int g2 = p.ctas_per_rank * n_local;
+        if (out_dtype == 27)
+            return b_mn ? launch_pair_k<__nv_bfloat16, true>(p, g2, coop, stream) : launch_pair_k<__nv_bfloat16, false>(p, g2, coop, stream);
+        return b_mn ? launch_pair_k<__half, true>(p, g2, coop, stream) : launch_pair_k<__half, false>(p, g2, coop, stream);
+    }
+    const int grid = per_rank * n_local;
     if (out_dtype == 27)
         return b_mn ? launch_k<__nv_bfloat16, true>(p, grid, coop, stream) : launch_k<__nv_bfloat16, false>(p, grid, coop, stream);
     return b_mn ? launch_k<__half, true>(p, grid, coop, stream) : launch_k<__half, false>(p, grid, coop, stream);
