@@ -31,7 +31,8 @@ constexpr int kSideSmemBytes = 32 * 1024;  // next to the GEMM stages: push stag
 constexpr int kPushLanesShared = kSideSmemBytes / kPushPieceBytes;   // lanes of a CTA that also runs the GEMM
 constexpr int kGemmSmemBytes =
     kStages * (kAStageBytes + kBStageBytes) + kSideSmemBytes + 1024 /*align*/ + 512 /*barriers*/;
-constexpr int kAgSubChunks = 8;             // an all-gather chunk (BM rows) is pushed as 8 units of 16 rows
+constexpr int kAgSubChunks = 32;            // an all-gather chunk (BM rows) is pushed as 32 units of 4 rows: many more
+                                            // units than pusher lanes, so the slab of the rank that needs it first goes first
 
 struct alignas(64) RankArgs {
     CUtensorMap tmA;    // A as passed by the caller: [rows, K], K innermost, box {BK, BM}

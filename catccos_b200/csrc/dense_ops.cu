@@ -6,6 +6,7 @@
 
 #include "gemm_fused.cuh"
 #include "gemm_pair.cuh"
+#include "gemm_pair_rs.cuh"
 #include "ptx.cuh"
 
 namespace cb {
@@ -54,10 +55,9 @@ static int launch_kernel(const FusedParams &p, int grid, bool cooperative, cudaS
     return CATCCOS_OK;
 }
 
-// CTA-pair (cta_group::2) variant of AllGather-Matmul
-template <typename T, bool B_MN>
-static int launch_pair(const FusedParams &p, int grid, bool cooperative, cudaStream_t stream) {
-    auto kern = pair_agmm_kernel<T, B_MN>;
+// CTA-pair (cta_group::2) kernels
+template <typename K>
+static int launch_pair_kernel(K kern, const FusedParams &p, int grid, bool cooperative, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
     if (e == cudaSuccess) {
         if (cooperative) {
@@ -74,6 +74,15 @@ static int launch_pair(const FusedParams &p, int grid, bool cooperative, cudaStr
         return CATCCOS_ERR_CUDA;
     }
     return CATCCOS_OK;
+}
+
+template <typename T, bool B_MN>
+static int launch_pair(int op, const FusedParams &p, int grid, bool coop, cudaStream_t stream) {
+    switch (op) {
+        case OP_AGMM: return launch_pair_kernel(pair_agmm_kernel<T, B_MN>, p, grid, coop, stream);
+        case OP_MMRS: return launch_pair_kernel(pair_rs_kernel<OP_MMRS, T, B_MN>, p, grid, coop, stream);
+        default: return launch_pair_kernel(pair_rs_kernel<OP_MMAR, T, B_MN>, p, grid, coop, stream);
+    }
 }
 
 template <int OP, typename T>
@@ -159,9 +168,9 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         }
     }
 
-    // AllGather-Matmul runs on CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
-    bool use_pair = (op == OP_AGMM);
-    if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = use_pair && atoi(e) != 0;
+    // the operators run on CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
+    bool use_pair = true;
+    if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = atoi(e) != 0;
     FusedParams p;
     memset(&p, 0, sizeof(p));
     const CUtensorMapDataType dt = dtype == 27 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -235,8 +244,10 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         p.ctas_per_rank = per_rank & ~1;
         p.push_ctas = 0;
         const int g2 = p.ctas_per_rank * n_local;
-        if (bf16) return b_mn ? launch_pair<__nv_bfloat16, true>(p, g2, coop, stream) : launch_pair<__nv_bfloat16, false>(p, g2, coop, stream);
-        return b_mn ? launch_pair<__half, true>(p, g2, coop, stream) : launch_pair<__half, false>(p, g2, coop, stream);
+        if (bf16)
+            return b_mn ? launch_pair<__nv_bfloat16, true>(op, p, g2, coop, stream)
+                        : launch_pair<__nv_bfloat16, false>(op, p, g2, coop, stream);
+        return b_mn ? launch_pair<__half, true>(op, p, g2, coop, stream) : launch_pair<__half, false>(op, p, g2, coop, stream);
     }
     const int grid = per_rank * n_local;
     switch (op) {

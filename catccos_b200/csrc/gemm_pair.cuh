@@ -107,21 +107,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer ----
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int t = pair; t < num_tiles && ok; t += pairs) {
-                int s, mi2, ni;
-                bool gathered;
-                decode(t, s, mi2, ni, gathered);
-                const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;    // this CTA's 128 rows
-                if (gathered && !p.compute_only && row_in_src < p.M) {
-                    const uint32_t w = kFlagOpBase + (s * mt_ag + (row_in_src / BM)) * kAgSubChunks;
-                    for (int q = 0; q < kAgSubChunks && ok; ++q)
-                        ok = wait_flag_ge(flag_ptr(p, rank, w + q), p.epoch, ctl, W_AG_CHUNK, w + q);
-                    if (!ok) break;
-                    fence_proxy_async();
-                }
+        // the whole warp polls the flags of a gathered chunk (one lane per unit), lane 0 issues the loads
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += pairs) {
+            int s, mi2, ni;
+            bool gathered;
+            decode(t, s, mi2, ni, gathered);
+            const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;    // this CTA's 128 rows
+            if (gathered && !p.compute_only && row_in_src < p.M) {
+                const uint32_t w = kFlagOpBase + (s * mt_ag + (row_in_src / BM)) * kAgSubChunks;
+                if (!(ok = wait_flags_warp(flag_ptr(p, rank, w), kAgSubChunks, p.epoch, ctl, W_AG_CHUNK, w))) break;
+                fence_proxy_async();
+            }
+            if (lane == 0) {
                 const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
                 const int a_row = (gathered ? s * p.M : 0) + row_in_src;
                 const int n_half = ni * BN + static_cast<int>(cr) * 128;         // this CTA's 128 columns of B
@@ -142,11 +141,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     }
                 }
             }
-            if (!ok) {
-                // loads already issued still land in shared memory; give them time (bounded)
-                const uint64_t t0 = globaltimer_ns();
-                while (globaltimer_ns() - t0 < 20000ull) {
-                }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+        }
+        if (!ok && lane == 0) {
+            // loads already issued still land in shared memory; give them time (bounded)
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 20000ull) {
             }
         }
     } else if (warp == 1) {

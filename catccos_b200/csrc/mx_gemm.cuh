@@ -117,8 +117,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
-    const uint32_t tmem_sfa = tmem_base + BN;        // 4 columns
-    const uint32_t tmem_sfb = tmem_base + BN + 4;    // 8 columns
+    // scale factors: 4 (A) + 8 (B) columns per K-step, four sets used in turn so that the copy for
+    // one K-step does not have to wait for the MMAs of the step before it
+    const uint32_t tmem_sf0 = tmem_base + BN;
 
     WaitCtl ctl;
     ctl.abort_smem = &sh->abort_flag;
@@ -209,6 +210,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
                     const uint32_t b_addr = a_addr + kMxAStage;
                     const uint32_t sf_addr = b_addr + kMxBStage;
                     // scale atoms: 32 rows x 16 B, 8-row groups 128 B apart, no swizzle
+                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * 16u;
+                    const uint32_t tmem_sfb = tmem_sfa + 4;
                     tmem_cp_32x128b_warpx4(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
                     tmem_cp_32x128b_warpx4(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
                     tmem_cp_32x128b_warpx4(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));

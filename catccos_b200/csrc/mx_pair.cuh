@@ -86,8 +86,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     cluster_sync();
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
-    const uint32_t tmem_sfa = tmem_base + BN;
-    const uint32_t tmem_sfb = tmem_base + BN + 4;
+    // scale factors: 4 (A) + 8 (B) columns per K-step, four sets used in turn so that the copy for
+    // one K-step does not have to wait for the MMAs of the step before it
+    const uint32_t tmem_sf0 = tmem_base + BN;
 
     WaitCtl ctl;
     ctl.abort_smem = &sh->abort_flag;
@@ -107,22 +108,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer ----
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int t = pair; t < num_tiles && ok; t += pairs) {
-                int s, mi2, ni;
-                bool gathered;
-                decode(t, s, mi2, ni, gathered);
-                const int chunk = mi2 * 2 + static_cast<int>(cr);       // this CTA's 128-row chunk of the source rank
-                const bool have_rows = chunk < mt;
-                if (gathered && !p.compute_only && have_rows) {
-                    const uint32_t w = kFlagOpBase + (s * mt + chunk) * kMxFlagsPerChunk;
-                    for (int q = 0; q < kMxFlagsPerChunk && ok; ++q)
-                        ok = wait_flag_ge(flagp(rank, w + q), p.epoch, ctl, W_MXAG, w + q);
-                    if (!ok) break;
-                    fence_proxy_async();
-                }
+        // the whole warp polls the flags of a gathered chunk (one lane per unit), lane 0 issues the loads
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += pairs) {
+            int s, mi2, ni;
+            bool gathered;
+            decode(t, s, mi2, ni, gathered);
+            const int chunk = mi2 * 2 + static_cast<int>(cr);       // this CTA's 128-row chunk of the source rank
+            const bool have_rows = chunk < mt;
+            if (gathered && !p.compute_only && have_rows) {
+                const uint32_t w = kFlagOpBase + (s * mt + chunk) * kMxFlagsPerChunk;
+                if (!(ok = wait_flags_warp(flagp(rank, w), kMxFlagsPerChunk, p.epoch, ctl, W_MXAG, w))) break;
+                fence_proxy_async();
+            }
+            if (lane == 0) {
                 const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
                 const CUtensorMap *tsfa = gathered ? &ra.tmSfag : &ra.tmSfa;
                 const int a_row = (gathered ? s * p.M : 0) + chunk * BM;
@@ -148,10 +148,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     if (second_b_atom) tma_load_2d_pair(ssf + 1024, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb4 + kb);
                 }
             }
-            if (!ok) {
-                const uint64_t t0 = globaltimer_ns();
-                while (globaltimer_ns() - t0 < 20000ull) {
-                }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+        }
+        if (!ok && lane == 0) {
+            const uint64_t t0 = globaltimer_ns();
+            while (globaltimer_ns() - t0 < 20000ull) {
             }
         }
     } else if (warp == 1) {
@@ -174,6 +175,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const uint32_t a_addr = smem_u32(smem_a + st * kMxPA);
                     const uint32_t b_addr = smem_u32(smem_b + st * kMxPB);
                     const uint32_t sf_addr = smem_u32(smem_sf + st * kMxPSf);
+                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * 16u;
+                    const uint32_t tmem_sfb = tmem_sfa + 4;
                     tmem_cp_32x128b_warpx4_pair(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
                     tmem_cp_32x128b_warpx4_pair(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
                     tmem_cp_32x128b_warpx4_pair(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));

@@ -339,6 +339,17 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t *flag, uint32_t expe
     return true;
 }
 
+// Whole warp: lane q waits for flags[q], q + 32, ... (< count); every lane gets true when all are up.
+__device__ __forceinline__ bool wait_flags_warp(const uint32_t *flags, int count, uint32_t expected, const WaitCtl &c,
+                                                int where, int index0) {
+    bool mine = true;
+    for (int q = threadIdx.x & 31; q < count && mine; q += 32)
+        mine = wait_flag_ge(flags + q, expected, c, where, index0 + q);
+    const bool all = __all_sync(0xffffffffu, mine);
+    __syncwarp();
+    return all;
+}
+
 // ---------------------------------------------------------------- helpers ----
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
