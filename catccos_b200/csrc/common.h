@@ -25,6 +25,9 @@ constexpr int kStages = 4;
 constexpr int kAStageBytes = BM * BK * 2;   // 16 KiB
 constexpr int kBStageBytes = BN * BK * 2;   // 32 KiB
 constexpr int kGemmThreads = 256;           // warp 0 TMA, 1 MMA, 2-5 epilogue, 6-7 comm
+constexpr int kPairAgThreads = 352;         // pair AllGather-Matmul kernels: warps 6-9 are one push lane each (a
+                                            // blocking bulk-copy wait stalls its whole warp, so lanes do not share one);
+                                            // warp 10 polls the arrival flags of the CTA's coming tiles
 constexpr int kPushPieceBytes = 8 * 1024;  // all-gather push: one staging piece per pusher lane
 constexpr int kPushLanes = 24;             // lanes (threads with a piece in flight) of a dedicated pusher CTA
 constexpr int kSideSmemBytes = 32 * 1024;  // next to the GEMM stages: push staging (AG-MM) or epilogue row staging
@@ -51,6 +54,7 @@ struct FusedParams {
                                       // 0: every CTA pushes from its comm warp next to its GEMM tiles
     int M, N, K;                      // AG-MM: M = rows held by one rank; MM-RS / MM-AR: M = total rows
     uint32_t epoch;
+    uint32_t entered_need;            // a peer's data region may be written once it has entered this epoch
     int compute_only;                 // measurement mode: no peer traffic, no flag waits (data left by an earlier launch)
     uint64_t timeout_ns;
     int *status;                      // cb::StatusWord[ST_WORDS], device memory

@@ -1,6 +1,7 @@
 // Host launchers of the f16/bf16 fused kernels: tensor maps, shape checks, launch.
 #include "dense_ops.h"
 
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -57,15 +58,15 @@ static int launch_kernel(const FusedParams &p, int grid, bool cooperative, cudaS
 
 // CTA-pair (cta_group::2) kernels
 template <typename K>
-static int launch_pair_kernel(K kern, const FusedParams &p, int grid, bool cooperative, cudaStream_t stream) {
+static int launch_pair_kernel(K kern, int threads, const FusedParams &p, int grid, bool cooperative, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
     if (e == cudaSuccess) {
         if (cooperative) {
             void *args[] = {const_cast<FusedParams *>(&p)};
-            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(threads), args,
                                             kPairSmemBytes, stream);
         } else {
-            kern<<<grid, kGemmThreads, kPairSmemBytes, stream>>>(p);
+            kern<<<grid, threads, kPairSmemBytes, stream>>>(p);
             e = cudaGetLastError();
         }
     }
@@ -79,9 +80,9 @@ static int launch_pair_kernel(K kern, const FusedParams &p, int grid, bool coope
 template <typename T, bool B_MN>
 static int launch_pair(int op, const FusedParams &p, int grid, bool coop, cudaStream_t stream) {
     switch (op) {
-        case OP_AGMM: return launch_pair_kernel(pair_agmm_kernel<T, B_MN>, p, grid, coop, stream);
-        case OP_MMRS: return launch_pair_kernel(pair_rs_kernel<OP_MMRS, T, B_MN>, p, grid, coop, stream);
-        default: return launch_pair_kernel(pair_rs_kernel<OP_MMAR, T, B_MN>, p, grid, coop, stream);
+        case OP_AGMM: return launch_pair_kernel(pair_agmm_kernel<T, B_MN>, kPairAgThreads, p, grid, coop, stream);
+        case OP_MMRS: return launch_pair_kernel(pair_rs_kernel<OP_MMRS, T, B_MN>, kGemmThreads, p, grid, coop, stream);
+        default: return launch_pair_kernel(pair_rs_kernel<OP_MMAR, T, B_MN>, kGemmThreads, p, grid, coop, stream);
     }
 }
 
@@ -94,18 +95,25 @@ static int launch_t(const FusedParams &p, int grid, bool coop, cudaStream_t s, b
     return bf16 ? launch_b<OP, __nv_bfloat16>(p, grid, coop, s, b_mn) : launch_b<OP, __half>(p, grid, coop, s, b_mn);
 }
 
-size_t dense_symmetric_bytes(int op, int world, int m, int n, int k) {
+// one half of the (double-buffered) data region, rounded up to the 1024-byte alignment of the halves
+static size_t dense_half_bytes(int op, int world, int m, int n, int k) {
     const size_t es = 2;
-    if (world <= 1) return 0;
+    size_t b = 0;
     switch (op) {
-        case OP_AGMM: return static_cast<size_t>(world) * m * k * es;
-        case OP_MMRS: return static_cast<size_t>(m) * n * es;
+        case OP_AGMM: b = static_cast<size_t>(world) * m * k * es; break;
+        case OP_MMRS: b = static_cast<size_t>(m) * n * es; break;
         case OP_MMAR: {
             const size_t mr = (m + world - 1) / world;
-            return 2 * static_cast<size_t>(world) * mr * n * es;
+            b = 2 * static_cast<size_t>(world) * mr * n * es;
+            break;
         }
     }
-    return 0;
+    return (b + 1023) / 1024 * 1024;
+}
+
+size_t dense_symmetric_bytes(int op, int world, int m, int n, int k) {
+    if (world <= 1) return 0;
+    return 2 * dense_half_bytes(op, world, m, n, k);
 }
 
 int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, const DenseArgs *args, void *symmetric,
@@ -168,6 +176,17 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         }
     }
 
+    // which half of the region this launch uses, and how far the peers must have come (see next_slot)
+    const uint32_t epoch = t->epoch + 1;
+    uint64_t sig = slot_sig(0x44454E5345ull, static_cast<uint64_t>(op));
+    sig = slot_sig(sig, static_cast<uint64_t>(dtype));
+    sig = slot_sig(sig, static_cast<uint64_t>(m));
+    sig = slot_sig(sig, static_cast<uint64_t>(n));
+    sig = slot_sig(sig, static_cast<uint64_t>(k));
+    sig = slot_sig(sig, symm_off);
+    const LaunchSlot slot = peek_slot(t, sig, epoch);
+    if (R > 1) symm_off += static_cast<uint64_t>(slot.half) * dense_half_bytes(op, R, m, n, k);
+
     // the operators run on CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
     bool use_pair = true;
     if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = atoi(e) != 0;
@@ -227,7 +246,8 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.M = m;
     p.N = n;
     p.K = k;
-    p.epoch = ++t->epoch;
+    p.epoch = epoch;
+    p.entered_need = slot.entered_need;
     p.compute_only = (t->debug_flags & 1u) ? 1 : 0;
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
@@ -236,11 +256,12 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     const bool coop = n_local > 1;
     const bool bf16 = dtype == 27;
     const bool b_mn = trans_b == 0;
+    if (use_pair && per_rank < 2) {
+        set_error("the CTA-pair kernel needs at least 2 CTAs per rank");
+        return CATCCOS_ERR_INVALID;
+    }
+    commit_slot(t, sig, epoch, slot);
     if (use_pair) {
-        if (per_rank < 2) {
-            set_error("the CTA-pair kernel needs at least 2 CTAs per rank");
-            return CATCCOS_ERR_INVALID;
-        }
         p.ctas_per_rank = per_rank & ~1;
         p.push_ctas = 0;
         const int g2 = p.ctas_per_rank * n_local;

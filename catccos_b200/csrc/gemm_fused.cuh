@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                     bool w = true;
                     if (remote) {
                         // the owner must have entered this epoch before its staging rows are overwritten
-                        w = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + tl.peer), p.epoch, ctl, W_ENTERED, tl.peer);
+                        w = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + tl.peer), p.entered_need, ctl, W_ENTERED, tl.peer);
                     } else {
                         // own rows: every peer's partial of this tile must have landed in my staging rows
                         for (int s = 0; s < R && w; ++s) {
@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                     const int r0 = chunk * BM + sub * (BM / kAgSubChunks);
                     const int r1 = min(p.M, r0 + BM / kAgSubChunks);
                     if (!((entered_ok >> d) & 1)) {
-                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d)))
+                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d)))
                             break;
                         entered_ok |= 1u << d;
                     }

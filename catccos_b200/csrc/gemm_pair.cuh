@@ -31,10 +31,11 @@ struct PairSmem {
     uint64_t push_bar[kPushLanesShared];
     uint32_t tmem_base;
     int abort_flag;
+    uint32_t tiles_ready;           // tiles of this CTA (in its own order) whose gathered rows are known to be in
 };
 
 template <typename T, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
     pair_agmm_kernel(const __grid_constant__ FusedParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -73,6 +74,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         mbar_init(&sh->drain, 1);
         for (int l = 0; l < kPushLanesShared; ++l) mbar_init(&sh->push_bar[l], 1);
         sh->abort_flag = 0;
+        sh->tiles_ready = 0;
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
@@ -107,19 +109,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer ----
-        // the whole warp polls the flags of a gathered chunk (one lane per unit), lane 0 issues the loads
-        uint32_t it = 0;
+        // lane 0 issues the loads; the arrival flags of gathered rows are polled ahead of it by warp 10
+        uint32_t it = 0, seq = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += pairs) {
+        uint64_t prod_wait_ns = 0;
+        for (int t = pair; t < num_tiles && ok; t += pairs, ++seq) {
             int s, mi2, ni;
             bool gathered;
             decode(t, s, mi2, ni, gathered);
             const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;    // this CTA's 128 rows
-            if (gathered && !p.compute_only && row_in_src < p.M) {
-                const uint32_t w = kFlagOpBase + (s * mt_ag + (row_in_src / BM)) * kAgSubChunks;
-                if (!(ok = wait_flags_warp(flag_ptr(p, rank, w), kAgSubChunks, p.epoch, ctl, W_AG_CHUNK, w))) break;
-                fence_proxy_async();
+            if (gathered && !p.compute_only && row_in_src < p.M && lane == 0) {
+                const uint64_t tw0 = p.trace ? globaltimer_ns() : 0;
+                ok = wait_smem_counter_gt(&sh->tiles_ready, seq, ctl, W_AG_CHUNK);
+                if (p.trace) {
+                    if (prod_wait_ns == 0) CB_TRACE(TR_PROD_WAIT_FIRST, tw0);
+                    prod_wait_ns += globaltimer_ns() - tw0 + 1;
+                }
             }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
             if (lane == 0) {
                 const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
                 const int a_row = (gathered ? s * p.M : 0) + row_in_src;
@@ -143,6 +151,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
         }
+        if (lane == 0) CB_TRACE(TR_PROD_WAIT_NS, prod_wait_ns);
         if (!ok && lane == 0) {
             // loads already issued still land in shared memory; give them time (bounded)
             const uint64_t t0 = globaltimer_ns();
@@ -156,14 +165,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             constexpr uint32_t idesc = make_idesc_f16(fmt, BM2, BN, 0, B_MN ? 1 : 0);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
+            uint64_t wait_tmem = 0, wait_smem = 0;
             for (int t = pair; t < num_tiles && ok; t += pairs) {
                 const uint32_t acc = tcount & 1;
+                const uint64_t tm0 = p.trace ? globaltimer_ns() : 0;
                 if (!(ok = mbar_wait(&sh->tmem_empty[acc], ((tcount >> 1) & 1) ^ 1, ctl, W_TMEM_EMPTY))) break;
+                if (p.trace) wait_tmem += globaltimer_ns() - tm0;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % kPStages;
+                    const uint64_t ts0 = p.trace ? globaltimer_ns() : 0;
                     if (!(ok = mbar_wait(&sh->full[st], (it / kPStages) & 1, ctl, W_MBAR_FULL))) break;
+                    if (p.trace) wait_smem += globaltimer_ns() - ts0;
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + st * kPAStage);
                     const uint32_t b_addr = smem_u32(smem_b + st * kPBStage);
@@ -183,6 +197,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 umma_commit_pair(mapa_cluster(smem_u32(&sh->tmem_full[acc]), 1));
                 ++tcount;
             }
+            CB_TRACE(TR_MMA_WAIT_TMEM_NS, wait_tmem);
+            CB_TRACE(TR_MMA_WAIT_SMEM_NS, wait_smem);
             CB_TRACE(TR_TILES, tcount);
             if (!ok) {
                 umma_commit_pair(mapa_cluster(smem_u32(&sh->drain), 0));
@@ -232,15 +248,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty[acc]), 0));
             ++tcount;
         }
-    } else if (warp == 6) {
-        // ------------------------------------------------------ all-gather push ----
-        const int ctid = lane;
+    } else if (warp == 10) {
+        // ------------------------------------------------------------ flag scout ----
+        // walks this CTA's tiles ahead of the producer and waits (whole warp, one lane per unit) for
+        // the rows of every gathered chunk; the count of cleared tiles goes to shared memory
         if (R > 1 && !p.compute_only) {
-            if (cta == 0 && ctid < R && ctid != rank) {
-                fence_sys();
-                st_release_sys(flag_ptr(p, ctid, kFlagEntered + rank), p.epoch);
+            uint32_t seq = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += pairs, ++seq) {
+                int s, mi2, ni;
+                bool gathered;
+                decode(t, s, mi2, ni, gathered);
+                const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;
+                if (gathered && row_in_src < p.M) {
+                    const uint32_t w = kFlagOpBase + (s * mt_ag + (row_in_src / BM)) * kAgSubChunks;
+                    if (!(ok = wait_flags_warp(flag_ptr(p, rank, w), kAgSubChunks, p.epoch, ctl, W_AG_CHUNK, w))) break;
+                    fence_proxy_async_global();     // rows seen through the flags -> the producer's TMA loads
+                }
+                if (lane == 0) st_release_cta_smem(&sh->tiles_ready, seq + 1);
             }
-            if (ctid < kPushLanesShared) {
+        }
+    } else {
+        // ------------------------------------------------------ all-gather push ----
+        // warps 6..9: one push lane per warp
+        const int ctid = warp - 6;
+        if (R > 1 && !p.compute_only) {
+            if (warp == 6 && cta == 0 && lane < R && lane != rank) {
+                fence_sys();
+                st_release_sys(flag_ptr(p, lane, kFlagEntered + rank), p.epoch);
+            }
+            __syncwarp();
+            if (lane == 0 && ctid < kPushLanesShared) {
                 // same units, order and flags as the one-CTA kernel: destination rank-1 first, units of
                 // BM/kAgSubChunks rows, one flag per unit, every lane owns whole units
                 const int units_per_dest = mt_ag * kAgSubChunks;
@@ -253,6 +291,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 bool ok = true;
                 uint32_t entered_ok = 0;
                 uint32_t piece = 0;
+                uint64_t entered_wait_ns = 0;
+                if (ctid == 0) CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
                 for (int u = lane_id; u < total && ok; u += n_lanes) {
                     const int jj = u / units_per_dest;
                     const int d = (rank + R - 1 - jj) % R;
@@ -261,7 +301,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const int r0 = chunk * BM + sub * (BM / kAgSubChunks);
                     const int r1 = min(p.M, r0 + BM / kAgSubChunks);
                     if (!((entered_ok >> d) & 1)) {
-                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d))) break;
+                        const uint64_t te0 = p.trace ? globaltimer_ns() : 0;
+                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d))) break;
+                        if (p.trace) entered_wait_ns += globaltimer_ns() - te0;
                         entered_ok |= 1u << d;
                     }
                     if (r1 > r0) {
@@ -280,11 +322,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     }
                     if (!ok) break;
                     bulk_wait<0>();
-                    fence_proxy_async();
+                    fence_proxy_async_global();
                     fence_sys();
                     st_release_sys(flag_ptr(p, d, kFlagOpBase + (rank * mt_ag + chunk) * kAgSubChunks + sub), p.epoch);
                 }
                 bulk_wait<0>();
+                if (ctid == 0) {
+                    CB_TRACE(TR_PUSH_END, globaltimer_ns());
+                    CB_TRACE(TR_EPI_WAIT_NS, entered_wait_ns);     // time this lane waited for peers to enter
+                }
             }
         }
     }

@@ -215,7 +215,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         auto publish = [&](bool everything) -> bool {
             if (!pend) return true;
             if (everything) bulk_wait<0>(); else bulk_wait<BN / 128>();
-            fence_proxy_async();
+            fence_proxy_async_global();
             if (!epi.sync(ctl)) return false;
             if (etid == 0) {
                 fence_sys();
@@ -255,7 +255,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 if (etid == 0) {
                     bool w = true;
                     if (remote) {
-                        w = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d);
+                        w = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d);
                     } else {
                         for (int s = 0; s < R && w; ++s) {
                             if (s == rank) continue;
@@ -333,7 +333,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         *reinterpret_cast<uint4 *>(my_row_smem + (c & 3) * 64 + g * 16) =
                             make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
                     if ((c & 3) == 3) {
-                        fence_proxy_async();
+                        fence_proxy_async_smem();
                         const int colh = n0 + (c >> 2) * 128;
                         if (row_ok && colh < p.N) {
                             const uint32_t len = static_cast<uint32_t>(min(128, p.N - colh)) * sizeof(T);

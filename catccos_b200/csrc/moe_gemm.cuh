@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_grouped_gemm_kernel(const
                     for (int g = 0; g < 8; ++g)
                         *reinterpret_cast<uint4 *>(my_row + g * 16) = make_uint4(
                             pk[h * 32 + g * 4], pk[h * 32 + g * 4 + 1], pk[h * 32 + g * 4 + 2], pk[h * 32 + g * 4 + 3]);
-                    fence_proxy_async();
+                    fence_proxy_async_smem();
                     if (row_ok) {
                         bulk_store(dst + h * 64, my_row, 128);
                         bulk_commit();
@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_grouped_gemm_kernel(const
         }
         if (MODE == 2) {
             bulk_wait<0>();
-            fence_proxy_async();
+            fence_proxy_async_global();
         }
     }
 

@@ -50,6 +50,7 @@ struct MxParams {
     int world, rank_base, n_local, ctas_per_rank;
     int M, N, K;              // M = rows held by one rank
     uint32_t epoch;
+    uint32_t entered_need;     // a peer's data region may be written once it has entered this epoch
     int compute_only;
     uint64_t timeout_ns;
     int *status;
@@ -319,7 +320,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
                         dst = p.heap_base[d] + p.sf_off + (static_cast<size_t>(rank) * mt + chunk) * kb4 * 512;
                     }
                     if (!((entered_ok >> d) & 1)) {
-                        if (!(ok = wait_flag_ge(flagp(rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d))) break;
+                        if (!(ok = wait_flag_ge(flagp(rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d))) break;
                         entered_ok |= 1u << d;
                     }
                     for (size_t off = 0; off < bytes && ok; off += kPushPieceBytes, ++piece) {

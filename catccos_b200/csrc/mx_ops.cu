@@ -46,11 +46,16 @@ static int encode_atoms(const DriverApi *api, CUtensorMap *tm, const void *base,
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// one half of the (double-buffered) gathered region: codes, then scale atoms
+static size_t mx_ag_half_bytes(int world, int m, int k) {
+    const size_t data = align_up(static_cast<size_t>(world) * m * k, 1024);
+    return align_up(data + static_cast<size_t>(world) * sf_atoms_bytes(m, k), 1024);
+}
+
 size_t mx_ag_symmetric_bytes(int world, int m, int n, int k) {
     (void)n;
     if (world <= 1) return 0;
-    const size_t data = align_up(static_cast<size_t>(world) * m * k, 1024);
-    return data + static_cast<size_t>(world) * sf_atoms_bytes(m, k);
+    return 2 * mx_ag_half_bytes(world, m, k);
 }
 
 size_t mx_ag_workspace_bytes(int m, int n, int k) {
@@ -64,10 +69,10 @@ static int launch_pair_k(const MxParams &p, int grid, bool coop, cudaStream_t st
     if (e == cudaSuccess) {
         if (coop) {
             void *args[] = {const_cast<MxParams *>(&p)};
-            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kPairAgThreads), args,
                                             kMxPairSmemBytes, stream);
         } else {
-            kern<<<grid, kGemmThreads, kMxPairSmemBytes, stream>>>(p);
+            kern<<<grid, kPairAgThreads, kMxPairSmemBytes, stream>>>(p);
             e = cudaGetLastError();
         }
     }
@@ -125,6 +130,9 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
     const int mt = (m + BM - 1) / BM;
     const size_t need = mx_ag_symmetric_bytes(R, m, n, k);
     uint64_t symm_off = 0, sf_off = 0;
+    const uint32_t epoch = t->epoch + 1;
+    LaunchSlot slot{0, epoch};
+    uint64_t sig = 0;
     if (R > 1) {
         uint8_t *sp = static_cast<uint8_t *>(symmetric);
         uint8_t *b = t->base[t->my_pe];
@@ -133,6 +141,12 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
             return CATCCOS_ERR_INVALID;
         }
         symm_off = static_cast<uint64_t>(sp - b);
+        sig = slot_sig(0x4D584147ull, static_cast<uint64_t>(m));
+        sig = slot_sig(sig, static_cast<uint64_t>(n));
+        sig = slot_sig(sig, static_cast<uint64_t>(k));
+        sig = slot_sig(sig, symm_off);
+        slot = peek_slot(t, sig, epoch);      // which half of the region this launch uses
+        symm_off += static_cast<uint64_t>(slot.half) * mx_ag_half_bytes(R, m, k);
         sf_off = symm_off + align_up(static_cast<size_t>(R) * m * k, 1024);
         if (kFlagOpBase + static_cast<size_t>(R) * mt * kMxFlagsPerChunk > kFlagWords) {
             set_error("shape needs more flags than the flag region holds");
@@ -201,13 +215,15 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
     p.M = m;
     p.N = n;
     p.K = k;
-    p.epoch = ++t->epoch;
+    p.epoch = epoch;
+    p.entered_need = slot.entered_need;
     p.compute_only = (t->debug_flags & 1u) ? 1 : 0;
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
     p.trace = t->trace_dev;
     const bool coop = n_local > 1;
     const bool b_mn = trans_b == 0;
+    commit_slot(t, sig, epoch, slot);
     if (use_pair && per_rank >= 2) {
         p.ctas_per_rank = per_rank & ~1;
         const int g2 = p.ctas_per_rank * n_local;

@@ -28,10 +28,11 @@ struct MxPairSmem {
     uint64_t push_bar[kMxPushLanes];
     uint32_t tmem_base;
     int abort_flag;
+    uint32_t tiles_ready;           // tiles of this CTA (in its own order) whose gathered rows and scales are in
 };
 
 template <typename TOut, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
     mx_pair_agmm_kernel(const __grid_constant__ MxParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -69,6 +70,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         mbar_init(&sh->drain, 1);
         for (int l = 0; l < kMxPushLanes; ++l) mbar_init(&sh->push_bar[l], 1);
         sh->abort_flag = 0;
+        sh->tiles_ready = 0;
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
@@ -108,20 +110,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer ----
-        // the whole warp polls the flags of a gathered chunk (one lane per unit), lane 0 issues the loads
-        uint32_t it = 0;
+        // lane 0 issues the loads; the arrival flags of gathered rows are polled ahead of it by warp 10
+        uint32_t it = 0, seq = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += pairs) {
+        for (int t = pair; t < num_tiles && ok; t += pairs, ++seq) {
             int s, mi2, ni;
             bool gathered;
             decode(t, s, mi2, ni, gathered);
             const int chunk = mi2 * 2 + static_cast<int>(cr);       // this CTA's 128-row chunk of the source rank
             const bool have_rows = chunk < mt;
-            if (gathered && !p.compute_only && have_rows) {
-                const uint32_t w = kFlagOpBase + (s * mt + chunk) * kMxFlagsPerChunk;
-                if (!(ok = wait_flags_warp(flagp(rank, w), kMxFlagsPerChunk, p.epoch, ctl, W_MXAG, w))) break;
-                fence_proxy_async();
+            if (gathered && !p.compute_only && have_rows && lane == 0) {
+                ok = wait_smem_counter_gt(&sh->tiles_ready, seq, ctl, W_MXAG);
             }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
             if (lane == 0) {
                 const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
                 const CUtensorMap *tsfa = gathered ? &ra.tmSfag : &ra.tmSfa;
@@ -244,15 +246,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             }
             ++tcount;
         }
-    } else if (warp == 6) {
-        // ------------------------------------------------------------------ push ----
-        const int ctid = lane;
+    } else if (warp == 10) {
+        // ------------------------------------------------------------ flag scout ----
+        // walks this CTA's tiles ahead of the producer and waits (whole warp, one lane per unit) for
+        // the rows and scales of every gathered chunk; the count of cleared tiles goes to shared memory
         if (R > 1 && !p.compute_only) {
-            if (cta == 0 && ctid < R && ctid != rank) {
-                fence_sys();
-                st_release_sys(flagp(ctid, kFlagEntered + rank), p.epoch);
+            uint32_t seq = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += pairs, ++seq) {
+                int s, mi2, ni;
+                bool gathered;
+                decode(t, s, mi2, ni, gathered);
+                const int chunk = mi2 * 2 + static_cast<int>(cr);
+                if (gathered && chunk < mt) {
+                    const uint32_t w = kFlagOpBase + (s * mt + chunk) * kMxFlagsPerChunk;
+                    if (!(ok = wait_flags_warp(flagp(rank, w), kMxFlagsPerChunk, p.epoch, ctl, W_MXAG, w))) break;
+                    fence_proxy_async_global();     // rows seen through the flags -> the producer's TMA loads
+                }
+                if (lane == 0) st_release_cta_smem(&sh->tiles_ready, seq + 1);
             }
-            if (ctid < kMxPushLanes) {
+        }
+    } else {
+        // ------------------------------------------------------------------ push ----
+        // warps 6..9: one push lane per warp
+        const int ctid = warp - 6;
+        if (R > 1 && !p.compute_only) {
+            if (warp == 6 && cta == 0 && lane < R && lane != rank) {
+                fence_sys();
+                st_release_sys(flagp(lane, kFlagEntered + rank), p.epoch);
+            }
+            __syncwarp();
+            if (lane == 0 && ctid < kMxPushLanes) {
                 const int units_per_dest = mt * kMxFlagsPerChunk;
                 const int total = (R - 1) * units_per_dest;
                 const size_t row_bytes = static_cast<size_t>(p.K);
@@ -283,7 +307,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         dst = p.heap_base[d] + p.sf_off + (static_cast<size_t>(rank) * mt + chunk) * kb4 * 512;
                     }
                     if (!((entered_ok >> d) & 1)) {
-                        if (!(ok = wait_flag_ge(flagp(rank, kFlagEntered + d), p.epoch, ctl, W_ENTERED, d))) break;
+                        if (!(ok = wait_flag_ge(flagp(rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d))) break;
                         entered_ok |= 1u << d;
                     }
                     for (size_t off = 0; off < bytes && ok; off += kPushPieceBytes, ++piece) {
@@ -297,7 +321,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     }
                     if (!ok) break;
                     bulk_wait<0>();
-                    fence_proxy_async();
+                    fence_proxy_async_global();
                     fence_sys();
                     st_release_sys(flagp(d, kFlagOpBase + (rank * mt + chunk) * kMxFlagsPerChunk + sub), p.epoch);
                 }

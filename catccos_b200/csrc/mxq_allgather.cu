@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kQagThreads) mxq_allgather_kernel(const QagPar
             }
             if (!ok) break;
             bulk_wait<0>();
-            fence_proxy_async();
+            fence_proxy_async_global();
             fence_sys();
             st_release_sys(flagp(d, kFlagOpBase + rank * units + un), p.epoch);
         }

@@ -144,6 +144,10 @@ __device__ __forceinline__ void bulk_wait() {
 // Orders earlier generic-proxy accesses (including acquired remote writes) before
 // later async-proxy (TMA) accesses of the same memory.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// the same, restricted to one state space: shared-memory writes of this thread before a bulk copy
+// reads them, or global memory seen through flags before TMA reads it
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 // --------------------------------------------------------------- tcgen05 ----
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t ncols) {
@@ -337,6 +341,26 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t *flag, uint32_t expe
         }
     }
     return true;
+}
+
+// Bounded spin until a counter in shared memory, advanced by another warp of the CTA, exceeds idx.
+__device__ __forceinline__ bool wait_smem_counter_gt(const uint32_t *ctr, uint32_t idx, const WaitCtl &c, int where) {
+    uint32_t spins = 0, seen;
+    for (;;) {
+        asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(ctr)) : "memory");
+        if (seen > idx) return true;
+        if ((++spins & 255u) == 0) {
+            if (*c.abort_smem) return false;
+            if (globaltimer_ns() > c.deadline_ns) {
+                report_failure(c, ERR_FLAG_TIMEOUT, where, static_cast<int>(idx), static_cast<int>(idx) + 1,
+                               static_cast<int>(seen));
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void st_release_cta_smem(uint32_t *ctr, uint32_t v) {
+    asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(ctr)), "r"(v) : "memory");
 }
 
 // Whole warp: lane q waits for flags[q], q + 32, ... (< count); every lane gets true when all are up.

@@ -58,6 +58,10 @@ struct Team {
     uint64_t timeout_ns = 10ull * 1000 * 1000 * 1000;
     unsigned long long *trace_dev = nullptr;   // optional per-CTA trace buffer (catccos_debug_set_trace)
     uint32_t debug_flags = 0;      // bit 0: compute-only launches (exposed-communication measurement)
+    // double-buffered operator regions (see next_slot)
+    uint64_t last_sig = 0;
+    uint32_t last_sig_epoch = 0;
+    int last_half = 0;
     // host rendezvous
     int sock = -1;
     std::string sock_prefix;
@@ -65,6 +69,36 @@ struct Team {
     struct Pending { int type; int from; uint32_t seq; int fd; };
     std::vector<Pending> pending;
 };
+
+// The dense and MXFP8 operators keep two copies ("halves") of their symmetric data region and
+// alternate between them when the same operator is launched back to back with the same shape and
+// buffer.  A rank may then write into a peer's half as soon as that peer has ENTERED the previous
+// launch (which, in stream order, means it has finished the launch before that one, the last
+// reader of this half); otherwise it has to wait until the peer has entered this launch.  Ranks
+// that run ahead or behind by up to one launch no longer stall one another.
+struct LaunchSlot {
+    int half;                // which half this launch uses
+    uint32_t entered_need;   // peers must have entered this epoch before their half is overwritten
+};
+inline LaunchSlot peek_slot(const Team *t, uint64_t sig, uint32_t epoch) {
+    LaunchSlot s;
+    if (sig == t->last_sig && t->last_sig_epoch + 1 == epoch) {
+        s.half = t->last_half ^ 1;
+        s.entered_need = epoch - 1;
+    } else {
+        s.half = 0;
+        s.entered_need = epoch;
+    }
+    return s;
+}
+// called once nothing can stop the launch any more: consumes the epoch and records the slot
+inline void commit_slot(Team *t, uint64_t sig, uint32_t epoch, const LaunchSlot &s) {
+    t->epoch = epoch;
+    t->last_sig = sig;
+    t->last_sig_epoch = epoch;
+    t->last_half = s.half;
+}
+inline uint64_t slot_sig(uint64_t h, uint64_t v) { return (h ^ v) * 0x9E3779B97F4A7C15ull + 0x632BE59BD9B4E019ull; }
 
 Team *team();                       // the process-wide team, nullptr before init
 int team_init(int my_pe, int n_pes, uint64_t local_mem_size, const char *ip_port);

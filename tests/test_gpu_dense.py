@@ -73,6 +73,54 @@ def test_matmul_reduce_scatter(world, trans_b, m, n, k):
         assert_reduced_close(outs[r], [p[r * mr:(r + 1) * mr] for p in partials], k, TOL, f"mmrs rank {r}")
 
 
+@pytest.mark.parametrize("comm_name", ["ALLGATHER_MATMUL", "MATMUL_REDUCE_SCATTER"])
+def test_back_to_back_launches_with_new_inputs(comm_name):
+    """Three launches of one operator without a sync in between, each with its own inputs: the
+    operator alternates between the two halves of its symmetric region, and a launch may start
+    writing a peer's half while that peer still reads the other one."""
+    rt = _rt()
+    world, k, n = 4, 192, 520
+    comm = getattr(rt, comm_name)
+    ag = comm_name == "ALLGATHER_MATMUL"
+    m = 320 if ag else 1024
+    til = rt.tiling(m, k, n, world)
+    need = rt.symmetric_bytes(comm, rt.BF16, til)
+    rounds = []
+    for i in range(3):
+        if ag:
+            a, b = inputs.allgather_matmul_inputs(world, m, k, n, torch.bfloat16)
+        else:
+            a, b = inputs.matmul_reduce_scatter_inputs(world, m, k, n, torch.bfloat16)
+        a = [x.roll(7 * i, 0) * (-1) ** i for x in a]     # the generators seed by rank only: make the launches differ
+        rounds.append((a, b))
+    out_shape = (world * m, n) if ag else (m // world, n)
+    with rt.emulated_team(world, max(need, 1 << 20)):
+        symm = rt.shmem_malloc(max(need, 1024))
+        outs = []
+        keep = []
+        for a, b in rounds:
+            a_d = [dev(x) for x in a]
+            b_d = [dev(x) for x in b]
+            c_d = [torch.full(out_shape, float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+            rt.launch_emulated(comm, a_d, b_d, c_d, symm, til, trans_b=0)
+            keep.append((a_d, b_d))
+            outs.append(c_d)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+        outs = [[c.cpu() for c in c_d] for c_d in outs]
+    for i, (a, b) in enumerate(rounds):
+        if ag:
+            gold = dense.golden_allgather_matmul(a, b)
+            for r in range(world):
+                assert_close_to_golden(outs[i][r], gold[r], k, TOL, f"launch {i} rank {r}")
+        else:
+            partials = [dense.matmul_fp32(x, y) for x, y in zip(a, b)]
+            mr = m // world
+            for r in range(world):
+                assert_reduced_close(outs[i][r], [p[r * mr:(r + 1) * mr] for p in partials], k, TOL,
+                                     f"launch {i} rank {r}")
+
+
 @pytest.mark.parametrize("world,m,n,k,dtype", [
     (2, 512, 2048, 1024, torch.float16),      # benchmark configuration 1
     (4, 300, 264, 128, torch.float16),        # ragged rows per rank
