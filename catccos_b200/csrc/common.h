@@ -61,6 +61,18 @@ struct FusedParams {
     unsigned long long *trace;        // optional: kTraceSlots %globaltimer stamps per CTA (nullptr = off)
 };
 
+// Output tensor maps of the pair reduce-scatter kernel, per local rank: box {64 columns, 32 rows},
+// 128-byte swizzle.  out[d]: d == this rank -> its rows of the operator's output; d != rank -> this
+// rank's slot of rank d's staging rows.  fin[d] (Matmul-AllReduce): this rank's rows of rank d's
+// "final" region.  Every map covers exactly the rows that exist, so ragged tiles are clipped by TMA.
+struct alignas(64) RsMaps {
+    CUtensorMap out[kMaxRanks];
+    CUtensorMap fin[kMaxRanks];
+};
+struct RsMapsAll {
+    RsMaps r[kMaxRanks];      // indexed by LOCAL rank like FusedParams::ranks
+};
+
 // Per-CTA trace slots (nanoseconds of %globaltimer).
 enum TraceSlot : int {
     TR_START = 0, TR_END = 1,

@@ -1,6 +1,7 @@
 // Host launchers of the f16/bf16 fused kernels: tensor maps, shape checks, launch.
 #include "dense_ops.h"
 
+#include <algorithm>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -77,12 +78,33 @@ static int launch_pair_kernel(K kern, int threads, const FusedParams &p, int gri
     return CATCCOS_OK;
 }
 
+template <typename K>
+static int launch_pair_rs_kernel(K kern, const FusedParams &p, const RsMapsAll &maps, int grid, bool cooperative,
+                                 cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+    if (e == cudaSuccess) {
+        if (cooperative) {
+            void *args[] = {const_cast<FusedParams *>(&p), const_cast<RsMapsAll *>(&maps)};
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
+                                            kPairSmemBytes, stream);
+        } else {
+            kern<<<grid, kGemmThreads, kPairSmemBytes, stream>>>(p, maps);
+            e = cudaGetLastError();
+        }
+    }
+    if (e != cudaSuccess) {
+        set_error("pair reduce-scatter kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
 template <typename T, bool B_MN>
-static int launch_pair(int op, const FusedParams &p, int grid, bool coop, cudaStream_t stream) {
+static int launch_pair(int op, const FusedParams &p, const RsMapsAll &maps, int grid, bool coop, cudaStream_t stream) {
     switch (op) {
         case OP_AGMM: return launch_pair_kernel(pair_agmm_kernel<T, B_MN>, kPairAgThreads, p, grid, coop, stream);
-        case OP_MMRS: return launch_pair_kernel(pair_rs_kernel<OP_MMRS, T, B_MN>, kGemmThreads, p, grid, coop, stream);
-        default: return launch_pair_kernel(pair_rs_kernel<OP_MMAR, T, B_MN>, kGemmThreads, p, grid, coop, stream);
+        case OP_MMRS: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMRS, T, B_MN>, p, maps, grid, coop, stream);
+        default: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMAR, T, B_MN>, p, maps, grid, coop, stream);
     }
 }
 
@@ -260,15 +282,47 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         set_error("the CTA-pair kernel needs at least 2 CTAs per rank");
         return CATCCOS_ERR_INVALID;
     }
+    // output tensor maps of the pair reduce-scatter kernel (see RsMaps)
+    static thread_local RsMapsAll maps;
+    if (use_pair && op != OP_AGMM) {
+        const int mr = (op == OP_MMAR) ? (m + R - 1) / R : m / R;
+        auto rows_valid = [&](int d) { return std::min(m, (d + 1) * mr) - d * mr; };
+        const size_t row_b = static_cast<size_t>(n) * 2;
+        for (int l = 0; l < n_local; ++l) {
+            const int pe = t->emulated ? l : t->my_pe;
+            RsMaps &mp = maps.r[l];
+            for (int d = 0; d < R; ++d) {
+                const int rv_d = rows_valid(d), rv_me = rows_valid(pe);
+                if (d == pe) {
+                    if (rv_me <= 0) continue;
+                    uint8_t *base = static_cast<uint8_t *>(args[l].C) + (op == OP_MMAR ? static_cast<size_t>(pe) * mr * row_b : 0);
+                    int rc = encode_2d(api, &mp.out[d], dt, base, n, rv_me, row_b, 64, 32);
+                    if (rc) return rc;
+                    continue;
+                }
+                if (rv_d > 0) {
+                    // this rank's slot of rank d's staging rows (compute-only measurement: of its own)
+                    uint8_t *base = t->base[p.compute_only ? pe : d] + symm_off + static_cast<size_t>(pe) * mr * row_b;
+                    int rc = encode_2d(api, &mp.out[d], dt, base, n, rv_d, row_b, 64, 32);
+                    if (rc) return rc;
+                }
+                if (op == OP_MMAR && rv_me > 0) {
+                    uint8_t *base = t->base[d] + symm_off + (static_cast<size_t>(R) * mr + static_cast<size_t>(pe) * mr) * row_b;
+                    int rc = encode_2d(api, &mp.fin[d], dt, base, n, rv_me, row_b, 64, 32);
+                    if (rc) return rc;
+                }
+            }
+        }
+    }
     commit_slot(t, sig, epoch, slot);
     if (use_pair) {
         p.ctas_per_rank = per_rank & ~1;
         p.push_ctas = 0;
         const int g2 = p.ctas_per_rank * n_local;
         if (bf16)
-            return b_mn ? launch_pair<__nv_bfloat16, true>(op, p, g2, coop, stream)
-                        : launch_pair<__nv_bfloat16, false>(op, p, g2, coop, stream);
-        return b_mn ? launch_pair<__half, true>(op, p, g2, coop, stream) : launch_pair<__half, false>(op, p, g2, coop, stream);
+            return b_mn ? launch_pair<__nv_bfloat16, true>(op, p, maps, g2, coop, stream)
+                        : launch_pair<__nv_bfloat16, false>(op, p, maps, g2, coop, stream);
+        return b_mn ? launch_pair<__half, true>(op, p, maps, g2, coop, stream) : launch_pair<__half, false>(op, p, maps, g2, coop, stream);
     }
     const int grid = per_rank * n_local;
     switch (op) {

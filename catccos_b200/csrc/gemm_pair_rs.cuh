@@ -2,10 +2,10 @@
 //
 // Main loop of the pair AllGather-Matmul kernel (256 x 256 tile per pair, every CTA loads its own
 // 128 rows of A and 128 columns of B, accumulator of its 128 rows in its own TMEM); each CTA's
-// epilogue then treats its 128 x 256 half exactly as the one-CTA kernel treats a tile: a partial
-// half-tile goes to the owner's staging rows as 256-byte bulk row stores followed by one flag,
-// the own rows are reduced in fixed rank order (own fp32 accumulator first) once every peer's
-// flag for that half-tile is up.  Flag words and symmetric layout are the one-CTA kernel's, so
+// epilogue then treats its 128 x 256 half as the one-CTA kernel treats a tile: a partial
+// half-tile goes to the owner's staging rows (tiled TMA stores, 32 rows x 64 columns each)
+// followed by one flag, the own rows are reduced in fixed rank order (own fp32 accumulator
+// first) once every peer's flag for that half-tile is up.  Flag words and symmetric layout are the one-CTA kernel's, so
 // both kernels serve the same buffers.
 #pragma once
 #include <type_traits>
@@ -26,12 +26,12 @@ struct PairRsSmem {
     uint64_t epi_bar;               // the CTA's 128 epilogue threads
     uint32_t tmem_base;
     int abort_flag;
-    int epi_ok;
+    int epi_ok[2];                  // verdicts of the epilogue's peer checks, used in turn
 };
 
 template <int OP, typename T, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-    pair_rs_kernel(const __grid_constant__ FusedParams p) {
+    pair_rs_kernel(const __grid_constant__ FusedParams p, const __grid_constant__ RsMapsAll maps) {
     static_assert(OP == OP_MMRS || OP == OP_MMAR, "reduce-scatter family only");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -40,7 +40,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     uint8_t *smem_side = smem + kPStages * (kPAStage + kPBStage);
     PairRsSmem *sh = reinterpret_cast<PairRsSmem *>(smem_side + kSideSmemBytes);
     static_assert(sizeof(PairRsSmem) <= 512, "barrier block outgrew its budget");
-    static_assert(BM * 256 <= kSideSmemBytes, "epilogue row staging");
+    static_assert(4 * 2 * 32 * 128 <= kSideSmemBytes, "epilogue staging: 4 warps x 2 buffers x 32 rows x 128 B");
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -52,6 +52,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int rank = p.rank_base + lrank;
     const int R = p.world;
     const RankArgs &ra = p.ranks[lrank];
+    const RsMaps &mp = maps.r[lrank];
     const int mr = rows_per_rank<OP>(p);                        // rows owned by one rank
     const int nt = ceil_div(p.N, BN);
     const int mt2 = ceil_div(mr, BM2);                          // pair tiles per owner along M
@@ -72,7 +73,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         mbar_init(&sh->drain, 1);
         mbar_init(&sh->epi_bar, 128);
         sh->abort_flag = 0;
-        sh->epi_ok = 1;
+        sh->epi_ok[0] = sh->epi_ok[1] = 1;
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
@@ -94,14 +95,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     ctl.rank = rank;
     if (threadIdx.x == 0) CB_TRACE(TR_START, globaltimer_ns());
 
-    // pair tile t -> (owner d, 256-row tile mi2 of the owner's rows, column tile ni): owners rank+1,
-    // rank+2, ... and the own rows last; `lead_ok` is false when even the leader's half has no rows
+    // Tile order.  The owner's rows are cut into stripes of 256 rows (nt pair tiles each).  "Super-
+    // round" q sends stripe q of every peer (owners rank+1, rank+2, ...) and then reduces the OWN
+    // stripe q - lag, whose partials the peers sent `lag` super-rounds earlier.  Peer traffic is thus
+    // spread over the whole kernel instead of its first (R-1)/R, and only `lag` own stripes remain
+    // for the end.  A partial is at least (lag + 1) * nt tiles ahead of the own tile that needs it;
+    // lag is sized so that this is 1.5 tiles per CTA pair (compute, drain, store and the flag that
+    // follows one tile later take about one).
+    const int stripes = mt2;
+    int lag = (3 * pairs / 2 + nt - 1) / nt - 1;
+    lag = max(1, min(lag, stripes));
+    const int head = lag * (R - 1) * nt;                        // super-rounds 0 .. lag-1: peers only
+    const int body = (stripes - lag) * R * nt;                  // super-rounds lag .. stripes-1: peers, then own
     auto decode = [&](int t, int &d, int &mi2, int &ni, bool &lead_ok) {
-        const int j = t / per2;
-        const int u = t - j * per2;
+        int j;      // 0 .. R-2: peer rank+1+j;  R-1: own rows
+        if (t < head) {
+            const int q = t / ((R - 1) * nt);
+            const int u = t - q * (R - 1) * nt;
+            j = u / nt;
+            ni = u - j * nt;
+            mi2 = q;
+        } else if (t < head + body) {
+            const int v = t - head;
+            const int q = lag + v / (R * nt);
+            const int u = v - (q - lag) * R * nt;
+            j = u / nt;
+            ni = u - j * nt;
+            mi2 = (j == R - 1) ? q - lag : q;
+        } else {
+            const int v = t - head - body;
+            j = R - 1;
+            mi2 = stripes - lag + v / nt;
+            ni = v - (v / nt) * nt;
+        }
         d = (rank + 1 + j) % R;
-        mi2 = u / nt;
-        ni = u - mi2 * nt;
         lead_ok = d * mr + mi2 * BM2 < min(p.M, (d + 1) * mr);
     };
 
@@ -195,27 +222,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------------- epilogue ----
+        // Every epilogue warp owns 32 rows of the CTA's half-tile.  It drains them 64 columns at a
+        // time into its own swizzled staging buffer (32 rows x 128 B, two buffers) and lane 0 sends
+        // each buffer with ONE tiled TMA store: to the owner's staging rows over NVLink, to this
+        // rank's output, or (Matmul-AllReduce, own rows) to the output and every peer's final rows.
+        // 16 stores per half-tile; the tensor maps end at the last valid row, so ragged tiles are
+        // clipped by the copy engine.
         const int q = warp & 3;
         const int etid = (warp - 2) * 32 + lane;
         const int row_in_tile = q * 32 + lane;
         uint32_t tcount = 0;
         uint32_t entered_ok = 0;
+        uint32_t check_no = 0;
         bool ok = true;
         GroupSync epi{&sh->epi_bar, 0};
-        uint64_t epi_wait_ns = 0, epi_store_ns = 0;
+        uint64_t epi_wait_ns = 0, epi_store_ns = 0, flush_ns = 0;
         T *const C = reinterpret_cast<T *>(ra.C);
         const T *const my_stage = reinterpret_cast<const T *>(p.heap_base[rank] + p.symm_off);
-        uint8_t *my_row_smem = smem_side + row_in_tile * 256;
-        // A half-tile's flag is raised one tile late: its row stores then complete (a round trip to
-        // the peer) while the next accumulator is drained, instead of holding this one up.  The
-        // pending flag is always raised before this CTA waits for a peer, so no rank can wait for a
-        // flag whose writer waits for it.
+        uint8_t *const wbuf = smem_side + q * 8192;          // this warp's two 4 KiB staging buffers
+        constexpr int kSlabs = BN / 64;                       // stores (bulk groups) per half-tile and warp
+        // A half-tile's flag is raised one tile late: its stores then complete (a round trip to the
+        // peer) while the next accumulator is drained, instead of holding this one up.  The pending
+        // flag is always raised before this CTA waits for a peer, so no rank can wait for a flag
+        // whose writer waits for it.
         bool pend = false, pend_remote = false;
         int pend_d = 0, pend_tip = 0;
         auto publish = [&](bool everything) -> bool {
             if (!pend) return true;
-            if (everything) bulk_wait<0>(); else bulk_wait<BN / 128>();
-            fence_proxy_async_global();
+            if (lane == 0) {
+                if (everything) bulk_wait<0>(); else bulk_wait<kSlabs>();
+                fence_proxy_async_global();
+            }
             if (!epi.sync(ctl)) return false;
             if (etid == 0) {
                 fence_sys();
@@ -244,112 +281,128 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             const bool half_ok = out_row0 < row_end;            // this CTA's half holds rows of the owner
             const int row = out_row0 + row_in_tile;
             const bool row_ok = row < row_end;
+            const bool warp_ok = out_row0 + q * 32 < row_end;   // this warp has at least one row
             const int n0 = ni * BN;
             const int tile_in_peer = (mi2 * 2 + static_cast<int>(cr)) * nt + ni;
             const bool remote = d != rank;
             const bool comm = R > 1 && !p.compute_only && half_ok;
 
             if (comm && (remote ? !((entered_ok >> d) & 1) : true)) {
+                // This half-tile depends on peers: the owner must have entered (remote rows), or every
+                // peer's partial must be in (own rows).  Warp 2 looks once without blocking, lane s for
+                // rank s; only if something is missing is the pending flag raised first (which costs a
+                // round trip to a peer) and the wait made blocking.
                 const uint64_t tp0 = p.trace ? globaltimer_ns() : 0;
-                if (!(ok = publish(true))) break;
-                if (etid == 0) {
-                    bool w = true;
+                volatile int *verdict = &sh->epi_ok[check_no & 1];
+                ++check_no;
+                const uint32_t *my_flag = nullptr;      // the flag this lane looks at
+                uint32_t my_need = 0;
+                if (warp == 2) {
                     if (remote) {
-                        w = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d);
-                    } else {
-                        for (int s = 0; s < R && w; ++s) {
-                            if (s == rank) continue;
-                            const uint32_t wd = kFlagOpBase + s * per + tile_in_peer;
-                            w = wait_flag_ge(flag_ptr(p, rank, wd), p.epoch, ctl, W_RS_PARTIAL, wd);
+                        if (lane == 0) {
+                            my_flag = flag_ptr(p, rank, kFlagEntered + d);
+                            my_need = p.entered_need;
                         }
+                    } else if (lane < R && lane != rank) {
+                        my_flag = flag_ptr(p, rank, kFlagOpBase + lane * per + tile_in_peer);
+                        my_need = p.epoch;
                     }
-                    if (!w) *reinterpret_cast<volatile int *>(&sh->epi_ok) = 0;
+                    const bool up = !my_flag || static_cast<int32_t>(ld_acquire_sys(my_flag) - my_need) >= 0;
+                    if (__all_sync(0xffffffffu, up)) {
+                        if (lane == 0) *verdict = 1;
+                    } else if (lane == 0) {
+                        *verdict = 2;
+                    }
                 }
                 if (!(ok = epi.sync(ctl))) break;
-                if (!(ok = (*reinterpret_cast<volatile int *>(&sh->epi_ok) != 0))) break;
+                if (*verdict == 2) {
+                    if (!(ok = publish(true))) break;
+                    if (p.trace) flush_ns += globaltimer_ns() - tp0;
+                    if (warp == 2) {
+                        const bool w = !my_flag || wait_flag_ge(my_flag, my_need, ctl, remote ? W_ENTERED : W_RS_PARTIAL,
+                                                                 remote ? d : static_cast<int>(my_flag - flag_ptr(p, rank, 0)));
+                        const bool all_up = __all_sync(0xffffffffu, w);
+                        if (lane == 0) *verdict = all_up ? 1 : 0;
+                    }
+                    if (!(ok = epi.sync(ctl))) break;
+                }
+                if (!(ok = (*verdict == 1))) break;
                 if (remote) entered_ok |= 1u << d;
                 if (p.trace) epi_wait_ns += globaltimer_ns() - tp0;
             }
 
-            T *dst_row;
-            if (remote) {
-                // (compute-only measurement: same stores, into this rank's own staging rows)
-                T *stage = reinterpret_cast<T *>(p.heap_base[p.compute_only ? rank : d] + p.symm_off);
-                dst_row = stage + (static_cast<size_t>(rank) * mr + (row - d * mr)) * p.N;
-            } else {
-                dst_row = (OP == OP_MMRS) ? C + static_cast<size_t>(row - rank * mr) * p.N
-                                          : C + static_cast<size_t>(row) * p.N;
-            }
+            const int y_map = out_row0 - d * mr + q * 32;        // first row of this warp inside the maps of owner d
             const uint64_t te0 = p.trace ? globaltimer_ns() : 0;
             if (half_ok) {
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    if ((c & 3) == 0) bulk_wait_read<0>();      // my staging row is free again
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
-                    const int col = n0 + c * 32;
-                    const bool live = row_ok && col < p.N;
-                    const bool reduce = !remote && R > 1 && live;
-                    uint4 part[kMaxRanks][4];
-                    if (reduce) {
+                for (int sl = 0; sl < kSlabs; ++sl) {
+                    uint8_t *buf = wbuf + (sl & 1) * 4096;
+                    if (lane == 0) bulk_wait_read<1>();         // the store two slabs ago has read this buffer
+                    __syncwarp();
 #pragma unroll
-                        for (int s = 0; s < kMaxRanks; ++s) {
-                            if (s < R && s != rank) {
-                                const T *src = my_stage + (static_cast<size_t>(s) * mr + (row - rank * mr)) * p.N + col;
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int c = sl * 2 + cc;
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                        const int col = n0 + c * 32;
+                        const bool reduce = !remote && R > 1 && row_ok && col < p.N;
+                        uint4 part[kMaxRanks][4];
+                        if (reduce) {
 #pragma unroll
-                                for (int g = 0; g < 4; ++g)
-                                    part[s][g] = (col + g * 8 < p.N) ? *reinterpret_cast<const uint4 *>(src + g * 8)
-                                                                     : make_uint4(0, 0, 0, 0);
+                            for (int s = 0; s < kMaxRanks; ++s) {
+                                if (s < R && s != rank) {
+                                    const T *src = my_stage + (static_cast<size_t>(s) * mr + (row - rank * mr)) * p.N + col;
+#pragma unroll
+                                    for (int g = 0; g < 4; ++g)
+                                        part[s][g] = (col + g * 8 < p.N) ? *reinterpret_cast<const uint4 *>(src + g * 8)
+                                                                         : make_uint4(0, 0, 0, 0);
+                                }
                             }
                         }
-                    }
-                    tmem_ld_wait();
-                    float f[32];
+                        tmem_ld_wait();
+                        float f[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-                    if (reduce) {
-                        // fixed order: own fp32 accumulator, then the peers' partials by rank
+                        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+                        if (reduce) {
+                            // fixed order: own fp32 accumulator, then the peers' partials by rank
 #pragma unroll
-                        for (int s = 0; s < kMaxRanks; ++s) {
-                            if (s < R && s != rank) {
+                            for (int s = 0; s < kMaxRanks; ++s) {
+                                if (s < R && s != rank) {
 #pragma unroll
-                                for (int g = 0; g < 4; ++g) {
-                                    const uint32_t w4[4] = {part[s][g].x, part[s][g].y, part[s][g].z, part[s][g].w};
+                                    for (int g = 0; g < 4; ++g) {
+                                        const uint32_t w4[4] = {part[s][g].x, part[s][g].y, part[s][g].z, part[s][g].w};
 #pragma unroll
-                                    for (int h = 0; h < 4; ++h) {
-                                        const float2 x = Pack2<T>::unpack(w4[h]);
-                                        f[g * 8 + h * 2] += x.x;
-                                        f[g * 8 + h * 2 + 1] += x.y;
+                                        for (int h = 0; h < 4; ++h) {
+                                            const float2 x = Pack2<T>::unpack(w4[h]);
+                                            f[g * 8 + h * 2] += x.x;
+                                            f[g * 8 + h * 2 + 1] += x.y;
+                                        }
                                     }
                                 }
                             }
                         }
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) pk[i] = Pack2<T>::pack(f[2 * i], f[2 * i + 1]);
+                        // row `lane` of the buffer; 16-byte chunk j sits at j ^ (row & 7) (128-byte swizzle)
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const int j = (cc * 4 + g) ^ (lane & 7);
+                            *reinterpret_cast<uint4 *>(buf + lane * 128 + j * 16) =
+                                make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                        }
                     }
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) pk[i] = Pack2<T>::pack(f[2 * i], f[2 * i + 1]);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g)
-                        *reinterpret_cast<uint4 *>(my_row_smem + (c & 3) * 64 + g * 16) =
-                            make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-                    if ((c & 3) == 3) {
-                        fence_proxy_async_smem();
-                        const int colh = n0 + (c >> 2) * 128;
-                        if (row_ok && colh < p.N) {
-                            const uint32_t len = static_cast<uint32_t>(min(128, p.N - colh)) * sizeof(T);
-                            bulk_store(dst_row + colh, my_row_smem, len);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int x = n0 + sl * 64;
+                        if (warp_ok && x < p.N) {
+                            tma_store_2d(&mp.out[d], buf, x, y_map);
                             if (OP == OP_MMAR && !remote && R > 1 && !p.compute_only) {
-                                // reduced rows -> every peer's "final" rows (second half of the region)
-                                const size_t final_off = static_cast<size_t>(R) * mr * p.N;
-                                for (int jj = 1; jj < R; ++jj) {
-                                    const int dd = (rank + jj) % R;
-                                    T *fin = reinterpret_cast<T *>(p.heap_base[dd] + p.symm_off) + final_off +
-                                             static_cast<size_t>(row) * p.N + colh;
-                                    bulk_store(fin, my_row_smem, len);
-                                }
+                                for (int jj = 1; jj < R; ++jj) tma_store_2d(&mp.fin[(rank + jj) % R], buf, x, y_map);
                             }
                         }
-                        bulk_commit();          // every thread, every 128 columns: the group count is uniform
+                        bulk_commit();          // one group per slab, stored or not: the count is uniform
                     }
                 }
             }
@@ -368,10 +421,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             ++tcount;
         }
         if (ok) ok = publish(true);
-        bulk_wait<0>();
+        if (lane == 0) bulk_wait<0>();
         if (etid == 0) {
             CB_TRACE(TR_EPI_WAIT_NS, epi_wait_ns);
             CB_TRACE(TR_EPI_STORE_NS, epi_store_ns);
+            CB_TRACE(TR_PROD_WAIT_NS, flush_ns);            // of the wait time: slow path (flag raised first)
         }
         if (OP == OP_MMAR && R > 1 && ok && !p.compute_only) {
             // second phase: copy the peers' reduced tiles from my "final" rows into D

@@ -129,6 +129,13 @@ __device__ __forceinline__ void bulk_store(void *gmem_dst, const void *smem_src,
                  "r"(smem_u32(smem_src)), "r"(bytes)
                  : "memory");
 }
+// 2-D tiled store shared -> global (this GPU's or a peer's memory) as part of the thread's current
+// bulk group; rows and columns past the tensor's extent are not written.
+__device__ __forceinline__ void tma_store_2d(const void *tmap, const void *smem_src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tmap), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // at most N committed groups may still be reading their shared-memory source
 template <int N>
