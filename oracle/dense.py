@@ -58,3 +58,22 @@ def golden_mx_allgather_matmul(a_codes_list, a_scales_list, b_codes_list, b_scal
         b = mxquant.dequant_mx_e4m3(np.ascontiguousarray(bc.T), np.ascontiguousarray(bs.T)).T
         outs.append(torch.matmul(torch.from_numpy(a), torch.from_numpy(np.ascontiguousarray(b))))
     return outs
+
+
+def golden_mx_matmul_reduce_scatter(a_codes_list, a_scales_list, b_codes_list, b_scales_list, fmt="e5m2"):
+    """MXFP8 Matmul-ReduceScatter golden: D = sum_r dequant(A_r) @ dequant(B_r) in fp32, rows
+    chunked over the ranks.
+
+    examples/ascend950_mxfp8_matmul_reduce_scatter/scripts/gen_data_mxfp8_mmrs.py:333-335 (per-rank
+    `a_fp32 @ b_fp32` on the dequantised operands) and :375-385 (sum over ranks, `torch.chunk` along
+    rows).  a_codes: uint8 [M,k] with scales [M, >=k/32]; b_codes: uint8 [k,N] with scales
+    [>=k/32, N]; blocks of 32 along k for both; `fmt` "e5m2" (what that example feeds) or "e4m3"."""
+    import numpy as np
+    from . import mxquant
+    total = None
+    for ac, asc, bc, bsc in zip(a_codes_list, a_scales_list, b_codes_list, b_scales_list):
+        a = mxquant.dequant_mx(ac, asc, fmt)
+        b = mxquant.dequant_mx(np.ascontiguousarray(bc.T), np.ascontiguousarray(bsc.T), fmt).T
+        c = torch.matmul(torch.from_numpy(a), torch.from_numpy(np.ascontiguousarray(b)))
+        total = c if total is None else total + c
+    return list(torch.chunk(total, len(a_codes_list), dim=0))

@@ -221,3 +221,47 @@ def dispatch_ffn_combine(x_list, expert_idx_list, probs_list, w1_q_list, w1_s_li
         inter["back"] = back
         return outs, inter
     return outs
+
+
+# --------------------------------------------------------------------------- #
+# Standalone AllToAllV-GroupedMatmul and GroupedMatmul-AllToAllV (MXFP8 operands)
+# --------------------------------------------------------------------------- #
+def alltoallv_grouped_matmul(a_deq_list, w_deq_lists, tokens_per_expert_all, ep, experts_per_rank):
+    """Dispatch then grouped GEMM, fp32 result per expert-owning rank.
+
+    examples/utils/gen_data_fp8_mx_alltoallv_gmm.py:575-605, 634-640: every rank's rows are
+    already grouped by global expert (`local_tokens_per_expert`); owner `o` receives, local
+    expert major and source rank minor, the rows of its experts and multiplies every local
+    expert's rows with that expert's [k, n] weight.  a_deq_list[r]: fp32 [m, k] dequantised
+    rows of rank r; w_deq_lists[o][le]: fp32 [k, n]."""
+    recv, blocks = alltoallv_dispatch(a_deq_list, tokens_per_expert_all, ep, experts_per_rank)
+    outs = []
+    for o in range(ep):
+        pos, parts = 0, []
+        for le, n in enumerate(blocks[o]):
+            a = torch.from_numpy(np.ascontiguousarray(recv[o][pos:pos + n]))
+            parts.append(torch.matmul(a, torch.from_numpy(np.ascontiguousarray(w_deq_lists[o][le]))).numpy())
+            pos += n
+        width = w_deq_lists[o][0].shape[1]
+        outs.append(np.concatenate(parts, axis=0) if parts else np.zeros((0, width), np.float32))
+    return outs, blocks
+
+
+def grouped_matmul_alltoallv(a_deq_list, w_deq_lists, tokens_per_expert_all, ep, experts_per_rank):
+    """Grouped GEMM on the expert owners, then every result row goes back to its source rank.
+
+    examples/utils/gen_data_gmm_alltoallv_fp8_mx.py:720-751, 796-806: owner `o` holds rows grouped
+    local expert major / source rank minor (counts `tokens_per_expert_all[src, o*E_local + le]`),
+    multiplies each local expert's rows with its weight, and rank `src` ends up with its rows in
+    global-expert order.  Only the first sum(counts) rows of a_deq_list[o] are used."""
+    t = np.asarray(tokens_per_expert_all, dtype=np.int64)
+    outs = []
+    for o in range(ep):
+        pos, parts = 0, []
+        for le in range(experts_per_rank):
+            n = int(t[:, o * experts_per_rank + le].sum())
+            a = torch.from_numpy(np.ascontiguousarray(a_deq_list[o][pos:pos + n]))
+            parts.append(torch.matmul(a, torch.from_numpy(np.ascontiguousarray(w_deq_lists[o][le]))).numpy())
+            pos += n
+        outs.append(np.concatenate(parts, axis=0))
+    return alltoallv_combine(outs, tokens_per_expert_all, ep, experts_per_rank)

@@ -228,3 +228,75 @@ def quantize_bf16_tensor(x: torch.Tensor, rounding: str = "rne"):
     """bf16 [M,K] tensor -> (codes uint8 tensor, scale-bytes uint8 tensor, dequant fp32 tensor)."""
     c, s, d = quantize_mx_e4m3(x.to(torch.float32).numpy(), rounding)
     return torch.from_numpy(c), torch.from_numpy(s), torch.from_numpy(d)
+
+
+# --------------------------------------------------------------------------- #
+# MXFP8 with e5m2 codes — the MXFP8 Matmul-ReduceScatter example quantises its
+# inputs this way (examples/ascend950_mxfp8_matmul_reduce_scatter/scripts/
+# gen_data_mxfp8_mmrs.py:26-243; emax = 15, :46-53)
+# --------------------------------------------------------------------------- #
+E5M2_EMAX = 15
+E5M2_MAX = 57344.0
+
+
+def e5m2_to_f32(code: np.ndarray) -> np.ndarray:
+    """float8_e5m2 bits -> fp32 (IEEE-like: exponent 31 is Inf/NaN)."""
+    code = np.asarray(code, dtype=np.uint8)
+    # e5m2 is the top byte of an IEEE half
+    return (code.astype(np.uint16) << np.uint16(8)).view(np.float16).astype(np.float32)
+
+
+def _e5m2_pos_lut() -> np.ndarray:
+    """The generator's table of non-negative e5m2 values, indexed by code 0..127
+    (gen_data_mxfp8_mmrs.py:124-154): codes 124..127 are stored as the maximum."""
+    v = e5m2_to_f32(np.arange(124, dtype=np.uint8)).astype(np.float64)
+    v = np.concatenate([v, np.full(4, E5M2_MAX)])
+    return v
+
+
+def f32_to_e5m2_nearest(x: np.ndarray) -> np.ndarray:
+    """Nearest table value after clamping to +-57344, as `_quantize_to_fp8` does
+    with `argmin(|lut - v|)` (gen_data_mxfp8_mmrs.py:172-184): the first table
+    index wins a tie, i.e. the value of smaller magnitude; the result is then
+    cast with `.to(torch.float8_e5m2)` (:283), exact for table values."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    lut = _e5m2_pos_lut()[:125]                      # 0 .. 57344, strictly increasing
+    a = np.minimum(np.abs(x.astype(np.float64)), E5M2_MAX)
+    hi = np.searchsorted(lut, a, side="left")        # first table value >= a
+    hi = np.clip(hi, 0, len(lut) - 1)
+    lo = np.clip(hi - 1, 0, len(lut) - 1)
+    pick_lo = (a - lut[lo]) <= (lut[hi] - a)         # tie -> lower index
+    idx = np.where(pick_lo, lo, hi).astype(np.uint8)
+    idx = np.where(idx == 124, np.uint8(123), idx)   # 57344 is code 123 (0x7B); 124 was only the table's alias
+    neg = (x < 0) & (idx != 0)
+    return np.where(neg, idx | np.uint8(0x80), idx).astype(np.uint8)
+
+
+def quantize_mx_e5m2(x: np.ndarray):
+    """Blocks of 32 along the last axis, scale 2^(floor(log2 amax) - 15), codes by
+    nearest table value (gen_data_mxfp8_mmrs.py:156-234).  Returns (codes uint8,
+    scale bytes padded to an even count with 127, dequant fp32)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    nb = (k + BLOCK - 1) // BLOCK
+    xp = np.zeros((m, nb * BLOCK), dtype=np.float32)
+    xp[:, :k] = x
+    blocks = xp.reshape(m, nb, BLOCK)
+    amax = np.abs(blocks).max(axis=-1)
+    exp = e8m0_exp(amax, E5M2_EMAX)
+    scale = np.exp2(exp.astype(np.float32)).astype(np.float32)
+    codes = f32_to_e5m2_nearest(blocks / scale[..., None])
+    deq = (e5m2_to_f32(codes) * scale[..., None]).reshape(m, nb * BLOCK)[:, :k].astype(np.float32).copy()
+    codes = codes.reshape(m, nb * BLOCK)[:, :k].copy()
+    sb = np.full((m, (nb + 1) // 2 * 2), 127, dtype=np.uint8)
+    sb[:, :nb] = exp_to_e8m0_byte(exp)
+    return codes, sb, deq
+
+
+def dequant_mx(codes: np.ndarray, scale_bytes: np.ndarray, fmt: str = "e4m3") -> np.ndarray:
+    """codes [M,K] uint8 (`fmt` "e4m3" or "e5m2"), scale bytes [M, >=ceil(K/32)] -> fp32 [M,K]."""
+    m, k = codes.shape
+    nb = (k + BLOCK - 1) // BLOCK
+    sc = np.exp2(scale_bytes[:, :nb].astype(np.float32) - 127.0).astype(np.float32)
+    val = e4m3_to_f32(codes) if fmt == "e4m3" else e5m2_to_f32(codes)
+    return (val * np.repeat(sc, BLOCK, axis=1)[:, :k]).astype(np.float32)

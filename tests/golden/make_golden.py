@@ -193,6 +193,86 @@ def moe_fixture():
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **out)
 
 
+
+def _scales_from_pairs(raw, rows, kblocks_padded):
+    """[rows, kb/2, 2] scale bytes -> [rows, kb]."""
+    return raw.reshape(rows, kblocks_padded)
+
+
+def mx_mmrs_fixture(ref_root):
+    """MXFP8 (e5m2) Matmul-ReduceScatter: the example's own generator, 2 ranks, transB = 1."""
+    sdir = os.path.join(ref_root, "examples", "ascend950_mxfp8_matmul_reduce_scatter", "scripts")
+    sys.path.insert(0, sdir)
+    mod = importlib.import_module("gen_data_mxfp8_mmrs")
+    m, k, n, world = 32, 64, 48, 2
+    out = {"shape": np.array([m, k, n, world])}
+    torch.manual_seed(77)
+    # the quantiser on its own: same draw as gen_data_fp8_e5m2 makes first
+    x = torch.randn((8, 96), dtype=torch.float32) * 3.0
+    qz = mod.MXFP8MatrixQuantizer(data_format="E5M2", axis=1, block_size=32)
+    with contextlib.redirect_stdout(io.StringIO()):
+        qx, sx = qz.quantize_matrix(x)
+    out["q_x"] = x.numpy()
+    out["q_codes"] = qx.to(torch.float8_e5m2).view(torch.uint8).numpy()
+    out["q_scale"] = sx.to(torch.float8_e8m0fnu).view(torch.uint8).numpy()
+    with tempfile.TemporaryDirectory() as td:
+        hi, lo = [], []
+        for r in range(world):
+            with contextlib.redirect_stdout(io.StringIO()):
+                c32, c16 = mod.gen_data(r, m, k, n, 0, 1, td)
+            hi.append(c32)
+            lo.append(c16)
+            out[f"a{r}"] = np.fromfile(os.path.join(td, f"rank_{r}_a.bin"), dtype=np.uint8).reshape(m, k)
+            out[f"b{r}"] = np.fromfile(os.path.join(td, f"rank_{r}_b.bin"), dtype=np.uint8).reshape(n, k)       # transB = 1
+            out[f"a_scale{r}"] = np.fromfile(os.path.join(td, f"rank_{r}_a_scale.bin"), dtype=np.uint8).reshape(m, k // 64, 2)
+            out[f"b_scale{r}"] = np.fromfile(os.path.join(td, f"rank_{r}_b_scale.bin"), dtype=np.uint8).reshape(n, k // 64, 2)
+        total = hi[0] + hi[1]
+        out["golden"] = torch.cat(list(torch.chunk(total, world, dim=0)), dim=0).numpy()
+        out["golden_low"] = (lo[0] + lo[1]).view(torch.uint16).numpy()
+    np.savez_compressed(os.path.join(HERE, "mx_mmrs.npz"), **out)
+
+
+def alltoallv_gmm_fixture(ref_root):
+    """Standalone MXFP8 AllToAllV-GroupedMatmul and GroupedMatmul-AllToAllV: the reference's
+    generators run as scripts (2 ranks, 4 experts), files read back."""
+    utils_dir = os.path.join(ref_root, "examples", "utils")
+    env = dict(os.environ, PYTHONPATH=utils_dir)
+    out = {}
+    world, m, n, k, experts = 2, 16, 32, 64, 4
+    out["shape"] = np.array([world, m, n, k, experts])
+    with tempfile.TemporaryDirectory() as td:
+        subprocess.check_call([sys.executable, os.path.join(utils_dir, "gen_data_fp8_mx_alltoallv_gmm.py"), "a2av_gmm",
+                               "bf16", str(world), str(m), str(n), str(k), "0", "0", "--expert", str(experts), "--ep",
+                               str(world), td], stdout=subprocess.DEVNULL, env=env)
+        for r in range(world):
+            out[f"d_a{r}"] = np.fromfile(os.path.join(td, f"input_a_{r}.bin"), dtype=np.uint8).reshape(m, k)
+            out[f"d_a_scale{r}"] = np.fromfile(os.path.join(td, f"input_a_scale_{r}.bin"), dtype=np.uint8).reshape(m, k // 64, 2)
+            out[f"d_b{r}"] = np.fromfile(os.path.join(td, f"input_b_{r}.bin"), dtype=np.uint8).reshape(experts // world, k, n)
+            out[f"d_b_scale{r}"] = np.fromfile(os.path.join(td, f"input_b_scale_{r}.bin"), dtype=np.uint8).reshape(
+                experts // world, k // 64, n, 2)
+            out[f"d_local_tokens{r}"] = np.fromfile(os.path.join(td, f"local_tokens_per_expert_{r}.bin"), dtype=np.int32)
+            out[f"d_global_tokens{r}"] = np.fromfile(os.path.join(td, f"global_tokens_per_local_expert_{r}.bin"),
+                                                     dtype=np.int32).reshape(world, experts // world)
+            out[f"d_golden{r}"] = np.fromfile(os.path.join(td, f"golden_{r}.bin"), dtype=np.float32).reshape(world * m, n)
+    with tempfile.TemporaryDirectory() as td:
+        os.makedirs(os.path.join(td, "output"))
+        m2 = 32          # rows of A per owner; the generator draws m2 / world rows per (source, owner)
+        out["c_m"] = np.array([m2])
+        subprocess.check_call([sys.executable, os.path.join(utils_dir, "gen_data_gmm_alltoallv_fp8_mx.py"), "gmm_a2av",
+                               "bf16", str(world), str(m2), str(n), str(k), "0", "0", "--expert", str(experts), "--ep",
+                               str(world)], stdout=subprocess.DEVNULL, env=env, cwd=td)
+        o = os.path.join(td, "output")
+        for r in range(world):
+            out[f"c_a{r}"] = np.fromfile(os.path.join(o, f"a_gm_{r}.bin"), dtype=np.uint8).reshape(m2, k)
+            out[f"c_a_scale{r}"] = np.fromfile(os.path.join(o, f"a_scale_{r}.bin"), dtype=np.uint8).reshape(m2, k // 64, 2)
+            out[f"c_b{r}"] = np.fromfile(os.path.join(o, f"b_gm_{r}.bin"), dtype=np.uint8).reshape(experts // world, k, n)
+            out[f"c_b_scale{r}"] = np.fromfile(os.path.join(o, f"b_scale_{r}.bin"), dtype=np.uint8).reshape(
+                experts // world, k // 64, n, 2)
+            out[f"c_local_tokens{r}"] = np.fromfile(os.path.join(o, f"local_tokens_per_expert_{r}.bin"), dtype=np.int32)
+            out[f"c_golden{r}"] = np.fromfile(os.path.join(o, f"golden_{r}.bin"), dtype=np.float32).reshape(world * m2, n)
+    np.savez_compressed(os.path.join(HERE, "alltoallv_gmm.npz"), **out)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     sys.path.insert(0, os.path.join(ref_root, "examples", "utils"))
@@ -202,6 +282,8 @@ def main():
     dense_fixture(ref_root)
     swizzle_fixture(ref_root)
     moe_fixture()
+    mx_mmrs_fixture(ref_root)
+    alltoallv_gmm_fixture(ref_root)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -187,3 +187,71 @@ def test_moe_full_pipeline(golden_dir):
         # final weighted sum: fp32 accumulate (device definition) vs the reference's bf16 CPU fallback
         err = np.abs(outs[r] - ref) / np.maximum(1.0, np.abs(ref))
         assert err.max() <= 2 ** -6
+
+
+def test_mx_e5m2_quantiser_bit_exact(golden_dir):
+    """e5m2 codes and E8M0 scales of the MXFP8 Matmul-ReduceScatter example's generator."""
+    f = _load(golden_dir, "mx_mmrs.npz")
+    codes, scale, _ = mxquant.quantize_mx_e5m2(f["q_x"])
+    assert np.array_equal(codes, f["q_codes"])
+    assert np.array_equal(scale, f["q_scale"])
+    # every finite e5m2 value survives a decode / encode round trip
+    allc = np.array([c for c in range(256) if (c & 0x7C) != 0x7C], dtype=np.uint8)
+    back = mxquant.f32_to_e5m2_nearest(mxquant.e5m2_to_f32(allc))
+    assert np.array_equal(back & 0x7F, allc & 0x7F)
+
+
+def test_mx_matmul_reduce_scatter_golden(golden_dir):
+    f = _load(golden_dir, "mx_mmrs.npz")
+    m, k, n, world = [int(v) for v in f["shape"]]
+    a = [f[f"a{r}"] for r in range(world)]
+    a_s = [f[f"a_scale{r}"].reshape(m, -1) for r in range(world)]
+    b = [np.ascontiguousarray(f[f"b{r}"].T) for r in range(world)]                       # files hold B^T (transB = 1)
+    b_s = [np.ascontiguousarray(f[f"b_scale{r}"].reshape(n, -1).T) for r in range(world)]
+    outs = dense.golden_mx_matmul_reduce_scatter(a, a_s, b, b_s, "e5m2")
+    mine = torch.cat(outs, dim=0).numpy()
+    assert mine.shape == f["golden"].shape
+    assert np.allclose(mine, f["golden"], rtol=1e-5, atol=1e-4)
+    low = mxquant.bf16_bits_to_f32(f["golden_low"]).reshape(m, n)
+    assert np.abs(mine - low).max() <= 2 ** -6 * max(1.0, np.abs(mine).max())
+
+
+def _a2av_operands(f, prefix, world, experts, m, k, n):
+    epr = experts // world
+    a = [mxquant.dequant_mx(f[f"{prefix}_a{r}"], f[f"{prefix}_a_scale{r}"].reshape(m, -1), "e4m3") for r in range(world)]
+    w = []
+    for r in range(world):
+        per = []
+        for le in range(epr):
+            codes = f[f"{prefix}_b{r}"][le]                                                # [k, n]
+            sc = f[f"{prefix}_b_scale{r}"][le].transpose(0, 2, 1).reshape(-1, n)           # [k/64, n, 2] -> [k/32, n]
+            per.append(np.ascontiguousarray(
+                mxquant.dequant_mx(np.ascontiguousarray(codes.T), np.ascontiguousarray(sc.T), "e4m3").T))
+        w.append(per)
+    return a, w
+
+
+def test_alltoallv_grouped_matmul_golden(golden_dir):
+    f = _load(golden_dir, "alltoallv_gmm.npz")
+    world, m, n, k, experts = [int(v) for v in f["shape"]]
+    a, w = _a2av_operands(f, "d", world, experts, m, k, n)
+    counts = np.stack([f[f"d_local_tokens{r}"] for r in range(world)])
+    outs, blocks = moe.alltoallv_grouped_matmul(a, w, counts, world, experts // world)
+    for r in range(world):
+        assert blocks[r] == f[f"d_global_tokens{r}"].sum(axis=0).tolist()
+        rows = outs[r].shape[0]
+        assert np.allclose(outs[r], f[f"d_golden{r}"][:rows], rtol=1e-5, atol=1e-4)
+        assert not f[f"d_golden{r}"][rows:].any()
+
+
+def test_grouped_matmul_alltoallv_golden(golden_dir):
+    f = _load(golden_dir, "alltoallv_gmm.npz")
+    world, _, n, k, experts = [int(v) for v in f["shape"]]
+    m2 = int(f["c_m"][0])
+    a, w = _a2av_operands(f, "c", world, experts, m2, k, n)
+    counts = np.stack([f[f"c_local_tokens{r}"] for r in range(world)])
+    back = moe.grouped_matmul_alltoallv(a, w, counts, world, experts // world)
+    for r in range(world):
+        rows = back[r].shape[0]
+        assert rows == int(counts[r].sum())
+        assert np.allclose(back[r], f[f"c_golden{r}"][:rows], rtol=1e-5, atol=1e-4)
