@@ -103,6 +103,38 @@ int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelPa
                                       static_cast<int>(tiling->k), static_cast<int>(transB));
 }
 
+// MXFP8 Matmul-ReduceScatter: KernelParams as set by the example's operator class
+// (examples/ascend950_mxfp8_matmul_reduce_scatter/ascend950_mxfp8_matmul_reduce_scatter_host.h:107:
+// SetKernelParams(a, b, c, aScale, bScale)).
+int launch_mx_rs_abi(int dtype, int code_format, void *stream, uint32_t blockNum, CatccosKernelParams *params,
+                     int n_params, uint8_t **workspaces, uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA,
+                     uint32_t transB) {
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    Team *t = team();
+    const int want = t->emulated ? t->n_pes : 1;
+    if (!params || n_params != want || !workspaces) {
+        set_error("MXFP8 Matmul-ReduceScatter: one parameter block and one workspace per local PE are required");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (transA) {
+        set_error("transA=1 is not supported");
+        return CATCCOS_ERR_INVALID;
+    }
+    MxAgArgs args[kMaxRanks];
+    for (int i = 0; i < n_params; ++i) {
+        if (params[i].customCount < 2 || !params[i].customPtrs) {
+            set_error("MXFP8 Matmul-ReduceScatter expects customPtrs = {aScale, bScale}");
+            return CATCCOS_ERR_INVALID;
+        }
+        args[i] = {params[i].ptrA, params[i].ptrB, params[i].ptrC, params[i].customPtrs[0], params[i].customPtrs[1],
+                   workspaces[i]};
+    }
+    return launch_mx_matmul_reduce_scatter(dtype, code_format, static_cast<cudaStream_t>(stream), blockNum, args,
+                                           symmetric, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
+                                           static_cast<int>(tiling->k), static_cast<int>(transB));
+}
+
 int launch_moe_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params, uint8_t **workspaces,
                    uint8_t *symmetric, CocTilingParams *tiling) {
     int rc = check_tiling(tiling);
@@ -322,6 +354,9 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
         return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
+    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER)
+        return dense_symmetric_bytes(OP_MMRS, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
+                                     static_cast<int>(tiling->k));
     if (commType == CATCCOS_MX_QUANT_ALLGATHER)
         return mxq_allgather_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n));
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0)
@@ -332,7 +367,8 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
 }
 size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
     (void)dataType;
-    if (tiling && commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
+    if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL ||
+                   commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER))
         return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
     if (tiling && commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0) {
@@ -371,6 +407,17 @@ DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16, OP_MMRS, CATCCOS_BF16)
 MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16, CATCCOS_FP16)
 MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16, CATCCOS_BF16)
 
+#define MXRS_LAUNCH(name, dtype, fmt)                                                                          \
+    int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
+             uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
+        (void)fftsAddr;                                                                                          \
+        return launch_mx_rs_abi(dtype, fmt, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB); \
+    }
+MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterFP16, CATCCOS_FP16, 1)
+MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterBF16, CATCCOS_BF16, 1)
+MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterFP16, CATCCOS_FP16, 0)
+MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterBF16, CATCCOS_BF16, 0)
+
 int LaunchAscend950BF16QuantAllGatherFP8E4M3FN(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params,
                                                uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling,
                                                uint32_t transA, uint32_t transB) {
@@ -399,6 +446,8 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
         return launch_dense_abi(op, dataType, stream, blockNum, params, 1, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
+    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_rs_abi(dataType, 1, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
@@ -420,6 +469,9 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
         return launch_dense_abi(op, dataType, stream, blockNum, params, t->n_pes, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
+                                transB);
+    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_rs_abi(dataType, 1, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
                                 transB);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling);

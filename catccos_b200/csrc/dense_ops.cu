@@ -117,6 +117,40 @@ static int launch_t(const FusedParams &p, int grid, bool coop, cudaStream_t s, b
     return bf16 ? launch_b<OP, __nv_bfloat16>(p, grid, coop, s, b_mn) : launch_b<OP, __half>(p, grid, coop, s, b_mn);
 }
 
+int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, bool allreduce, CUtensorMapDataType dt,
+                   void *const *outputs, int n_local, int m, int n, uint64_t symm_off, bool compute_only) {
+    const int R = t->n_pes;
+    const int mr = allreduce ? (m + R - 1) / R : m / R;
+    auto rows_valid = [&](int d) { return std::min(m, (d + 1) * mr) - d * mr; };
+    const size_t row_b = static_cast<size_t>(n) * 2;
+    for (int l = 0; l < n_local; ++l) {
+        const int pe = t->emulated ? l : t->my_pe;
+        RsMaps &mp = maps->r[l];
+        for (int d = 0; d < R; ++d) {
+            const int rv_d = rows_valid(d), rv_me = rows_valid(pe);
+            if (d == pe) {
+                if (rv_me <= 0) continue;
+                uint8_t *base = static_cast<uint8_t *>(outputs[l]) + (allreduce ? static_cast<size_t>(pe) * mr * row_b : 0);
+                int rc = encode_2d(api, &mp.out[d], dt, base, n, rv_me, row_b, 64, 32);
+                if (rc) return rc;
+                continue;
+            }
+            if (rv_d > 0) {
+                // this rank's slot of rank d's staging rows (compute-only measurement: of its own)
+                uint8_t *base = t->base[compute_only ? pe : d] + symm_off + static_cast<size_t>(pe) * mr * row_b;
+                int rc = encode_2d(api, &mp.out[d], dt, base, n, rv_d, row_b, 64, 32);
+                if (rc) return rc;
+            }
+            if (allreduce && rv_me > 0) {
+                uint8_t *base = t->base[d] + symm_off + (static_cast<size_t>(R) * mr + static_cast<size_t>(pe) * mr) * row_b;
+                int rc = encode_2d(api, &mp.fin[d], dt, base, n, rv_me, row_b, 64, 32);
+                if (rc) return rc;
+            }
+        }
+    }
+    return CATCCOS_OK;
+}
+
 // one half of the (double-buffered) data region, rounded up to the 1024-byte alignment of the halves
 static size_t dense_half_bytes(int op, int world, int m, int n, int k) {
     const size_t es = 2;
@@ -285,34 +319,10 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     // output tensor maps of the pair reduce-scatter kernel (see RsMaps)
     static thread_local RsMapsAll maps;
     if (use_pair && op != OP_AGMM) {
-        const int mr = (op == OP_MMAR) ? (m + R - 1) / R : m / R;
-        auto rows_valid = [&](int d) { return std::min(m, (d + 1) * mr) - d * mr; };
-        const size_t row_b = static_cast<size_t>(n) * 2;
-        for (int l = 0; l < n_local; ++l) {
-            const int pe = t->emulated ? l : t->my_pe;
-            RsMaps &mp = maps.r[l];
-            for (int d = 0; d < R; ++d) {
-                const int rv_d = rows_valid(d), rv_me = rows_valid(pe);
-                if (d == pe) {
-                    if (rv_me <= 0) continue;
-                    uint8_t *base = static_cast<uint8_t *>(args[l].C) + (op == OP_MMAR ? static_cast<size_t>(pe) * mr * row_b : 0);
-                    int rc = encode_2d(api, &mp.out[d], dt, base, n, rv_me, row_b, 64, 32);
-                    if (rc) return rc;
-                    continue;
-                }
-                if (rv_d > 0) {
-                    // this rank's slot of rank d's staging rows (compute-only measurement: of its own)
-                    uint8_t *base = t->base[p.compute_only ? pe : d] + symm_off + static_cast<size_t>(pe) * mr * row_b;
-                    int rc = encode_2d(api, &mp.out[d], dt, base, n, rv_d, row_b, 64, 32);
-                    if (rc) return rc;
-                }
-                if (op == OP_MMAR && rv_me > 0) {
-                    uint8_t *base = t->base[d] + symm_off + (static_cast<size_t>(R) * mr + static_cast<size_t>(pe) * mr) * row_b;
-                    int rc = encode_2d(api, &mp.fin[d], dt, base, n, rv_me, row_b, 64, 32);
-                    if (rc) return rc;
-                }
-            }
-        }
+        void *outs[kMaxRanks];
+        for (int l = 0; l < n_local; ++l) outs[l] = args[l].C;
+        int rc = encode_rs_maps(api, t, &maps, op == OP_MMAR, dt, outs, n_local, m, n, symm_off, p.compute_only != 0);
+        if (rc) return rc;
     }
     commit_slot(t, sig, epoch, slot);
     if (use_pair) {

@@ -20,4 +20,10 @@ size_t dense_symmetric_bytes(int op, int world, int m, int n, int k);
 int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, const DenseArgs *args, void *symmetric,
                  int m, int n, int k, int trans_a, int trans_b);
 
+// Output tensor maps of a pair reduce-scatter kernel for every local rank (see RsMaps): `outputs[l]` is local
+// rank l's output (reduce-scatter: [m/R, n]; all-reduce: [m, n]), 16-bit elements of type `dt`; `symm_off` the
+// offset of the launch's half of the staging region.
+int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, bool allreduce, CUtensorMapDataType dt,
+                   void *const *outputs, int n_local, int m, int n, uint64_t symm_off, bool compute_only);
+
 }  // namespace cb

@@ -6,7 +6,7 @@
 //
 //   catccos_run <kernel> <dtype> <rank_size> <rank_id> <ip_port> <m> <n> <k> <data_dir>
 //               [transA transB [topK expertNum [device_id [warmup timed]]]]
-//   kernel: mmar | agmm | a5agmm | mmrs | a5mmrs | a5fp8mxagmm | a5moe     dtype: 1 (fp16) | 27 (bf16)
+//   kernel: mmar | agmm | a5agmm | mmrs | a5mmrs | a5fp8mxagmm | a5mxfp8mmrs | a5moe     dtype: 1 (fp16) | 27 (bf16)
 //   catccos_run --list        prints the registered operator names
 #include <cuda_runtime.h>
 

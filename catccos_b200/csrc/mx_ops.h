@@ -21,4 +21,11 @@ size_t mx_ag_workspace_bytes(int m, int n, int k);
 int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t block_num, const MxAgArgs *args,
                                void *symmetric, int m, int n, int k, int trans_b);
 
+// Matmul-ReduceScatter on MXFP8 operands (codes `code_format` 0 = e4m3, 1 = e5m2; E8M0 scales per 32 along k):
+// D_r = rows r*m/R .. of sum_s A_s B_s.  m = rows of the full product, k = this rank's share of the
+// contraction; m/R must be a multiple of 128.  MxAgArgs as above with C = [m/R, n]; the symmetric region is that
+// of the f16/bf16 Matmul-ReduceScatter (dense_symmetric_bytes), the workspace mx_ag_workspace_bytes(m, n, k).
+int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t stream, uint32_t block_num,
+                                    const MxAgArgs *args, void *symmetric, int m, int n, int k, int trans_b);
+
 }  // namespace cb

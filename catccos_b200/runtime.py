@@ -11,6 +11,7 @@ from ._lib import CocTilingParams, KernelParams, check, lib
 MATMUL_ALLREDUCE = 0
 ALLGATHER_MATMUL = 1
 MATMUL_REDUCE_SCATTER = 3
+MXFP8_MATMUL_REDUCE_SCATTER = 18
 FP8_MX_ALLGATHER_MATMUL = 22
 MX_QUANT_ALLGATHER = 24
 DISPATCH_FFN_COMBINE = 32

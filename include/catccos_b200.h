@@ -166,6 +166,20 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16);
 
+/* MXFP8 Matmul-ReduceScatter (MatmulReduceScatterMxTla, include/catccos/dgemm/kernel/matmul_reduce_scatter_mx_tla.hpp:39;
+ * operator "Ascend950MxFp8MatmulReduceScatter", examples/ascend950_mxfp8_matmul_reduce_scatter/main.cpp:32-141 and
+ * ..._host.h:28-142): ptrA/ptrB = float8_e5m2 operands (what that example feeds), customPtrs = {aScale [m, k/64, 2],
+ * bScale (transB=0: [k/64, n, 2]; transB=1: [n, k/64, 2])} E8M0 bytes, ptrC = this rank's [m/rankSize, n] rows of the
+ * summed product in the 16-bit type the name gives; tiling m = rows of the full product (m/rankSize a multiple of
+ * 128), k = this rank's share of the contraction.  `workspace` = catccos_workspace_bytes() bytes, `symmetric` as for
+ * Matmul-ReduceScatter.  The E4M3 names take float8_e4m3fn operands (no reference counterpart of their own: the
+ * reference kernel is a template over the element type).  Status: compiled for sm_100a, parity test not yet run
+ * on a GPU. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterBF16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterBF16);
+
 /* MxQuantAllGather (include/catccos/comm/kernel/mx_quant_allgather.hpp:57-288; registered as
  * REGISTER_KERNEL_FUNC(Ascend950BF16QuantAllGather, MX_QUANT_ALLGATHER, FP8E4M3FN), launch_map.h:91): KernelParams as in
  * examples/ascend950_mx_quant_allgather/mx_quant_allgather_host.h:48 — ptrA = input bf16 [m, n], ptrB = gathered

@@ -26,6 +26,7 @@ enum CocCommType {
     ASCEND950_ALLGATHER_MATMUL = CATCCOS_ASCEND950_ALLGATHER_MATMUL,
     MATMUL_REDUCE_SCATTER = CATCCOS_MATMUL_REDUCE_SCATTER,
     ASCEND950_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER,
+    ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER,
     ASCEND950_FP8_MX_ALLGATHER_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL,
     MX_QUANT_ALLGATHER = CATCCOS_MX_QUANT_ALLGATHER,
     ASCEND950_DISPATCH_FFN_COMBINE = CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE,
@@ -81,6 +82,7 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"mmrs", MATMUL_REDUCE_SCATTER},
         {"a5mmrs", ASCEND950_MATMUL_REDUCE_SCATTER},
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
+        {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
         {"a5moe", ASCEND950_DISPATCH_FFN_COMBINE},
     };
     return m;
@@ -98,6 +100,7 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {MATMUL_REDUCE_SCATTER, "MatmulReduceScatter"},
         {ASCEND950_MATMUL_REDUCE_SCATTER, "Ascend950MatmulReduceScatter"},
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
+        {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
         {ASCEND950_DISPATCH_FFN_COMBINE, "Ascend950DispatchFFNCombine"},
     };
     return m;

@@ -157,6 +157,38 @@ public:
 };
 REGISTER_OPERATOR("Ascend950Fp8MxAllGatherMatmul", Ascend950Fp8MxAllGatherMatmulOperator);
 
+// MXFP8 Matmul-ReduceScatter (examples/ascend950_mxfp8_matmul_reduce_scatter/ascend950_mxfp8_matmul_reduce_scatter_host.h):
+// float8_e5m2 operands, customPtrs = {aScale, bScale}, rank r's rows written at offset r*size of output.bin.
+class Ascend950MxFp8MatmulReduceScatterOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t sizeA = static_cast<size_t>(t.m) * t.k, sizeB = static_cast<size_t>(t.k) * t.n;
+        const size_t kb = (static_cast<size_t>(t.k) + 63) / 64 * 2;
+        const size_t sizeC = static_cast<size_t>(t.m) * t.n / t.rankSize * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), sizeA, 60),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), sizeB, 60), DeviceZeros(sizeC),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a_scale"), t.m * kb, 121),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b_scale"), t.n * kb, 121));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        const size_t cSize = static_cast<size_t>(t.m) * t.n / t.rankSize * 2;
+        catccos_host::WriteDeviceBuffer(dataFile + "/output.bin", params.ptrC, cSize, rankId * cSize);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &t) override {
+        return catccos_workspace_bytes(ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, BF16, &t);
+    }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return t.m > 0 && t.k % 32 == 0 && t.n % 16 == 0 && rankSize >= 1 && rankSize <= MAX_RANK_SIZE &&
+               t.m % rankSize == 0 && (t.m / rankSize) % 128 == 0 &&
+               catccos_symmetric_bytes(ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, BF16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950MxFp8MatmulReduceScatter", Ascend950MxFp8MatmulReduceScatterOperator);
+
 // MoE dispatch -> FFN -> combine (examples/ascend950_dispatch_ffn_combine/ascend950_dispatch_ffn_combine_host.h):
 // customPtrs = {b2, expertIdx, probs, bScale, b2Scale}.
 class Ascend950DispatchFFNCombineOperator : public CatccosOperator {

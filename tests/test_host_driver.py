@@ -20,7 +20,8 @@ def driver():
 def test_registry_lists_every_operator_on_the_path(driver):
     out = subprocess.run([driver, "--list"], capture_output=True, text=True, check=True).stdout.split()
     assert set(out) == {"MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend950AllGatherMatmul",
-                        "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine"}
+                        "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
+                        "Ascend950MxFp8MatmulReduceScatter"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
