@@ -8,6 +8,9 @@
 // the consumer's TMA reads it (AllGather-Matmul) or written by the producing epilogue straight
 // into the owner's staging rows (Matmul-ReduceScatter / Matmul-AllReduce); readiness travels as
 // single-writer epoch flags with release/acquire at system scope.  Every wait is bounded.
+//
+// This is the one-CTA (128 x 256 tile) form: the fallback of the CTA-pair kernels in gemm_pair.cuh and
+// gemm_pair_rs.cuh (CATCCOS_TWO_CTA=0) and the kernel behind catccos_gemm_no_alloc.
 #pragma once
 #include <type_traits>
 
@@ -502,10 +505,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) fused_gemm_kernel(const __gri
                 // All-gather push: my rows go into every peer's gathered region with bulk copies
                 // (global -> shared -> peer global), destination rank-1 first (it consumes my rows
                 // first), in units of BM/kAgSubChunks rows with one flag per unit.  Every pushing
-                // thread ("lane") owns a 16 KiB staging piece and whole units, so a unit's flag has a
-                // single writer.  Default: each GEMM CTA pushes with two lanes of its comm warp
-                // (staging next to the GEMM stages); optionally a few CTAs are dedicated to pushing
-                // with 12 lanes each (the GEMM stage area is free there).
+                // thread ("lane") owns a kPushPieceBytes staging piece and whole units, so a unit's flag
+                // has a single writer.  Default: each GEMM CTA pushes with kPushLanesShared lanes of its
+                // comm warp (staging next to the GEMM stages); optionally a few CTAs are dedicated to
+                // pushing with kPushLanes lanes each (the GEMM stage area is free there).  (This one-CTA
+                // kernel is the fallback; the pair kernel gives every lane a warp of its own.)
                 const int units_per_dest = mt_ag * kAgSubChunks;
                 const int total = (R - 1) * units_per_dest;
                 const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);

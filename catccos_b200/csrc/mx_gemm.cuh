@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
                 st_release_sys(flagp(ctid, kFlagEntered + rank), p.epoch);
             }
             if (ctid < kMxPushLanes) {
-                // units per destination: for every chunk (128 rows) kAgSubChunks data units of 16 rows and
+                // units per destination: for every chunk (128 rows) kAgSubChunks data units of BM/kAgSubChunks rows and
                 // one unit with the chunk's scale atoms; destination rank-1 first
                 const int units_per_dest = mt * kMxFlagsPerChunk;
                 const int total = (R - 1) * units_per_dest;
