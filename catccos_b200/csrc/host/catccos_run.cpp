@@ -8,6 +8,8 @@
 //               [transA transB [topK expertNum [device_id [warmup timed]]]]
 //   kernel: mmar | agmm | a5agmm | mmrs | a5mmrs | a5fp8mxagmm | a5mxfp8mmrs | a5moe     dtype: 1 (fp16) | 27 (bf16)
 //   catccos_run --list        prints the registered operator names
+//   catccos_run --check <kernel> <rank_size> <m> <n> <k> [topK expertNum]
+//                             CheckCocTilingParams + symmetric / workspace bytes, no device needed
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -20,6 +22,36 @@
 int main(int argc, char **argv) {
     if (argc >= 2 && std::string(argv[1]) == "--list") {
         for (const auto &n : OperatorRegistry::Instance().Names()) std::cout << n << "\n";
+        return 0;
+    }
+    if (argc >= 7 && std::string(argv[1]) == "--check") {
+        // catccos_run --check <kernel> <rank_size> <m> <n> <k> [topK expertNum]: the operator's tiling check and
+        // buffer sizes, without touching a device
+        const CocCommType ct = GetCommType(argv[2]);
+        if (ct == UNKNOWN) {
+            std::cerr << "unknown kernel " << argv[2] << "\n";
+            return 1;
+        }
+        auto chk = OperatorRegistry::Instance().CreateOperator(CommTypeOpNameMap().at(ct));
+        if (!chk) return 1;
+        CocTilingParams t{};
+        const int rs = std::atoi(argv[3]);
+        t.m = static_cast<uint32_t>(std::atoi(argv[4]));
+        t.n = static_cast<uint32_t>(std::atoi(argv[5]));
+        t.k = static_cast<uint32_t>(std::atoi(argv[6]));
+        t.topK = argc > 7 ? std::atoi(argv[7]) : 1;
+        t.expertNum = argc > 8 ? std::atoi(argv[8]) : 0;
+        t.m0 = M0;
+        t.n0 = N0;
+        t.k0 = K0;
+        t.rankSize = rs;
+        t.epSize = rs;
+        if (rs < 1 || !chk->CheckCocTilingParams(static_cast<uint32_t>(rs), t)) {
+            std::cout << "rejected\n";
+            return 2;
+        }
+        const CocCommType actual = chk->GetActualKernelType(t);
+        std::cout << "ok " << catccos_symmetric_bytes(actual, BF16, &t) << " " << chk->GetWorkspaceSize(t) << "\n";
         return 0;
     }
     if (argc < 10) {

@@ -83,3 +83,44 @@ def test_two_rank_driver_run(driver, tmp_path):
         raw = np.fromfile(os.path.join(tmp_path, f"output_{r}.bin"), dtype=np.uint16).reshape(world * m, n)
         ok, precision, eb = verify.reference_check(torch.from_numpy(raw).view(torch.bfloat16), gold[r], k)
         assert ok, (r, precision, eb)
+
+
+def _check(driver, *args):
+    r = subprocess.run([driver, "--check", *[str(a) for a in args]], capture_output=True, text=True)
+    return r.returncode, r.stdout.split()
+
+
+@pytest.mark.parametrize("args", [
+    ("mmar", 2, 512, 2048, 1024),                      # benchmark configuration 1
+    ("agmm", 8, 1024, 4096, 8192),                     # 2
+    ("mmrs", 8, 8192, 8192, 2048),                     # 3
+    ("a5fp8mxagmm", 8, 2048, 4096, 7168),              # 4
+    ("a5moe", 8, 4096, 4096, 7168, 8, 256),            # 5 (n = 2 x intermediate)
+    ("a5mxfp8mmrs", 8, 8192, 8192, 2048),
+    ("a5agmm", 1, 8, 8, 8),
+])
+def test_operator_classes_accept_the_benchmark_configurations(driver, args):
+    """CheckCocTilingParams of every operator class, and the buffers fit the reference's 1004 MiB symmetric buffer."""
+    rc, out = _check(driver, *args)
+    assert rc == 0 and out[0] == "ok", out
+    assert int(out[1]) <= 1004 * 1024 * 1024
+
+
+@pytest.mark.parametrize("args", [
+    ("mmrs", 8, 8190, 8192, 2048),                     # rows not divisible by the ranks
+    ("agmm", 8, 1024, 4100, 8192),                     # n not a multiple of 8 (16-byte rows)
+    ("agmm", 8, 65536, 4096, 8192),                    # gathered A would not fit the symmetric buffer
+    ("a5fp8mxagmm", 8, 2048, 4096, 7170),              # k not a multiple of the 32-element scale block
+    ("a5mxfp8mmrs", 2, 192, 256, 128),                 # rows per rank not a multiple of 128
+    ("a5moe", 8, 4096, 4096, 7000, 8, 256),            # k % 256, as the reference operator demands
+    ("a5moe", 8, 4096, 4096, 7168, 8, 250),            # experts not divisible by the ranks
+    ("mmar", 0, 512, 2048, 1024),                      # no ranks
+])
+def test_operator_classes_reject_unusable_tilings(driver, args):
+    rc, out = _check(driver, *args)
+    assert rc == 2 and out == ["rejected"], out
+
+
+def test_check_mode_reports_unknown_kernels(driver):
+    rc, _ = _check(driver, "nope", 2, 8, 8, 8)
+    assert rc == 1
