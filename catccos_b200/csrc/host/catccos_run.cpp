@@ -10,18 +10,51 @@
 //   catccos_run --list        prints the registered operator names
 //   catccos_run --check <kernel> <rank_size> <m> <n> <k> [topK expertNum]
 //                             CheckCocTilingParams + symmetric / workspace bytes, no device needed
+//   catccos_run --estimate <kernel> <rank_size> <m> <n> <k> [m0 blockNum]
+//                             the B200 cost model's tiling choice and predicted time, no device needed
 #include <cuda_runtime.h>
 
 #include <cstdlib>
 #include <iostream>
 #include <string>
 
+#include "catccos_host/cost_model.h"
 #include "catccos_host/launch_map.h"
 #include "catccos_host/operators.h"
 
 int main(int argc, char **argv) {
     if (argc >= 2 && std::string(argv[1]) == "--list") {
         for (const auto &n : OperatorRegistry::Instance().Names()) std::cout << n << "\n";
+        return 0;
+    }
+    if (argc >= 7 && std::string(argv[1]) == "--estimate") {
+        // catccos_run --estimate <kernel> <rank_size> <m> <n> <k> [m0 blockNum]: the cost model's choice (or the
+        // cost of the given candidate): "m0 blockNum cost_us compute_us comm_us"
+        const CocCommType ct = GetCommType(argv[2]);
+        const uint32_t rs = static_cast<uint32_t>(std::atoi(argv[3]));
+        const COCMatMulInfo info{std::atoll(argv[4]), std::atoll(argv[6]), std::atoll(argv[5])};
+        CostModelResult r;
+        if (argc >= 9) {
+            catccos_cost::Family family;
+            bool mx;
+            if (ct == UNKNOWN || !catccos_cost::FamilyOf(ct, family, mx)) {
+                std::cout << "unsupported\n";
+                return 2;
+            }
+            CostModelTiling t;
+            t.m0 = static_cast<uint32_t>(std::atoi(argv[7]));
+            t.n0 = 256;
+            t.k0 = mx ? 128 : 64;
+            t.blockNum = static_cast<uint32_t>(std::atoi(argv[8]));
+            r = catccos_cost::Evaluate(info, family, mx, rs, t, CostModelHardwareConfig{});
+        } else {
+            r = ct == UNKNOWN ? CostModelResult{} : SelectCostModelTiling(info, ct, rs);
+        }
+        if (!r.IsSuccess()) {
+            std::cout << (r.status == CostModelStatus::UNSUPPORTED ? "unsupported" : "invalid") << "\n";
+            return 2;
+        }
+        std::printf("%u %u %.2f %.2f %.2f\n", r.tiling.m0, r.tiling.blockNum, r.cost, r.computeUs, r.commUs);
         return 0;
     }
     if (argc >= 7 && std::string(argv[1]) == "--check") {
