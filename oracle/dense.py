@@ -77,3 +77,13 @@ def golden_mx_matmul_reduce_scatter(a_codes_list, a_scales_list, b_codes_list, b
         c = torch.matmul(torch.from_numpy(a), torch.from_numpy(np.ascontiguousarray(b)))
         total = c if total is None else total + c
     return list(torch.chunk(total, len(a_codes_list), dim=0))
+
+
+def golden_fp4_allgather_matmul(a_list, b_list):
+    """FP4 AllGather-Matmul golden on operands that are already dequantised to fp32 (MXFP4:
+    mxquant.dequant_mxfp4, NVFP4: mxquant.dequant_nvfp4): C_r = cat_s(A_s) @ B_r in fp32, as
+    examples/utils/gen_data_fp4_mx_allgather_matmul.py:665-677 does for MXFP4.  a_list[s]: [m, k],
+    b_list[r]: [k, n]."""
+    import numpy as np
+    gathered = torch.from_numpy(np.concatenate(a_list, axis=0))
+    return [torch.matmul(gathered, torch.from_numpy(np.ascontiguousarray(b))) for b in b_list]

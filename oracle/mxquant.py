@@ -300,3 +300,68 @@ def dequant_mx(codes: np.ndarray, scale_bytes: np.ndarray, fmt: str = "e4m3") ->
     sc = np.exp2(scale_bytes[:, :nb].astype(np.float32) - 127.0).astype(np.float32)
     val = e4m3_to_f32(codes) if fmt == "e4m3" else e5m2_to_f32(codes)
     return (val * np.repeat(sc, BLOCK, axis=1)[:, :k]).astype(np.float32)
+
+
+# --------------------------------------------------------------------------- #
+# FP4 operands of the GEMM goldens
+# --------------------------------------------------------------------------- #
+def unpack_e2m1(packed: np.ndarray, k: int) -> np.ndarray:
+    """[M, ceil(k/2)] bytes -> fp32 [M, k]; low nibble = even column
+    (examples/utils/gen_data_fp4_mx_allgather_matmul.py:521-543)."""
+    packed = np.asarray(packed, dtype=np.uint8)
+    idx = np.empty((packed.shape[0], packed.shape[1] * 2), dtype=np.uint8)
+    idx[:, 0::2] = packed & 0x0F
+    idx[:, 1::2] = packed >> 4
+    return _E2M1_LUT[idx[:, :k]]
+
+
+def dequant_mxfp4(packed: np.ndarray, scale_bytes: np.ndarray, k: int) -> np.ndarray:
+    """MXFP4: e2m1 nibbles [M, ceil(k/2)] and E8M0 bytes per 32 along k -> fp32 [M, k]."""
+    nb = (k + BLOCK - 1) // BLOCK
+    sc = np.exp2(scale_bytes[:, :nb].astype(np.float32) - 127.0).astype(np.float32)
+    return (unpack_e2m1(packed, k) * np.repeat(sc, BLOCK, axis=1)[:, :k]).astype(np.float32)
+
+
+# NVFP4 has no counterpart in the reference (its FP4 is MXFP4): PARITY UNPINNED.  The definition
+# below is the published one: e2m1 codes, one e4m3 scale per 16 elements along k, one fp32 scale per
+# tensor; tensor scale = amax / (448 * 6), block scale = e4m3_rne(block amax / (6 * tensor scale)),
+# codes = e2m1 nearest (ties to the even code) of x / (block scale * tensor scale).
+NVFP4_BLOCK = 16
+
+
+def _e2m1_rne_index(v: np.ndarray) -> np.ndarray:
+    """Nearest e2m1 magnitude index 0..7 with ties to the even mantissa code."""
+    grid = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6], dtype=np.float64)
+    a = np.minimum(np.abs(v.astype(np.float64)), 6.0)
+    hi = np.clip(np.searchsorted(grid, a, side="left"), 0, 7)
+    lo = np.clip(hi - 1, 0, 7)
+    dl, dh = a - grid[lo], grid[hi] - a
+    pick_lo = (dl < dh) | ((dl == dh) & (lo % 2 == 0))
+    return np.where(pick_lo, lo, hi).astype(np.uint8)
+
+
+def quantize_nvfp4(x: np.ndarray):
+    """x fp32 [M, K] (K % 16 == 0) -> (nibble indices [M,K], packed bytes [M,K/2], e4m3 scale bytes
+    [M, K/16], tensor scale fp32, dequant fp32 [M,K])."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    m, k = x.shape
+    assert k % NVFP4_BLOCK == 0
+    amax = float(np.abs(x).max())
+    tscale = np.float32(amax / (E4M3_MAX * E2M1_MAX)) if amax > 0 else np.float32(1.0)
+    blocks = x.reshape(m, k // NVFP4_BLOCK, NVFP4_BLOCK)
+    bmax = np.abs(blocks).max(axis=-1)
+    sbyte = f32_to_e4m3_rne((bmax / (np.float32(E2M1_MAX) * tscale)).astype(np.float32))
+    sval = e4m3_to_f32(sbyte) * tscale
+    safe = np.where(sval > 0, sval, np.float32(1.0))
+    mag = _e2m1_rne_index(blocks / safe[..., None])
+    idx = np.where(blocks < 0, mag | np.uint8(8), mag).astype(np.uint8)
+    idx = np.where(mag == 0, np.uint8(0), idx)                      # no negative zero
+    deq = (_E2M1_LUT[idx] * sval[..., None]).reshape(m, k).astype(np.float32)
+    idx = idx.reshape(m, k)
+    packed = (idx[:, 0::2] | (idx[:, 1::2] << 4)).astype(np.uint8)
+    return idx, packed, sbyte, tscale, deq
+
+
+def dequant_nvfp4(packed: np.ndarray, scale_bytes: np.ndarray, tscale, k: int) -> np.ndarray:
+    sc = e4m3_to_f32(scale_bytes) * np.float32(tscale)
+    return (unpack_e2m1(packed, k) * np.repeat(sc, NVFP4_BLOCK, axis=1)[:, :k]).astype(np.float32)

@@ -273,6 +273,25 @@ def alltoallv_gmm_fixture(ref_root):
     np.savez_compressed(os.path.join(HERE, "alltoallv_gmm.npz"), **out)
 
 
+
+def fp4_agmm_fixture(ref_root):
+    """MXFP4 (e2m1, E8M0 per 32) AllGather-Matmul: the reference's generator as a script, 2 ranks, transB = 1."""
+    utils_dir = os.path.join(ref_root, "examples", "utils")
+    env = dict(os.environ, PYTHONPATH=utils_dir)
+    world, m, n, k = 2, 16, 32, 64
+    out = {"shape": np.array([world, m, n, k])}
+    with tempfile.TemporaryDirectory() as td:
+        subprocess.check_call([sys.executable, os.path.join(utils_dir, "gen_data_fp4_mx_allgather_matmul.py"), "fp4agmm",
+                               "bf16", str(world), str(m), str(n), str(k), "0", "1", td], stdout=subprocess.DEVNULL, env=env)
+        for r in range(world):
+            out[f"a{r}"] = np.fromfile(os.path.join(td, f"input_a_{r}.bin"), dtype=np.uint8).reshape(m, k // 2)
+            out[f"a_scale{r}"] = np.fromfile(os.path.join(td, f"input_a_scale_{r}.bin"), dtype=np.uint8).reshape(m, -1)
+            out[f"b{r}"] = np.fromfile(os.path.join(td, f"input_b_{r}.bin"), dtype=np.uint8).reshape(n, k // 2)    # B^T
+            out[f"b_scale{r}"] = np.fromfile(os.path.join(td, f"input_b_scale_{r}.bin"), dtype=np.uint8).reshape(n, -1)
+            out[f"golden{r}"] = np.fromfile(os.path.join(td, f"golden_{r}.bin"), dtype=np.float32).reshape(world * m, n)
+    np.savez_compressed(os.path.join(HERE, "fp4_agmm.npz"), **out)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     sys.path.insert(0, os.path.join(ref_root, "examples", "utils"))
@@ -284,6 +303,7 @@ def main():
     moe_fixture()
     mx_mmrs_fixture(ref_root)
     alltoallv_gmm_fixture(ref_root)
+    fp4_agmm_fixture(ref_root)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -255,3 +255,30 @@ def test_grouped_matmul_alltoallv_golden(golden_dir):
         rows = back[r].shape[0]
         assert rows == int(counts[r].sum())
         assert np.allclose(back[r], f[f"c_golden{r}"][:rows], rtol=1e-5, atol=1e-4)
+
+
+def test_mxfp4_allgather_matmul_golden(golden_dir):
+    """MXFP4 operands (packed e2m1, E8M0 per 32) of the reference's FP4 AllGather-Matmul generator."""
+    f = _load(golden_dir, "fp4_agmm.npz")
+    world, m, n, k = [int(v) for v in f["shape"]]
+    a = [mxquant.dequant_mxfp4(f[f"a{r}"], f[f"a_scale{r}"], k) for r in range(world)]
+    b = [np.ascontiguousarray(mxquant.dequant_mxfp4(f[f"b{r}"], f[f"b_scale{r}"], k).T) for r in range(world)]   # files hold B^T
+    outs = dense.golden_fp4_allgather_matmul(a, b)
+    for r in range(world):
+        assert np.allclose(outs[r].numpy(), f[f"golden{r}"], rtol=1e-5, atol=1e-5)
+
+
+def test_nvfp4_definition_round_trips():
+    """NVFP4 is not in the reference (parity unpinned): check the definition against itself — values on
+    the e2m1 x e4m3 grid survive quantisation exactly, everything else lands within half a step."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((8, 64)).astype(np.float32) * 3
+    idx, packed, sb, ts, deq = mxquant.quantize_nvfp4(x)
+    assert packed.shape == (8, 32) and sb.shape == (8, 4)
+    assert np.array_equal(mxquant.dequant_nvfp4(packed, sb, ts, 64), deq)
+    idx2, packed2, sb2, ts2, deq2 = mxquant.quantize_nvfp4(deq)       # grid values: a fixed point
+    assert np.allclose(deq2, deq, rtol=0, atol=1e-6 * np.abs(deq).max())
+    sval = np.repeat(mxquant.e4m3_to_f32(sb) * ts, 16, axis=1)
+    assert (np.abs(deq - x) <= 1.0 * sval + 1e-6).all()              # largest e2m1 step is 2 (between 4 and 6): half of it
+    # ties go to the even code: 2.5 -> 2, 3.5 -> 4 (in units of the block scale)
+    assert mxquant._e2m1_rne_index(np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])).tolist() == [0, 2, 2, 4, 4, 6, 6]
