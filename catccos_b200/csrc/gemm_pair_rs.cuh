@@ -316,6 +316,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 }
                 if (!(ok = epi.sync(ctl))) break;
                 if (*verdict == 2) {
+                    // every thread has to have read the first verdict before warp 2 overwrites it
+                    if (!(ok = epi.sync(ctl))) break;
                     if (!(ok = publish(true))) break;
                     if (p.trace) flush_ns += globaltimer_ns() - tp0;
                     if (warp == 2) {

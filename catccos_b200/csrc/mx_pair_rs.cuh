@@ -306,6 +306,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 }
                 if (!(ok = epi.sync(ctl))) break;
                 if (*verdict == 2) {
+                    // every thread has to have read the first verdict before warp 2 overwrites it
+                    if (!(ok = epi.sync(ctl))) break;
                     if (!(ok = publish(true))) break;
                     if (warp == 2) {
                         const bool w = !my_flag || wait_flag_ge(my_flag, my_need, ctl, remote ? W_ENTERED : W_RS_PARTIAL,
