@@ -293,7 +293,9 @@ def fp4_agmm_fixture(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     sys.path.insert(0, os.path.join(ref_root, "examples", "utils"))
     torch.manual_seed(0)
     mx_quant_fixture()
