@@ -51,6 +51,10 @@ SIGNATURES = {
     "catccos_debug_wait_unset_flag": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint32]),
     "catccos_debug_set_flags": (ctypes.c_int, [ctypes.c_uint32]),
     "catccos_debug_set_trace": (ctypes.c_int, [ctypes.c_void_p]),
+    "catccos_debug_rs_tile_order": (ctypes.c_int, [ctypes.c_int32] * 5 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32,
+                                                                        ctypes.POINTER(ctypes.c_int32)]),
+    "catccos_debug_ag_tile_order": (ctypes.c_int, [ctypes.c_int32] * 4 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
+    "catccos_debug_ag_push_order": (ctypes.c_int, [ctypes.c_int32] * 3 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
     "catccos_symmetric_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(CocTilingParams)]),
     "catccos_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(CocTilingParams)]),
     "catccos_launch": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32] + LAUNCH_ARGS),

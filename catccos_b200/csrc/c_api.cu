@@ -7,6 +7,7 @@
 #include "mx_quant.h"
 #include "mxq_allgather.h"
 #include "ptx.cuh"
+#include "sched.h"
 #include "symm_heap.h"
 
 using namespace cb;
@@ -341,6 +342,50 @@ int catccos_debug_set_trace(void *device_buf) {
     }
     team()->trace_dev = static_cast<unsigned long long *>(device_buf);
     return CATCCOS_OK;
+}
+
+int catccos_debug_rs_tile_order(int32_t world, int32_t rank, int32_t rows_per_rank, int32_t n, int32_t pairs, int32_t *out,
+                                int32_t capacity, int32_t *lag) {
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || rows_per_rank < 1 || n < 1 || pairs < 1 ||
+        (!out && capacity > 0)) {
+        set_error("catccos_debug_rs_tile_order: invalid argument");
+        return -CATCCOS_ERR_INVALID;
+    }
+    const int nt = (n + BN - 1) / BN, stripes = (rows_per_rank + 2 * BM - 1) / (2 * BM);
+    const RsOrder o = rs_order_make(world, nt, stripes, pairs);
+    if (lag) *lag = o.lag;
+    const int tiles = rs_order_tiles(o);
+    for (int t = 0; t < tiles && t < capacity; ++t) rs_order_decode(o, rank, t, out[3 * t], out[3 * t + 1], out[3 * t + 2]);
+    return tiles;
+}
+
+int catccos_debug_ag_tile_order(int32_t world, int32_t rank, int32_t m, int32_t n, int32_t *out, int32_t capacity) {
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || m < 1 || n < 1 || (!out && capacity > 0)) {
+        set_error("catccos_debug_ag_tile_order: invalid argument");
+        return -CATCCOS_ERR_INVALID;
+    }
+    const int nt = (n + BN - 1) / BN, per_src = ((m + 2 * BM - 1) / (2 * BM)) * nt;
+    const int tiles = world * per_src;
+    for (int t = 0; t < tiles && t < capacity; ++t)
+        ag_order_decode(world, per_src, nt, rank, t, out[3 * t], out[3 * t + 1], out[3 * t + 2]);
+    return tiles;
+}
+
+int catccos_debug_ag_push_order(int32_t world, int32_t rank, int32_t m, int32_t *out, int32_t capacity) {
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || m < 1 || (!out && capacity > 0)) {
+        set_error("catccos_debug_ag_push_order: invalid argument");
+        return -CATCCOS_ERR_INVALID;
+    }
+    const int units_per_dest = ((m + BM - 1) / BM) * kAgSubChunks;
+    const int total = (world - 1) * units_per_dest;
+    for (int u = 0; u < total && u < capacity; ++u) {
+        int d, cu;
+        ag_push_decode(world, units_per_dest, rank, u, d, cu);
+        out[3 * u] = d;
+        out[3 * u + 1] = cu / kAgSubChunks;
+        out[3 * u + 2] = cu % kAgSubChunks;
+    }
+    return total;
 }
 
 size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {

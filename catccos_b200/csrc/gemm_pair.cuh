@@ -13,6 +13,7 @@
 #include "common.h"
 #include "gemm_fused.cuh"
 #include "ptx.cuh"
+#include "sched.h"
 
 namespace cb {
 
@@ -99,12 +100,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
 
     // tile t -> (source rank s, 256-row tile mi2, column tile ni); own rows first, then rank+1, ...
     auto decode = [&](int t, int &s, int &mi2, int &ni, bool &gathered) {
-        const int j = t / per_src;
-        const int u = t - j * per_src;
-        s = (rank + j) % R;
-        mi2 = u / nt;
-        ni = u - mi2 * nt;
-        gathered = (j != 0);
+        ag_order_decode(R, per_src, nt, rank, t, s, mi2, ni);
+        gathered = (s != rank);
     };
 
     if (warp == 0) {
@@ -294,9 +291,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                 uint64_t entered_wait_ns = 0;
                 if (ctid == 0) CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
                 for (int u = lane_id; u < total && ok; u += n_lanes) {
-                    const int jj = u / units_per_dest;
-                    const int d = (rank + R - 1 - jj) % R;
-                    const int cu = u - jj * units_per_dest;
+                    int d, cu;
+                    ag_push_decode(R, units_per_dest, rank, u, d, cu);
                     const int chunk = cu / kAgSubChunks, sub = cu % kAgSubChunks;
                     const int r0 = chunk * BM + sub * (BM / kAgSubChunks);
                     const int r1 = min(p.M, r0 + BM / kAgSubChunks);

@@ -14,6 +14,7 @@
 #include "gemm_fused.cuh"
 #include "gemm_pair.cuh"
 #include "ptx.cuh"
+#include "sched.h"
 
 namespace cb {
 
@@ -95,40 +96,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     ctl.rank = rank;
     if (threadIdx.x == 0) CB_TRACE(TR_START, globaltimer_ns());
 
-    // Tile order.  The owner's rows are cut into stripes of 256 rows (nt pair tiles each).  "Super-
-    // round" q sends stripe q of every peer (owners rank+1, rank+2, ...) and then reduces the OWN
-    // stripe q - lag, whose partials the peers sent `lag` super-rounds earlier.  Peer traffic is thus
-    // spread over the whole kernel instead of its first (R-1)/R, and only `lag` own stripes remain
-    // for the end.  A partial is at least (lag + 1) * nt tiles ahead of the own tile that needs it;
-    // lag is sized so that this is 1.5 tiles per CTA pair (compute, drain, store and the flag that
-    // follows one tile later take about one).
-    const int stripes = mt2;
-    int lag = (3 * pairs / 2 + nt - 1) / nt - 1;
-    lag = max(1, min(lag, stripes));
-    const int head = lag * (R - 1) * nt;                        // super-rounds 0 .. lag-1: peers only
-    const int body = (stripes - lag) * R * nt;                  // super-rounds lag .. stripes-1: peers, then own
+    // tile order: super-rounds of peer stripes followed by a lagging own stripe (sched.h)
+    const RsOrder order = rs_order_make(R, nt, mt2, pairs);
     auto decode = [&](int t, int &d, int &mi2, int &ni, bool &lead_ok) {
-        int j;      // 0 .. R-2: peer rank+1+j;  R-1: own rows
-        if (t < head) {
-            const int q = t / ((R - 1) * nt);
-            const int u = t - q * (R - 1) * nt;
-            j = u / nt;
-            ni = u - j * nt;
-            mi2 = q;
-        } else if (t < head + body) {
-            const int v = t - head;
-            const int q = lag + v / (R * nt);
-            const int u = v - (q - lag) * R * nt;
-            j = u / nt;
-            ni = u - j * nt;
-            mi2 = (j == R - 1) ? q - lag : q;
-        } else {
-            const int v = t - head - body;
-            j = R - 1;
-            mi2 = stripes - lag + v / nt;
-            ni = v - (v / nt) * nt;
-        }
-        d = (rank + 1 + j) % R;
+        rs_order_decode(order, rank, t, d, mi2, ni);
         lead_ok = d * mr + mi2 * BM2 < min(p.M, (d + 1) * mr);
     };
 

@@ -9,6 +9,7 @@
 // per SM instead of 49.5 KiB, six stages instead of four.
 #pragma once
 #include "mx_gemm.cuh"
+#include "sched.h"
 
 namespace cb {
 
@@ -100,12 +101,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
     if (threadIdx.x == 0) CB_MX_TRACE(TR_START, globaltimer_ns());
     auto flagp = [&](int pe, uint32_t word) { return reinterpret_cast<uint32_t *>(p.heap_base[pe]) + word; };
     auto decode = [&](int t, int &s, int &mi2, int &ni, bool &gathered) {
-        const int j = t / per_src;
-        const int u = t - j * per_src;
-        s = (rank + j) % R;
-        mi2 = u / nt;
-        ni = u - mi2 * nt;
-        gathered = (j != 0);
+        ag_order_decode(R, per_src, nt, rank, t, s, mi2, ni);
+        gathered = (s != rank);
     };
 
     if (warp == 0) {
@@ -288,9 +285,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                 uint32_t entered_ok = 0;
                 uint32_t piece = 0;
                 for (int u = lane_id; u < total && ok; u += n_lanes) {
-                    const int jj = u / units_per_dest;
-                    const int d = (rank + R - 1 - jj) % R;
-                    const int cu = u - jj * units_per_dest;
+                    int d, cu;
+                    ag_push_decode(R, units_per_dest, rank, u, d, cu);
                     const int chunk = cu / kMxFlagsPerChunk, sub = cu % kMxFlagsPerChunk;
                     const uint8_t *src;
                     uint8_t *dst;

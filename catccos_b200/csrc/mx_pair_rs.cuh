@@ -9,6 +9,7 @@
 #pragma once
 #include "gemm_pair_rs.cuh"
 #include "mx_pair.cuh"
+#include "sched.h"
 
 namespace cb {
 
@@ -112,34 +113,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     if (threadIdx.x == 0) CB_MX_TRACE(TR_START, globaltimer_ns());
     auto flagp = [&](int pe, uint32_t word) { return reinterpret_cast<uint32_t *>(p.heap_base[pe]) + word; };
 
-    // tile order: the super-round order of the f16/bf16 pair reduce-scatter kernel
-    const int stripes = mt2;
-    int lag = (3 * pairs / 2 + nt - 1) / nt - 1;
-    lag = max(1, min(lag, stripes));
-    const int head = lag * (R - 1) * nt;
-    const int body = (stripes - lag) * R * nt;
+    // tile order: super-rounds of peer stripes followed by a lagging own stripe (sched.h)
+    const RsOrder order = rs_order_make(R, nt, mt2, pairs);
     auto decode = [&](int t, int &d, int &mi2, int &ni, bool &lead_ok) {
-        int j;
-        if (t < head) {
-            const int q = t / ((R - 1) * nt);
-            const int u = t - q * (R - 1) * nt;
-            j = u / nt;
-            ni = u - j * nt;
-            mi2 = q;
-        } else if (t < head + body) {
-            const int v = t - head;
-            const int q = lag + v / (R * nt);
-            const int u = v - (q - lag) * R * nt;
-            j = u / nt;
-            ni = u - j * nt;
-            mi2 = (j == R - 1) ? q - lag : q;
-        } else {
-            const int v = t - head - body;
-            j = R - 1;
-            mi2 = stripes - lag + v / nt;
-            ni = v - (v / nt) * nt;
-        }
-        d = (rank + 1 + j) % R;
+        rs_order_decode(order, rank, t, d, mi2, ni);
         lead_ok = d * mr + mi2 * BM2 < (d + 1) * mr;
     };
 

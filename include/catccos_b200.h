@@ -128,6 +128,20 @@ CATCCOS_API int catccos_debug_set_flags(uint32_t flags);
  * stamps and accumulated wait times of later launches; NULL switches tracing off. */
 CATCCOS_API int catccos_debug_set_trace(void *device_buf);
 
+/* The work orders of the CTA-pair kernels, computed on the host by the very functions the kernels use
+ * (no device needed; no reference counterpart of their own — the reference's orders are CommSwizzle::GetCoord,
+ * include/catccos/catccos.hpp:165-193, and its block schedulers).  Each call fills `out` with up to `capacity`
+ * triples and returns how many the order has, or a negative CATCCOS_ERR_* code.
+ *   rs_tile_order: pair tiles of Matmul-ReduceScatter / AllReduce for `rank`: (owner, 256-row stripe, column tile);
+ *                  `rows_per_rank` rows per owner, `pairs` CTA pairs; *lag (optional) receives the own-stripe lag.
+ *   ag_tile_order: pair tiles of AllGather-Matmul: (source rank, 256-row tile, column tile); m = rows of one rank.
+ *   ag_push_order: all-gather push units of `rank`: (destination, 128-row chunk, unit inside the chunk). */
+CATCCOS_API int catccos_debug_rs_tile_order(int32_t world, int32_t rank, int32_t rows_per_rank, int32_t n, int32_t pairs,
+                                            int32_t *out, int32_t capacity, int32_t *lag);
+CATCCOS_API int catccos_debug_ag_tile_order(int32_t world, int32_t rank, int32_t m, int32_t n, int32_t *out,
+                                            int32_t capacity);
+CATCCOS_API int catccos_debug_ag_push_order(int32_t world, int32_t rank, int32_t m, int32_t *out, int32_t capacity);
+
 /* Bytes of the `symmetric` buffer an operator carves for itself (the reference sizes it as one
  * fixed SHMEM_BUFF_BYTES allocation, utils/info.h:35). */
 CATCCOS_API size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling);

@@ -1,0 +1,124 @@
+"""Properties of the kernels' work orders, computed on the host by the functions the kernels themselves
+use (catccos_b200/csrc/sched.h through catccos_debug_*_order).  No device needed."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from catccos_b200 import lib
+
+BM, BN, SUB = 128, 256, 32          # rows of a push chunk, columns of a tile, push units per chunk
+
+
+def _rs(world, rank, rows_per_rank, n, pairs):
+    cap = 1 << 16
+    out = (ctypes.c_int32 * (3 * cap))()
+    lag = ctypes.c_int32()
+    cnt = lib().catccos_debug_rs_tile_order(world, rank, rows_per_rank, n, pairs, out, cap, ctypes.byref(lag))
+    assert 0 <= cnt <= cap
+    return np.frombuffer(out, dtype=np.int32, count=3 * cnt).reshape(cnt, 3).copy(), lag.value
+
+
+def _ag(world, rank, m, n):
+    cap = 1 << 16
+    out = (ctypes.c_int32 * (3 * cap))()
+    cnt = lib().catccos_debug_ag_tile_order(world, rank, m, n, out, cap)
+    assert 0 <= cnt <= cap
+    return np.frombuffer(out, dtype=np.int32, count=3 * cnt).reshape(cnt, 3).copy()
+
+
+def _push(world, rank, m):
+    cap = 1 << 16
+    out = (ctypes.c_int32 * (3 * cap))()
+    cnt = lib().catccos_debug_ag_push_order(world, rank, m, out, cap)
+    assert 0 <= cnt <= cap
+    return np.frombuffer(out, dtype=np.int32, count=3 * cnt).reshape(cnt, 3).copy()
+
+
+RS_SHAPES = [(8, 1024, 8192, 74), (4, 2048, 8192, 74), (2, 4096, 8192, 74), (1, 8192, 8192, 74), (2, 256, 2048, 74),
+             (8, 128, 512, 9), (4, 75, 264, 18), (3, 700, 520, 24), (8, 1024, 8192, 9)]
+
+
+@pytest.mark.parametrize("world,rows,n,pairs", RS_SHAPES)
+def test_reduce_scatter_order_visits_every_tile_once(world, rows, n, pairs):
+    nt, stripes = -(-n // BN), -(-rows // (2 * BM))
+    want = {(d, s, c) for d in range(world) for s in range(stripes) for c in range(nt)}
+    for rank in range(world):
+        order, lag = _rs(world, rank, rows, n, pairs)
+        assert len(order) == len(want) and {tuple(x) for x in order} == want
+        assert 1 <= lag <= stripes
+
+
+@pytest.mark.parametrize("world,rows,n,pairs", [s for s in RS_SHAPES if s[0] > 1])
+def test_partials_are_sent_before_the_own_tile_that_sums_them(world, rows, n, pairs):
+    """For every own tile of a rank, every peer's partial of it sits at least (lag + 1) * nt positions
+    earlier in that peer's order (lag * nt when the lag spans all stripes, i.e. own rows simply come
+    last): all ranks walk their orders at the same pace, so the partial is computed, stored and
+    flagged before the own tile's epilogue asks for it."""
+    nt, stripes = -(-n // BN), -(-rows // (2 * BM))
+    orders = [_rs(world, r, rows, n, pairs) for r in range(world)]
+    for me in range(world):
+        mine, lag = orders[me]
+        own_pos = {(s, c): i for i, (d, s, c) in enumerate(mine) if d == me}
+        for peer in range(world):
+            if peer == me:
+                continue
+            sent = {(s, c): i for i, (d, s, c) in enumerate(orders[peer][0]) if d == me}
+            assert sent.keys() == own_pos.keys()
+            head_start = min(own_pos[k] - sent[k] for k in own_pos)
+            assert head_start >= (lag + 1 if lag < stripes else lag) * nt
+
+
+def test_reduce_scatter_lag_gives_one_and_a_half_tiles_per_pair_when_the_shape_allows():
+    # benchmark shape at 4 ranks: 8 stripes, 32 column tiles, 74 pairs -> lag 3: (3 + 1) * 32 = 128 >= 1.5 * 74
+    _, lag = _rs(4, 0, 2048, 8192, 74)
+    assert lag == 3
+    # at 8 ranks there are only 4 stripes: lag 3 as well; peer traffic still covers all but 3 of 32 stripe slots
+    _, lag8 = _rs(8, 0, 1024, 8192, 74)
+    assert lag8 == 3
+    # a single stripe: own rows necessarily last
+    order, lag1 = _rs(2, 1, 256, 2048, 74)
+    assert lag1 == 1 and [d for d, _, _ in order] == [0] * 8 + [1] * 8
+
+
+@pytest.mark.parametrize("world,m,n", [(8, 1024, 4096), (4, 2048, 4096), (2, 320, 520), (1, 200, 264), (8, 100, 256)])
+def test_allgather_order_own_rows_first_then_sources_in_ring_order(world, m, n):
+    nt, mt2 = -(-n // BN), -(-m // (2 * BM))
+    for rank in range(world):
+        order = _ag(world, rank, m, n)
+        assert len(order) == world * mt2 * nt
+        assert {tuple(x) for x in order} == {(s, a, b) for s in range(world) for a in range(mt2) for b in range(nt)}
+        sources = [int(s) for s in order[::mt2 * nt, 0]]
+        assert sources == [(rank + j) % world for j in range(world)]
+        # inside a source: 256-row tile major, so a chunk's flags are needed once for a run of nt tiles
+        first = order[:mt2 * nt]
+        assert [tuple(x[1:]) for x in first] == [(a, b) for a in range(mt2) for b in range(nt)]
+
+
+@pytest.mark.parametrize("world,m", [(8, 1024), (4, 2048), (2, 4096), (3, 200)])
+def test_push_order_serves_the_first_consumer_first_and_every_unit_once(world, m):
+    chunks = -(-m // BM)
+    per_dest = chunks * SUB
+    for rank in range(world):
+        push = _push(world, rank, m)
+        assert len(push) == (world - 1) * per_dest
+        dests = [int(d) for d in push[::per_dest, 0]]
+        assert dests == [(rank - 1 - j) % world for j in range(world - 1)]          # rank-1 consumes my rows first
+        for j, d in enumerate(dests):
+            block = push[j * per_dest:(j + 1) * per_dest]
+            assert (block[:, 0] == d).all()
+            assert [tuple(x[1:]) for x in block] == [(c, u) for c in range(chunks) for u in range(SUB)]   # row order
+    # consumer side: rank r multiplies source r+1 right after its own rows, and r+1 pushes to r first
+    for r in range(world):
+        src_after_own = (r + 1) % world
+        assert int(_push(world, src_after_own, m)[0, 0]) == r
+
+
+def test_order_functions_reject_bad_arguments():
+    out = (ctypes.c_int32 * 3)()
+    assert lib().catccos_debug_rs_tile_order(0, 0, 128, 256, 4, out, 1, None) < 0
+    assert lib().catccos_debug_rs_tile_order(2, 2, 128, 256, 4, out, 1, None) < 0
+    assert lib().catccos_debug_ag_tile_order(9, 0, 128, 256, out, 1) < 0
+    assert lib().catccos_debug_ag_push_order(2, 0, 0, out, 1) < 0
+    # a short buffer is filled up to its capacity and the full count is still reported
+    assert lib().catccos_debug_ag_tile_order(2, 0, 256, 512, out, 1) == 4
