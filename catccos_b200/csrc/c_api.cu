@@ -388,6 +388,24 @@ int catccos_debug_ag_push_order(int32_t world, int32_t rank, int32_t m, int32_t 
     return total;
 }
 
+int catccos_debug_slot_sequence(const uint64_t *sigs, const uint8_t *foreign_before, int32_t n, int32_t *half,
+                                int32_t *need_back) {
+    if (!sigs || !half || !need_back || n < 0) {
+        set_error("catccos_debug_slot_sequence: invalid argument");
+        return CATCCOS_ERR_INVALID;
+    }
+    Team t;     // a scratch team: only its launch bookkeeping is used
+    for (int i = 0; i < n; ++i) {
+        if (foreign_before && foreign_before[i]) ++t.epoch;
+        const uint32_t epoch = t.epoch + 1;
+        const LaunchSlot s = peek_slot(&t, sigs[i], epoch);
+        commit_slot(&t, sigs[i], epoch, s);
+        half[i] = s.half;
+        need_back[i] = static_cast<int32_t>(epoch - s.entered_need);
+    }
+    return CATCCOS_OK;
+}
+
 size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
     (void)dataType;
     if (!tiling) return 0;

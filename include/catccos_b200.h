@@ -141,6 +141,13 @@ CATCCOS_API int catccos_debug_rs_tile_order(int32_t world, int32_t rank, int32_t
 CATCCOS_API int catccos_debug_ag_tile_order(int32_t world, int32_t rank, int32_t m, int32_t n, int32_t *out,
                                             int32_t capacity);
 CATCCOS_API int catccos_debug_ag_push_order(int32_t world, int32_t rank, int32_t m, int32_t *out, int32_t capacity);
+/* The double-buffering decision of the dense and MXFP8 launchers, replayed on the host for a sequence of `n`
+ * launches: sigs[i] identifies operator + shape + buffer of launch i, foreign_before[i] != 0 means a launch of
+ * another operator family (which consumes an epoch) happened just before it.  half[i] receives the half of the
+ * symmetric region launch i uses, need_back[i] how many epochs back a peer may be and still be written to
+ * (1: it has entered the previous launch; 0: it must have entered this one).  No device needed. */
+CATCCOS_API int catccos_debug_slot_sequence(const uint64_t *sigs, const uint8_t *foreign_before, int32_t n, int32_t *half,
+                                            int32_t *need_back);
 
 /* Bytes of the `symmetric` buffer an operator carves for itself (the reference sizes it as one
  * fixed SHMEM_BUFF_BYTES allocation, utils/info.h:35). */

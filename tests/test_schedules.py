@@ -122,3 +122,33 @@ def test_order_functions_reject_bad_arguments():
     assert lib().catccos_debug_ag_push_order(2, 0, 0, out, 1) < 0
     # a short buffer is filled up to its capacity and the full count is still reported
     assert lib().catccos_debug_ag_tile_order(2, 0, 256, 512, out, 1) == 4
+
+
+def _slots(sigs, foreign=None):
+    n = len(sigs)
+    a = (ctypes.c_uint64 * n)(*sigs)
+    f = (ctypes.c_uint8 * n)(*(foreign or [0] * n))
+    half, back = (ctypes.c_int32 * n)(), (ctypes.c_int32 * n)()
+    assert lib().catccos_debug_slot_sequence(a, f, n, half, back) == 0
+    return list(half), list(back)
+
+
+def test_double_buffered_regions_alternate_only_for_back_to_back_identical_launches():
+    """Same operator, shape and buffer launched back to back: the halves alternate and a peer needs only to
+    have entered the previous launch.  Anything else in between (another shape, another operator family)
+    makes the next launch strict again: half 0, peers must have entered this very launch."""
+    A, B = 0x1111, 0x2222
+    half, back = _slots([A, A, A, A])
+    assert half == [0, 1, 0, 1] and back == [0, 1, 1, 1]
+    half, back = _slots([A, B, A, A, B, B])
+    assert half == [0, 0, 0, 1, 0, 1] and back == [0, 0, 0, 1, 0, 1]
+    # a MoE / quantise-all-gather launch between two identical launches consumes an epoch: strict again
+    half, back = _slots([A, A, A, A], foreign=[0, 0, 1, 0])
+    assert half == [0, 1, 0, 1] and back == [0, 1, 0, 1]
+    # safety argument in numbers: whenever a launch may write to a peer that is one launch behind, the launch
+    # that peer may still be running uses the OTHER half
+    for seq in ([A] * 7, [A, A, B, B, B, A, A, A]):
+        half, back = _slots(seq)
+        for i in range(1, len(seq)):
+            if back[i] == 1:
+                assert seq[i - 1] == seq[i] and half[i - 1] != half[i]
