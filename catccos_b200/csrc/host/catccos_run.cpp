@@ -10,6 +10,8 @@
 //   catccos_run --list        prints the registered operator names
 //   catccos_run --check <kernel> <rank_size> <m> <n> <k> [topK expertNum]
 //                             CheckCocTilingParams + symmetric / workspace bytes, no device needed
+//   catccos_run --tilings <kernel> <rank_size> <m> <n> <k> <csv>
+//                             the operator's tiling candidates with the model's prediction, as a CSV
 //   catccos_run --estimate <kernel> <rank_size> <m> <n> <k> [m0 blockNum]
 //                             the B200 cost model's tiling choice and predicted time, no device needed
 #include <cuda_runtime.h>
@@ -21,10 +23,32 @@
 #include "catccos_host/cost_model.h"
 #include "catccos_host/launch_map.h"
 #include "catccos_host/operators.h"
+#include "catccos_host/tiling.h"
 
 int main(int argc, char **argv) {
     if (argc >= 2 && std::string(argv[1]) == "--list") {
         for (const auto &n : OperatorRegistry::Instance().Names()) std::cout << n << "\n";
+        return 0;
+    }
+    if (argc >= 8 && std::string(argv[1]) == "--tilings") {
+        // catccos_run --tilings <kernel> <rank_size> <m> <n> <k> <csv>: writes the tiling candidates of the operator
+        // (those its CheckCocTilingParams accepts) with the cost model's prediction, one CSV row each
+        const CocCommType ct = GetCommType(argv[2]);
+        if (ct == UNKNOWN) {
+            std::cerr << "unknown kernel " << argv[2] << "\n";
+            return 1;
+        }
+        CocTilingParams t{};
+        t.m = static_cast<uint32_t>(std::atoi(argv[4]));
+        t.n = static_cast<uint32_t>(std::atoi(argv[5]));
+        t.k = static_cast<uint32_t>(std::atoi(argv[6]));
+        t.topK = 1;
+        t.epSize = static_cast<uint32_t>(std::atoi(argv[3]));
+        std::vector<TilingCandidate> cands;
+        const std::string opName = CommTypeOpNameMap().at(ct);
+        GetTilings(cands, t, opName, std::atoi(argv[3]));
+        if (!CreateTilingFile(argv[7]) || !WriteTilingInfos(opName, cands, argv[7])) return 1;
+        std::cout << cands.size() << "\n";
         return 0;
     }
     if (argc >= 7 && std::string(argv[1]) == "--estimate") {

@@ -67,3 +67,23 @@ def test_unsupported_and_invalid_requests(driver):
     assert _estimate(driver, "nope", 8, 4096, 4096, 7168) == (2, ["unsupported"])
     assert _estimate(driver, "agmm", 0, 4096, 4096, 7168) == (2, ["invalid"])
     assert _estimate(driver, "agmm", 2, 4096, 4096, 7168, 192, 148) == (2, ["invalid"])      # no such tile
+
+
+def test_tiling_candidates_csv(driver, tmp_path):
+    """GetTilings / CreateTilingFile / WriteTilingInfos of include/catccos_host/tiling.h (the reference's
+    tests/dynamic_tiling/include/tiling.h): candidates the operator accepts, one CSV row each."""
+    path = tmp_path / "tilings.csv"
+    r = subprocess.run([driver, "--tilings", "agmm", "8", "1024", "4096", "8192", str(path)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.split() == ["6"]
+    rows = path.read_text().strip().splitlines()
+    assert rows[0] == "Op,M,K,N,Transpose A,Transpose B,M0,N0,K0,blockNum,Model(us),Time(us)"
+    body = [x.split(",") for x in rows[1:]]
+    assert len(body) == 6 and all(b[0] == "AllGatherMatmul" and b[1:4] == ["1024", "8192", "4096"] for b in body)
+    assert {(b[6], b[9]) for b in body} == {("128", "148"), ("128", "74"), ("128", "37"), ("256", "148"), ("256", "74"), ("256", "36")}
+    best = min(body, key=lambda b: float(b[10]))
+    assert (best[6], best[9]) == ("256", "148") and all(b[11] == "" for b in body)      # the measured column is left open
+    # the MXFP8 operator has pair kernels only; a shape the operator rejects yields no candidates
+    r = subprocess.run([driver, "--tilings", "a5fp8mxagmm", "8", "2048", "4096", "7168", str(path)], capture_output=True, text=True)
+    assert r.stdout.split() == ["3"]
+    r = subprocess.run([driver, "--tilings", "mmrs", "8", "8190", "8192", "2048", str(path)], capture_output=True, text=True)
+    assert r.stdout.split() == ["0"]
