@@ -55,6 +55,10 @@ SIGNATURES = {
                                                                         ctypes.POINTER(ctypes.c_int32)]),
     "catccos_debug_ag_tile_order": (ctypes.c_int, [ctypes.c_int32] * 4 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
     "catccos_debug_ag_push_order": (ctypes.c_int, [ctypes.c_int32] * 3 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
+    "catccos_fp4_gemm_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32]),
+    "catccos_fp4_gemm": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float, ctypes.c_uint32,
+                                        ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]),
     "catccos_debug_slot_sequence": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint8), ctypes.c_int32,
                                                    ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]),
     "catccos_symmetric_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(CocTilingParams)]),

@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libcatccos_b200.so")
 DRIVER = os.path.join(HERE, "catccos_run")
-SOURCES = ["symm_heap.cu", "dense_ops.cu", "c_api.cu", "no_alloc.cu", "mx_quant.cu", "mx_ops.cu", "moe_aux.cu", "moe_ops.cu", "mxq_allgather.cu"]
+SOURCES = ["symm_heap.cu", "dense_ops.cu", "c_api.cu", "no_alloc.cu", "mx_quant.cu", "mx_ops.cu", "moe_aux.cu", "moe_ops.cu", "mxq_allgather.cu", "fp4_gemm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
 

@@ -2,6 +2,7 @@
 #include "../../include/catccos_b200.h"
 
 #include "dense_ops.h"
+#include "fp4_gemm.h"
 #include "moe_ops.h"
 #include "mx_ops.h"
 #include "mx_quant.h"
@@ -404,6 +405,21 @@ int catccos_debug_slot_sequence(const uint64_t *sigs, const uint8_t *foreign_bef
         need_back[i] = static_cast<int32_t>(epoch - s.entered_need);
     }
     return CATCCOS_OK;
+}
+
+size_t catccos_fp4_gemm_workspace_bytes(int32_t format, uint32_t m, uint32_t n, uint32_t k) {
+    return fp4_gemm_workspace_bytes(format, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k));
+}
+int catccos_fp4_gemm(void *stream, int32_t format, int32_t dataType, const void *A, const void *B, void *C, const void *aScale,
+                     const void *bScale, float alpha, uint32_t m, uint32_t n, uint32_t k, void *workspace, uint32_t blockNum) {
+    if (m > (1u << 30) || n > (1u << 30) || k > (1u << 30)) {
+        set_error("catccos_fp4_gemm: dimension too large");
+        return CATCCOS_ERR_INVALID;
+    }
+    return launch_fp4_gemm(static_cast<cudaStream_t>(stream), format, dataType, static_cast<const uint8_t *>(A),
+                           static_cast<const uint8_t *>(B), C, static_cast<const uint8_t *>(aScale),
+                           static_cast<const uint8_t *>(bScale), alpha, static_cast<int>(m), static_cast<int>(n),
+                           static_cast<int>(k), static_cast<uint8_t *>(workspace), blockNum);
 }
 
 size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {

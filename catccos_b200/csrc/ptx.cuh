@@ -189,6 +189,28 @@ __device__ __forceinline__ void umma_mxf8(uint32_t d_tmem, uint64_t adesc, uint6
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
         : "memory");
 }
+// Block-scaled FP4 (e2m1 data, two per byte, K = 64 per instruction).  VEC4 = true: NVFP4, one UE4M3
+// scale per 16 along K (four per instruction, scale_vec::4X); false: MXFP4, one UE8M0 scale per 32
+// (two per instruction, scale_vec::2X; the descriptor's sf_id picks the byte pair).
+template <bool VEC4>
+__device__ __forceinline__ void umma_fp4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa_tmem,
+                                         uint32_t sfb_tmem, uint32_t accumulate) {
+    if (VEC4) {
+        asm volatile(
+            "{\n .reg .pred P;\n setp.ne.b32 P, %6, 0;\n"
+            " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], P;\n}\n" ::"r"(
+                d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n .reg .pred P;\n setp.ne.b32 P, %6, 0;\n"
+            " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], P;\n}\n" ::"r"(
+                d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+            : "memory");
+    }
+}
 // All previously issued tcgen05.mma of this thread arrive on `bar` when they complete.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -312,6 +334,13 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t fmt, uint32_t m, 
 __host__ __device__ constexpr uint32_t make_idesc_mxf8(uint32_t m, uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id) {
     return (b_sf_id << 4) | (0u << 7) | (0u << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) |
            (a_sf_id << 29);
+}
+
+// Instruction descriptor, kind::mxf4nvf4 block-scaled: e2m1 x e2m1 (format code 1), K-major A and B;
+// ue8m0 = 1: UE8M0 scales (MXFP4), 0: UE4M3 scales (NVFP4).
+__host__ __device__ constexpr uint32_t make_idesc_fp4(uint32_t m, uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id,
+                                                      uint32_t ue8m0) {
+    return (b_sf_id << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (ue8m0 << 23) | ((m >> 4) << 24) | (a_sf_id << 29);
 }
 
 // ------------------------------------------------- system-scope flag ops ----

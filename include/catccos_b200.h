@@ -229,6 +229,20 @@ CATCCOS_API int catccos_launch_emulated(int32_t commType, int32_t dataType, void
                             CatccosKernelParams *params, uint8_t **workspaces, uint8_t *symmetric,
                             CocTilingParams *tiling, uint32_t transA, uint32_t transB);
 
+/* ------------------------------------------------------------------------ FP4 GEMM ---- */
+/* Block-scaled FP4 GEMM on one GPU: C[m, n] = alpha * dequant(A)[m, k] x dequant(B)[n, k]^T, fp32 accumulation,
+ * C in the 16-bit `dataType` (CATCCOS_FP16 / CATCCOS_BF16).  A and B hold two e2m1 codes per byte (low nibble =
+ * even k), both K-major (B as [n, k]).  format 0 = MXFP4: one E8M0 scale per 32 along k, scale rows
+ * [rows, even(k/32)] as the reference's FP4 operators store them (examples/ascend950_fp4_mx_allgather_matmul,
+ * golden examples/utils/gen_data_fp4_mx_allgather_matmul.py:563-677); format 1 = NVFP4: one E4M3 scale per 16
+ * along k, rows [rows, k/16], the two fp32 tensor scales multiplied into `alpha` (no reference counterpart: the
+ * reference's FP4 is MXFP4).  k % 64 == 0, n % 8 == 0.  `workspace`: catccos_fp4_gemm_workspace_bytes() bytes of
+ * device memory.  Needs no catccos_shmem_init.  Status: compiled for sm_100a, parity test not yet run on a GPU. */
+CATCCOS_API size_t catccos_fp4_gemm_workspace_bytes(int32_t format, uint32_t m, uint32_t n, uint32_t k);
+CATCCOS_API int catccos_fp4_gemm(void *stream, int32_t format, int32_t dataType, const void *A, const void *B, void *C,
+                                 const void *aScale, const void *bScale, float alpha, uint32_t m, uint32_t n, uint32_t k,
+                                 void *workspace, uint32_t blockNum);
+
 /* ------------------------------------------------------------------- host-buffer form ---- */
 /* The operator classes' AllocateDeviceSpace() (host -> device copy of the inputs), kernel launch
  * and WriteResultFile() (device -> host copy of the result) in one synchronous call, with memory
