@@ -56,3 +56,45 @@ def test_calls_fail_loudly_without_a_gpu_or_heap(library):
     assert lib.catccos_shmem_init(0, 2, 1 << 20, b"") == 1      # empty rendezvous string, as set_attr()
     # tiling struct layout: 17 uint32 fields
     assert ctypes.sizeof(library.CocTilingParams) == 17 * 4
+
+
+def test_error_behaviour_of_the_boundary_without_a_device():
+    """What a caller sees before any device work: status codes and messages, as the reference's host code
+    expects them (utils/shmem_init.h:16-39 rejects an empty ip_port; an unregistered (commType, dataType) pair
+    gives no kernel, tests/dynamic_tiling/include/launch_map.h:31-39)."""
+    import ctypes
+    from catccos_b200 import KernelParams, lib, runtime as rt
+    L = lib()
+    t = rt.tiling(1024, 8192, 4096, 8)
+    kp = KernelParams()
+    assert L.catccos_launch(rt.ALLGATHER_MATMUL, rt.BF16, None, 0, 0, ctypes.byref(kp), None, None, ctypes.byref(t), 0, 0) == 2
+    assert b"not initialised" in L.catccos_last_error()                       # CATCCOS_ERR_NOT_INIT
+    assert L.catccos_launch(99, rt.BF16, None, 0, 0, ctypes.byref(kp), None, None, ctypes.byref(t), 0, 0) == 1
+    assert b"no kernel registered for commType=99" in L.catccos_last_error()   # CATCCOS_ERR_INVALID
+    assert L.catccos_shmem_init(0, 2, 1 << 20, b"") == 1 and b"ip_port" in L.catccos_last_error()
+    assert L.catccos_shmem_init(3, 2, 1 << 20, b"tcp://127.0.0.1:1") == 1 and b"bad PE numbering" in L.catccos_last_error()
+    assert not L.catccos_shmem_malloc(1024)
+    assert L.catccos_shmem_my_pe() == -1 and L.catccos_shmem_n_pes() == 0
+
+
+def test_buffer_sizes_of_the_benchmark_configurations():
+    """Pure host arithmetic of catccos_symmetric_bytes / catccos_workspace_bytes: the dense and MXFP8 operators
+    keep two halves of their region; everything fits the reference's 1004 MiB symmetric buffer."""
+    import ctypes
+    from catccos_b200 import lib, runtime as rt
+    L = lib()
+
+    def symm(comm, dt, m, k, n, ranks, **kw):
+        t = rt.tiling(m, k, n, ranks, **kw)
+        return L.catccos_symmetric_bytes(comm, dt, ctypes.byref(t)), L.catccos_workspace_bytes(comm, dt, ctypes.byref(t))
+
+    assert symm(rt.ALLGATHER_MATMUL, rt.BF16, 1024, 8192, 4096, 8)[0] == 2 * 8 * 1024 * 8192 * 2
+    assert symm(rt.MATMUL_REDUCE_SCATTER, rt.BF16, 8192, 2048, 8192, 8)[0] == 2 * 8192 * 8192 * 2
+    assert symm(rt.MATMUL_ALLREDUCE, rt.FP16, 512, 1024, 2048, 2)[0] == 2 * (2 * 2 * 256 * 2048 * 2)
+    assert symm(rt.ALLGATHER_MATMUL, rt.BF16, 1024, 8192, 4096, 1) == (0, 0)           # a single rank needs nothing
+    s, w = symm(rt.FP8_MX_ALLGATHER_MATMUL, rt.BF16, 2048, 7168, 4096, 8)
+    assert 2 * 8 * 2048 * 7168 < s <= 1004 << 20 and w > 0
+    s, w = symm(rt.DISPATCH_FFN_COMBINE, rt.BF16, 4096, 7168, 4096, 8, topK=8, expertNum=256, epSize=8)
+    assert 0 < s <= 1004 << 20 and w > 0
+    assert symm(rt.MXFP8_MATMUL_REDUCE_SCATTER, rt.BF16, 8192, 2048, 8192, 8)[0] == 2 * 8192 * 8192 * 2
+    assert L.catccos_fp4_gemm_workspace_bytes(1, 128, 256, 256) == 2048 + 4096 + 64    # atoms of A, of B, status words
