@@ -78,3 +78,52 @@ def test_e4m3_rne_agrees_with_the_lut_rounding_away_from_ties(v):
     fa, fb = mxquant.e4m3_to_f32(a), mxquant.e4m3_to_f32(b)
     c = np.clip(v, -448, 448)
     assert np.allclose(np.abs(fa - c), np.abs(fb - c), rtol=0, atol=0)
+
+
+# ----------------------------------------------------------------------------------------- MoE routing ----
+from oracle import moe   # noqa: E402
+
+routing = st.integers(1, 4).flatmap(lambda ep: st.tuples(
+    st.just(ep), st.integers(1, 3), st.integers(1, 24), st.integers(1, 3), st.integers(0, 2 ** 31 - 1)))
+
+
+@settings(**SET)
+@given(routing)
+def test_dispatch_then_combine_is_the_identity_and_tables_agree(cfg):
+    """For any routing: the stable sort keeps equal experts in token order, every row reaches its expert's owner
+    in (local expert, source rank) order, the way back restores the permuted rows exactly, and the device-side
+    tables (cumsumMM) describe the same layout as the golden's all-to-all-v."""
+    ep, epr, m, top_k, seed = cfg
+    experts = ep * epr
+    rng = np.random.default_rng(seed)
+    idx = [rng.integers(0, experts, size=(m, top_k)).astype(np.int32) for _ in range(ep)]
+    xs = [rng.integers(0, 1000, size=(m, 4)).astype(np.float32) + 10000 * r for r in range(ep)]   # rows tagged by rank
+    srcs, counts, routed = [], [], []
+    for r in range(ep):
+        s, c = moe.moe_init_routing(idx[r], experts)
+        flat = idx[r].reshape(-1)
+        assert (np.diff(flat[s]) >= 0).all()                                  # sorted by expert
+        same = np.diff(flat[s]) == 0
+        assert (np.diff(s)[same] > 0).all()                                   # stable inside an expert
+        assert c.sum() == m * top_k and np.array_equal(c, np.bincount(flat, minlength=experts))
+        inv = moe.expanded_row_idx_src_to_dst(s)
+        assert np.array_equal(inv[s], np.arange(m * top_k))
+        srcs.append(s); counts.append(c); routed.append(moe.permute_rows(xs[r], s, top_k))
+    table = np.stack(counts)
+    recv, blocks = moe.alltoallv_dispatch(routed, table, ep, epr)
+    for o in range(ep):
+        assert blocks[o] == table[:, o * epr:(o + 1) * epr].sum(axis=0).tolist()
+        # rows of local expert le coming from ranks < r, as the device schedulers count them
+        cum = moe.cumsum_mm(table, o, ep, epr)
+        pos = 0
+        for le in range(epr):
+            for src in range(ep):
+                n = int(table[src, o * epr + le])
+                assert int(cum[src, le]) - n == (int(cum[src - 1, le]) if src else 0)
+                seg = recv[o][pos:pos + n]
+                assert (seg[:, 0] // 10000 == src).all() or n == 0            # rows really come from `src`
+                pos += n
+        assert pos == recv[o].shape[0]
+    back = moe.alltoallv_combine(recv, table, ep, epr)
+    for r in range(ep):
+        assert np.array_equal(back[r], routed[r])
