@@ -31,11 +31,11 @@ RS_M, RS_KLOCAL, RS_N = 8192, 2048, 8192           # matmul_reduce_scatter bf16 
 AR_M, AR_K, AR_N = 512, 1024, 2048                 # matmul_allreduce fp16 (configuration 1)
 MX_M_TOTAL, MX_K, MX_N = 16384, 7168, 4096         # MXFP8 allgather_matmul (configuration 4)
 MOE_M, MOE_K, MOE_N, MOE_TOPK = 4096, 7168, 4096, 8  # MoE (configuration 5), 32 experts per rank
-NVLINK_GBS = 770.0                                 # measured peer-copy bandwidth per direction on this pool
+NVLINK_GBS = 770.0                                 # measured peer-copy bandwidth per direction (900 nominal)
 
 
 def measured_peaks(sustained):
-    """cuBLAS bf16 peak measured on this pool: the sustained figure when the timed steps sit inside
+    """Measured cuBLAS bf16 peak of this GPU type: the sustained figure when the timed steps sit inside
     a long load bracket, the burst figure when they are timed cold."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -149,6 +149,134 @@ def host_inputs(wl, rank, torch):
         a = torch.randn(wl["a_shape"], generator=g).to(dt)
         b = (torch.randn(wl["b_shape"], generator=g) * 0.02).to(dt)
     return a, b, dt
+
+
+
+TOL = {"bf16": 1e-2, "fp16": 1e-2, "mxfp8": 2e-2}
+
+
+def _sample_rows(n_rows, count, seed, torch):
+    """Seeded row sample that always holds the first and the last row."""
+    count = min(count, n_rows)
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.randperm(n_rows, generator=g)[:count]
+    idx[0] = 0
+    idx[-1] = n_rows - 1
+    return torch.unique(idx)
+
+
+def _rel_err(actual, golden, torch):
+    from oracle import verify                      # checker only
+    return verify.max_rel_err(actual, golden)
+
+
+def parity_dense(op, wl, rank, world, a_h, b_h, c_dev, torch):
+    """Compares a seeded sample of this rank's output rows with the fp32 CPU golden of the operator
+    (the oracle port of the reference's host golden) on the same seeded inputs.  Runs after the timed
+    region.  Returns (max relative error, rows checked)."""
+    from oracle import dense                       # checker only
+    if op == "agmm":
+        m = wl["m"]
+        sources = sorted({rank, (rank + 1) % world, (rank + world - 1) % world, (rank + world // 2) % world})
+        per_src = max(64, 512 // len(sources))
+        worst, rows = 0.0, 0
+        bf = b_h.to(torch.float32)
+        for s in sources:
+            a_s = a_h if s == rank else host_inputs(wl, s, torch)[0]
+            idx = _sample_rows(m, per_src, 777 + s, torch)
+            gold = torch.matmul(a_s[idx].to(torch.float32), bf)
+            got = c_dev[(s * m + idx).cuda()].cpu()
+            worst = max(worst, _rel_err(got, gold, torch))
+            rows += idx.numel()
+        return worst, rows
+    # reduce family: this rank's output rows are sums over all ranks' products
+    m_total = wl["m"]
+    if op == "mmrs":
+        mr = m_total // world
+        idx_out = _sample_rows(mr, 256, 555 + rank, torch)
+        idx_in = idx_out + rank * mr
+    else:
+        idx_out = _sample_rows(m_total, 256, 555, torch)
+        idx_in = idx_out
+    gold = None
+    for r in range(world):
+        a_r, b_r = (a_h, b_h) if r == rank else host_inputs(wl, r, torch)[:2]
+        part = dense.matmul_fp32(a_r[idx_in], b_r)
+        gold = part if gold is None else gold + part
+    got = c_dev[idx_out.cuda()].cpu()
+    return _rel_err(got, gold, torch), idx_out.numel()
+
+
+def _dequant_e4m3_fast(codes, scales, torch):
+    """dequant of MXFP8 rows on the host: uint8 codes [r, k], E8M0 bytes [r, >= k/32] -> fp32 [r, k]
+    (table lookup of the oracle's e4m3 decoding; oracle.mxquant.dequant_mx_e4m3 is the slow form)."""
+    import numpy as np
+    from oracle import mxquant                     # checker only
+    lut = torch.from_numpy(mxquant.e4m3_to_f32(np.arange(256, dtype=np.uint8)))
+    r, k = codes.shape
+    v = lut[codes.to(torch.int64)].view(r, k // 32, 32)
+    sc = torch.exp2(scales[:, :k // 32].to(torch.float32) - 127.0)
+    return (v * sc[:, :, None]).view(r, k)
+
+
+def parity_mxag(wl, rank, world, act, a_codes, a_scale, wq_t, ws_t, c_dev, torch, dist):
+    """MXFP8 AllGather-Matmul: the step's own quantisation must be bit-exact (codes and scales of a
+    row sample against the oracle), and sampled rows of the gathered product (own rows, nearest
+    and farthest peers) must match dequant(A) x dequant(B) in fp32."""
+    import numpy as np
+    from oracle import mxquant                     # checker only
+    m, k = wl["m"], wl["k"]
+    idx = _sample_rows(m, 96, 4242, torch)         # the same local rows on every rank
+    mine = act[idx.cuda()].contiguous()
+    if world > 1:
+        allrows = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allrows, mine)
+    else:
+        allrows = [mine]
+    q, sc, _ = mxquant.quantize_mx_e4m3(mine.cpu().to(torch.float32).numpy(), "rne")
+    bit_exact = bool(np.array_equal(q, a_codes[idx.cuda()].cpu().numpy()) and
+                     np.array_equal(sc[:, :k // 32], a_scale[idx.cuda()].cpu().numpy()[:, :k // 32]))
+    b_deq_t = _dequant_e4m3_fast(wq_t.cpu(), ws_t.cpu(), torch)             # [n, k]
+    worst, rows = 0.0, 0
+    for s in sorted({rank, (rank + 1) % world, (rank + world - 1) % world, (rank + world // 2) % world}):
+        qs, ss, a_deq = mxquant.quantize_mx_e4m3(allrows[s].cpu().to(torch.float32).numpy(), "rne")
+        gold = torch.matmul(torch.from_numpy(a_deq), b_deq_t.t())
+        got = c_dev[(s * m + idx).cuda()].cpu()
+        worst = max(worst, _rel_err(got, gold, torch))
+        rows += idx.numel()
+    return worst, rows, bit_exact
+
+
+def parity_moe(wl, rank, world, x, idx_dev, probs, expert_weights, c_dev, torch):
+    """MoE: the full dispatch -> GEMM1 -> SwiGLU -> quant -> GEMM2 -> combine -> un-permute golden
+    (oracle.moe stages) for a few of this rank's tokens, using the weights of whichever experts,
+    local or remote, those tokens were routed to."""
+    import numpy as np
+    from oracle import moe, mxquant                # checker only
+    k, n, top_k = wl["k"], wl["n"], wl["top_k"]
+    toks = _sample_rows(wl["m"], 3, 31 + rank, torch)
+    xs = x[toks.cuda()].cpu().to(torch.float32).numpy()
+    ids = idx_dev[toks.cuda()].cpu().numpy()
+    pr = probs[toks.cuda()].cpu().numpy()
+    _, _, x_deq = mxquant.quantize_mx_e4m3(xs, "rne")
+    cols = _sample_rows(k, 512, 99, torch)          # output columns checked (GEMM2 rows of W2)
+    rows_back = np.zeros((len(toks), top_k, cols.numel()), dtype=np.float32)
+    for e in np.unique(ids):
+        q1, s1, q2, s2 = expert_weights(int(e))
+        w1 = _dequant_e4m3_fast(q1.cpu(), s1.cpu(), torch)                   # [n, k]
+        w2 = _dequant_e4m3_fast(q2[cols.cuda()].cpu(), s2[cols.cuda()].cpu(), torch)   # [cols, n/2]
+        t_sel, k_sel = np.nonzero(ids == e)
+        c1 = torch.matmul(torch.from_numpy(x_deq[t_sel]), w1.t()).to(torch.bfloat16).to(torch.float32).numpy()
+        glu = moe.swiglu_bf16(c1)
+        _, _, g_deq = mxquant.quantize_mx_e4m3(glu, "rne")
+        c2 = torch.matmul(torch.from_numpy(g_deq), w2.t()).to(torch.bfloat16).to(torch.float32).numpy()
+        rows_back[t_sel, k_sel] = c2
+    acc = np.zeros((len(toks), cols.numel()), dtype=np.float32)
+    for j in range(top_k):                          # fp32 multiply then add in slot order, as moe.unpermute_fp32
+        acc = (acc + rows_back[:, j] * pr[:, j:j + 1].astype(np.float32)).astype(np.float32)
+    gold = torch.from_numpy(mxquant.bf16_bits_to_f32(mxquant.f32_to_bf16_bits(acc)).reshape(acc.shape))
+    got = c_dev[toks.cuda()][:, cols.cuda()].cpu()
+    return _rel_err(got, gold, torch), int(toks.numel())
 
 
 def cpu_golden_rate(wl, sample_rows, torch):
@@ -315,13 +443,17 @@ def main():
             w1s = torch.empty((el, n, k // 32), dtype=torch.uint8, device="cuda")
             w2q = torch.empty((el, k, n // 2), dtype=torch.uint8, device="cuda")
             w2s = torch.empty((el, k, (n // 2) // 32), dtype=torch.uint8, device="cuda")
+            def expert_weights(e_global):
+                """MXFP8 weights of one expert, seeded by its global index so that every rank can
+                regenerate them (the parity check needs the weights of experts other ranks own)."""
+                ge = torch.Generator(device="cuda").manual_seed(9000 + e_global)
+                wt = (torch.randn((n, k), generator=ge, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                q1, s1 = quant_rows(wt)
+                wt = (torch.randn((k, n // 2), generator=ge, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                q2, s2 = quant_rows(wt)
+                return q1, s1[:, :k // 32], q2, s2[:, :(n // 2) // 32]
             for e in range(el):
-                wt = (torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
-                cq, cs = quant_rows(wt)
-                w1q[e], w1s[e] = cq, cs[:, :k // 32]
-                wt = (torch.randn((k, n // 2), generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
-                cq, cs = quant_rows(wt)
-                w2q[e], w2s[e] = cq, cs[:, :(n // 2) // 32]
+                w1q[e], w1s[e], w2q[e], w2s[e] = expert_weights(rank * el + e)
             # top-8 routing: softmax(N(0,1) logits + log of a Zipf(1.1) weight per expert), renormalised gate weights
             logits = torch.randn((m, experts), generator=gen, device="cuda")
             zipf = torch.arange(1, experts + 1, device="cuda", dtype=torch.float32).pow(-1.1)

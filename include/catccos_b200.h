@@ -194,8 +194,7 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16);
  * summed product in the 16-bit type the name gives; tiling m = rows of the full product (m/rankSize a multiple of
  * 128), k = this rank's share of the contraction.  `workspace` = catccos_workspace_bytes() bytes, `symmetric` as for
  * Matmul-ReduceScatter.  The E4M3 names take float8_e4m3fn operands (no reference counterpart of their own: the
- * reference kernel is a template over the element type).  Status: compiled for sm_100a, parity test not yet run
- * on a GPU. */
+ * reference kernel is a template over the element type). */
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterBF16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterFP16);
@@ -237,7 +236,7 @@ CATCCOS_API int catccos_launch_emulated(int32_t commType, int32_t dataType, void
  * golden examples/utils/gen_data_fp4_mx_allgather_matmul.py:563-677); format 1 = NVFP4: one E4M3 scale per 16
  * along k, rows [rows, k/16], the two fp32 tensor scales multiplied into `alpha` (no reference counterpart: the
  * reference's FP4 is MXFP4).  k % 64 == 0, n % 8 == 0.  `workspace`: catccos_fp4_gemm_workspace_bytes() bytes of
- * device memory.  Needs no catccos_shmem_init.  Status: compiled for sm_100a, parity test not yet run on a GPU. */
+ * device memory.  Needs no catccos_shmem_init. */
 CATCCOS_API size_t catccos_fp4_gemm_workspace_bytes(int32_t format, uint32_t m, uint32_t n, uint32_t k);
 CATCCOS_API int catccos_fp4_gemm(void *stream, int32_t format, int32_t dataType, const void *A, const void *B, void *C,
                                  const void *aScale, const void *bScale, float alpha, uint32_t m, uint32_t n, uint32_t k,

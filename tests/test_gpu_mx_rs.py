@@ -1,8 +1,5 @@
 """MXFP8 Matmul-ReduceScatter (e5m2 codes, as the reference's example feeds; tolerance 2e-2)
-against the CPU oracle, through the C-ABI, world sizes 1/2/4 as emulated PEs.
-
-The kernel is compiled for sm_100a but its parity run on a GPU is still outstanding, so this
-file runs only when CATCCOS_TEST_MX_RS=1 is set; nothing in it is expected to fail."""
+against the CPU oracle, through the C-ABI, world sizes 1/2/4 as emulated PEs."""
 import ctypes
 import os
 
@@ -13,9 +10,7 @@ import torch
 from oracle import dense, mxquant
 from tests.gpu_util import assert_reduced_close, dev
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("CATCCOS_TEST_MX_RS") != "1",
-                                 reason="MXFP8 Matmul-ReduceScatter: parity run outstanding (set CATCCOS_TEST_MX_RS=1)")]
+pytestmark = pytest.mark.gpu
 TOL_MX = 2e-2
 
 
