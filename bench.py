@@ -152,6 +152,31 @@ def host_inputs(wl, rank, torch):
 
 
 
+def bind_to_gpu_numa_node(local_rank, torch):
+    """Runs this process on the CPUs of the NUMA node its GPU hangs off, so that pinned host buffers
+    allocated afterwards are node-local (first touch) and host<->device copies do not cross the
+    socket interconnect.  Best effort: returns the node or None."""
+    try:
+        pr = torch.cuda.get_device_properties(local_rank)
+        dev = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{dev}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return node
+    except (OSError, ValueError, AttributeError):
+        pass
+    return None
+
+
 TOL = {"bf16": 1e-2, "fp16": 1e-2, "mxfp8": 2e-2}
 
 
@@ -338,6 +363,7 @@ def main():
     ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar", "mxag", "moe", "quant"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -544,6 +570,7 @@ def main():
     # end to end through the host-buffer entry point: H2D of A and B, fused launch, D2H of C, every step
     e2e = None
     if not args.no_e2e and dense_op:
+        numa_node = bind_to_gpu_numa_node(local_rank, torch)
         a_p, b_p = a_h.pin_memory(), b_h.pin_memory()
         c_p = torch.empty(wl["c_shape"], dtype=dt).pin_memory()
 
@@ -561,10 +588,46 @@ def main():
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         e2e = {"value": world * wl["flops"] * args.steps / e2e_s / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": a_p.numel() * 2 + b_p.numel() * 2, "d2h_bytes_per_step": c_p.numel() * 2,
-               "ms_per_step": e2e_s / args.steps * 1e3}
+               "ms_per_step": e2e_s / args.steps * 1e3, "host_numa_node": numa_node}
         # the copy that came back must be the device result (guards against a stale host buffer)
         if not torch.equal(c_p[:64], c_d[:64].cpu()):
             raise SystemExit("end-to-end result differs from the device-resident result")
+
+    # parity: after the timed region, one more plain step, then a seeded sample of this rank's output
+    # against the CPU golden (oracle) on every rank; the worst rank is reported and a miss fails the run
+    parity = None
+    if not args.no_parity:
+        step()
+        barrier()
+        rc_, words_ = rt.last_status()
+        if rc_ != 0:
+            raise SystemExit(f"device wait ran out: {words_}")
+        bit_exact = None
+        if dense_op:
+            err, rows = parity_dense(args.op, wl, rank, world, a_h, b_h, c_d, torch)
+        elif args.op == "mxag":
+            err, rows, bit_exact = parity_mxag(wl, rank, world, act, a_codes, a_scale, wq_t, ws_t, c_d, torch, dist)
+        elif args.op == "moe":
+            err, rows = parity_moe(wl, rank, world, x, idx, probs, expert_weights, c_d, torch)
+        else:   # quant: bit-exact codes and scales on a row sample
+            import numpy as np
+            from oracle import mxquant             # checker only
+            ridx = _sample_rows(wl["m"], 256, 11, torch)
+            q, sc, _ = mxquant.quantize_mx_e4m3(x[ridx.cuda()].cpu().to(torch.float32).numpy(), "rne")
+            bit_exact = bool(np.array_equal(q, q_codes[ridx.cuda()].cpu().numpy()) and
+                             np.array_equal(sc[:, :wl["k"] // 32], q_scales[ridx.cuda()].cpu().numpy()))
+            err, rows = 0.0, int(ridx.numel())
+        tol = TOL.get(wl["dtype"], 0.0)
+        if err != err:                              # NaN
+            err = float("inf")
+        err = max_over_ranks(err)
+        if bit_exact is not None:
+            bit_exact = max_over_ranks(0.0 if bit_exact else 1.0) == 0.0
+        parity = {"max_rel_err": err, "rows": rows, "tol": tol, "ranks_checked": world,
+                  "golden": "fp32 CPU golden (oracle) on the same seeded inputs, sampled rows of every rank's output",
+                  "ok": bool(err <= tol and bit_exact is not False)}
+        if bit_exact is not None:
+            parity["quant_bit_exact"] = bit_exact
 
     if rank == 0:
         peak_tf, peak_hbm, peak_kind = measured_peaks(load_steps > 0)
@@ -577,7 +640,7 @@ def main():
                 "config": {"workload": wl["desc"], "op": wl["name"], "l2": "operands (235 MB) larger than L2"},
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak_hbm, "unit": "GB/s", "frac": gbs / peak_hbm,
                              "traffic": None, "peak_kind": "of measured (STREAM-style copy)"},
-                "e2e": None, "gpu_launches": args.steps * launches_per_step, "clocks": clocks,
+                "e2e": None, "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "parity": parity,
             }
             print(json.dumps(line), flush=True)
         else:
@@ -605,7 +668,7 @@ def main():
                              "t_gemm_peak_us": t_gemm_us, "t_comm_peak_us": t_comm_us,
                              "frac_of_max_gemm_comm": max(t_gemm_us, t_comm_us) / (ms_per_step * 1e3)},
                 "exposed_comm_frac": exposed, "compute_only_ms_per_step": compute_only_ms,
-                "e2e": e2e, "gpu_launches": args.steps * launches_per_step, "clocks": clocks,
+                "e2e": e2e, "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "parity": parity,
             }
             if args.op == "moe":
                 line["config"]["hottest_rank_rows_over_mean"] = moe_imbalance
@@ -618,6 +681,8 @@ def main():
     rt.shmem_finalize()
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
 
 
 if __name__ == "__main__":

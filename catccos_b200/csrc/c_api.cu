@@ -11,6 +11,8 @@
 #include "sched.h"
 #include "symm_heap.h"
 
+#include <algorithm>
+
 using namespace cb;
 
 namespace {
@@ -195,10 +197,14 @@ size_t catccos_sf_atoms_bytes(uint32_t rows, uint32_t k) { return sf_atoms_bytes
 
 // ---- host-buffer form ------------------------------------------------------------------
 namespace {
+constexpr int kHostRunChunks = 8;
 struct HostRunCache {
-    void *dA = nullptr, *dB = nullptr, *dC = nullptr, *symm = nullptr;
-    size_t bytesA = 0, bytesB = 0, bytesC = 0, bytesSymm = 0;
-    cudaStream_t stream = nullptr;
+    void *dA = nullptr, *dB = nullptr, *dC = nullptr;
+    size_t bytesA = 0, bytesB = 0, bytesC = 0;
+    cudaStream_t in = nullptr, run = nullptr, out = nullptr;     // host->device, kernels, device->host
+    cudaEvent_t landed[kHostRunChunks + 1] = {};                  // B, then every chunk of A
+    cudaEvent_t done[kHostRunChunks] = {};                        // a chunk's rows of C are complete
+    bool ready = false;
 } g_hr;
 
 int ensure(void **p, size_t *have, size_t want) {
@@ -214,12 +220,46 @@ int ensure(void **p, size_t *have, size_t want) {
     *have = want;
     return CATCCOS_OK;
 }
+int ensure_host_run_streams() {
+    if (g_hr.ready) return CATCCOS_OK;
+    cudaError_t e = cudaStreamCreateWithFlags(&g_hr.in, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&g_hr.run, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&g_hr.out, cudaStreamNonBlocking);
+    for (int i = 0; i <= kHostRunChunks && e == cudaSuccess; ++i)
+        e = cudaEventCreateWithFlags(&g_hr.landed[i], cudaEventDisableTiming);
+    for (int i = 0; i < kHostRunChunks && e == cudaSuccess; ++i)
+        e = cudaEventCreateWithFlags(&g_hr.done[i], cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        set_error("creating the host-buffer path's streams failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    g_hr.ready = true;
+    return CATCCOS_OK;
+}
 void release_host_run_cache() {
     if (g_hr.dA) cudaFree(g_hr.dA);
     if (g_hr.dB) cudaFree(g_hr.dB);
     if (g_hr.dC) cudaFree(g_hr.dC);
-    if (g_hr.stream) cudaStreamDestroy(g_hr.stream);
+    if (g_hr.in) cudaStreamDestroy(g_hr.in);
+    if (g_hr.run) cudaStreamDestroy(g_hr.run);
+    if (g_hr.out) cudaStreamDestroy(g_hr.out);
+    for (cudaEvent_t ev : g_hr.landed)
+        if (ev) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : g_hr.done)
+        if (ev) cudaEventDestroy(ev);
     g_hr = HostRunCache();
+}
+// after the streams have drained: a bounded device wait that ran out must not pass for success
+int host_run_status() {
+    int w[ST_WORDS];
+    int rc = team_read_status(w);
+    if (rc) return rc;
+    if (w[ST_CODE] != 0) {
+        set_error("device wait ran out: code=%d site=%d rank=%d index=%d expected=%d seen=%d", w[ST_CODE], w[ST_WHERE],
+                  w[ST_RANK], w[ST_INDEX], w[ST_EXPECTED], w[ST_SEEN]);
+        return CATCCOS_ERR_DEVICE_WAIT;
+    }
+    return CATCCOS_OK;
 }
 }  // namespace
 
@@ -587,29 +627,58 @@ int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, cons
     const size_t need = dense_symmetric_bytes(op, static_cast<int>(R), static_cast<int>(m), static_cast<int>(n),
                                               static_cast<int>(k));
     if ((rc = ensure(&g_hr.dA, &g_hr.bytesA, bytesA)) || (rc = ensure(&g_hr.dB, &g_hr.bytesB, bytesB)) ||
-        (rc = ensure(&g_hr.dC, &g_hr.bytesC, bytesC)))
+        (rc = ensure(&g_hr.dC, &g_hr.bytesC, bytesC)) || (rc = ensure_host_run_streams()))
         return rc;
-    if (need > g_hr.bytesSymm) {
-        if (g_hr.symm) team_free(g_hr.symm);
-        g_hr.symm = team_malloc(need);
-        if (!g_hr.symm) return CATCCOS_ERR_NOMEM;
-        g_hr.bytesSymm = need;
+    // the symmetric region of this path sits at the end of the heap, outside the stack that the
+    // caller's catccos_shmem_malloc / catccos_shmem_free calls grow and shrink
+    void *symm = nullptr;
+    if (need > 0 && !(symm = team_top_region(need))) return CATCCOS_ERR_NOMEM;
+    cudaError_t e = cudaSuccess;
+    if (R == 1 && m >= 2 * 256 * kHostRunChunks) {
+        // One PE: the operator is a plain GEMM, so it is cut into row chunks and the three stages
+        // overlap -- chunk i's rows of C travel to the host while chunk i+1 is multiplied and chunk
+        // i+2 is still arriving.  B goes first (every chunk needs all of it).
+        const size_t rows_per = (m / kHostRunChunks + 255) / 256 * 256;
+        cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.in);
+        cudaEventRecord(g_hr.landed[0], g_hr.in);
+        cudaStreamWaitEvent(g_hr.run, g_hr.landed[0], 0);
+        int chunk = 0;
+        for (size_t r0 = 0; r0 < m && !rc; r0 += rows_per, ++chunk) {
+            const size_t rows = std::min(rows_per, m - r0);
+            uint8_t *a = static_cast<uint8_t *>(g_hr.dA) + r0 * k * 2;
+            uint8_t *c = static_cast<uint8_t *>(g_hr.dC) + r0 * n * 2;
+            cudaMemcpyAsync(a, static_cast<const uint8_t *>(hostA) + r0 * k * 2, rows * k * 2, cudaMemcpyHostToDevice, g_hr.in);
+            cudaEventRecord(g_hr.landed[chunk + 1], g_hr.in);
+            cudaStreamWaitEvent(g_hr.run, g_hr.landed[chunk + 1], 0);
+            CocTilingParams sub = *tiling;
+            sub.m = static_cast<uint32_t>(rows);
+            CatccosKernelParams kp{a, static_cast<uint8_t *>(g_hr.dB), c, nullptr, 0};
+            rc = launch_dense_abi(op, dataType, g_hr.run, blockNum, &kp, 1, nullptr, &sub, transA, transB);
+            if (rc) break;
+            cudaEventRecord(g_hr.done[chunk], g_hr.run);
+            cudaStreamWaitEvent(g_hr.out, g_hr.done[chunk], 0);
+            cudaMemcpyAsync(static_cast<uint8_t *>(hostC) + r0 * n * 2, c, rows * n * 2, cudaMemcpyDeviceToHost, g_hr.out);
+        }
+        e = cudaStreamSynchronize(g_hr.in);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(g_hr.run);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(g_hr.out);
+    } else {
+        // several PEs: the fused launch needs this rank's whole A and B; the copies are stream-ordered around it
+        cudaMemcpyAsync(g_hr.dA, hostA, bytesA, cudaMemcpyHostToDevice, g_hr.run);
+        cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.run);
+        CatccosKernelParams kp{static_cast<uint8_t *>(g_hr.dA), static_cast<uint8_t *>(g_hr.dB),
+                               static_cast<uint8_t *>(g_hr.dC), nullptr, 0};
+        rc = launch_dense_abi(op, dataType, g_hr.run, blockNum, &kp, 1, static_cast<uint8_t *>(symm), tiling, transA,
+                              transB);
+        if (!rc) cudaMemcpyAsync(hostC, g_hr.dC, bytesC, cudaMemcpyDeviceToHost, g_hr.run);
+        e = cudaStreamSynchronize(g_hr.run);
     }
-    if (!g_hr.stream) cudaStreamCreateWithFlags(&g_hr.stream, cudaStreamNonBlocking);
-    cudaMemcpyAsync(g_hr.dA, hostA, bytesA, cudaMemcpyHostToDevice, g_hr.stream);
-    cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.stream);
-    CatccosKernelParams kp{static_cast<uint8_t *>(g_hr.dA), static_cast<uint8_t *>(g_hr.dB),
-                           static_cast<uint8_t *>(g_hr.dC), nullptr, 0};
-    rc = launch_dense_abi(op, dataType, g_hr.stream, blockNum, &kp, 1, static_cast<uint8_t *>(g_hr.symm), tiling,
-                          transA, transB);
-    if (rc) return rc;
-    cudaMemcpyAsync(hostC, g_hr.dC, bytesC, cudaMemcpyDeviceToHost, g_hr.stream);
-    cudaError_t e = cudaStreamSynchronize(g_hr.stream);
     if (e != cudaSuccess) {
         set_error("host-buffer run failed: %s", cudaGetErrorString(e));
         return CATCCOS_ERR_CUDA;
     }
-    return CATCCOS_OK;
+    if (rc) return rc;
+    return host_run_status();
 }
 
 }  // extern "C"

@@ -74,61 +74,84 @@ __device__ __host__ __forceinline__ size_t sf_atom_offset(uint32_t row, uint32_t
            (kb & 3u);
 }
 
-// One thread quantises 8 consecutive values; 4 neighbouring threads share a 32-value block.
-// A CTA walks whole rows; every thread keeps kQuantUnroll 16-byte loads in flight.
+// 256-bit global accesses (one 32-byte sector per thread and instruction); addresses 32-byte aligned
+struct alignas(32) Vec8 {
+    uint4 lo, hi;
+};
+__device__ __forceinline__ Vec8 ld_stream_256(const void *p) {
+    Vec8 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x), "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_256(void *p, const uint2 &a, const uint2 &b, const uint2 &c, const uint2 &d) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a.x), "r"(a.y), "r"(b.x), "r"(b.y),
+                 "r"(c.x), "r"(c.y), "r"(d.x), "r"(d.y)
+                 : "memory");
+}
+
+// One thread owns one whole 32-value block: 64 contiguous input bytes (two 256-bit loads, or four
+// 128-bit ones when the buffers are only 16-byte aligned), the block's largest magnitude and scale
+// without any exchange between threads, 32 contiguous code bytes (one 256-bit store) and one scale
+// byte.  A warp covers 32 consecutive blocks, so every load and store instruction touches whole
+// 32-byte sectors and a warp's scale bytes are one contiguous 32-byte run.  Blocks are walked flat
+// over the matrix (grid-stride) with the (row, k-block) pair advanced incrementally.
 // codes: [rows, k] bytes (row stride code_ld).  scales_rm: optional [rows, scale_ld] bytes.
 // sf_atoms: optional tcgen05 atom layout.
-constexpr int kQuantUnroll = 4;
-__global__ void __launch_bounds__(256) mx_quant_kernel(const uint4 *__restrict__ in, int rows, int k, uint8_t *codes,
+template <bool WIDE>
+__global__ void __launch_bounds__(256) mx_quant_kernel(const uint8_t *__restrict__ in, int rows, int k, uint8_t *codes,
                                                        size_t code_ld, uint8_t *scales_rm, int scale_ld,
                                                        uint8_t *sf_atoms, int kb4_count) {
-    const int vec_per_row = k >> 3;                  // k % 32 == 0, so vec_per_row % 4 == 0
     const int nblocks = k >> 5;
-    const int lane = threadIdx.x & 31;
-    const bool wide_scales = scales_rm && (scale_ld & 7) == 0 && (reinterpret_cast<uintptr_t>(scales_rm) & 7) == 0;
-    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-        const uint4 *src = in + static_cast<size_t>(row) * vec_per_row;
-        uint8_t *crow = codes + static_cast<size_t>(row) * code_ld;
-        for (int v0 = threadIdx.x; v0 - static_cast<int>(threadIdx.x) < vec_per_row; v0 += 256 * kQuantUnroll) {
-            uint4 x[kQuantUnroll];
+    const long long total = static_cast<long long>(rows) * nblocks;
+    const long long stride = static_cast<long long>(gridDim.x) * 256;
+    long long b = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+    if (b >= total) return;
+    int row = static_cast<int>(b / nblocks);
+    int kb = static_cast<int>(b - static_cast<long long>(row) * nblocks);
+    const int step_row = static_cast<int>(stride / nblocks);
+    const int step_kb = static_cast<int>(stride - static_cast<long long>(step_row) * nblocks);
+    const size_t row_bytes = static_cast<size_t>(k) * 2;
+    for (; b < total; b += stride) {
+        const uint8_t *src = in + static_cast<size_t>(row) * row_bytes + static_cast<size_t>(kb) * 64;
+        uint4 x[4];
+        if (WIDE) {
+            const Vec8 v0 = ld_stream_256(src), v1 = ld_stream_256(src + 32);
+            x[0] = v0.lo;
+            x[1] = v0.hi;
+            x[2] = v1.lo;
+            x[3] = v1.hi;
+        } else {
 #pragma unroll
-            for (int u = 0; u < kQuantUnroll; ++u) {
-                const int v = v0 + u * 256;
-                x[u] = v < vec_per_row ? __ldg(src + v) : make_uint4(0, 0, 0, 0);
-            }
+            for (int i = 0; i < 4; ++i) x[i] = __ldg(reinterpret_cast<const uint4 *>(src) + i);
+        }
+        const uint32_t am = max(max(bf16_abs_max(x[0]), bf16_abs_max(x[1])), max(bf16_abs_max(x[2]), bf16_abs_max(x[3])));
+        uint32_t sb;
+        float inv;
+        block_scale(am, &sb, &inv);
+        const bool has_nan = am > 0x7F80u;
+        uint2 q[4];
 #pragma unroll
-            for (int u = 0; u < kQuantUnroll; ++u) {
-                const int v = v0 + u * 256;
-                // whole warps take this branch together except in a row's last partial warp, whose groups
-                // of 4 lanes (one 32-value block) are still complete
-                if (v - lane >= vec_per_row) continue;
-                const bool live = v < vec_per_row;
-                uint32_t am = bf16_abs_max(x[u]);
-                am = max(am, __shfl_xor_sync(0xffffffffu, am, 1));
-                am = max(am, __shfl_xor_sync(0xffffffffu, am, 2));
-                uint32_t sb;
-                float inv;
-                block_scale(am, &sb, &inv);
-                if (live) *reinterpret_cast<uint2 *>(crow + v * 8) = quantise8(x[u], inv, am > 0x7F80u);
-                const int kb = v >> 2;
-                // the warp's 8 block scales -> lane 0 (one 8-byte store) when the layout allows it
-                // lanes 0,4,...,28 hold the bytes; three shuffles fold them into lane 0
-                uint32_t lo = sb | (__shfl_down_sync(0xffffffffu, sb, 4) << 8);
-                lo |= __shfl_down_sync(0xffffffffu, lo, 8) << 16;
-                const uint32_t hi = __shfl_down_sync(0xffffffffu, lo, 16);
-                const bool full_warp = (v - lane) + 32 <= vec_per_row;
-                if (scales_rm) {
-                    if (wide_scales && full_warp) {
-                        if (lane == 0)
-                            *reinterpret_cast<uint2 *>(scales_rm + static_cast<size_t>(row) * scale_ld + kb) = make_uint2(lo, hi);
-                    } else if (live && (v & 3) == 0) {
-                        scales_rm[static_cast<size_t>(row) * scale_ld + kb] = static_cast<uint8_t>(sb);
-                    }
-                    if (live && (v & 3) == 0 && kb == nblocks - 1 && (nblocks & 1))
-                        scales_rm[static_cast<size_t>(row) * scale_ld + kb + 1] = 127;
-                }
-                if (sf_atoms && live && (v & 3) == 0) sf_atoms[sf_atom_offset(row, kb, kb4_count)] = static_cast<uint8_t>(sb);
-            }
+        for (int i = 0; i < 4; ++i) q[i] = quantise8(x[i], inv, has_nan);
+        uint8_t *dst = codes + static_cast<size_t>(row) * code_ld + static_cast<size_t>(kb) * 32;
+        if (WIDE) {
+            st_256(dst, q[0], q[1], q[2], q[3]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) *reinterpret_cast<uint2 *>(dst + i * 8) = q[i];
+        }
+        if (scales_rm) {
+            uint8_t *srow = scales_rm + static_cast<size_t>(row) * scale_ld;
+            srow[kb] = static_cast<uint8_t>(sb);
+            if (kb == nblocks - 1 && (nblocks & 1)) srow[kb + 1] = 127;      // rows are padded to an even count
+        }
+        if (sf_atoms) sf_atoms[sf_atom_offset(row, kb, kb4_count)] = static_cast<uint8_t>(sb);
+        row += step_row;
+        kb += step_kb;
+        if (kb >= nblocks) {
+            kb -= nblocks;
+            ++row;
         }
     }
 }
@@ -236,11 +259,17 @@ int mx_quant_launch(cudaStream_t stream, const void *in_bf16, int rows, int k, u
             return CATCCOS_ERR_CUDA;
         }
     }
-    const size_t vecs = static_cast<size_t>(rows) * (k / 8);
-    int grid = grid_for(vecs, 256);
-    if (grid > rows) grid = rows;
-    mx_quant_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4 *>(in_bf16), rows, k, codes, code_ld,
-                                                            scales_rm, scale_ld, sf_atoms, kb4);
+    // one thread per 32-value block; a grid of whole waves (all resident CTAs of every SM) walks the matrix
+    const size_t blocks32 = static_cast<size_t>(rows) * (k / 32);
+    const int grid = grid_for(blocks32, 256);
+    const bool wide = (reinterpret_cast<uintptr_t>(in_bf16) & 31) == 0 && (reinterpret_cast<uintptr_t>(codes) & 31) == 0 &&
+                      (code_ld & 31) == 0;
+    if (wide)
+        mx_quant_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(in_bf16), rows, k, codes, code_ld,
+                                                        scales_rm, scale_ld, sf_atoms, kb4);
+    else
+        mx_quant_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(in_bf16), rows, k, codes, code_ld,
+                                                         scales_rm, scale_ld, sf_atoms, kb4);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_error("mx_quant_kernel launch failed: %s", cudaGetErrorString(e));

@@ -1,13 +1,18 @@
 // GEMM entry point for callers that must not allocate device memory.
 //
 // Some hosts of this library cannot call cudaMalloc (or anything that allocates) at the point
-// where they need a GEMM: code that runs while a stream is being captured, plugins living inside
-// another runtime that owns and budgets all device memory, or latency-critical loops where an
-// allocation's implicit synchronisation is not acceptable.  The regular launchers need the
+// where they need a GEMM: plugins living inside another runtime that owns and budgets all device
+// memory (an allocation behind its back breaks its accounting or fails outright), and
+// latency-critical loops where an allocation's implicit device synchronisation is not
+// acceptable.  The regular launchers need the
 // symmetric heap object, which allocates when it is created.  This file offers the single-rank
 // tcgen05 GEMM (AllGather-Matmul with a world of one) with the only scratch it needs — the device
 // status words and the per-CTA trace slots — in a fixed array that is part of the library image.
 #include "../../include/catccos_b200.h"
+
+#include <stdlib.h>
+
+#include <mutex>
 
 #include "dense_ops.h"
 #include "gemm_fused.cuh"
@@ -34,7 +39,16 @@ struct DeviceSetup {
     int num_sms = 0;
 };
 DeviceSetup g_setup[kMaxDevices];
+std::mutex g_setup_mutex;               // first calls from several host threads set a device up once
 
+template <typename T, bool B_MN>
+cudaError_t allow_smem() {
+    return cudaFuncSetAttribute(fused_gemm_kernel<OP_AGMM, T, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kGemmSmemBytes);
+}
+
+// Once per device, with that device current: the array's device address and the shared-memory
+// attribute of every kernel variant the entry point can launch.
 int setup_current_device(DeviceSetup **out) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
@@ -42,6 +56,7 @@ int setup_current_device(DeviceSetup **out) {
         set_error("cudaGetDevice failed or device index out of range: %s", cudaGetErrorString(e));
         return CATCCOS_ERR_CUDA;
     }
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
     DeviceSetup &s = g_setup[dev];
     if (!s.ready) {
         void *ptr = nullptr;
@@ -51,8 +66,12 @@ int setup_current_device(DeviceSetup **out) {
             return CATCCOS_ERR_CUDA;
         }
         e = cudaDeviceGetAttribute(&s.num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess) e = allow_smem<__nv_bfloat16, true>();
+        if (e == cudaSuccess) e = allow_smem<__nv_bfloat16, false>();
+        if (e == cudaSuccess) e = allow_smem<__half, true>();
+        if (e == cudaSuccess) e = allow_smem<__half, false>();
         if (e != cudaSuccess) {
-            set_error("cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+            set_error("device set-up of the allocation-free GEMM failed: %s", cudaGetErrorString(e));
             return CATCCOS_ERR_CUDA;
         }
         s.scratch = static_cast<unsigned char *>(ptr);
@@ -60,6 +79,15 @@ int setup_current_device(DeviceSetup **out) {
     }
     *out = &s;
     return CATCCOS_OK;
+}
+
+// bounded device waits: CATCCOS_WAIT_TIMEOUT_MS as for the other launchers, 10 s by default
+uint64_t wait_timeout_ns() {
+    if (const char *e = getenv("CATCCOS_WAIT_TIMEOUT_MS")) {
+        const long ms = atol(e);
+        if (ms > 0) return static_cast<uint64_t>(ms) * 1000000ull;
+    }
+    return 10ull * 1000 * 1000 * 1000;
 }
 
 int encode(const DriverApi *api, CUtensorMap *tm, CUtensorMapDataType dt, const void *base, uint64_t inner,
@@ -80,12 +108,8 @@ int encode(const DriverApi *api, CUtensorMap *tm, CUtensorMapDataType dt, const 
 
 template <typename T, bool B_MN>
 int launch(const FusedParams &p, int grid, cudaStream_t stream) {
-    auto kern = fused_gemm_kernel<OP_AGMM, T, B_MN>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
-    if (e == cudaSuccess) {
-        kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(p);
-        e = cudaGetLastError();
-    }
+    fused_gemm_kernel<OP_AGMM, T, B_MN><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(p);
+    const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_error("no-alloc GEMM launch failed: %s", cudaGetErrorString(e));
         return CATCCOS_ERR_CUDA;
@@ -157,7 +181,7 @@ int catccos_gemm_no_alloc(void *stream, const void *A, const void *B, void *C, u
     p.K = static_cast<int>(k);
     p.epoch = 1;
     p.compute_only = 0;
-    p.timeout_ns = 10ull * 1000 * 1000 * 1000;
+    p.timeout_ns = wait_timeout_ns();
     p.status = reinterpret_cast<int *>(s->scratch);
     p.trace = reinterpret_cast<unsigned long long *>(s->scratch + kNoAllocStatusBytes);
     const bool bf16 = dataType == CATCCOS_BF16;

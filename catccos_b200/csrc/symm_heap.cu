@@ -432,14 +432,35 @@ void *team_malloc(size_t bytes) {
         return nullptr;
     }
     const size_t aligned = (bytes + 1023) / 1024 * 1024;
-    if (t->bump + aligned > t->heap_bytes) {
-        set_error("symmetric heap exhausted: %zu bytes requested, %zu left", bytes, t->heap_bytes - t->bump);
+    if (t->bump + aligned > t->heap_bytes - t->top_reserved) {
+        set_error("symmetric heap exhausted: %zu bytes requested, %zu left", bytes,
+                  t->heap_bytes - t->top_reserved - t->bump);
         return nullptr;
     }
     void *p = t->base[t->my_pe] + t->bump;
     t->alloc_stack.push_back(t->bump);
     t->bump += aligned;
     return p;
+}
+
+// A region at the END of the heap, outside the bump stack that catccos_shmem_malloc/free drive, for
+// library-internal buffers (the host-buffer entry point).  Collective like team_malloc: every PE
+// asks for the same size in the same order.  Grows in place (same end, lower start); never shrinks.
+void *team_top_region(size_t bytes) {
+    Team *t = g_team;
+    if (!t) {
+        set_error("symmetric heap not initialised");
+        return nullptr;
+    }
+    const size_t aligned = (bytes + 1023) / 1024 * 1024;
+    if (aligned > t->top_reserved) {
+        if (t->bump + aligned > t->heap_bytes) {
+            set_error("symmetric heap exhausted: %zu bytes needed at the top, %zu free", bytes, t->heap_bytes - t->bump);
+            return nullptr;
+        }
+        t->top_reserved = aligned;
+    }
+    return t->base[t->my_pe] + (t->heap_bytes - t->top_reserved);
 }
 
 int team_free(void *p) {

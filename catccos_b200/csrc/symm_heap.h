@@ -51,6 +51,7 @@ struct Team {
     size_t heap_bytes = 0;         // per PE, flag region included
     size_t bump = kFlagBytes;      // next free byte of the (symmetric) bump allocator
     std::vector<size_t> alloc_stack;   // offsets of live allocations, in order
+    size_t top_reserved = 0;       // bytes at the end of the heap held by team_top_region (not part of the stack)
     uint8_t *base[kMaxRanks] = {};
     CUmemGenericAllocationHandle handles[kMaxRanks] = {};
     uint32_t epoch = 0;            // launches so far; identical on all PEs by collective-call order
@@ -106,6 +107,7 @@ int team_init_emulated(int n_pes, uint64_t local_mem_size);
 int team_finalize();
 void *team_malloc(size_t bytes);    // collective: same offset on every PE; nullptr when exhausted
 int team_free(void *p);             // stack discipline: frees p and everything allocated after it
+void *team_top_region(size_t bytes);   // collective: library-internal region at the end of the heap, outside the stack
 int team_host_barrier();
 void *team_ptr(const void *local, int pe);
 int team_read_status(int *out_words /* ST_WORDS */);

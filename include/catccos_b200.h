@@ -267,22 +267,24 @@ CATCCOS_API size_t catccos_sf_atoms_bytes(uint32_t rows, uint32_t k);
 
 /* ------------------------------------------------------------- allocation-free GEMM ---- */
 /* No counterpart in the reference.  For callers that cannot allocate device memory where they
- * need a GEMM — code running while a stream is being captured, plugins inside a runtime that owns
- * and budgets all device memory, loops that cannot afford the implicit synchronisation of an
- * allocation.  Computes C[m,n] = A[m,k] * B (transB=0: B[k,n]; transB=1: B[n,k]) in FP16 or BF16
- * with fp32 accumulation on the current device, asynchronously on `stream`, with the same
- * tcgen05 kernel as the AllGather-Matmul launchers at a world size of one.  It needs no
- * catccos_shmem_init and calls no cudaMalloc/cudaFree or allocating library routine: the only
- * scratch the kernel needs (8 status words and 16 trace slots per CTA) lives in a fixed array of
- * about 33 KiB inside the library image, which every GPU that loads the library holds until the
- * process exits.
+ * need a GEMM: plugins inside a runtime that owns and budgets all device memory (an allocation
+ * made behind its back breaks its accounting or simply fails), and loops that cannot afford the
+ * implicit device synchronisation of an allocation.  Computes C[m,n] = A[m,k] * B (transB=0:
+ * B[k,n]; transB=1: B[n,k]) in FP16 or BF16 with fp32 accumulation on the current device,
+ * asynchronously on `stream`, with the same tcgen05 kernel as the AllGather-Matmul launchers at a
+ * world size of one.  It needs no catccos_shmem_init and calls no cudaMalloc/cudaFree or
+ * allocating library routine: the only scratch the kernel needs (8 status words and 16 trace
+ * slots per CTA) lives in a fixed array of about 33 KiB inside the library image, which every GPU
+ * that loads the library holds until the process exits.
  *   - Limit: at most 256 CTAs (the array has trace slots for 256); on a device with more SMs pass
  *     blockNum <= 256, otherwise CATCCOS_ERR_INVALID.  n and k must be multiples of 8, every
  *     dimension at most 2^30, pointers 16-byte aligned.
- *   - The first call on each device looks up the array's device address (once per device, with
- *     that device current); make that first call before any stream capture begins.
+ *   - The first call on each device does the set-up for that device (with that device current,
+ *     once, under a lock): it looks up the array's device address and sets the shared-memory
+ *     attribute of every kernel variant.  That first call should come before any stream capture.
  *   - All calls on a device share the array and each call clears it first (on `stream`): calls
  *     that overlap on the GPU (different streams) race on the status words and trace slots.
+ *   - Waits inside the kernel are bounded by CATCCOS_WAIT_TIMEOUT_MS (default 10 s).
  * catccos_gemm_no_alloc_status synchronises the device and copies the 8 status words (and, if
  * `trace` is not NULL, 16 uint64 trace slots for each of `traceCtas` CTAs) of the last call. */
 CATCCOS_API int catccos_gemm_no_alloc(void *stream, const void *A, const void *B, void *C, uint32_t m, uint32_t n,

@@ -1,10 +1,11 @@
 """The allocation-free GEMM entry point (catccos_gemm_no_alloc) against the regular launcher.
 
-For users whose code cannot allocate device memory at the call site (stream capture in progress,
-a host runtime that owns all device memory, latency-critical loops): the entry point keeps its
-scratch in a fixed array inside the library.  Checked here through the C-ABI, two calls in a
-row, bit for bit against catccos_launch_emulated on the same inputs (same kernel, so no
-tolerance is needed), plus the documented size limit.  Collected last on purpose.
+For users whose code cannot allocate device memory at the call site (a plugin inside a host
+runtime that owns all device memory, latency-critical loops that cannot take an allocation's
+implicit synchronisation): the entry point keeps its scratch in a fixed array inside the
+library.  Checked here through the C-ABI, two calls in a row, bit for bit against
+catccos_launch_emulated on the same inputs (same kernel, so no tolerance is needed) and within
+1e-2 of the fp32 CPU golden, plus the documented size limit.  Collected last on purpose.
 """
 import ctypes
 
@@ -48,6 +49,11 @@ def test_no_alloc_gemm_matches_regular_launcher(dtype, trans_b):
         assert rc == 0, words
     assert not torch.isnan(ref.float()).any()
     assert torch.equal(outs[0], ref) and torch.equal(outs[1], ref)
+
+    # and the CPU golden of the product (fp32 accumulation), as for the other dense operators
+    from oracle import dense, verify
+    bf = b.cpu().t() if trans_b else b.cpu()
+    assert verify.max_rel_err(outs[1].cpu(), dense.matmul_fp32(a.cpu(), bf)) <= 1e-2
 
 
 def test_no_alloc_gemm_rejects_what_it_cannot_hold():
