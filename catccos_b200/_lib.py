@@ -53,7 +53,8 @@ SIGNATURES = {
     "catccos_debug_set_trace": (ctypes.c_int, [ctypes.c_void_p]),
     "catccos_debug_rs_tile_order": (ctypes.c_int, [ctypes.c_int32] * 5 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32,
                                                                         ctypes.POINTER(ctypes.c_int32)]),
-    "catccos_debug_ag_tile_order": (ctypes.c_int, [ctypes.c_int32] * 4 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
+    "catccos_debug_ag_group_rows": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int32, ctypes.c_int64]),
+    "catccos_debug_ag_tile_order": (ctypes.c_int, [ctypes.c_int32] * 5 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
     "catccos_debug_ag_push_order": (ctypes.c_int, [ctypes.c_int32] * 3 + [ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]),
     "catccos_fp4_gemm_workspace_bytes": (ctypes.c_size_t, [ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32]),
     "catccos_fp4_gemm": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,

@@ -254,6 +254,11 @@ int host_run_status() {
     int w[ST_WORDS];
     int rc = team_read_status(w);
     if (rc) return rc;
+    if (w[ST_CODE] == ERR_PARTIAL_RANGE) {
+        set_error("rank %d sent a partial product beyond the fp16 range of the reduce-scatter exchange: the result is not "
+                  "valid; set CATCCOS_RS_EXCHANGE=native to exchange partials in the output type", w[ST_RANK]);
+        return CATCCOS_ERR_RANGE;
+    }
     if (w[ST_CODE] != 0) {
         set_error("device wait ran out: code=%d site=%d rank=%d index=%d expected=%d seen=%d", w[ST_CODE], w[ST_WHERE],
                   w[ST_RANK], w[ST_INDEX], w[ST_EXPECTED], w[ST_SEEN]);
@@ -340,6 +345,11 @@ int catccos_last_status(int32_t *words8) {
     if (rc) return rc;
     if (words8)
         for (int i = 0; i < ST_WORDS; ++i) words8[i] = w[i];
+    if (w[ST_CODE] == ERR_PARTIAL_RANGE) {
+        set_error("rank %d sent a partial product beyond the fp16 range of the reduce-scatter exchange: the result is not "
+                  "valid; set CATCCOS_RS_EXCHANGE=native to exchange partials in the output type", w[ST_RANK]);
+        return CATCCOS_ERR_RANGE;
+    }
     if (w[ST_CODE] != 0) {
         set_error("device wait ran out: code=%d site=%d rank=%d index=%d expected=%d seen=%d", w[ST_CODE], w[ST_WHERE],
                   w[ST_RANK], w[ST_INDEX], w[ST_EXPECTED], w[ST_SEEN]);
@@ -400,16 +410,26 @@ int catccos_debug_rs_tile_order(int32_t world, int32_t rank, int32_t rows_per_ra
     return tiles;
 }
 
-int catccos_debug_ag_tile_order(int32_t world, int32_t rank, int32_t m, int32_t n, int32_t *out, int32_t capacity) {
+int catccos_debug_ag_tile_order(int32_t world, int32_t rank, int32_t m, int32_t n, int32_t group, int32_t *out,
+                                int32_t capacity) {
     if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || m < 1 || n < 1 || (!out && capacity > 0)) {
         set_error("catccos_debug_ag_tile_order: invalid argument");
         return -CATCCOS_ERR_INVALID;
     }
-    const int nt = (n + BN - 1) / BN, per_src = ((m + 2 * BM - 1) / (2 * BM)) * nt;
-    const int tiles = world * per_src;
+    const int nt = (n + BN - 1) / BN, mt2 = (m + 2 * BM - 1) / (2 * BM);
+    const int tiles = world * mt2 * nt;
+    if (group < 1) group = 1;
     for (int t = 0; t < tiles && t < capacity; ++t)
-        ag_order_decode(world, per_src, nt, rank, t, out[3 * t], out[3 * t + 1], out[3 * t + 2]);
+        ag_order_grouped(world, mt2, nt, group, rank, t, out[3 * t], out[3 * t + 1], out[3 * t + 2]);
     return tiles;
+}
+
+int catccos_debug_ag_group_rows(int64_t tile_bytes, int32_t pairs, int64_t l2_budget_bytes) {
+    if (tile_bytes < 1 || pairs < 1 || l2_budget_bytes < 1) {
+        set_error("catccos_debug_ag_group_rows: invalid argument");
+        return -CATCCOS_ERR_INVALID;
+    }
+    return ag_order_group_rows(tile_bytes, pairs, l2_budget_bytes);
 }
 
 int catccos_debug_ag_push_order(int32_t world, int32_t rank, int32_t m, int32_t *out, int32_t capacity) {

@@ -58,6 +58,11 @@ struct FusedParams {
     int compute_only;                 // measurement mode: no peer traffic, no flag waits (data left by an earlier launch)
     uint64_t timeout_ns;
     int *status;                      // cb::StatusWord[ST_WORDS], device memory
+    int *sched;                       // tile queue of the pair AllGather-Matmul: per local rank {next tile, pairs finished},
+                                      // zero between launches (the last pair to finish clears them)
+    int rs_fp16;                      // reduce family: partial tiles cross the link as fp16 (11-bit mantissa) whatever
+                                      // the output type; 0: in the output type
+    int ag_group;                     // 256-row tiles per L2 group of the AllGather-Matmul tile order (sched.h)
     unsigned long long *trace;        // optional: kTraceSlots %globaltimer stamps per CTA (nullptr = off)
 };
 

@@ -151,6 +151,15 @@ int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, bool allreduc
     return CATCCOS_OK;
 }
 
+// Exchange format of the reduce family's partial tiles: fp16 by default (its 11-bit mantissa keeps the sum of
+// up to seven rounded partials within the 1e-2 gate where bf16 partials do not; a partial beyond the fp16
+// range is reported through the status words), CATCCOS_RS_EXCHANGE=native sends them in the output type,
+// as the reference does (include/catccos/dgemm/kernel/matmul_reduce_scatter.hpp:314).
+int rs_exchange_fp16() {
+    const char *e = getenv("CATCCOS_RS_EXCHANGE");
+    return (e && strcmp(e, "native") == 0) ? 0 : 1;
+}
+
 // one half of the (double-buffered) data region, rounded up to the 1024-byte alignment of the halves
 static size_t dense_half_bytes(int op, int world, int m, int n, int k) {
     const size_t es = 2;
@@ -307,6 +316,8 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.compute_only = (t->debug_flags & 1u) ? 1 : 0;
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
+    p.rs_fp16 = rs_exchange_fp16();
+    p.sched = t->sched_dev;
     p.trace = t->trace_dev;
 
     const bool coop = n_local > 1;
@@ -328,6 +339,16 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     if (use_pair) {
         p.ctas_per_rank = per_rank & ~1;
         p.push_ctas = 0;
+        // L2 grouping of the AllGather-Matmul tile order: rows of A per group from an L2 budget
+        // (CATCCOS_AG_GROUP overrides the choice, CATCCOS_AG_L2_MB the budget)
+        long long l2_mb = 88;
+        if (const char *e = getenv("CATCCOS_AG_L2_MB")) l2_mb = atoll(e) > 0 ? atoll(e) : l2_mb;
+        p.ag_group = ag_order_group_rows(256ll * k * 2, p.ctas_per_rank / 2, l2_mb << 20);
+        const int mt2 = (m + 2 * BM - 1) / (2 * BM);
+        if (R > 1 && p.ag_group > mt2) p.ag_group = p.ag_group / mt2 * mt2;      // whole sources per group
+        if (const char *e = getenv("CATCCOS_AG_GROUP")) {
+            if (atoi(e) > 0) p.ag_group = atoi(e);
+        }
         const int g2 = p.ctas_per_rank * n_local;
         if (bf16)
             return b_mn ? launch_pair<__nv_bfloat16, true>(op, p, maps, g2, coop, stream)

@@ -20,6 +20,9 @@ size_t dense_symmetric_bytes(int op, int world, int m, int n, int k);
 int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, const DenseArgs *args, void *symmetric,
                  int m, int n, int k, int trans_a, int trans_b);
 
+// 1: the reduce family exchanges its partial tiles as fp16 (default), 0: in the output type (CATCCOS_RS_EXCHANGE=native)
+int rs_exchange_fp16();
+
 // Output tensor maps of a pair reduce-scatter kernel for every local rank (see RsMaps): `outputs[l]` is local
 // rank l's output (reduce-scatter: [m/R, n]; all-reduce: [m, n]), 16-bit elements of type `dt`; `symm_off` the
 // offset of the launch's half of the staging region.

@@ -5,8 +5,10 @@
 // rows in its own TMEM; the leader CTA issues one M=256 MMA per 16 K-elements that reads both
 // CTAs' shared memory.  Per SM and K-step this moves 32 KiB from L2 instead of the 48 KiB of the
 // one-CTA 128 x 256 tile, which is what limits that kernel, and leaves room for 6 pipeline stages.
-// Everything around the main loop (tile order, all-gather push lanes, flags, bounded waits,
-// epilogue) is the one-CTA kernel's.
+// The all-gather push lanes, flags and bounded waits are the one-CTA kernel's.  Tiles are handed out
+// dynamically: every pair starts on tile `pair` and then takes the next unclaimed tile of its rank from
+// a global counter, so a pair that had to wait for a peer's rows simply ends up with fewer tiles
+// instead of finishing late; the tile sequence itself is the L2-grouped order of sched.h.
 #pragma once
 #include <type_traits>
 
@@ -23,6 +25,10 @@ constexpr int kPBStage = 128 * BK * 2;         // 128 columns of B   : 16 KiB
 constexpr int kPairSmemBytes = kPStages * (kPAStage + kPBStage) + kSideSmemBytes + 1024 + 512;
 constexpr int BM2 = 2 * BM;                    // rows of a pair's tile
 
+constexpr int kTileRing = 8;                   // claimed tiles travel to the roles through a ring of this many slots
+constexpr uint32_t kTileAhead = 3;             // tiles claimed beyond the last one the epilogues have finished
+constexpr uint32_t kTileEnd = 0xFFFFFFFFu;     // ring entry: no tiles left
+
 struct PairSmem {
     uint64_t full[kPStages];        // used in the leader: both CTAs' loads of a stage have landed
     uint64_t empty[kPStages];       // per CTA: the pair's MMAs have finished reading this stage
@@ -32,7 +38,11 @@ struct PairSmem {
     uint64_t push_bar[kPushLanesShared];
     uint32_t tmem_base;
     int abort_flag;
-    uint32_t tiles_ready;           // tiles of this CTA (in its own order) whose gathered rows are known to be in
+    uint32_t tiles_ready;           // tiles of this CTA (in claim order) whose gathered rows are known to be in
+    uint32_t ring[kTileRing];       // tile index of claim number seq at [seq % kTileRing] (written by the leader's warp 10)
+    uint32_t claimed;               // number of valid ring entries so far
+    uint32_t done_self;             // tiles this CTA's epilogue has finished
+    uint32_t done_peer;             // leader only: the same count of the other CTA
 };
 
 template <typename T, bool B_MN>
@@ -76,6 +86,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
         for (int l = 0; l < kPushLanesShared; ++l) mbar_init(&sh->push_bar[l], 1);
         sh->abort_flag = 0;
         sh->tiles_ready = 0;
+        sh->claimed = 0;
+        sh->done_self = 0;
+        sh->done_peer = 0;
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
@@ -98,34 +111,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
     ctl.rank = rank;
     if (threadIdx.x == 0) CB_TRACE(TR_START, globaltimer_ns());
 
-    // tile t -> (source rank s, 256-row tile mi2, column tile ni); own rows first, then rank+1, ...
+    // tile t -> (source rank s, 256-row tile mi2, column tile ni): own rows first, then rank+1, ..., in L2 groups
     auto decode = [&](int t, int &s, int &mi2, int &ni, bool &gathered) {
-        ag_order_decode(R, per_src, nt, rank, t, s, mi2, ni);
+        ag_order_grouped(R, mt2, nt, p.ag_group, rank, t, s, mi2, ni);
         gathered = (s != rank);
+    };
+    // claim number seq -> tile index, once the leader's warp 10 has published it (kTileEnd: no more tiles)
+    auto claimed_tile = [&](uint32_t seq, uint32_t &t) -> bool {
+        if (!wait_cluster_counter_gt(&sh->claimed, seq, ctl, W_TILE_QUEUE)) return false;
+        t = sh->ring[seq % kTileRing];
+        return true;
     };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer ----
         // lane 0 issues the loads; the arrival flags of gathered rows are polled ahead of it by warp 10
-        uint32_t it = 0, seq = 0;
+        uint32_t it = 0;
         bool ok = true;
         uint64_t prod_wait_ns = 0;
-        for (int t = pair; t < num_tiles && ok; t += pairs, ++seq) {
-            int s, mi2, ni;
-            bool gathered;
-            decode(t, s, mi2, ni, gathered);
-            const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;    // this CTA's 128 rows
-            if (gathered && !p.compute_only && row_in_src < p.M && lane == 0) {
-                const uint64_t tw0 = p.trace ? globaltimer_ns() : 0;
-                ok = wait_smem_counter_gt(&sh->tiles_ready, seq, ctl, W_AG_CHUNK);
-                if (p.trace) {
-                    if (prod_wait_ns == 0) CB_TRACE(TR_PROD_WAIT_FIRST, tw0);
-                    prod_wait_ns += globaltimer_ns() - tw0 + 1;
+        if (lane == 0) {
+            for (uint32_t seq = 0; ok; ++seq) {
+                uint32_t tq;
+                if (!(ok = claimed_tile(seq, tq)) || tq == kTileEnd) break;
+                int s, mi2, ni;
+                bool gathered;
+                decode(static_cast<int>(tq), s, mi2, ni, gathered);
+                const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;    // this CTA's 128 rows
+                if (gathered && !p.compute_only && row_in_src < p.M) {
+                    const uint64_t tw0 = p.trace ? globaltimer_ns() : 0;
+                    if (!(ok = wait_smem_counter_gt(&sh->tiles_ready, seq, ctl, W_AG_CHUNK))) break;
+                    if (p.trace) {
+                        if (prod_wait_ns == 0) CB_TRACE(TR_PROD_WAIT_FIRST, tw0);
+                        prod_wait_ns += globaltimer_ns() - tw0 + 1;
+                    }
                 }
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
-            if (lane == 0) {
                 const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
                 const int a_row = (gathered ? s * p.M : 0) + row_in_src;
                 const int n_half = ni * BN + static_cast<int>(cr) * 128;         // this CTA's 128 columns of B
@@ -146,7 +165,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                     }
                 }
             }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
         }
         if (lane == 0) CB_TRACE(TR_PROD_WAIT_NS, prod_wait_ns);
         if (!ok && lane == 0) {
@@ -163,7 +181,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             uint64_t wait_tmem = 0, wait_smem = 0;
-            for (int t = pair; t < num_tiles && ok; t += pairs) {
+            for (;;) {
+                uint32_t tq;
+                if (!(ok = claimed_tile(tcount, tq)) || tq == kTileEnd) break;
                 const uint32_t acc = tcount & 1;
                 const uint64_t tm0 = p.trace ? globaltimer_ns() : 0;
                 if (!(ok = mbar_wait(&sh->tmem_empty[acc], ((tcount >> 1) & 1) ^ 1, ctl, W_TMEM_EMPTY))) break;
@@ -212,10 +232,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
         uint32_t tcount = 0;
         bool ok = true;
         T *const C = reinterpret_cast<T *>(ra.C);
-        for (int t = pair; t < num_tiles && ok; t += pairs) {
+        for (;;) {
+            uint32_t tq;
+            if (!(ok = claimed_tile(tcount, tq)) || tq == kTileEnd) break;
             int s, mi2, ni;
             bool gathered;
-            decode(t, s, mi2, ni, gathered);
+            decode(static_cast<int>(tq), s, mi2, ni, gathered);
             const uint32_t acc = tcount & 1;
             if (!(ok = mbar_wait(&sh->tmem_full[acc], (tcount >> 1) & 1, ctl, W_TMEM_FULL))) break;
             tc_fence_after();
@@ -244,18 +266,51 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty[acc]), 0));
             ++tcount;
+            // progress of this CTA's epilogue, which paces the claiming of further tiles
+            if (warp == 2 && lane == 0) {
+                if (cr == 0) st_release_cta_smem(&sh->done_self, tcount);
+                else st_release_cluster_smem(mapa_cluster(smem_u32(&sh->done_peer), 0), tcount);
+            }
         }
     } else if (warp == 10) {
-        // ------------------------------------------------------------ flag scout ----
-        // walks this CTA's tiles ahead of the producer and waits (whole warp, one lane per unit) for
-        // the rows of every gathered chunk; the count of cleared tiles goes to shared memory
-        if (R > 1 && !p.compute_only) {
-            uint32_t seq = 0;
-            bool ok = true;
-            for (int t = pair; t < num_tiles && ok; t += pairs, ++seq) {
+        // ------------------------------------------------- tile queue and flag scout ----
+        // Leader: claims the pair's next tile (the first one is tile `pair`, the others come from the
+        // rank's counter), publishes it to both CTAs, at most kTileAhead tiles beyond the epilogues.
+        // Both CTAs: wait (whole warp, one lane per unit) for the rows of a gathered tile's chunk and
+        // publish the count of cleared tiles to the producer.
+        bool ok = true;
+        int *const next_tile = p.sched + 2 * lrank;
+        for (uint32_t seq = 0; ok; ++seq) {
+            uint32_t tq = 0;
+            if (cr == 0) {
+                if (lane == 0) {
+                    if (seq >= kTileAhead) {
+                        ok = wait_smem_counter_gt(&sh->done_self, seq - kTileAhead, ctl, W_TILE_QUEUE) &&
+                             wait_cluster_counter_gt(&sh->done_peer, seq - kTileAhead, ctl, W_TILE_QUEUE);
+                    }
+                    if (ok) {
+                        const int t = seq == 0 ? pair : pairs + atomicAdd(next_tile, 1);
+                        tq = t < num_tiles ? static_cast<uint32_t>(t) : kTileEnd;
+                        sh->ring[seq % kTileRing] = tq;
+                        st_cluster_smem(mapa_cluster(smem_u32(&sh->ring[seq % kTileRing]), 1), tq);
+                        st_release_cta_smem(&sh->claimed, seq + 1);
+                        st_release_cluster_smem(mapa_cluster(smem_u32(&sh->claimed), 1), seq + 1);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                tq = __shfl_sync(0xffffffffu, tq, 0);
+                if (!ok) break;
+            } else {
+                if (lane == 0) ok = claimed_tile(seq, tq);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                tq = __shfl_sync(0xffffffffu, tq, 0);
+                if (!ok) break;
+            }
+            if (tq == kTileEnd) break;
+            if (R > 1 && !p.compute_only) {
                 int s, mi2, ni;
                 bool gathered;
-                decode(t, s, mi2, ni, gathered);
+                decode(static_cast<int>(tq), s, mi2, ni, gathered);
                 const int row_in_src = mi2 * BM2 + static_cast<int>(cr) * BM;
                 if (gathered && row_in_src < p.M) {
                     const uint32_t w = kFlagOpBase + (s * mt_ag + (row_in_src / BM)) * kAgSubChunks;
@@ -263,6 +318,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                     fence_proxy_async_global();     // rows seen through the flags -> the producer's TMA loads
                 }
                 if (lane == 0) st_release_cta_smem(&sh->tiles_ready, seq + 1);
+            }
+        }
+        // the last pair of the rank to run out of tiles leaves the counters at zero for the next launch
+        if (cr == 0 && lane == 0) {
+            if (!ok) {
+                // this pair gave up: the other roles must not wait for tiles that will not come
+                const uint32_t seq_end = sh->claimed;
+                sh->ring[seq_end % kTileRing] = kTileEnd;
+                st_cluster_smem(mapa_cluster(smem_u32(&sh->ring[seq_end % kTileRing]), 1), kTileEnd);
+                st_release_cta_smem(&sh->claimed, seq_end + 1);
+                st_release_cluster_smem(mapa_cluster(smem_u32(&sh->claimed), 1), seq_end + 1);
+            }
+            __threadfence();
+            if (atomicAdd(next_tile + 1, 1) == pairs - 1) {
+                next_tile[0] = 0;
+                next_tile[1] = 0;
+                __threadfence();
             }
         }
     } else {

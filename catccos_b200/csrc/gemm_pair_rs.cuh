@@ -218,6 +218,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         // whose writer waits for it.
         bool pend = false, pend_remote = false;
         int pend_d = 0, pend_tip = 0;
+        const bool fp16x = p.rs_fp16 != 0;       // exchange format of the partial tiles
+        float amax_sent = 0.0f;                  // largest magnitude this thread sent as fp16
         auto publish = [&](bool everything) -> bool {
             if (!pend) return true;
             if (lane == 0) {
@@ -346,7 +348,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                                         const uint32_t w4[4] = {part[s][g].x, part[s][g].y, part[s][g].z, part[s][g].w};
 #pragma unroll
                                         for (int h = 0; h < 4; ++h) {
-                                            const float2 x = Pack2<T>::unpack(w4[h]);
+                                            const float2 x = unpack_partial<T>(w4[h], fp16x);
                                             f[g * 8 + h * 2] += x.x;
                                             f[g * 8 + h * 2 + 1] += x.y;
                                         }
@@ -355,8 +357,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                             }
                         }
                         uint32_t pk[16];
+                        if (remote && fp16x) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) pk[i] = Pack2<T>::pack(f[2 * i], f[2 * i + 1]);
+                            for (int i = 0; i < 32; ++i) amax_sent = fmaxf(amax_sent, fabsf(f[i]));
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            pk[i] = remote ? pack_partial<T>(f[2 * i], f[2 * i + 1], fp16x) : Pack2<T>::pack(f[2 * i], f[2 * i + 1]);
                         // row `lane` of the buffer; 16-byte chunk j sits at j ^ (row & 7) (128-byte swizzle)
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
@@ -395,6 +402,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
         if (ok) ok = publish(true);
         if (lane == 0) bulk_wait<0>();
+        if (!(amax_sent <= 65504.0f)) report_partial_range(p.status, rank, static_cast<int>(tcount));
         if (etid == 0) {
             CB_TRACE(TR_EPI_WAIT_NS, epi_wait_ns);
             CB_TRACE(TR_EPI_STORE_NS, epi_store_ns);

@@ -374,6 +374,7 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
     p.epoch = epoch;
     p.entered_need = slot.entered_need;
     p.compute_only = compute_only ? 1 : 0;
+    p.rs_fp16 = rs_exchange_fp16();
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
     p.trace = t->trace_dev;

@@ -27,6 +27,7 @@ struct MxRsParams {
     uint32_t epoch;
     uint32_t entered_need;
     int compute_only;
+    int rs_fp16;                     // partial tiles cross the link as fp16 (0: in the output type)
     uint64_t timeout_ns;
     int *status;
     unsigned long long *trace;
@@ -224,6 +225,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         uint8_t *const wbuf = smem_side + q * 8192;
         constexpr int kSlabs = BN / 64;
         bool pend = false;
+        const bool fp16x = p.rs_fp16 != 0;       // exchange format of the partial tiles
+        float amax_sent = 0.0f;                  // largest magnitude this thread sent as fp16
         int pend_d = 0, pend_tip = 0;
         auto publish = [&](bool everything) -> bool {
             if (!pend) return true;
@@ -339,7 +342,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                                         const uint32_t w4[4] = {part[s][g].x, part[s][g].y, part[s][g].z, part[s][g].w};
 #pragma unroll
                                         for (int h = 0; h < 4; ++h) {
-                                            const float2 x = Pack2<TOut>::unpack(w4[h]);
+                                            const float2 x = unpack_partial<TOut>(w4[h], fp16x);
                                             f[g * 8 + h * 2] += x.x;
                                             f[g * 8 + h * 2 + 1] += x.y;
                                         }
@@ -348,8 +351,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                             }
                         }
                         uint32_t pk[16];
+                        if (remote && fp16x) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) pk[i] = Pack2<TOut>::pack(f[2 * i], f[2 * i + 1]);
+                            for (int i = 0; i < 32; ++i) amax_sent = fmaxf(amax_sent, fabsf(f[i]));
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            pk[i] = remote ? pack_partial<TOut>(f[2 * i], f[2 * i + 1], fp16x) : Pack2<TOut>::pack(f[2 * i], f[2 * i + 1]);
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
                             const int j = (cc * 4 + g) ^ (lane & 7);
@@ -380,6 +388,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             ++tcount;
         }
         if (ok) ok = publish(true);
+        if (!(amax_sent <= 65504.0f)) report_partial_range(p.status, rank, static_cast<int>(tcount));
         if (lane == 0) bulk_wait<0>();
     } else if (warp == 6) {
         // tell every peer that this rank has entered the epoch: its staging rows may be overwritten

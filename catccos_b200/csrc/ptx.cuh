@@ -17,11 +17,15 @@ enum StatusWord : int {
     ST_SEEN = 5,
     ST_WORDS = 8
 };
-enum ErrCode : int { ERR_NONE = 0, ERR_FLAG_TIMEOUT = 1, ERR_MBAR_TIMEOUT = 2, ERR_ABORTED = 3 };
+enum ErrCode : int {
+    ERR_NONE = 0, ERR_FLAG_TIMEOUT = 1, ERR_MBAR_TIMEOUT = 2, ERR_ABORTED = 3,
+    ERR_MOE_CAPACITY = 4,      // MoE: the routing needs more receive rows than the buffer holds
+    ERR_PARTIAL_RANGE = 5      // reduce family: a partial product does not fit the fp16 exchange format
+};
 enum WaitSite : int {
     W_ENTERED = 1, W_AG_CHUNK = 2, W_RS_PARTIAL = 3, W_AR_FINAL = 4, W_MBAR_FULL = 5, W_MBAR_EMPTY = 6,
     W_TMEM_FULL = 7, W_TMEM_EMPTY = 8, W_DRAIN = 9, W_TEST = 10, W_MOE_COUNTS = 11, W_MOE_ROWS = 12,
-    W_MOE_ACT = 13, W_MOE_COMBINE = 14, W_MXAG = 15
+    W_MOE_ACT = 13, W_MOE_COMBINE = 14, W_MXAG = 15, W_TILE_QUEUE = 16
 };
 
 struct WaitCtl {
@@ -399,6 +403,36 @@ __device__ __forceinline__ void st_release_cta_smem(uint32_t *ctr, uint32_t v) {
     asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(ctr)), "r"(v) : "memory");
 }
 
+// Words in the shared memory of a CTA of this cluster, given by their shared::cluster address (mapa_cluster):
+// plain store, release store at cluster scope, and the matching acquire load / bounded wait on this
+// CTA's own copy (the writer may be the other CTA of the pair).
+__device__ __forceinline__ void st_cluster_smem(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_cluster_smem(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.release.cluster.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_cluster_smem(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.cluster.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool wait_cluster_counter_gt(const uint32_t *ctr, uint32_t idx, const WaitCtl &c, int where) {
+    uint32_t spins = 0, seen;
+    for (;;) {
+        seen = ld_acquire_cluster_smem(ctr);
+        if (seen > idx) return true;
+        if ((++spins & 255u) == 0) {
+            if (*c.abort_smem) return false;
+            if (globaltimer_ns() > c.deadline_ns) {
+                report_failure(c, ERR_FLAG_TIMEOUT, where, static_cast<int>(idx), static_cast<int>(idx) + 1,
+                               static_cast<int>(seen));
+                return false;
+            }
+        }
+    }
+}
+
 // Whole warp: lane q waits for flags[q], q + 32, ... (< count); every lane gets true when all are up.
 __device__ __forceinline__ bool wait_flags_warp(const uint32_t *flags, int count, uint32_t expected, const WaitCtl &c,
                                                 int where, int index0) {
@@ -434,5 +468,23 @@ template <> struct Pack2<__half> {
         return __half22float2(*reinterpret_cast<__half2 *>(&u));
     }
 };
+
+// Reduce family: a partial tile travels as fp16 (when `fp16` is set) or in the output type T.
+template <typename T>
+__device__ __forceinline__ uint32_t pack_partial(float a, float b, bool fp16) {
+    return fp16 ? Pack2<__half>::pack(a, b) : Pack2<T>::pack(a, b);
+}
+template <typename T>
+__device__ __forceinline__ float2 unpack_partial(uint32_t u, bool fp16) {
+    return fp16 ? Pack2<__half>::unpack(u) : Pack2<T>::unpack(u);
+}
+// a value beyond the fp16 range was sent as a partial: recorded (first error wins), nothing is aborted
+__device__ __forceinline__ void report_partial_range(int *status, int rank, int tile) {
+    if (atomicCAS(status + ST_CODE, 0, ERR_PARTIAL_RANGE) == 0) {
+        status[ST_WHERE] = W_RS_PARTIAL;
+        status[ST_RANK] = rank;
+        status[ST_INDEX] = tile;
+    }
+}
 
 }  // namespace cb

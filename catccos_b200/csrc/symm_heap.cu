@@ -287,8 +287,10 @@ static int common_setup(Team *t, uint64_t local_mem_size, const DriverApi **api_
     if (gran == 0) gran = 2u << 20;
     const size_t want = static_cast<size_t>(local_mem_size) + kFlagBytes;
     t->heap_bytes = (want + gran - 1) / gran * gran;
-    RT_TRY(cudaMalloc(&t->status_dev, ST_WORDS * sizeof(int)));
-    RT_TRY(cudaMemset(t->status_dev, 0, ST_WORDS * sizeof(int)));
+    // status words followed by the tile-queue counters of the fused kernels (two per local rank)
+    RT_TRY(cudaMalloc(&t->status_dev, (ST_WORDS + 2 * kMaxRanks) * sizeof(int)));
+    RT_TRY(cudaMemset(t->status_dev, 0, (ST_WORDS + 2 * kMaxRanks) * sizeof(int)));
+    t->sched_dev = t->status_dev + ST_WORDS;
     if (const char *e = getenv("CATCCOS_WAIT_TIMEOUT_MS")) {
         const long ms = atol(e);
         if (ms > 0) t->timeout_ns = static_cast<uint64_t>(ms) * 1000000ull;
@@ -497,7 +499,8 @@ int team_read_status(int *out) {
 int team_reset_status() {
     Team *t = g_team;
     if (!t) return CATCCOS_ERR_NOT_INIT;
-    RT_TRY(cudaMemset(t->status_dev, 0, ST_WORDS * sizeof(int)));
+    // also the tile-queue counters: a launch that gave up may have left them non-zero
+    RT_TRY(cudaMemset(t->status_dev, 0, (ST_WORDS + 2 * kMaxRanks) * sizeof(int)));
     return CATCCOS_OK;
 }
 

@@ -56,6 +56,7 @@ struct Team {
     CUmemGenericAllocationHandle handles[kMaxRanks] = {};
     uint32_t epoch = 0;            // launches so far; identical on all PEs by collective-call order
     int *status_dev = nullptr;     // StatusWord[ST_WORDS]
+    int *sched_dev = nullptr;      // tile-queue counters: {next tile, pairs finished} per local rank, zero between launches
     uint64_t timeout_ns = 10ull * 1000 * 1000 * 1000;
     unsigned long long *trace_dev = nullptr;   // optional per-CTA trace buffer (catccos_debug_set_trace)
     uint32_t debug_flags = 0;      // bit 0: compute-only launches (exposed-communication measurement)

@@ -34,7 +34,9 @@ enum {
     CATCCOS_ERR_CUDA = 3,        /* a CUDA call failed, or no driver/GPU is present */
     CATCCOS_ERR_BOOTSTRAP = 4,   /* rendezvous with the peer processes failed or timed out */
     CATCCOS_ERR_NOMEM = 5,
-    CATCCOS_ERR_DEVICE_WAIT = 6  /* a device-side wait ran out: see catccos_last_status */
+    CATCCOS_ERR_DEVICE_WAIT = 6, /* a device-side wait ran out: see catccos_last_status */
+    CATCCOS_ERR_RANGE = 7        /* a partial product of Matmul-ReduceScatter / AllReduce left the fp16 range of the
+                                    exchange format (see CATCCOS_RS_EXCHANGE): the result is not valid */
 };
 
 /* utils/info.h:95-114 — same 17 fields, same order. */
@@ -110,7 +112,8 @@ CATCCOS_API int catccos_shmem_barrier_all(void);
 /* ----------------------------------------------------------------------- diagnostics ---- */
 CATCCOS_API const char *catccos_last_error(void);
 /* Synchronises the device and copies the 8 status words {code, wait site, rank, flag index,
- * expected, seen, -, -}.  Returns CATCCOS_ERR_DEVICE_WAIT when code != 0.  (The reference has no
+ * expected, seen, -, -}.  Returns CATCCOS_ERR_DEVICE_WAIT when code != 0 (CATCCOS_ERR_RANGE for code 5: a
+ * partial product left the range of the reduce family's fp16 exchange format).  (The reference has no
  * return codes from kernels and unbounded device waits: utils/utils.h:26-40,
  * include/catccos/arch/cross_rank_sync.hpp:88-97.) */
 CATCCOS_API int catccos_last_status(int32_t *words8);
@@ -134,13 +137,19 @@ CATCCOS_API int catccos_debug_set_trace(void *device_buf);
  * triples and returns how many the order has, or a negative CATCCOS_ERR_* code.
  *   rs_tile_order: pair tiles of Matmul-ReduceScatter / AllReduce for `rank`: (owner, 256-row stripe, column tile);
  *                  `rows_per_rank` rows per owner, `pairs` CTA pairs; *lag (optional) receives the own-stripe lag.
- *   ag_tile_order: pair tiles of AllGather-Matmul: (source rank, 256-row tile, column tile); m = rows of one rank.
+ *   ag_tile_order: pair tiles of AllGather-Matmul in claim order: (source rank, 256-row tile, column tile); m = rows
+ *                  of one rank, `group` = 256-row tiles per L2 group (own and gathered rows are grouped separately;
+ *                  column-tile major inside a group, odd groups backwards).
  *   ag_push_order: all-gather push units of `rank`: (destination, 128-row chunk, unit inside the chunk). */
 CATCCOS_API int catccos_debug_rs_tile_order(int32_t world, int32_t rank, int32_t rows_per_rank, int32_t n, int32_t pairs,
                                             int32_t *out, int32_t capacity, int32_t *lag);
-CATCCOS_API int catccos_debug_ag_tile_order(int32_t world, int32_t rank, int32_t m, int32_t n, int32_t *out,
-                                            int32_t capacity);
+CATCCOS_API int catccos_debug_ag_tile_order(int32_t world, int32_t rank, int32_t m, int32_t n, int32_t group,
+                                            int32_t *out, int32_t capacity);
 CATCCOS_API int catccos_debug_ag_push_order(int32_t world, int32_t rank, int32_t m, int32_t *out, int32_t capacity);
+/* The launcher's choice of `group`: the largest number of 256-row tiles (1..16) for which the group's rows of A
+ * plus the column tiles of B in flight with them (`pairs` CTA pairs) stay inside `l2_budget_bytes`;
+ * tile_bytes = 256 * k * element size. */
+CATCCOS_API int catccos_debug_ag_group_rows(int64_t tile_bytes, int32_t pairs, int64_t l2_budget_bytes);
 /* The double-buffering decision of the dense and MXFP8 launchers, replayed on the host for a sequence of `n`
  * launches: sigs[i] identifies operator + shape + buffer of launch i, foreign_before[i] != 0 means a launch of
  * another operator family (which consumes an epoch) happened just before it.  half[i] receives the half of the

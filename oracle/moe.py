@@ -265,3 +265,145 @@ def grouped_matmul_alltoallv(a_deq_list, w_deq_lists, tokens_per_expert_all, ep,
             pos += n
         outs.append(np.concatenate(parts, axis=0))
     return alltoallv_combine(outs, tokens_per_expert_all, ep, experts_per_rank)
+
+
+# --------------------------------------------------------------------------- #
+# AllToAllV-AllGather and ReduceScatter-AllToAllV block schedulers (EP x TP layouts)
+# --------------------------------------------------------------------------- #
+def _cdiv(a, b):
+    return -(-int(a) // int(b))
+
+
+def _clip_sub(a, b):
+    return max(int(a) - int(b), 0)
+
+
+class AllToAllVAllGatherSchedule:
+    """Bookkeeping of `BlockCommSchedulerAllToAllVAllGather`
+    (include/catccos/comm/block/comm_block_scheduler_alltoallv_allgather.hpp:27-178) over an
+    `AllToAllVAllGatherProblemShape` (include/catccos/dgemm/alltoallv_allgather_problem_shape.hpp:
+    20-133): rank_size = ep_size * tp_size ranks, `local_tokens_per_expert[e]` = tokens this rank
+    sends for global expert e, `global_tokens_per_local_expert[r * L + le]` = tokens rank r sends
+    to this rank's local expert le.  One communication round moves at most `comm_rows` rows per
+    peer, cut into blocks of `block_shape` (rows, columns)."""
+
+    def __init__(self, k, rank_size, rank_idx, ep_size, expert_num, local_tokens_per_expert,
+                 global_tokens_per_local_expert, comm_rows, block_shape):
+        self.k, self.rank_size, self.rank_idx, self.ep_size = k, rank_size, rank_idx, ep_size
+        self.local_experts = expert_num // ep_size
+        self.comm_rows = comm_rows
+        self.block_shape = tuple(block_shape)
+        self.block_grid = (_cdiv(comm_rows, block_shape[0]), _cdiv(k, block_shape[1]))       # :52-53
+        self.core_loops = self.block_grid[0] * self.block_grid[1] * rank_size                # :54
+        loc = np.asarray(local_tokens_per_expert, dtype=np.int64).reshape(ep_size, self.local_experts)
+        glo = np.asarray(global_tokens_per_local_expert, dtype=np.int64).reshape(rank_size, self.local_experts)
+        self.input_split = loc.sum(axis=1)                                                   # :58-61
+        self.input_offset = np.concatenate([[0], np.cumsum(self.input_split)[:-1]])          # :62-63
+        self.output_split = glo.sum(axis=1)                                                  # :68-71
+        loops = [_cdiv(v, comm_rows) for v in self.input_split] + [_cdiv(v, comm_rows) for v in self.output_split]
+        self.comm_loops = max([0] + loops)                                                   # :64-65, :72-73
+
+    def actual_receive_accum(self, comm_idx):
+        """Blocks this rank receives in round `comm_idx` (:83-94)."""
+        total = 0
+        for r in range(self.rank_size):
+            rows = min(self.comm_rows, _clip_sub(self.output_split[r], comm_idx * self.comm_rows))
+            total += _cdiv(rows, self.block_shape[0]) * _cdiv(self.k, self.block_shape[1])
+        return total
+
+    def block_offset(self, task_idx):
+        """Task -> ((row, column) offset inside the round, destination rank): destination rank
+        fastest, then block column, then block row (:128-135)."""
+        dst = task_idx % self.rank_size
+        blk = task_idx // self.rank_size
+        return ((blk // self.block_grid[1]) * self.block_shape[0], (blk % self.block_grid[1]) * self.block_shape[1]), dst
+
+    def source_offset(self, comm_idx, offset, dst_rank):
+        """`RemapperSrc::operator()` (:143-151): row of this rank's expert-sorted tokens."""
+        ep = dst_rank % self.ep_size
+        return int(self.input_offset[ep]) + comm_idx * self.comm_rows + offset[0], offset[1]
+
+    def actual_block_shape(self, comm_idx, offset, dst_rank):
+        """`RemapActualBlockShape` (:153-176): the block clipped to what is left for that peer."""
+        ep = dst_rank % self.ep_size
+        rows_left = min(self.comm_rows, _clip_sub(self.input_split[ep], comm_idx * self.comm_rows))
+        return (min(self.block_shape[0], _clip_sub(rows_left, offset[0])),
+                min(self.block_shape[1], _clip_sub(self.k, offset[1])))
+
+
+class ReduceScatterAllToAllVSchedule:
+    """Bookkeeping of `BlockCommSchedulerReduceScatterAllToAllV`
+    (include/catccos/comm/block/comm_block_scheduler_reducescatter_alltoallv.hpp:27-302), the way
+    back of GroupedMatmul-AllToAllV: results leave in rounds of `blocks_per_comm` GEMM blocks
+    (`mmad_block` = rows x columns of one GEMM block) and every communication block of
+    `comm_block` finds its destination row through the expert it belongs to."""
+
+    def __init__(self, n, rank_size, ep_size, expert_num, local_tokens_per_expert, global_tokens_per_local_expert,
+                 blocks_per_comm, src_ep, mmad_block, comm_block, core_split, deterministic=False):
+        self.n, self.rank_size, self.ep_size, self.src_ep = n, rank_size, ep_size, src_ep
+        self.local_experts = L = expert_num // ep_size
+        self.blocks_per_comm = blocks_per_comm
+        self.mmad_block, self.comm_block = tuple(mmad_block), tuple(comm_block)
+        comm_shape = (blocks_per_comm * mmad_block[0], mmad_block[1])                        # :143
+        self.block_grid = (_cdiv(comm_shape[0], comm_block[0]), _cdiv(comm_shape[1], comm_block[1]))
+        tiles = self.block_grid[0] * self.block_grid[1]
+        if deterministic:                                                                    # :146-151
+            self.core_split = (core_split[0] * core_split[1], 1)
+            self.core_loops = _cdiv(tiles, self.core_split[0]) * self.core_split[0]
+        else:
+            self.core_split = tuple(core_split)
+            self.core_loops = tiles
+        n_loops = _cdiv(n, mmad_block[1])                                                    # :154
+        loc = np.asarray(local_tokens_per_expert, dtype=np.int64).reshape(ep_size, L)
+        glo = np.asarray(global_tokens_per_local_expert, dtype=np.int64).reshape(rank_size, L)
+        self.split_in_expert = np.array([[_cdiv(t, mmad_block[0]) * n_loops for t in row] for row in loc])   # :160
+        self.input_split = self.split_in_expert.sum(axis=1)
+        flat = loc.reshape(-1)
+        self.input_offset = np.concatenate([[0], np.cumsum(flat)[:-1]]).reshape(ep_size, L)  # :162-163
+        self.actual_mmad_shape = [(int(loc[src_ep, le]), n) for le in range(L)]              # :169-173
+        self.mmad_grid = [(_cdiv(r, mmad_block[0]), _cdiv(c, mmad_block[1])) for r, c in self.actual_mmad_shape]
+        self.output_split = np.array([sum(_cdiv(t, mmad_block[0]) for t in row) * n_loops for row in glo])   # :175-180
+        loops = [_cdiv(v, blocks_per_comm) for v in self.input_split] + [_cdiv(v, blocks_per_comm) for v in self.output_split]
+        self.comm_loops = max([0] + loops)
+        self.start_expert, self.accum_blocks, self.mmad_idx = 0, 0, 0
+        self.comm_offset, self.actual_comm_shape = 0, (0, 0)
+
+    def update_comm_context(self, comm_idx):                                                 # :194-202
+        self.comm_offset = comm_idx * self.blocks_per_comm
+        blocks = min(self.blocks_per_comm, _clip_sub(self.input_split[self.src_ep], self.comm_offset))
+        self.actual_comm_shape = (blocks * self.mmad_block[0], self.mmad_block[1])
+
+    def update_local_expert_context(self, offset):                                           # :204-217
+        self.mmad_idx = self.comm_offset + offset[0] // self.mmad_block[0]
+        while self.start_expert < self.local_experts:
+            step = int(self.split_in_expert[self.src_ep][self.start_expert])
+            if self.accum_blocks + step > self.mmad_idx:
+                break
+            self.accum_blocks += step
+            self.start_expert += 1
+
+    def actual_receive_accum(self):                                                          # :219-229
+        return int(sum(1 for r in range(self.rank_size) if self.comm_offset < self.output_split[r]))
+
+    def block_offset(self, task_idx):                                                        # :253-260
+        m = task_idx // self.block_grid[1]
+        return m * self.comm_block[0], (task_idx - m * self.block_grid[1]) * self.comm_block[1]
+
+    def destination(self, offset):
+        """`RemapperDst::operator()` (:262-287): ((row, column) in the source rank's expert-sorted
+        output, rows and columns left inside the GEMM block)."""
+        from . import swizzle
+        le = self.start_expert
+        idx = self.mmad_idx - self.accum_blocks
+        br, bc = swizzle.matrix_swizzle_coord(self.mmad_grid[le][0], self.mmad_grid[le][1], idx, 7, 1)
+        off = (br * self.mmad_block[0], bc * self.mmad_block[1])
+        shape = self.actual_mmad_shape[le]
+        actual = (min(self.mmad_block[0], _clip_sub(shape[0], off[0])), min(self.mmad_block[1], _clip_sub(shape[1], off[1])))
+        inside = (offset[0] % self.mmad_block[0], offset[1] % self.mmad_block[1])
+        residue = (actual[0] - min(actual[0], inside[0]), actual[1] - min(actual[1], inside[1]))
+        dst = (int(self.input_offset[self.src_ep][le]) + off[0] + inside[0], off[1] + inside[1])
+        return dst, residue
+
+    def actual_block_shape(self, offset):                                                    # :289-300
+        return (min(self.comm_block[0], _clip_sub(self.actual_comm_shape[0], offset[0])),
+                min(self.comm_block[1], _clip_sub(self.actual_comm_shape[1], offset[1])))

@@ -179,3 +179,37 @@ def test_bounded_wait_reports_and_context_survives():
         assert rc == 0
         x = torch.ones(4, device="cuda")
         assert float(x.sum()) == 4.0
+
+
+def test_partials_beyond_the_fp16_exchange_range_are_reported(monkeypatch):
+    """The reduce family sends its partial tiles as fp16 (11-bit mantissa) by default.  A partial
+    product beyond 65504 does not fit: the launch finishes, the status words say so
+    (CATCCOS_ERR_RANGE), and CATCCOS_RS_EXCHANGE=native, which sends partials in the bf16 output
+    type as the reference does, computes the same operator correctly."""
+    from catccos_b200 import lib
+    rt = _rt()
+    world, m, n, k = 2, 512, 256, 128
+    a = [torch.full((m, k), 300.0, dtype=torch.bfloat16) for _ in range(world)]
+    b = [torch.full((k, n), 100.0 + r, dtype=torch.bfloat16) for r in range(world)]     # partials of about 3.8e6
+    gold = dense.golden_matmul_reduce_scatter(a, b)
+    til = rt.tiling(m, k, n, world)
+    need = rt.symmetric_bytes(rt.MATMUL_REDUCE_SCATTER, rt.BF16, til)
+
+    def run():
+        with rt.emulated_team(world, max(need, 1 << 20)):
+            symm = rt.shmem_malloc(max(need, 1024))
+            c_d = [torch.zeros((m // world, n), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+            rt.launch_emulated(rt.MATMUL_REDUCE_SCATTER, [dev(x) for x in a], [dev(x) for x in b], c_d, symm, til)
+            rc, words = rt.last_status()
+            assert lib().catccos_reset_status() == 0
+            return rc, words, [c.cpu() for c in c_d]
+
+    monkeypatch.delenv("CATCCOS_RS_EXCHANGE", raising=False)
+    rc, words, _ = run()
+    assert rc == 7 and words[0] == 5, (rc, words)
+    assert b"fp16 range" in lib().catccos_last_error()
+    monkeypatch.setenv("CATCCOS_RS_EXCHANGE", "native")
+    rc, words, outs = run()
+    assert rc == 0, words
+    for r in range(world):
+        assert_close_to_golden(outs[r], gold[r], k, TOL, f"native exchange rank {r}")

@@ -19,10 +19,10 @@ def _rs(world, rank, rows_per_rank, n, pairs):
     return np.frombuffer(out, dtype=np.int32, count=3 * cnt).reshape(cnt, 3).copy(), lag.value
 
 
-def _ag(world, rank, m, n):
+def _ag(world, rank, m, n, group=4):
     cap = 1 << 16
     out = (ctypes.c_int32 * (3 * cap))()
-    cnt = lib().catccos_debug_ag_tile_order(world, rank, m, n, out, cap)
+    cnt = lib().catccos_debug_ag_tile_order(world, rank, m, n, group, out, cap)
     assert 0 <= cnt <= cap
     return np.frombuffer(out, dtype=np.int32, count=3 * cnt).reshape(cnt, 3).copy()
 
@@ -81,18 +81,50 @@ def test_reduce_scatter_lag_gives_one_and_a_half_tiles_per_pair_when_the_shape_a
     assert lag1 == 1 and [d for d, _, _ in order] == [0] * 8 + [1] * 8
 
 
-@pytest.mark.parametrize("world,m,n", [(8, 1024, 4096), (4, 2048, 4096), (2, 320, 520), (1, 200, 264), (8, 100, 256)])
-def test_allgather_order_own_rows_first_then_sources_in_ring_order(world, m, n):
+@pytest.mark.parametrize("group", [1, 3, 4, 8, 16])
+@pytest.mark.parametrize("world,m,n", [(8, 1024, 4096), (4, 2048, 4096), (2, 320, 520), (1, 200, 264), (8, 100, 256),
+                                       (1, 8192, 4096)])
+def test_allgather_order_own_rows_first_then_sources_in_ring_order(world, m, n, group):
     nt, mt2 = -(-n // BN), -(-m // (2 * BM))
     for rank in range(world):
-        order = _ag(world, rank, m, n)
+        order = _ag(world, rank, m, n, group)
         assert len(order) == world * mt2 * nt
         assert {tuple(x) for x in order} == {(s, a, b) for s in range(world) for a in range(mt2) for b in range(nt)}
-        sources = [int(s) for s in order[::mt2 * nt, 0]]
-        assert sources == [(rank + j) % world for j in range(world)]
-        # inside a source: 256-row tile major, so a chunk's flags are needed once for a run of nt tiles
-        first = order[:mt2 * nt]
-        assert [tuple(x[1:]) for x in first] == [(a, b) for a in range(mt2) for b in range(nt)]
+        # every own tile comes before any tile that needs a peer's rows
+        assert (order[:mt2 * nt, 0] == rank).all()
+        # gathered sources are first needed in ring order rank+1, rank+2, ... (the order the peers push in)
+        seen = []
+        for s in order[mt2 * nt:, 0]:
+            if int(s) not in seen:
+                seen.append(int(s))
+        assert seen == [(rank + j) % world for j in range(1, world)]
+
+
+@pytest.mark.parametrize("group", [4, 8, 16])
+def test_allgather_order_groups_share_operands(group):
+    """Inside an L2 group the walk is column-tile major: `group` consecutive tiles share one column tile
+    of B, a window of `pairs` consecutive tiles touches about group + pairs/group operand tiles
+    instead of pairs/nt + nt, and a group starts on the column tile the previous one ended on."""
+    world, m, n, pairs = 1, 8192, 4096, 74
+    nt, mt2 = n // BN, m // (2 * BM)
+    order = _ag(world, 0, m, n, group)
+    for g0 in range(0, len(order), group):
+        run = order[g0:g0 + group]
+        assert len({int(x) for x in run[:, 2]}) == 1 and len({int(x) for x in run[:, 1]}) == group
+    worst = max(len({int(x) for x in order[w:w + pairs, 1]}) + len({int(x) for x in order[w:w + pairs, 2]})
+                for w in range(0, len(order) - pairs))
+    assert worst <= group + -(-pairs // group) + 2 + (group if group < mt2 else 0)
+    step = group * nt
+    for g in range(1, mt2 // group):
+        assert order[g * step, 2] == order[g * step - 1, 2]
+
+
+def test_allgather_group_rows_are_about_the_square_root_of_the_pairs():
+    # K = 8192 bf16: a 256-row operand tile is 4 MiB; 74 pairs -> 8 rows of A and 10 columns of B in flight
+    assert lib().catccos_debug_ag_group_rows(4 << 20, 74, 88 << 20) == 8
+    assert lib().catccos_debug_ag_group_rows(4 << 20, 9, 88 << 20) == 3
+    assert lib().catccos_debug_ag_group_rows(64 << 20, 74, 88 << 20) == 8      # nothing fits: smallest footprint
+    assert lib().catccos_debug_ag_group_rows(4 << 20, 1, 88 << 20) == 1
 
 
 @pytest.mark.parametrize("world,m", [(8, 1024), (4, 2048), (2, 4096), (3, 200)])
@@ -118,10 +150,10 @@ def test_order_functions_reject_bad_arguments():
     out = (ctypes.c_int32 * 3)()
     assert lib().catccos_debug_rs_tile_order(0, 0, 128, 256, 4, out, 1, None) < 0
     assert lib().catccos_debug_rs_tile_order(2, 2, 128, 256, 4, out, 1, None) < 0
-    assert lib().catccos_debug_ag_tile_order(9, 0, 128, 256, out, 1) < 0
+    assert lib().catccos_debug_ag_tile_order(9, 0, 128, 256, 4, out, 1) < 0
     assert lib().catccos_debug_ag_push_order(2, 0, 0, out, 1) < 0
     # a short buffer is filled up to its capacity and the full count is still reported
-    assert lib().catccos_debug_ag_tile_order(2, 0, 256, 512, out, 1) == 4
+    assert lib().catccos_debug_ag_tile_order(2, 0, 256, 512, 4, out, 1) == 4
 
 
 def _slots(sigs, foreign=None):
