@@ -16,6 +16,7 @@
 #include "gemm_fused.cuh"
 #include "ptx.cuh"
 #include "sched.h"
+#include "tile_queue.cuh"
 
 namespace cb {
 
@@ -24,10 +25,6 @@ constexpr int kPAStage = BM * BK * 2;          // 128 rows of A      : 16 KiB
 constexpr int kPBStage = 128 * BK * 2;         // 128 columns of B   : 16 KiB
 constexpr int kPairSmemBytes = kPStages * (kPAStage + kPBStage) + kSideSmemBytes + 1024 + 512;
 constexpr int BM2 = 2 * BM;                    // rows of a pair's tile
-
-constexpr int kTileRing = 8;                   // claimed tiles travel to the roles through a ring of this many slots
-constexpr uint32_t kTileAhead = 3;             // tiles claimed beyond the last one the epilogues have finished
-constexpr uint32_t kTileEnd = 0xFFFFFFFFu;     // ring entry: no tiles left
 
 struct PairSmem {
     uint64_t full[kPStages];        // used in the leader: both CTAs' loads of a stage have landed
@@ -39,10 +36,7 @@ struct PairSmem {
     uint32_t tmem_base;
     int abort_flag;
     uint32_t tiles_ready;           // tiles of this CTA (in claim order) whose gathered rows are known to be in
-    uint32_t ring[kTileRing];       // tile index of claim number seq at [seq % kTileRing] (written by the leader's warp 10)
-    uint32_t claimed;               // number of valid ring entries so far
-    uint32_t done_self;             // tiles this CTA's epilogue has finished
-    uint32_t done_peer;             // leader only: the same count of the other CTA
+    TileQueue tq;                   // claimed tiles (written by the leader's warp 10)
 };
 
 template <typename T, bool B_MN>
@@ -86,9 +80,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
         for (int l = 0; l < kPushLanesShared; ++l) mbar_init(&sh->push_bar[l], 1);
         sh->abort_flag = 0;
         sh->tiles_ready = 0;
-        sh->claimed = 0;
-        sh->done_self = 0;
-        sh->done_peer = 0;
+        tq_init(&sh->tq);
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
@@ -117,11 +109,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
         gathered = (s != rank);
     };
     // claim number seq -> tile index, once the leader's warp 10 has published it (kTileEnd: no more tiles)
-    auto claimed_tile = [&](uint32_t seq, uint32_t &t) -> bool {
-        if (!wait_cluster_counter_gt(&sh->claimed, seq, ctl, W_TILE_QUEUE)) return false;
-        t = sh->ring[seq % kTileRing];
-        return true;
-    };
+    auto claimed_tile = [&](uint32_t seq, uint32_t &t) -> bool { return tq_get(&sh->tq, seq, t, ctl); };
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer ----
@@ -267,10 +255,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty[acc]), 0));
             ++tcount;
             // progress of this CTA's epilogue, which paces the claiming of further tiles
-            if (warp == 2 && lane == 0) {
-                if (cr == 0) st_release_cta_smem(&sh->done_self, tcount);
-                else st_release_cluster_smem(mapa_cluster(smem_u32(&sh->done_peer), 0), tcount);
-            }
+            if (warp == 2 && lane == 0) tq_done(&sh->tq, cr, tcount);
         }
     } else if (warp == 10) {
         // ------------------------------------------------- tile queue and flag scout ----
@@ -283,20 +268,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
         for (uint32_t seq = 0; ok; ++seq) {
             uint32_t tq = 0;
             if (cr == 0) {
-                if (lane == 0) {
-                    if (seq >= kTileAhead) {
-                        ok = wait_smem_counter_gt(&sh->done_self, seq - kTileAhead, ctl, W_TILE_QUEUE) &&
-                             wait_cluster_counter_gt(&sh->done_peer, seq - kTileAhead, ctl, W_TILE_QUEUE);
-                    }
-                    if (ok) {
-                        const int t = seq == 0 ? pair : pairs + atomicAdd(next_tile, 1);
-                        tq = t < num_tiles ? static_cast<uint32_t>(t) : kTileEnd;
-                        sh->ring[seq % kTileRing] = tq;
-                        st_cluster_smem(mapa_cluster(smem_u32(&sh->ring[seq % kTileRing]), 1), tq);
-                        st_release_cta_smem(&sh->claimed, seq + 1);
-                        st_release_cluster_smem(mapa_cluster(smem_u32(&sh->claimed), 1), seq + 1);
-                    }
-                }
+                if (lane == 0) ok = tq_claim(&sh->tq, seq, pair, pairs, num_tiles, next_tile, ctl, tq);
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 tq = __shfl_sync(0xffffffffu, tq, 0);
                 if (!ok) break;
@@ -322,20 +294,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
         }
         // the last pair of the rank to run out of tiles leaves the counters at zero for the next launch
         if (cr == 0 && lane == 0) {
-            if (!ok) {
-                // this pair gave up: the other roles must not wait for tiles that will not come
-                const uint32_t seq_end = sh->claimed;
-                sh->ring[seq_end % kTileRing] = kTileEnd;
-                st_cluster_smem(mapa_cluster(smem_u32(&sh->ring[seq_end % kTileRing]), 1), kTileEnd);
-                st_release_cta_smem(&sh->claimed, seq_end + 1);
-                st_release_cluster_smem(mapa_cluster(smem_u32(&sh->claimed), 1), seq_end + 1);
-            }
-            __threadfence();
-            if (atomicAdd(next_tile + 1, 1) == pairs - 1) {
-                next_tile[0] = 0;
-                next_tile[1] = 0;
-                __threadfence();
-            }
+            if (!ok) tq_publish_end(&sh->tq);      // this pair gave up: nobody waits for claims that will not come
+            tq_retire(next_tile, pairs);
         }
     } else {
         // ------------------------------------------------------ all-gather push ----

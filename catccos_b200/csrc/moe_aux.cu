@@ -49,7 +49,10 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
 
     if (tid == 0) abort_flag = 0;
     for (int i = tid; i < 32 * E; i += blockDim.x) cnt[i] = 0;
-    if (tid < 4) meta->done_counter[tid] = 0;
+    if (tid < 4) {
+        meta->done_counter[tid] = 0;
+        meta->tile_queue[tid >> 1][tid & 1] = 0;
+    }
     if (tid == 0) meta->overflow = 0;
     // this rank's symmetric data regions may be overwritten from now on
     if (tid < R && tid != rank) {

@@ -32,6 +32,7 @@ struct MoeMeta {
     int tile_prefix[kMoeMaxLocalExperts + 1];       // exclusive prefix of row tiles (128 rows) over local experts
     int total_rows;                                 // rows received (unpadded)
     unsigned int done_counter[4];                   // last-CTA-out counters of the pipeline's kernels
+    int tile_queue[2][2];                           // next-tile counters of the two pair GEMMs (zeroed by the routing kernel)
     int overflow;                                   // receive buffer too small for the routing
 };
 

@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "moe_gemm.cuh"
+#include "moe_pair.cuh"
 #include "mx_quant.h"
 
 namespace cb {
@@ -73,6 +74,37 @@ static int encode_u8(const DriverApi *api, CUtensorMap *tm, const void *base, ui
                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled (MoE) failed: %d", static_cast<int>(r));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+// scale atoms as a 2-D tensor: rows of 128 u32 (= one 512-byte atom), one atom per load
+static int encode_atoms(const DriverApi *api, CUtensorMap *tm, const void *base, uint64_t n_atoms) {
+    cuuint64_t dims[2] = {128, n_atoms};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, 1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = api->TensorMapEncodeTiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides,
+                                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (MoE scale atoms) failed: %d", static_cast<int>(r));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+template <int MODE>
+static int launch_pair_gemm(const MoePairParams &p, cudaStream_t stream) {
+    auto kern = moe_pair_gemm_kernel<MODE>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMoePairSmemBytes);
+    if (e == cudaSuccess) {
+        kern<<<p.ctas_per_rank * p.n_local, kGemmThreads, kMoePairSmemBytes, stream>>>(p);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        set_error("MoE pair grouped GEMM launch failed: %s", cudaGetErrorString(e));
         return CATCCOS_ERR_CUDA;
     }
     return CATCCOS_OK;
@@ -177,6 +209,30 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
     g2.Nw = k;
     g2.counter_slot = 2;
 
+    // the grouped GEMMs run on CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
+    bool use_pair = per_rank >= 2;
+    if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = use_pair && atoi(e) != 0;
+    static thread_local MoePairParams q1, q2;
+    memset(&q1, 0, sizeof(q1));
+    for (int pe = 0; pe < R; ++pe) q1.heap_base[pe] = t->base[pe];
+    q1.combine_off = p.lay.combine_off;
+    q1.world = R;
+    q1.rank_base = p.rank_base;
+    q1.n_local = n_local;
+    q1.ctas_per_rank = per_rank & ~1;
+    q1.experts = experts;
+    q1.experts_per_rank = el;
+    q1.epoch = p.epoch;
+    q1.timeout_ns = p.timeout_ns;
+    q1.status = p.status;
+    q2 = q1;
+    q1.Kin = k;
+    q1.Nw = n;
+    q1.counter_slot = 1;
+    q2.Kin = n / 2;
+    q2.Nw = k;
+    q2.counter_slot = 2;
+
     struct Ws { uint8_t *recv_atoms, *w1_atoms, *w2_atoms, *act_codes, *act_atoms; } ws[kMaxRanks];
     for (int l = 0; l < n_local; ++l) {
         const MoeArgs &a = args[l];
@@ -225,6 +281,24 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
         r2.act_codes = nullptr;
         r2.act_sf = nullptr;
         r2.meta = ra.meta;
+        if (use_pair) {
+            MoePairRankArgs &p1 = q1.ranks[l];
+            p1.tmA = r1.tmA;
+            p1.tmB = r1.tmB;
+            if ((rc = encode_atoms(api, &p1.tmSfa, ws[l].recv_atoms, sf_atoms_bytes(z.rows_cap, k) / 512))) return rc;
+            if ((rc = encode_atoms(api, &p1.tmSfb, ws[l].w1_atoms, sf_atoms_bytes(el * n, k) / 512))) return rc;
+            p1.act_codes = ws[l].act_codes;
+            p1.act_sf = ws[l].act_atoms;
+            p1.meta = ra.meta;
+            MoePairRankArgs &p2 = q2.ranks[l];
+            p2.tmA = r2.tmA;
+            p2.tmB = r2.tmB;
+            if ((rc = encode_atoms(api, &p2.tmSfa, ws[l].act_atoms, sf_atoms_bytes(z.rows_cap, n / 2) / 512))) return rc;
+            if ((rc = encode_atoms(api, &p2.tmSfb, ws[l].w2_atoms, sf_atoms_bytes(el * k, n / 2) / 512))) return rc;
+            p2.act_codes = nullptr;
+            p2.act_sf = nullptr;
+            p2.meta = ra.meta;
+        }
     }
 
     int rc;
@@ -243,8 +317,13 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
                                      ws[l].recv_atoms)))
             return rc;
     }
-    if ((rc = launch_gemm<1>(g1, stream))) return rc;
-    if ((rc = launch_gemm<2>(g2, stream))) return rc;
+    if (use_pair) {
+        if ((rc = launch_pair_gemm<1>(q1, stream))) return rc;
+        if ((rc = launch_pair_gemm<2>(q2, stream))) return rc;
+    } else {
+        if ((rc = launch_gemm<1>(g1, stream))) return rc;
+        if ((rc = launch_gemm<2>(g2, stream))) return rc;
+    }
     return moe_launch_unpermute(p, stream);
 }
 

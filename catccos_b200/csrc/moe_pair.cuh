@@ -1,0 +1,415 @@
+// Grouped (ragged-M) block-scaled MXFP8 GEMM for the MoE expert FFN on CTA pairs (tcgen05 cta_group::2).
+//
+// A pair computes a 256-row x 256-column tile of ONE local expert: CTA c of the pair takes the
+// expert's 128-row tile 2 * j + c (an expert's rows start on a multiple of 128 in the receive
+// buffer; the second half of an expert's last pair tile may be empty and is then masked), its half
+// of the expert's weight tile, and both weight scale atoms.  Per K-step an SM pulls 33.5 KiB from
+// L2 instead of the 49.5 KiB of the one-CTA kernel (moe_gemm.cuh), which was bound by exactly that
+// feed, and there is room for six pipeline stages.  Tiles are handed out dynamically (tile_queue.cuh)
+// in expert order, so an expert with many rows is shared by all pairs and the pairs that finish
+// early take what is left.
+//   MODE 1 (up projection): the pair's B tile is 128 "act" rows (CTA 0) + 128 "gate" rows (CTA 1) of
+//     the expert's [N, K] weight; every CTA's accumulator holds act | gate for its 128 rows, and the
+//     epilogue applies y = bf16(act * sigmoid(act) * gate) and MX-quantises y (moe_gemm.cuh, MODE 1).
+//   MODE 2 (down projection): plain 256-wide tile; rows go back to their source rank's combine buffer.
+// Reference: include/catccos/dgemm/kernel/ascend950_alltoall_gmm.hpp:57-506,
+// include/catccos/dgemm/kernel/ascend950_gmm_alltoall.hpp:104-486; golden examples/utils/gen_data_moe.py:546-588.
+#pragma once
+#include <cuda_fp8.h>
+
+#include "moe_common.h"
+#include "moe_gemm.cuh"
+#include "mx_pair.cuh"
+#include "tile_queue.cuh"
+
+namespace cb {
+
+constexpr int kMoePStages = 6;
+constexpr int kMoePSf = 1536;                                            // A atom + two B atoms
+constexpr int kMoePStageBytes = kMxPA + kMxPB + kMoePSf;                 // 33.5 KiB
+constexpr int kMoePairSmemBytes = kMoePStages * kMoePStageBytes + kMoeSideBytes + 1024 + 1024;
+static_assert(kMoePairSmemBytes <= 232448, "shared memory budget");
+
+struct alignas(64) MoePairRankArgs {
+    CUtensorMap tmA;          // activations [rows_cap, Kin] bytes, box {128, 128}
+    CUtensorMap tmB;          // weights [E_local * Nw, Kin] bytes, box {128, 128}
+    CUtensorMap tmSfa;        // activation scale atoms as rows of 128 u32, box {128, 1}
+    CUtensorMap tmSfb;        // weight scale atoms, the same
+    uint8_t *act_codes;       // MODE 1 out: [rows_cap, Nw/2]
+    uint8_t *act_sf;          // MODE 1 out: atoms [rows_cap/128][(Nw/2)/128][512]
+    MoeMeta *meta;
+};
+
+struct MoePairParams {
+    MoePairRankArgs ranks[kMaxRanks];
+    uint8_t *heap_base[kMaxRanks];
+    uint64_t combine_off;      // MODE 2: bf16 [m*topK, Nw] combine buffer inside every heap
+    int world, rank_base, n_local, ctas_per_rank;      // ctas_per_rank is even
+    int Kin, Nw;
+    int experts, experts_per_rank;
+    int counter_slot;          // MoeMeta::done_counter / tile_queue slot of this launch
+    uint32_t epoch;
+    uint64_t timeout_ns;
+    int *status;
+};
+
+struct MoePairSmem {
+    uint64_t full[kMoePStages];     // in the leader: both CTAs' loads landed
+    uint64_t empty[kMoePStages];    // per CTA
+    uint64_t tmem_full;             // per CTA
+    uint64_t tmem_empty;            // in the leader: 8 epilogue warps of the pair
+    uint64_t drain;
+    uint32_t tmem_base;
+    int abort_flag;
+    TileQueue tq;
+    int pprefix[kMoeMaxLocalExperts + 1];    // exclusive prefix of pair tiles (256 rows) over the local experts
+};
+
+struct MoePairTile {
+    int le;          // local expert
+    int ni;          // column tile
+    int row0;        // first receive row of THIS CTA's 128 rows
+    int rows;        // valid rows of this CTA's half (0..128)
+    int mi;          // this CTA's 128-row tile inside the expert
+};
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    moe_pair_gemm_kernel(const __grid_constant__ MoePairParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem_a + kMoePStages * kMxPA;
+    uint8_t *smem_sf = smem_b + kMoePStages * kMxPB;
+    uint8_t *smem_side = smem_sf + kMoePStages * kMoePSf;
+    MoePairSmem *sh = reinterpret_cast<MoePairSmem *>(smem_side + kMoeSideBytes);
+    static_assert(sizeof(MoePairSmem) <= 1024, "barrier block outgrew its budget");
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int lrank = blockIdx.x / p.ctas_per_rank;
+    const int cta = blockIdx.x - lrank * p.ctas_per_rank;
+    const int pair = cta >> 1, pairs = p.ctas_per_rank >> 1;
+    const uint32_t cr = cluster_ctarank();
+    const int rank = p.rank_base + lrank;
+    const int R = p.world;
+    const int EL = p.experts_per_rank;
+    const MoePairRankArgs &ra = p.ranks[lrank];
+    MoeMeta *meta = ra.meta;
+    const int n_tiles = (MODE == 1) ? (p.Nw / 2) / 128 : p.Nw / BN;
+    const int kblocks = (p.Kin + MX_BK - 1) / MX_BK;
+    const bool skip_all = meta->overflow != 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMoePStages; ++s) {
+            mbar_init(&sh->full[s], 2);
+            mbar_init(&sh->empty[s], 1);
+        }
+        mbar_init(&sh->tmem_full, 1);
+        mbar_init(&sh->tmem_empty, 8);
+        mbar_init(&sh->drain, 1);
+        sh->abort_flag = 0;
+        tq_init(&sh->tq);
+        int run = 0;
+        for (int le = 0; le < EL; ++le) {
+            sh->pprefix[le] = run;
+            run += (meta->tile_prefix[le + 1] - meta->tile_prefix[le] + 1) / 2;
+        }
+        sh->pprefix[EL] = skip_all ? 0 : run;
+        mbar_init_fence();
+        prefetch_tensormap(&ra.tmA);
+        prefetch_tensormap(&ra.tmB);
+        prefetch_tensormap(&ra.tmSfa);
+        prefetch_tensormap(&ra.tmSfb);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(&sh->tmem_base, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+    const uint32_t tmem_sf0 = tmem_base + BN;      // four sets of 4 (A) + 8 (B) scale columns, used in turn
+    const int num_tiles = sh->pprefix[EL] * n_tiles;
+
+    WaitCtl ctl;
+    ctl.abort_smem = &sh->abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+
+    // linear pair-tile id -> this CTA's part of the tile; ids grow inside a pair, so `le_hint` only moves forward
+    auto decode = [&](int t, int &le_hint) {
+        MoePairTile tl;
+        const int g = t / n_tiles;
+        tl.ni = t - g * n_tiles;
+        while (le_hint + 1 < EL && g >= sh->pprefix[le_hint + 1]) ++le_hint;
+        tl.le = le_hint;
+        tl.mi = (g - sh->pprefix[le_hint]) * 2 + static_cast<int>(cr);
+        tl.row0 = meta->seg_base[le_hint] + tl.mi * BM;
+        tl.rows = max(0, min(BM, meta->seg_rows[le_hint] - tl.mi * BM));
+        return tl;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer ----
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            int le_hint = 0;
+            for (uint32_t seq = 0; ok; ++seq) {
+                uint32_t tq;
+                if (!(ok = tq_get(&sh->tq, seq, tq, ctl)) || tq == kTileEnd) break;
+                const MoePairTile tl = decode(static_cast<int>(tq), le_hint);
+                // this CTA's half of the pair's 256 weight rows, and the weight rows of both halves (scale atoms)
+                int b_row0, b_row1;
+                if (MODE == 1) {
+                    b_row0 = tl.le * p.Nw + tl.ni * 128;          // act rows
+                    b_row1 = b_row0 + p.Nw / 2;                    // gate rows
+                } else {
+                    b_row0 = tl.le * p.Nw + tl.ni * BN;
+                    b_row1 = b_row0 + 128;
+                }
+                const int b_mine = cr == 0 ? b_row0 : b_row1;
+                const int sfa_atom0 = (tl.row0 >> 7) * kblocks;
+                const int sfb_atom0 = (b_row0 >> 7) * kblocks, sfb_atom1 = (b_row1 >> 7) * kblocks;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int st = it % kMoePStages;
+                    const uint32_t ph = (it / kMoePStages) & 1;
+                    if (!(ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY))) break;
+                    const uint32_t full_leader = mapa_cluster(smem_u32(&sh->full[st]), 0);
+                    uint8_t *ssf = smem_sf + st * kMoePSf;
+                    mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB + kMoePSf);
+                    tma_load_2d_pair(smem_a + st * kMxPA, &ra.tmA, full_leader, kb * MX_BK, tl.row0);
+                    tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, kb * MX_BK, b_mine);
+                    tma_load_2d_pair(ssf, &ra.tmSfa, full_leader, 0, sfa_atom0 + kb);
+                    tma_load_2d_pair(ssf + 512, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb);
+                    tma_load_2d_pair(ssf + 1024, &ra.tmSfb, full_leader, 0, sfb_atom1 + kb);
+                }
+            }
+            if (!ok) {
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 20000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------- MMA issuer (leader CTA only) ----
+        if (lane == 0 && cr == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (;;) {
+                uint32_t tq;
+                if (!(ok = tq_get(&sh->tq, tcount, tq, ctl)) || tq == kTileEnd) break;
+                if (!(ok = mbar_wait(&sh->tmem_empty, (tcount & 1) ^ 1, ctl, W_TMEM_EMPTY))) break;
+                tc_fence_after();
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int st = it % kMoePStages;
+                    if (!(ok = mbar_wait(&sh->full[st], (it / kMoePStages) & 1, ctl, W_MBAR_FULL))) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem_a + st * kMxPA);
+                    const uint32_t b_addr = smem_u32(smem_b + st * kMxPB);
+                    const uint32_t sf_addr = smem_u32(smem_sf + st * kMoePSf);
+                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * 16u;
+                    const uint32_t tmem_sfb = tmem_sfa + 4;
+                    tmem_cp_32x128b_warpx4_pair(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
+                    tmem_cp_32x128b_warpx4_pair(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
+                    tmem_cp_32x128b_warpx4_pair(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));
+#pragma unroll
+                    for (int k = 0; k < MX_BK / 32; ++k) {
+                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                        const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024);
+                        umma_mxf8_pair(tmem_base, ad, bd, make_idesc_mxf8(2 * BM, BN, k, k), tmem_sfa, tmem_sfb, (kb | k) != 0);
+                    }
+                    umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 0));
+                    umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 1));
+                }
+                if (!ok) break;
+                umma_commit_pair(mapa_cluster(smem_u32(&sh->tmem_full), 0));
+                umma_commit_pair(mapa_cluster(smem_u32(&sh->tmem_full), 1));
+                ++tcount;
+            }
+            if (!ok) {
+                umma_commit_pair(mapa_cluster(smem_u32(&sh->drain), 0));
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(&sh->drain, 0)) {
+                    if (globaltimer_ns() - t0 > 2000000ull) break;
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- epilogue ----
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        uint32_t tcount = 0;
+        bool ok = true;
+        int le_hint = 0;
+        for (;;) {
+            uint32_t tq;
+            if (!(ok = tq_get(&sh->tq, tcount, tq, ctl)) || tq == kTileEnd) break;
+            const MoePairTile tl = decode(static_cast<int>(tq), le_hint);
+            if (!(ok = mbar_wait(&sh->tmem_full, tcount & 1, ctl, W_TMEM_FULL))) break;
+            tc_fence_after();
+            const bool row_ok = row_in_tile < tl.rows;
+            const int row = tl.row0 + row_in_tile;
+            if (MODE == 1) {
+                // act half -> bf16-rounded values kept packed; gate half chunk by chunk
+                uint32_t act[64];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        act[c * 16 + i] =
+                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                }
+                uint32_t scale_word = 0;
+                const int half_n = p.Nw / 2;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + 128 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                    tmem_ld_wait();
+                    if (c == 3) {
+                        // accumulator fully read: the MMA thread may start the next tile
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
+                    }
+                    float y[32];
+                    uint32_t am = 0;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 a2 = Pack2<__nv_bfloat16>::unpack(act[c * 16 + i]);
+                        const float2 g2 = Pack2<__nv_bfloat16>::unpack(
+                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])));
+                        const float y0 = a2.x * (1.0f / (1.0f + expf(-a2.x))) * g2.x;
+                        const float y1 = a2.y * (1.0f / (1.0f + expf(-a2.y))) * g2.y;
+                        const uint32_t pk = Pack2<__nv_bfloat16>::pack(y0, y1);      // y rounded to bf16
+                        am = max(am, max(pk & 0x7FFFu, (pk >> 16) & 0x7FFFu));
+                        const float2 yr = Pack2<__nv_bfloat16>::unpack(pk);
+                        y[2 * i] = yr.x;
+                        y[2 * i + 1] = yr.y;
+                    }
+                    const float amax = __uint_as_float(am << 16);
+                    uint32_t sb = 127u;
+                    float inv = 1.0f;
+                    if (!(amax < 1e-12f)) {
+                        const uint32_t e8 = (am >> 7) & 0xFFu;
+                        sb = e8 - 8u;
+                        inv = __uint_as_float((262u - e8) << 23);
+                    }
+                    scale_word |= sb << (8 * c);
+                    uint32_t code[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        uint32_t w = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) {
+                            const float x = y[i * 4 + b] * inv;
+                            const uint32_t cb8 = (x != x) ? (0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u))
+                                                          : static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+                            w |= cb8 << (8 * b);
+                        }
+                        code[i] = w;
+                    }
+                    if (row_ok) {
+                        uint8_t *dst = ra.act_codes + static_cast<size_t>(row) * half_n + tl.ni * 128 + c * 32;
+                        *reinterpret_cast<uint4 *>(dst) = make_uint4(code[0], code[1], code[2], code[3]);
+                        *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(code[4], code[5], code[6], code[7]);
+                    }
+                }
+                // the tile's 128 output columns are 4 k-blocks of the down projection = one atom column group;
+                // rows past the expert's count get the neutral scale so that stale bytes never reach the MMA.
+                // An empty half beyond the expert's last 128-row tile belongs to the next expert: left alone.
+                if (tl.rows > 0) {
+                    const int kb4_2 = (half_n + 127) / 128;
+                    uint8_t *sfdst = ra.act_sf + (static_cast<size_t>(row >> 7) * kb4_2 + tl.ni) * 512 + (row & 31) * 16 +
+                                     ((row >> 5) & 3) * 4;
+                    *reinterpret_cast<uint32_t *>(sfdst) = row_ok ? scale_word : 0x7F7F7F7Fu;
+                }
+            } else {
+                uint32_t pk[BN / 2];
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        pk[c * 16 + i] =
+                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
+                // which rank does this row go back to, and where in its expert-sorted order
+                __nv_bfloat16 *dst = nullptr;
+                if (row_ok) {
+                    const int w = tl.mi * BM + row_in_tile;
+                    int src = 0;
+                    while (src + 1 < R && w >= meta->cum_src[src + 1][tl.le]) ++src;
+                    const int e = rank * EL + tl.le;
+                    const int drow = meta->prefix_all[src][e] + (w - meta->cum_src[src][tl.le]);
+                    dst = reinterpret_cast<__nv_bfloat16 *>(p.heap_base[src] + p.combine_off) +
+                          static_cast<size_t>(drow) * p.Nw + tl.ni * BN;
+                }
+                uint8_t *my_row = smem_side + row_in_tile * 128;
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    bulk_wait_read<0>();
+#pragma unroll
+                    for (int g = 0; g < 8; ++g)
+                        *reinterpret_cast<uint4 *>(my_row + g * 16) = make_uint4(
+                            pk[h * 32 + g * 4], pk[h * 32 + g * 4 + 1], pk[h * 32 + g * 4 + 2], pk[h * 32 + g * 4 + 3]);
+                    fence_proxy_async_smem();
+                    if (row_ok) {
+                        bulk_store(dst + h * 64, my_row, 128);
+                        bulk_commit();
+                    }
+                }
+            }
+            ++tcount;
+            if (warp == 2 && lane == 0) tq_done(&sh->tq, cr, tcount);
+        }
+        if (MODE == 2) {
+            bulk_wait<0>();
+            fence_proxy_async_global();
+        }
+    } else if (warp == 6) {
+        // -------------------------------------------------------------- tile queue ----
+        if (cr == 0 && lane == 0) {
+            int *const counters = meta->tile_queue[p.counter_slot & 1];
+            bool ok = true;
+            for (uint32_t seq = 0; ok; ++seq) {
+                uint32_t tq;
+                if (!(ok = tq_claim(&sh->tq, seq, pair, pairs, num_tiles, counters, ctl, tq)) || tq == kTileEnd) break;
+            }
+            if (!ok) tq_publish_end(&sh->tq);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+    // MODE 2: the last CTA of this rank tells every rank that its combine rows are in place
+    if (MODE == 2 && threadIdx.x == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(&ra.meta->done_counter[p.counter_slot], 1u);
+        if (prev == static_cast<unsigned>(p.ctas_per_rank) - 1u) {
+            fence_sys();
+            for (int r = 0; r < R; ++r)
+                st_release_sys(reinterpret_cast<uint32_t *>(p.heap_base[r]) + kMoeFlagCombine + rank, p.epoch);
+        }
+    }
+}
+
+}  // namespace cb

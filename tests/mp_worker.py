@@ -85,6 +85,54 @@ def main():
         assert rc == 0, words
     check("mx_agmm", c, gold, 2e-2)
 
+    # MXFP8 Matmul-ReduceScatter (e5m2 operands as the reference's example feeds; partial tiles over NVLink)
+    mr_rows, k, n = 128, 256, 512
+    m = mr_rows * world
+    a_c, a_s, b_c, b_s = [], [], [], []
+    for r in range(world):
+        g = torch.Generator().manual_seed(700 + r)
+        act = torch.randn((m, k), generator=g).numpy()
+        w = (torch.randn((k, n), generator=g) * 0.02).numpy()
+        c_, s_, _ = mxquant.quantize_mx_e5m2(act); a_c.append(c_); a_s.append(s_)
+        ct, st, _ = mxquant.quantize_mx_e5m2(np.ascontiguousarray(w.T))
+        b_c.append(np.ascontiguousarray(ct.T)); b_s.append(np.ascontiguousarray(st.T))
+    gold = dense.golden_mx_matmul_reduce_scatter(a_c, a_s, b_c, b_s, "e5m2")[rank]
+    til = rt.tiling(m, k, n, world)
+    ws_bytes = lib().catccos_workspace_bytes(rt.MXFP8_MATMUL_REDUCE_SCATTER, rt.BF16, ctypes.byref(til))
+    wsp = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    bsr = b_s[rank]
+    bs_dev = np.ascontiguousarray(bsr.reshape(bsr.shape[0] // 2, 2, n).transpose(0, 2, 1))      # [k/64, n, 2]
+    d = torch.full((mr_rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for rep in range(2):
+        rt.launch(rt.MXFP8_MATMUL_REDUCE_SCATTER, torch.from_numpy(a_c[rank]).cuda(), torch.from_numpy(b_c[rank]).cuda(), d,
+                  symm, til, dtype=rt.BF16, custom=[torch.from_numpy(a_s[rank]).cuda(), torch.from_numpy(bs_dev).cuda()],
+                  workspace=wsp)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    check("mx_mmrs", d, gold, 2e-2)
+
+    # MxQuantAllGather: every rank ends with all ranks' codes and scales, byte for byte
+    m, n = 200, 1024
+    xs_q = [(torch.randn((m, n), generator=torch.Generator().manual_seed(900 + r)) * (0.5 + r)).to(torch.bfloat16)
+            for r in range(world)]
+    gc, gs = [], []
+    for x_ in xs_q:
+        c_, s_, _ = mxquant.quantize_mx_e4m3(x_.to(torch.float32).numpy(), "rne")
+        gc.append(c_); gs.append(s_)
+    gc, gs = np.concatenate(gc), np.concatenate(gs)
+    til = rt.tiling(m, 1, n, world)
+    assert rt.symmetric_bytes(rt.MX_QUANT_ALLGATHER, rt.FP8E4M3FN, til) <= (200 << 20)
+    s_d = torch.zeros((world * m, gs.shape[1]), dtype=torch.uint8, device="cuda")
+    c_d = torch.zeros((world * m, n), dtype=torch.uint8, device="cuda")
+    for rep in range(2):
+        rt.launch(rt.MX_QUANT_ALLGATHER, xs_q[rank].cuda(), s_d, c_d, symm, til, dtype=rt.FP8E4M3FN)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    same = bool(np.array_equal(c_d.cpu().numpy(), gc) and np.array_equal(s_d.cpu().numpy(), gs))
+    print(f"[rank {rank}] mx_quant_allgather: bit-exact {same}", flush=True)
+    if not same:
+        failures.append(("mx_quant_allgather", 1.0))
+
     # MoE dispatch -> FFN -> combine
     m, k, n, top_k, experts = 160, 512, 1024, 4, 4 * world
     epr = experts // world
