@@ -31,6 +31,7 @@ RS_M, RS_KLOCAL, RS_N = 8192, 2048, 8192           # matmul_reduce_scatter bf16 
 AR_M, AR_K, AR_N = 512, 1024, 2048                 # matmul_allreduce fp16 (configuration 1)
 MX_M_TOTAL, MX_K, MX_N = 16384, 7168, 4096         # MXFP8 allgather_matmul (configuration 4)
 MOE_M, MOE_K, MOE_N, MOE_TOPK = 4096, 7168, 4096, 8  # MoE (configuration 5), 32 experts per rank
+SPEC_BF16_TFLOPS, SPEC_NVLINK_GBS = 2250.0, 900.0  # datasheet: dense bf16 tensor peak, NVLink 5 per direction
 NVLINK_GBS = 770.0                                 # measured peer-copy bandwidth per direction (900 nominal)
 
 
@@ -132,6 +133,11 @@ def workload(op, world):
                     dtype="mxfp8", peak_scale=2.0, c_shape=(MOE_M, MOE_K),
                     desc=f"MoE dispatch->GMM->SwiGLU->GMM->combine: 4096 tokens/rank, hidden 7168, {experts} experts "
                          f"(32/rank), FFN 2048, top-8 Zipf(1.1) routing, MXFP8 weights")
+    if op == "fp4":
+        return dict(name="nvfp4_gemm", m=M_TOTAL, k=K_DIM, n=N_DIM, c_shape=(M_TOTAL, N_DIM), flops=2.0 * M_TOTAL * K_DIM * N_DIM,
+                    comm_bytes=0, dtype="nvfp4", peak_scale=4.0,
+                    desc="NVFP4 GEMM (one rank; the contraction under the FP4 operators): A[8192,8192] x B[4096,8192]^T, e2m1 "
+                         "codes with one UE4M3 scale per 16 along K (seeded random codes and scales), bf16 output [8192,4096]")
     if op == "quant":
         return dict(name="mx_quant_e4m3", m=MX_M_TOTAL, k=MX_K, n=0, c_shape=(MX_M_TOTAL, MX_K), flops=0.0, comm_bytes=0,
                     dtype="u8", hbm_bytes=MX_M_TOTAL * MX_K * (2 + 1 + 1.0 / 32),
@@ -177,7 +183,7 @@ def bind_to_gpu_numa_node(local_rank, torch):
     return None
 
 
-TOL = {"bf16": 1e-2, "fp16": 1e-2, "mxfp8": 2e-2}
+TOL = {"bf16": 1e-2, "fp16": 1e-2, "mxfp8": 2e-2, "nvfp4": 5e-2}
 
 
 def _sample_rows(n_rows, count, seed, torch):
@@ -360,7 +366,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar", "mxag", "moe", "quant"])
+    ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar", "mxag", "moe", "quant", "fp4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -436,6 +442,24 @@ def main():
                 check(lib().catccos_mx_quant(sptr, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(q_codes.data_ptr()),
                                              ctypes.c_void_p(q_scales.data_ptr()), None, wl["m"], wl["k"]))
             launches_per_step = 1
+        elif args.op == "fp4":
+            rt.shmem_init(rank, world, 1 << 20, f"tcp://{addr}:{port}")
+            m, k, n = wl["m"], wl["k"], wl["n"]
+            # any byte is a pair of e2m1 codes; scales: UE4M3 bytes 0x28..0x47 (2^-2 .. 1.875 x 2^1)
+            fa = torch.randint(0, 256, (m, k // 2), generator=gen, device="cuda", dtype=torch.uint8)
+            fb = torch.randint(0, 256, (n, k // 2), generator=gen, device="cuda", dtype=torch.uint8)
+            fsa = torch.randint(0x28, 0x48, (m, k // 16), generator=gen, device="cuda", dtype=torch.uint8)
+            fsb = torch.randint(0x28, 0x48, (n, k // 16), generator=gen, device="cuda", dtype=torch.uint8)
+            f_alpha = 2.0 ** -6
+            c_d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            wsp = torch.zeros(lib().catccos_fp4_gemm_workspace_bytes(1, m, n, k), dtype=torch.uint8, device="cuda")
+
+            def step():
+                check(lib().catccos_fp4_gemm(sptr, 1, rt.BF16, ctypes.c_void_p(fa.data_ptr()), ctypes.c_void_p(fb.data_ptr()),
+                                             ctypes.c_void_p(c_d.data_ptr()), ctypes.c_void_p(fsa.data_ptr()),
+                                             ctypes.c_void_p(fsb.data_ptr()), ctypes.c_float(f_alpha), m, n, k,
+                                             ctypes.c_void_p(wsp.data_ptr()), 0))
+            launches_per_step = 3
         elif args.op == "mxag":
             comm = rt.FP8_MX_ALLGATHER_MATMUL
             til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
@@ -617,6 +641,13 @@ def main():
             err, rows, bit_exact = parity_mxag(wl, rank, world, act, a_codes, a_scale, wq_t, ws_t, c_d, torch, dist)
         elif args.op == "moe":
             err, rows = parity_moe(wl, rank, world, x, idx, probs, expert_weights, c_d, torch)
+        elif args.op == "fp4":
+            from oracle import mxquant             # checker only
+            ridx = _sample_rows(wl["m"], 128, 17, torch)
+            a_deq = mxquant.dequant_nvfp4(fa[ridx.cuda()].cpu().numpy(), fsa[ridx.cuda()].cpu().numpy(), 1.0, wl["k"])
+            b_deq = mxquant.dequant_nvfp4(fb.cpu().numpy(), fsb.cpu().numpy(), f_alpha, wl["k"])
+            gold = torch.matmul(torch.from_numpy(a_deq), torch.from_numpy(b_deq).t())
+            err, rows = _rel_err(c_d[ridx.cuda()].cpu(), gold, torch), int(ridx.numel())
         else:   # quant: bit-exact codes and scales on a row sample
             import numpy as np
             from oracle import mxquant             # checker only
@@ -654,7 +685,7 @@ def main():
         else:
             peak_tf *= wl.get("peak_scale", 1.0)      # fp8 tensor peak taken as twice the measured bf16 figure
             if wl.get("peak_scale"):
-                peak_kind = "2 x " + peak_kind
+                peak_kind = f"{wl['peak_scale']:g} x " + peak_kind
             per_gpu_tflops = wl["flops"] / (ms_per_step * 1e-3) / 1e12
             t_gemm_us = wl["flops"] / (peak_tf * 1e12) * 1e6
             t_comm_us = wl["comm_bytes"] / (NVLINK_GBS * 1e9) * 1e6
@@ -669,12 +700,19 @@ def main():
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"],
                 "data": "synthetic",
                 "config": {"workload": wl["desc"], "op": wl["name"], "l2": "operands larger than L2 (126 MB)",
-                           "parallelism": f"tp{world}" if args.op != "moe" else f"ep{world}"},
+                           "parallelism": (f"ep{world}" if args.op == "moe" else "replicas" if args.op == "fp4" else f"tp{world}")},
                 "tflops_per_gpu": per_gpu_tflops,
                 "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak_tf, "unit": "TFLOP/s",
                              "frac": per_gpu_tflops / peak_tf, "traffic": traffic, "peak_kind": f"of {peak_kind}",
                              "t_gemm_peak_us": t_gemm_us, "t_comm_peak_us": t_comm_us,
-                             "frac_of_max_gemm_comm": max(t_gemm_us, t_comm_us) / (ms_per_step * 1e3)},
+                             "frac_of_max_gemm_comm": max(t_gemm_us, t_comm_us) / (ms_per_step * 1e3),
+                             # the same against the datasheet: dense tensor peak (2250 TFLOP/s bf16, x2 fp8, x4 fp4) and
+                             # 900 GB/s NVLink per direction
+                             "spec_peak": SPEC_BF16_TFLOPS * wl.get("peak_scale", 1.0),
+                             "frac_of_spec_peak": per_gpu_tflops / (SPEC_BF16_TFLOPS * wl.get("peak_scale", 1.0)),
+                             "frac_of_spec_max_gemm_comm":
+                                 max(wl["flops"] / (SPEC_BF16_TFLOPS * wl.get("peak_scale", 1.0) * 1e12),
+                                     wl["comm_bytes"] / (SPEC_NVLINK_GBS * 1e9)) / (ms_per_step * 1e-3)},
                 "exposed_comm_frac": exposed, "compute_only_ms_per_step": compute_only_ms,
                 "e2e": e2e, "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "parity": parity,
             }

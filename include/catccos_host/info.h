@@ -84,6 +84,7 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
         {"a5moe", ASCEND950_DISPATCH_FFN_COMBINE},
+        {"mxqtag", MX_QUANT_ALLGATHER},
     };
     return m;
 }
@@ -102,6 +103,7 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
         {ASCEND950_DISPATCH_FFN_COMBINE, "Ascend950DispatchFFNCombine"},
+        {MX_QUANT_ALLGATHER, "MxQuantAllGather"},
     };
     return m;
 }

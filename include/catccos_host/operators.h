@@ -229,4 +229,38 @@ public:
 };
 REGISTER_OPERATOR("Ascend950DispatchFFNCombine", Ascend950DispatchFFNCombineOperator);
 
+// MX quantisation + all-gather (examples/ascend950_mx_quant_allgather/mx_quant_allgather_host.h:48-74): every rank
+// quantises its bf16 [m, n] input to e4m3 + one E8M0 scale per 32 along n and ends with all ranks' codes
+// (ptrC, [rankSize*m, n]) and scales (ptrB, [rankSize*m, even(n/32)]).  Files: rank_<r>_input.bin in,
+// rank_<r>_output.bin and rank_<r>_mxscale.bin out.
+class MxQuantAllGatherOperator : public CatccosOperator {
+public:
+    static constexpr uint32_t MX_BLOCK_SIZE = 32;
+    static size_t ScalesPerRow(uint32_t n) { return (static_cast<size_t>(n) / MX_BLOCK_SIZE + 1) / 2 * 2; }
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t inputSize = static_cast<size_t>(t.m) * t.n * 2;
+        const size_t outputSize = static_cast<size_t>(t.m) * t.n * t.rankSize;
+        const size_t scaleSize = static_cast<size_t>(t.m) * ScalesPerRow(t.n) * t.rankSize;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_input"), inputSize),
+                               DeviceZeros(scaleSize), DeviceZeros(outputSize));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/rank_" + std::to_string(rankId) + "_output.bin", params.ptrC,
+                                        static_cast<size_t>(t.m) * t.n * t.rankSize);
+        catccos_host::WriteDeviceBuffer(dataFile + "/rank_" + std::to_string(rankId) + "_mxscale.bin", params.ptrB,
+                                        static_cast<size_t>(t.m) * ScalesPerRow(t.n) * t.rankSize);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &) override { return 0; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return MX_QUANT_ALLGATHER; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        if (t.m == 0 || t.n == 0 || t.n % MX_BLOCK_SIZE != 0) return false;
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return rankSize >= 1 && rankSize <= MAX_RANK_SIZE &&
+               catccos_symmetric_bytes(MX_QUANT_ALLGATHER, FP8E4M3FN, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("MxQuantAllGather", MxQuantAllGatherOperator);
+
 #endif  // CATCCOS_HOST_OPERATORS_H

@@ -21,7 +21,7 @@ def test_registry_lists_every_operator_on_the_path(driver):
     out = subprocess.run([driver, "--list"], capture_output=True, text=True, check=True).stdout.split()
     assert set(out) == {"MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend950AllGatherMatmul",
                         "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
-                        "Ascend950MxFp8MatmulReduceScatter"}
+                        "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
@@ -32,6 +32,22 @@ def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
         r = subprocess.run([driver, "mmar", "1", "1", "0", "tcp://127.0.0.1:1", "128", "256", "64", str(tmp_path)],
                            capture_output=True, text=True)
         assert r.returncode != 0 and "shmem init failed" in r.stderr
+
+
+@pytest.mark.gpu
+def test_single_rank_mx_quant_allgather_driver_run(driver, tmp_path):
+    """`mxqtag` through the host path with the reference's file names
+    (examples/ascend950_mx_quant_allgather/mx_quant_allgather_host.h:48-74): codes and scales byte for byte."""
+    from oracle import mxquant
+    m, n = 200, 1024
+    x = (torch.randn((m, n), generator=torch.Generator().manual_seed(3)) * 2).to(torch.bfloat16)
+    x.view(torch.uint16).numpy().tofile(os.path.join(tmp_path, "rank_0_input.bin"))
+    r = subprocess.run([driver, "mxqtag", "36", "1", "0", "tcp://127.0.0.1:8789", str(m), str(n), "1", str(tmp_path),
+                        "0", "0", "1", "0", "0", "1", "1"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    codes, scales, _ = mxquant.quantize_mx_e4m3(x.to(torch.float32).numpy(), "rne")
+    assert np.array_equal(np.fromfile(os.path.join(tmp_path, "rank_0_output.bin"), dtype=np.uint8).reshape(m, n), codes)
+    assert np.array_equal(np.fromfile(os.path.join(tmp_path, "rank_0_mxscale.bin"), dtype=np.uint8).reshape(m, -1), scales)
 
 
 def _write_dense_files(tmp_path, world, a, b, trans_b=False):
