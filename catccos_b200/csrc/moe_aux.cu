@@ -64,10 +64,12 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
     const int chunk = ((total + 31) / 32 + 31) / 32 * 32;
     const int begin = warp * chunk;
     const int end = min(total, begin + chunk);
+    // a negative expert id marks a row that takes no part (the all-to-all-v operators pad their row lists with them)
     for (int base = begin; base < end; base += 32) {
         const int i = base + lane;
-        const bool valid = i < end;
-        const int key = valid ? ra.expert_idx[i] : -1 - lane;
+        const int raw = i < end ? ra.expert_idx[i] : -1;
+        const bool valid = raw >= 0;
+        const int key = valid ? raw : -1 - lane;
         const unsigned mask = __match_any_sync(0xffffffffu, key);
         if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
         __syncwarp();
@@ -102,16 +104,17 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
     __syncthreads();
     for (int base = begin; base < end; base += 32) {
         const int i = base + lane;
-        const bool valid = i < end;
-        const int key = valid ? ra.expert_idx[i] : -1 - lane;
+        const int raw = i < end ? ra.expert_idx[i] : -1;
+        const bool valid = raw >= 0;
+        const int key = valid ? raw : -1 - lane;
         const unsigned mask = __match_any_sync(0xffffffffu, key);
         const int rnk = __popc(mask & ((1u << lane) - 1u));
-        int dst = 0;
+        int dst = -1;
         if (valid) dst = cnt[warp * E + key] + rnk;
         __syncwarp();
         if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
         __syncwarp();
-        if (valid) ra.expanded_row_idx[i] = dst;
+        if (i < end) ra.expanded_row_idx[i] = dst;
     }
 
     // ---- tokens-per-expert to every rank (the count all-gather), then the offset tables ----

@@ -233,45 +233,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_grouped_gemm_kernel(const
             const bool row_ok = row_in_tile < tl.rows;
             const int row = tl.row0 + row_in_tile;
             if (MODE == 1) {
-                // act half -> bf16-rounded values kept packed; gate half chunk by chunk
-                uint32_t act[64];
+                // Both halves leave TMEM at once, rounded to bf16 as the golden rounds the up projection, and the
+                // accumulator is handed back before any of the SwiGLU / quantisation arithmetic: that arithmetic
+                // (about as long as a tile's main loop on one warp per scheduler) then overlaps the next tile.
+                uint32_t act[64], gate[64];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 8; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        act[c * 16 + i] =
-                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t pk2 = Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                        if (c < 4) act[c * 16 + i] = pk2; else gate[(c - 4) * 16 + i] = pk2;
+                    }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->tmem_empty);
                 uint32_t scale_word = 0;
                 const int half_n = p.Nw / 2;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + 128 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
-                    tmem_ld_wait();
-                    if (c == 3) {
-                        // accumulator fully read: the MMA warp may start the next tile
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&sh->tmem_empty);
-                    }
-                    float y[32];
+                    uint32_t ypk[16];            // y rounded to bf16, two per word
                     uint32_t am = 0;
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const float2 a2 = Pack2<__nv_bfloat16>::unpack(act[c * 16 + i]);
-                        const float2 g2 = Pack2<__nv_bfloat16>::unpack(
-                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])));
-                        const float y0 = a2.x * (1.0f / (1.0f + expf(-a2.x))) * g2.x;
-                        const float y1 = a2.y * (1.0f / (1.0f + expf(-a2.y))) * g2.y;
-                        const uint32_t pk = Pack2<__nv_bfloat16>::pack(y0, y1);      // y rounded to bf16
-                        am = max(am, max(pk & 0x7FFFu, (pk >> 16) & 0x7FFFu));
-                        const float2 yr = Pack2<__nv_bfloat16>::unpack(pk);
-                        y[2 * i] = yr.x;
-                        y[2 * i + 1] = yr.y;
+                        const float2 g2 = Pack2<__nv_bfloat16>::unpack(gate[c * 16 + i]);
+                        // act * sigmoid(act) * gate; exp and reciprocal through the special-function unit
+                        const float y0 = a2.x * __frcp_rn(1.0f + __expf(-a2.x)) * g2.x;
+                        const float y1 = a2.y * __frcp_rn(1.0f + __expf(-a2.y)) * g2.y;
+                        ypk[i] = Pack2<__nv_bfloat16>::pack(y0, y1);
+                        am = max(am, max(ypk[i] & 0x7FFFu, (ypk[i] >> 16) & 0x7FFFu));
                     }
                     const float amax = __uint_as_float(am << 16);
                     uint32_t sb = 127u;
@@ -283,17 +277,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_grouped_gemm_kernel(const
                     }
                     scale_word |= sb << (8 * c);
                     uint32_t code[8];
+                    if (am <= 0x7F80u) {
+                        // no NaN in the chunk: two values per conversion
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        uint32_t w = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            const float x = y[i * 4 + b] * inv;
-                            const uint32_t cb8 = (x != x) ? (0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u))
-                                                          : static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
-                            w |= cb8 << (8 * b);
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 ya = Pack2<__nv_bfloat16>::unpack(ypk[2 * i]), yb = Pack2<__nv_bfloat16>::unpack(ypk[2 * i + 1]);
+                            const uint32_t lo = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(
+                                make_float2(ya.x * inv, ya.y * inv), __NV_SATFINITE, __NV_E4M3));
+                            const uint32_t hi = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(
+                                make_float2(yb.x * inv, yb.y * inv), __NV_SATFINITE, __NV_E4M3));
+                            code[i] = lo | (hi << 16);
                         }
-                        code[i] = w;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            uint32_t w = 0;
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const float2 yv = Pack2<__nv_bfloat16>::unpack(ypk[2 * i + (b >> 1)]);
+                                const float x = ((b & 1) ? yv.y : yv.x) * inv;
+                                const uint32_t cb8 = (x != x) ? (0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u))
+                                                              : static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+                                w |= cb8 << (8 * b);
+                            }
+                            code[i] = w;
+                        }
                     }
                     if (row_ok) {
                         uint8_t *dst = ra.act_codes + static_cast<size_t>(row) * half_n + tl.ni * 128 + c * 32;

@@ -95,9 +95,9 @@ static int encode_atoms(const DriverApi *api, CUtensorMap *tm, const void *base,
     return CATCCOS_OK;
 }
 
-template <int MODE>
-static int launch_pair_gemm(const MoePairParams &p, cudaStream_t stream) {
-    auto kern = moe_pair_gemm_kernel<MODE>;
+template <int MODE, typename TOut, bool B_MN>
+int launch_pair_gemm(const MoePairParams &p, cudaStream_t stream) {
+    auto kern = moe_pair_gemm_kernel<MODE, TOut, B_MN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMoePairSmemBytes);
     if (e == cudaSuccess) {
         kern<<<p.ctas_per_rank * p.n_local, kGemmThreads, kMoePairSmemBytes, stream>>>(p);
@@ -318,8 +318,8 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
             return rc;
     }
     if (use_pair) {
-        if ((rc = launch_pair_gemm<1>(q1, stream))) return rc;
-        if ((rc = launch_pair_gemm<2>(q2, stream))) return rc;
+        if ((rc = launch_pair_gemm<1, __nv_bfloat16, false>(q1, stream))) return rc;
+        if ((rc = launch_pair_gemm<2, __nv_bfloat16, false>(q2, stream))) return rc;
     } else {
         if ((rc = launch_gemm<1>(g1, stream))) return rc;
         if ((rc = launch_gemm<2>(g2, stream))) return rc;

@@ -11,7 +11,12 @@
 //   MODE 1 (up projection): the pair's B tile is 128 "act" rows (CTA 0) + 128 "gate" rows (CTA 1) of
 //     the expert's [N, K] weight; every CTA's accumulator holds act | gate for its 128 rows, and the
 //     epilogue applies y = bf16(act * sigmoid(act) * gate) and MX-quantises y (moe_gemm.cuh, MODE 1).
-//   MODE 2 (down projection): plain 256-wide tile; rows go back to their source rank's combine buffer.
+//   MODE 2 (down projection, and GroupedMatmul-AllToAllV): plain 256-wide tile; rows go back to their source
+//     rank's combine buffer, at the row's position in that rank's expert-sorted order.
+//   MODE 3 (AllToAllV-GroupedMatmul): plain 256-wide tile; rows are written to this rank's output in receive
+//     order (local expert major, source rank minor) without the 128-row padding of the receive buffer.
+// B_MN: the weights are [E_local, K, N] (K x N row-major per expert, the standalone operators' transB = 0)
+// instead of [E_local * N, K]; they are read through a 3-D tensor map whose third coordinate is the expert.
 // Reference: include/catccos/dgemm/kernel/ascend950_alltoall_gmm.hpp:57-506,
 // include/catccos/dgemm/kernel/ascend950_gmm_alltoall.hpp:104-486; golden examples/utils/gen_data_moe.py:546-588.
 #pragma once
@@ -32,11 +37,12 @@ static_assert(kMoePairSmemBytes <= 232448, "shared memory budget");
 
 struct alignas(64) MoePairRankArgs {
     CUtensorMap tmA;          // activations [rows_cap, Kin] bytes, box {128, 128}
-    CUtensorMap tmB;          // weights [E_local * Nw, Kin] bytes, box {128, 128}
+    CUtensorMap tmB;          // weights [E_local * Nw, Kin] bytes, box {128, 128};  B_MN: [E_local][Kin][Nw], box {128, 128, 1}
     CUtensorMap tmSfa;        // activation scale atoms as rows of 128 u32, box {128, 1}
     CUtensorMap tmSfb;        // weight scale atoms, the same
     uint8_t *act_codes;       // MODE 1 out: [rows_cap, Nw/2]
     uint8_t *act_sf;          // MODE 1 out: atoms [rows_cap/128][(Nw/2)/128][512]
+    void *out;                // MODE 3 out: 16-bit [rows, Nw]
     MoeMeta *meta;
 };
 
@@ -63,6 +69,7 @@ struct MoePairSmem {
     int abort_flag;
     TileQueue tq;
     int pprefix[kMoeMaxLocalExperts + 1];    // exclusive prefix of pair tiles (256 rows) over the local experts
+    int uprefix[kMoeMaxLocalExperts + 1];    // exclusive prefix of received rows (no padding) over the local experts
 };
 
 struct MoePairTile {
@@ -73,7 +80,7 @@ struct MoePairTile {
     int mi;          // this CTA's 128-row tile inside the expert
 };
 
-template <int MODE>
+template <int MODE, typename TOut, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     moe_pair_gemm_kernel(const __grid_constant__ MoePairParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -96,7 +103,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int EL = p.experts_per_rank;
     const MoePairRankArgs &ra = p.ranks[lrank];
     MoeMeta *meta = ra.meta;
-    const int n_tiles = (MODE == 1) ? (p.Nw / 2) / 128 : p.Nw / BN;
+    const int n_tiles = (MODE == 1) ? (p.Nw / 2) / 128 : (p.Nw + BN - 1) / BN;
+    const int nb128 = (p.Nw + 127) / 128;          // weight scale atoms (128 weight rows each) per expert
     const int kblocks = (p.Kin + MX_BK - 1) / MX_BK;
     const bool skip_all = meta->overflow != 0;
 
@@ -110,12 +118,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
         tq_init(&sh->tq);
-        int run = 0;
+        int run = 0, rows = 0;
         for (int le = 0; le < EL; ++le) {
             sh->pprefix[le] = run;
+            sh->uprefix[le] = rows;
             run += (meta->tile_prefix[le + 1] - meta->tile_prefix[le] + 1) / 2;
+            rows += meta->seg_rows[le];
         }
         sh->pprefix[EL] = skip_all ? 0 : run;
+        sh->uprefix[EL] = rows;
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
@@ -163,18 +174,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 uint32_t tq;
                 if (!(ok = tq_get(&sh->tq, seq, tq, ctl)) || tq == kTileEnd) break;
                 const MoePairTile tl = decode(static_cast<int>(tq), le_hint);
-                // this CTA's half of the pair's 256 weight rows, and the weight rows of both halves (scale atoms)
-                int b_row0, b_row1;
+                // the two 128-wide halves of the pair's weight tile (columns inside the expert); this CTA loads one
+                // of them, and the scale atoms of both
+                int n0, n1;
                 if (MODE == 1) {
-                    b_row0 = tl.le * p.Nw + tl.ni * 128;          // act rows
-                    b_row1 = b_row0 + p.Nw / 2;                    // gate rows
+                    n0 = tl.ni * 128;                 // act rows
+                    n1 = n0 + p.Nw / 2;               // gate rows
                 } else {
-                    b_row0 = tl.le * p.Nw + tl.ni * BN;
-                    b_row1 = b_row0 + 128;
+                    n0 = tl.ni * BN;
+                    n1 = n0 + 128;
                 }
-                const int b_mine = cr == 0 ? b_row0 : b_row1;
+                const int n_mine = cr == 0 ? n0 : n1;
                 const int sfa_atom0 = (tl.row0 >> 7) * kblocks;
-                const int sfb_atom0 = (b_row0 >> 7) * kblocks, sfb_atom1 = (b_row1 >> 7) * kblocks;
+                const int sfb_atom0 = (tl.le * nb128 + (n0 >> 7)) * kblocks, sfb_atom1 = (tl.le * nb128 + (n1 >> 7)) * kblocks;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % kMoePStages;
                     const uint32_t ph = (it / kMoePStages) & 1;
@@ -183,7 +195,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     uint8_t *ssf = smem_sf + st * kMoePSf;
                     mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB + kMoePSf);
                     tma_load_2d_pair(smem_a + st * kMxPA, &ra.tmA, full_leader, kb * MX_BK, tl.row0);
-                    tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, kb * MX_BK, b_mine);
+                    if (B_MN)
+                        tma_load_3d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, n_mine, kb * MX_BK, tl.le);
+                    else
+                        tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, kb * MX_BK, tl.le * p.Nw + n_mine);
                     tma_load_2d_pair(ssf, &ra.tmSfa, full_leader, 0, sfa_atom0 + kb);
                     tma_load_2d_pair(ssf + 512, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb);
                     tma_load_2d_pair(ssf + 1024, &ra.tmSfb, full_leader, 0, sfb_atom1 + kb);
@@ -220,8 +235,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                     for (int k = 0; k < MX_BK / 32; ++k) {
                         const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
-                        const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024);
-                        umma_mxf8_pair(tmem_base, ad, bd, make_idesc_mxf8(2 * BM, BN, k, k), tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
+                                                 : make_smem_desc(b_addr + k * 32, 16, 1024);
+                        const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, k, k) | (B_MN ? (1u << 16) : 0u);
+                        umma_mxf8_pair(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
                     }
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 0));
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 1));
@@ -255,45 +272,39 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             const bool row_ok = row_in_tile < tl.rows;
             const int row = tl.row0 + row_in_tile;
             if (MODE == 1) {
-                // act half -> bf16-rounded values kept packed; gate half chunk by chunk
-                uint32_t act[64];
+                // Both halves leave TMEM at once, rounded to bf16 as the golden rounds the up projection, and the
+                // accumulator is handed back before any of the SwiGLU / quantisation arithmetic: that arithmetic
+                // (about as long as a tile's main loop on one warp per scheduler) then overlaps the next tile.
+                uint32_t act[64], gate[64];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 8; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        act[c * 16 + i] =
-                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t pk2 = Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                        if (c < 4) act[c * 16 + i] = pk2; else gate[(c - 4) * 16 + i] = pk2;
+                    }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
                 uint32_t scale_word = 0;
                 const int half_n = p.Nw / 2;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + 128 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
-                    tmem_ld_wait();
-                    if (c == 3) {
-                        // accumulator fully read: the MMA thread may start the next tile
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
-                    }
-                    float y[32];
+                    uint32_t ypk[16];            // y rounded to bf16, two per word
                     uint32_t am = 0;
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const float2 a2 = Pack2<__nv_bfloat16>::unpack(act[c * 16 + i]);
-                        const float2 g2 = Pack2<__nv_bfloat16>::unpack(
-                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])));
-                        const float y0 = a2.x * (1.0f / (1.0f + expf(-a2.x))) * g2.x;
-                        const float y1 = a2.y * (1.0f / (1.0f + expf(-a2.y))) * g2.y;
-                        const uint32_t pk = Pack2<__nv_bfloat16>::pack(y0, y1);      // y rounded to bf16
-                        am = max(am, max(pk & 0x7FFFu, (pk >> 16) & 0x7FFFu));
-                        const float2 yr = Pack2<__nv_bfloat16>::unpack(pk);
-                        y[2 * i] = yr.x;
-                        y[2 * i + 1] = yr.y;
+                        const float2 g2 = Pack2<__nv_bfloat16>::unpack(gate[c * 16 + i]);
+                        // act * sigmoid(act) * gate; exp and reciprocal through the special-function unit
+                        const float y0 = a2.x * __frcp_rn(1.0f + __expf(-a2.x)) * g2.x;
+                        const float y1 = a2.y * __frcp_rn(1.0f + __expf(-a2.y)) * g2.y;
+                        ypk[i] = Pack2<__nv_bfloat16>::pack(y0, y1);
+                        am = max(am, max(ypk[i] & 0x7FFFu, (ypk[i] >> 16) & 0x7FFFu));
                     }
                     const float amax = __uint_as_float(am << 16);
                     uint32_t sb = 127u;
@@ -305,17 +316,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     }
                     scale_word |= sb << (8 * c);
                     uint32_t code[8];
+                    if (am <= 0x7F80u) {
+                        // no NaN in the chunk: two values per conversion
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        uint32_t w = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            const float x = y[i * 4 + b] * inv;
-                            const uint32_t cb8 = (x != x) ? (0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u))
-                                                          : static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
-                            w |= cb8 << (8 * b);
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 ya = Pack2<__nv_bfloat16>::unpack(ypk[2 * i]), yb = Pack2<__nv_bfloat16>::unpack(ypk[2 * i + 1]);
+                            const uint32_t lo = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(
+                                make_float2(ya.x * inv, ya.y * inv), __NV_SATFINITE, __NV_E4M3));
+                            const uint32_t hi = static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(
+                                make_float2(yb.x * inv, yb.y * inv), __NV_SATFINITE, __NV_E4M3));
+                            code[i] = lo | (hi << 16);
                         }
-                        code[i] = w;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            uint32_t w = 0;
+#pragma unroll
+                            for (int b = 0; b < 4; ++b) {
+                                const float2 yv = Pack2<__nv_bfloat16>::unpack(ypk[2 * i + (b >> 1)]);
+                                const float x = ((b & 1) ? yv.y : yv.x) * inv;
+                                const uint32_t cb8 = (x != x) ? (0x7Fu | ((__float_as_uint(x) >> 24) & 0x80u))
+                                                              : static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+                                w |= cb8 << (8 * b);
+                            }
+                            code[i] = w;
+                        }
                     }
                     if (row_ok) {
                         uint8_t *dst = ra.act_codes + static_cast<size_t>(row) * half_n + tl.ni * 128 + c * 32;
@@ -341,35 +366,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        pk[c * 16 + i] =
-                            Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                        pk[c * 16 + i] = Pack2<TOut>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
-                // which rank does this row go back to, and where in its expert-sorted order
-                __nv_bfloat16 *dst = nullptr;
-                if (row_ok) {
-                    const int w = tl.mi * BM + row_in_tile;
-                    int src = 0;
-                    while (src + 1 < R && w >= meta->cum_src[src + 1][tl.le]) ++src;
-                    const int e = rank * EL + tl.le;
-                    const int drow = meta->prefix_all[src][e] + (w - meta->cum_src[src][tl.le]);
-                    dst = reinterpret_cast<__nv_bfloat16 *>(p.heap_base[src] + p.combine_off) +
-                          static_cast<size_t>(drow) * p.Nw + tl.ni * BN;
-                }
-                uint8_t *my_row = smem_side + row_in_tile * 128;
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    bulk_wait_read<0>();
-#pragma unroll
-                    for (int g = 0; g < 8; ++g)
-                        *reinterpret_cast<uint4 *>(my_row + g * 16) = make_uint4(
-                            pk[h * 32 + g * 4], pk[h * 32 + g * 4 + 1], pk[h * 32 + g * 4 + 2], pk[h * 32 + g * 4 + 3]);
-                    fence_proxy_async_smem();
+                const int col0 = tl.ni * BN;
+                const int w = tl.mi * BM + row_in_tile;              // row inside the expert
+                if (MODE == 3) {
+                    // receive order without padding: rows of the experts before this one, then w
                     if (row_ok) {
-                        bulk_store(dst + h * 64, my_row, 128);
-                        bulk_commit();
+                        TOut *dst = static_cast<TOut *>(ra.out) + static_cast<size_t>(sh->uprefix[tl.le] + w) * p.Nw + col0;
+#pragma unroll
+                        for (int g = 0; g < BN / 8; ++g)
+                            if (col0 + g * 8 < p.Nw)
+                                *reinterpret_cast<uint4 *>(dst + g * 8) =
+                                    make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                    }
+                } else {
+                    // which rank does this row go back to, and where in its expert-sorted order
+                    TOut *dst = nullptr;
+                    if (row_ok) {
+                        int src = 0;
+                        while (src + 1 < R && w >= meta->cum_src[src + 1][tl.le]) ++src;
+                        const int e = rank * EL + tl.le;
+                        const int drow = meta->prefix_all[src][e] + (w - meta->cum_src[src][tl.le]);
+                        dst = reinterpret_cast<TOut *>(p.heap_base[src] + p.combine_off) + static_cast<size_t>(drow) * p.Nw + col0;
+                    }
+                    uint8_t *my_row = smem_side + row_in_tile * 128;
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        bulk_wait_read<0>();
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            *reinterpret_cast<uint4 *>(my_row + g * 16) = make_uint4(
+                                pk[h * 32 + g * 4], pk[h * 32 + g * 4 + 1], pk[h * 32 + g * 4 + 2], pk[h * 32 + g * 4 + 3]);
+                        fence_proxy_async_smem();
+                        const int cols_left = p.Nw - (col0 + h * 64);        // Nw is a multiple of 8: whole 16-byte pieces
+                        if (row_ok && cols_left > 0) {
+                            bulk_store(dst + h * 64, my_row, static_cast<uint32_t>(min(64, cols_left)) * 2u);
+                            bulk_commit();
+                        }
                     }
                 }
             }

@@ -253,6 +253,15 @@ __device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const void *tma
         ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
         : "memory");
 }
+// the same for a 3-D tensor (used for per-expert weight matrices: the third coordinate picks the expert, so a
+// tile that runs past an expert's rows is zero-filled instead of reading its neighbour)
+__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const void *tmap, uint32_t bar_cluster_addr, int c0,
+                                                 int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
                  "r"(ncols)
