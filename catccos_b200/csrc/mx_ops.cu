@@ -71,10 +71,10 @@ static int launch_pair_k(const MxParams &p, int grid, bool coop, cudaStream_t st
     if (e == cudaSuccess) {
         if (coop) {
             void *args[] = {const_cast<MxParams *>(&p)};
-            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kPairAgThreads), args,
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kMxPairThreads), args,
                                             kMxPairSmemBytes, stream);
         } else {
-            kern<<<grid, kPairAgThreads, kMxPairSmemBytes, stream>>>(p);
+            kern<<<grid, kMxPairThreads, kMxPairSmemBytes, stream>>>(p);
             e = cudaGetLastError();
         }
     }

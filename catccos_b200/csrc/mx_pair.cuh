@@ -16,8 +16,10 @@ namespace cb {
 constexpr int kMxPStages = 6;
 constexpr int kMxPA = BM * MX_BK;               // 16 KiB
 constexpr int kMxPB = 128 * MX_BK;              // 16 KiB
-constexpr int kMxPSf = 1536;                    // A atom + two B atoms
-constexpr int kMxPairSmemBytes = kMxPStages * (kMxPA + kMxPB + kMxPSf) + kMxSideBytes + 1024 + 512;
+constexpr int kMxPairThreads = 480;             // warps 0-10 as the f16/bf16 pair kernel, warps 11-14 feed the scale factors
+constexpr int kMxPSf = 1536;                    // kernels that still stage scale atoms in shared memory: A atom + two B atoms
+constexpr int kMxSfCols = 16;                   // TMEM columns of one stage's scales: 4 (A) + 8 (B), padded
+constexpr int kMxPairSmemBytes = kMxPStages * (kMxPA + kMxPB) + kMxSideBytes + 1024 + 512;
 static_assert(kMxPairSmemBytes <= 232448, "shared memory budget");
 
 struct MxPairSmem {
@@ -33,14 +35,13 @@ struct MxPairSmem {
 };
 
 template <typename TOut, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
     mx_pair_agmm_kernel(const __grid_constant__ MxParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
     uint8_t *smem_b = smem_a + kMxPStages * kMxPA;
-    uint8_t *smem_sf = smem_b + kMxPStages * kMxPB;
-    uint8_t *smem_push = smem_sf + kMxPStages * kMxPSf;
+    uint8_t *smem_push = smem_b + kMxPStages * kMxPB;
     MxPairSmem *sh = reinterpret_cast<MxPairSmem *>(smem_push + kMxSideBytes);
     static_assert(sizeof(MxPairSmem) <= 512, "barrier block outgrew its budget");
 
@@ -63,7 +64,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMxPStages; ++s) {
-            mbar_init(&sh->full[s], 2);
+            mbar_init(&sh->full[s], 2 + 8);      // two producers (with their bytes) + the pair's eight scale-factor warps
             mbar_init(&sh->empty[s], 1);
         }
         mbar_init(&sh->tmem_full, 1);
@@ -76,9 +77,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
         prefetch_tensormap(&ra.tmAg);
-        prefetch_tensormap(&ra.tmSfa);
-        prefetch_tensormap(&ra.tmSfag);
-        prefetch_tensormap(&ra.tmSfb);
     }
     if (warp == 1) {
         tmem_alloc_pair(&sh->tmem_base, 512);
@@ -89,8 +87,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
     cluster_sync();
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
-    // scale factors: 4 (A) + 8 (B) columns per K-step, four sets used in turn so that the copy for
-    // one K-step does not have to wait for the MMAs of the step before it
+    // scale factors: 4 (A) + 8 (B) TMEM columns per pipeline stage, written by warps 11-14 straight from
+    // global memory (tcgen05.st), so that nothing but MMAs sits in the tensor pipe's queue
     const uint32_t tmem_sf0 = tmem_base + BN;
 
     WaitCtl ctl;
@@ -123,28 +121,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             if (!ok) break;
             if (lane == 0) {
                 const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
-                const CUtensorMap *tsfa = gathered ? &ra.tmSfag : &ra.tmSfa;
                 const int a_row = (gathered ? s * p.M : 0) + chunk * BM;
-                // a chunk past the rank's rows has no scale atoms of its own: reuse the last chunk's (rows are masked)
-                const int sfa_atom0 = ((gathered ? s * mt : 0) + (have_rows ? chunk : mt - 1)) * kb4;
                 const int n_half = ni * BN + static_cast<int>(cr) * 128;
-                const int sfb_atom0 = (ni * 2) * kb4;
-                const bool second_b_atom = (ni * BN + 128) < p.N;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % kMxPStages;
                     const uint32_t ph = (it / kMxPStages) & 1;
                     if (!(ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY))) break;
                     const uint32_t full_leader = mapa_cluster(smem_u32(&sh->full[st]), 0);
-                    uint8_t *ssf = smem_sf + st * kMxPSf;
-                    mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB + 1024 + (second_b_atom ? 512 : 0));
+                    mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB);
                     tma_load_2d_pair(smem_a + st * kMxPA, tma, full_leader, kb * MX_BK, a_row);
                     if (B_MN)
                         tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, n_half, kb * MX_BK);
                     else
                         tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, kb * MX_BK, n_half);
-                    tma_load_2d_pair(ssf, tsfa, full_leader, 0, sfa_atom0 + kb);
-                    tma_load_2d_pair(ssf + 512, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb);
-                    if (second_b_atom) tma_load_2d_pair(ssf + 1024, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb4 + kb);
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -173,12 +162,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + st * kMxPA);
                     const uint32_t b_addr = smem_u32(smem_b + st * kMxPB);
-                    const uint32_t sf_addr = smem_u32(smem_sf + st * kMxPSf);
-                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * 16u;
+                    const uint32_t tmem_sfa = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols;   // written by warps 11-14
                     const uint32_t tmem_sfb = tmem_sfa + 4;
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));
 #pragma unroll
                     for (int k = 0; k < MX_BK / 32; ++k) {
                         const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
@@ -219,27 +204,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             decode(t, s, mi2, ni, gathered);
             if (!(ok = mbar_wait(&sh->tmem_full, tcount & 1, ctl, W_TMEM_FULL))) break;
             tc_fence_after();
-            uint32_t pk[BN / 2];
-#pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    pk[c * 16 + i] = Pack2<TOut>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
+            // two halves of 128 columns: the first half's stores are issued before the second half is read, and
+            // the accumulator goes back to the MMA thread right after the last TMEM read
             const int row = s * p.M + mi2 * 2 * BM + static_cast<int>(cr) * BM + row_in_tile;
-            if (row < (s + 1) * p.M) {
-                TOut *dst = C + static_cast<size_t>(row) * p.N + ni * BN;
+            const bool row_ok = row < (s + 1) * p.M;
+            TOut *dst = C + static_cast<size_t>(row) * p.N + ni * BN;
 #pragma unroll
-                for (int g = 0; g < BN / 8; ++g)
-                    if (ni * BN + g * 8 < p.N)
-                        *reinterpret_cast<uint4 *>(dst + g * 8) =
-                            make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t pk[BN / 4];
+#pragma unroll
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + (h * 4 + c) * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        pk[c * 16 + i] = Pack2<TOut>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                }
+                if (h == 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int g = 0; g < BN / 16; ++g)
+                        if (ni * BN + h * 128 + g * 8 < p.N)
+                            *reinterpret_cast<uint4 *>(dst + h * 128 + g * 8) =
+                                make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+                }
             }
             ++tcount;
         }
@@ -261,6 +254,53 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                     fence_proxy_async_global();     // rows seen through the flags -> the producer's TMA loads
                 }
                 if (lane == 0) st_release_cta_smem(&sh->tiles_ready, seq + 1);
+            }
+        }
+    } else if (warp >= 11) {
+        // ---------------------------------------------------------- scale factors ----
+        // Warp 11 + j owns TMEM lane quarter (11 + j) % 4.  Per pipeline stage every lane reads its 16-byte
+        // row of the A atom and of the two B atoms from global memory (the atoms are 512 contiguous bytes:
+        // one coalesced request per warp, the other three warps hit L1) and stores them into the stage's
+        // scale columns; the stage's "full" barrier in the leader counts these eight warps next to the loads.
+        const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        uint32_t it = 0, seq = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += pairs, ++seq) {
+            int s, mi2, ni;
+            bool gathered;
+            decode(t, s, mi2, ni, gathered);
+            const int chunk = mi2 * 2 + static_cast<int>(cr);
+            const bool have_rows = chunk < mt;
+            if (gathered && !p.compute_only && have_rows) {
+                if (lane == 0) ok = wait_smem_counter_gt(&sh->tiles_ready, seq, ctl, W_MXAG);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+            }
+            // a chunk past the rank's rows has no scale atoms of its own: reuse the last chunk's (rows are masked)
+            const uint8_t *sfa_base = gathered ? p.heap_base[rank] + p.sf_off : ra.sfa;
+            const uint8_t *sfa = sfa_base + (static_cast<size_t>((gathered ? s * mt : 0) + (have_rows ? chunk : mt - 1)) * kb4) * 512 + lane * 16;
+            const uint8_t *sfb0 = ra.sfb + static_cast<size_t>(ni * 2) * kb4 * 512 + lane * 16;
+            const bool second_b_atom = (ni * BN + 128) < p.N;
+            const uint8_t *sfb1 = second_b_atom ? sfb0 + static_cast<size_t>(kb4) * 512 : sfb0;
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int st = it % kMxPStages;
+                const uint32_t ph = (it / kMxPStages) & 1;
+                const uint4 va = __ldg(reinterpret_cast<const uint4 *>(sfa + static_cast<size_t>(kb) * 512));
+                const uint4 vb0 = __ldg(reinterpret_cast<const uint4 *>(sfb0 + static_cast<size_t>(kb) * 512));
+                const uint4 vb1 = __ldg(reinterpret_cast<const uint4 *>(sfb1 + static_cast<size_t>(kb) * 512));
+                // the MMAs that read this stage's scale columns six K-steps ago have finished
+                if (lane == 0) ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols + lane_field;
+                tmem_st_32x4(col, va);
+                tmem_st_32x4(col + 4, vb0);
+                tmem_st_32x4(col + 8, vb1);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->full[st]), 0));
             }
         }
     } else {
