@@ -535,9 +535,6 @@ def main():
                           custom=[w2q, idx, probs, w1s, w2s], workspace=wsp)
             launches_per_step = 10
 
-    if os.environ.get("BENCH_DEBUG_FLAGS"):          # kernel timing probes (results invalid): implies --no-parity
-        check(lib().catccos_debug_set_flags(int(os.environ["BENCH_DEBUG_FLAGS"])))
-        args.no_parity = True
     for _ in range(args.warmup):
         step()
     barrier()

@@ -79,28 +79,12 @@ static int encode_u8(const DriverApi *api, CUtensorMap *tm, const void *base, ui
     return CATCCOS_OK;
 }
 
-// scale atoms as a 2-D tensor: rows of 128 u32 (= one 512-byte atom), one atom per load
-static int encode_atoms(const DriverApi *api, CUtensorMap *tm, const void *base, uint64_t n_atoms) {
-    cuuint64_t dims[2] = {128, n_atoms};
-    cuuint64_t strides[1] = {512};
-    cuuint32_t box[2] = {128, 1};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = api->TensorMapEncodeTiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides,
-                                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_error("cuTensorMapEncodeTiled (MoE scale atoms) failed: %d", static_cast<int>(r));
-        return CATCCOS_ERR_CUDA;
-    }
-    return CATCCOS_OK;
-}
-
 template <int MODE, typename TOut, bool B_MN>
 int launch_pair_gemm(const MoePairParams &p, cudaStream_t stream) {
     auto kern = moe_pair_gemm_kernel<MODE, TOut, B_MN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMoePairSmemBytes);
     if (e == cudaSuccess) {
-        kern<<<p.ctas_per_rank * p.n_local, kGemmThreads, kMoePairSmemBytes, stream>>>(p);
+        kern<<<p.ctas_per_rank * p.n_local, kMoePairThreads, kMoePairSmemBytes, stream>>>(p);
         e = cudaGetLastError();
     }
     if (e != cudaSuccess) {
@@ -220,6 +204,7 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
     q1.rank_base = p.rank_base;
     q1.n_local = n_local;
     q1.ctas_per_rank = per_rank & ~1;
+    q1.rows_cap = z.rows_cap;
     q1.experts = experts;
     q1.experts_per_rank = el;
     q1.epoch = p.epoch;
@@ -285,16 +270,16 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
             MoePairRankArgs &p1 = q1.ranks[l];
             p1.tmA = r1.tmA;
             p1.tmB = r1.tmB;
-            if ((rc = encode_atoms(api, &p1.tmSfa, ws[l].recv_atoms, sf_atoms_bytes(z.rows_cap, k) / 512))) return rc;
-            if ((rc = encode_atoms(api, &p1.tmSfb, ws[l].w1_atoms, sf_atoms_bytes(el * n, k) / 512))) return rc;
+            p1.sfa = ws[l].recv_atoms;
+            p1.sfb = ws[l].w1_atoms;
             p1.act_codes = ws[l].act_codes;
             p1.act_sf = ws[l].act_atoms;
             p1.meta = ra.meta;
             MoePairRankArgs &p2 = q2.ranks[l];
             p2.tmA = r2.tmA;
             p2.tmB = r2.tmB;
-            if ((rc = encode_atoms(api, &p2.tmSfa, ws[l].act_atoms, sf_atoms_bytes(z.rows_cap, n / 2) / 512))) return rc;
-            if ((rc = encode_atoms(api, &p2.tmSfb, ws[l].w2_atoms, sf_atoms_bytes(el * k, n / 2) / 512))) return rc;
+            p2.sfa = ws[l].act_atoms;
+            p2.sfb = ws[l].w2_atoms;
             p2.act_codes = nullptr;
             p2.act_sf = nullptr;
             p2.meta = ra.meta;

@@ -30,16 +30,17 @@
 namespace cb {
 
 constexpr int kMoePStages = 6;
-constexpr int kMoePSf = 1536;                                            // A atom + two B atoms
-constexpr int kMoePStageBytes = kMxPA + kMxPB + kMoePSf;                 // 33.5 KiB
-constexpr int kMoePairSmemBytes = kMoePStages * kMoePStageBytes + kMoeSideBytes + 1024 + 1024;
+constexpr int kMoePStageBytes = kMxPA + kMxPB;                           // 32 KiB (scale factors go to TMEM directly)
+constexpr int kMoePairThreads = 448;      // warp 0: producer (lane 0) and tile queue (lane 1), 1: MMA, 2-9: epilogue, 10-13: scale factors
+constexpr int kMoePairSideBytes = 32 * 1024;   // MODE 2: 2 column halves x 128 rows x 128 B of row staging
+constexpr int kMoePairSmemBytes = kMoePStages * kMoePStageBytes + kMoePairSideBytes + 1024 + 1024;   // + alignment + barrier block
 static_assert(kMoePairSmemBytes <= 232448, "shared memory budget");
 
 struct alignas(64) MoePairRankArgs {
     CUtensorMap tmA;          // activations [rows_cap, Kin] bytes, box {128, 128}
     CUtensorMap tmB;          // weights [E_local * Nw, Kin] bytes, box {128, 128};  B_MN: [E_local][Kin][Nw], box {128, 128, 1}
-    CUtensorMap tmSfa;        // activation scale atoms as rows of 128 u32, box {128, 1}
-    CUtensorMap tmSfb;        // weight scale atoms, the same
+    const uint8_t *sfa;       // activation scale atoms [rows_cap/128][Kin/128][512]
+    const uint8_t *sfb;       // weight scale atoms [E_local * ceil(Nw/128)][Kin/128][512]
     uint8_t *act_codes;       // MODE 1 out: [rows_cap, Nw/2]
     uint8_t *act_sf;          // MODE 1 out: atoms [rows_cap/128][(Nw/2)/128][512]
     void *out;                // MODE 3 out: 16-bit [rows, Nw]
@@ -52,6 +53,7 @@ struct MoePairParams {
     uint64_t combine_off;      // MODE 2: bf16 [m*topK, Nw] combine buffer inside every heap
     int world, rank_base, n_local, ctas_per_rank;      // ctas_per_rank is even
     int Kin, Nw;
+    int rows_cap;              // rows of the activation buffer (a multiple of 128)
     int experts, experts_per_rank;
     int counter_slot;          // MoeMeta::done_counter / tile_queue slot of this launch
     uint32_t epoch;
@@ -81,15 +83,14 @@ struct MoePairTile {
 };
 
 template <int MODE, typename TOut, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMoePairThreads, 1)
     moe_pair_gemm_kernel(const __grid_constant__ MoePairParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
     uint8_t *smem_b = smem_a + kMoePStages * kMxPA;
-    uint8_t *smem_sf = smem_b + kMoePStages * kMxPB;
-    uint8_t *smem_side = smem_sf + kMoePStages * kMoePSf;
-    MoePairSmem *sh = reinterpret_cast<MoePairSmem *>(smem_side + kMoeSideBytes);
+    uint8_t *smem_side = smem_b + kMoePStages * kMxPB;
+    MoePairSmem *sh = reinterpret_cast<MoePairSmem *>(smem_side + kMoePairSideBytes);
     static_assert(sizeof(MoePairSmem) <= 1024, "barrier block outgrew its budget");
 
     const int warp = threadIdx.x >> 5;
@@ -110,11 +111,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMoePStages; ++s) {
-            mbar_init(&sh->full[s], 2);
+            mbar_init(&sh->full[s], 2 + 8);      // two producers (with their bytes) + the pair's eight scale-factor warps
             mbar_init(&sh->empty[s], 1);
         }
         mbar_init(&sh->tmem_full, 1);
-        mbar_init(&sh->tmem_empty, 8);
+        mbar_init(&sh->tmem_empty, 16);         // eight epilogue warps in each CTA of the pair
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
         tq_init(&sh->tq);
@@ -130,8 +131,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         mbar_init_fence();
         prefetch_tensormap(&ra.tmA);
         prefetch_tensormap(&ra.tmB);
-        prefetch_tensormap(&ra.tmSfa);
-        prefetch_tensormap(&ra.tmSfb);
     }
     if (warp == 1) {
         tmem_alloc_pair(&sh->tmem_base, 512);
@@ -142,7 +141,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     cluster_sync();
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
-    const uint32_t tmem_sf0 = tmem_base + BN;      // four sets of 4 (A) + 8 (B) scale columns, used in turn
+    const uint32_t tmem_sf0 = tmem_base + BN;      // 4 (A) + 8 (B) scale columns per pipeline stage, written by warps 8-11
     const int num_tiles = sh->pprefix[EL] * n_tiles;
 
     WaitCtl ctl;
@@ -165,6 +164,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     };
 
     if (warp == 0) {
+        // --------------------------------------- tile queue (leader, lane 1) ----
+        if (lane == 1 && cr == 0) {
+            int *const counters = meta->tile_queue[p.counter_slot & 1];
+            bool ok = true;
+            for (uint32_t seq = 0; ok; ++seq) {
+                uint32_t tq;
+                if (!(ok = tq_claim(&sh->tq, seq, pair, pairs, num_tiles, counters, ctl, tq)) || tq == kTileEnd) break;
+            }
+            if (!ok) tq_publish_end(&sh->tq);
+        }
         // ------------------------------------------------------------ TMA producer ----
         if (lane == 0) {
             uint32_t it = 0;
@@ -185,23 +194,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     n1 = n0 + 128;
                 }
                 const int n_mine = cr == 0 ? n0 : n1;
-                const int sfa_atom0 = (tl.row0 >> 7) * kblocks;
-                const int sfb_atom0 = (tl.le * nb128 + (n0 >> 7)) * kblocks, sfb_atom1 = (tl.le * nb128 + (n1 >> 7)) * kblocks;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % kMoePStages;
                     const uint32_t ph = (it / kMoePStages) & 1;
                     if (!(ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY))) break;
                     const uint32_t full_leader = mapa_cluster(smem_u32(&sh->full[st]), 0);
-                    uint8_t *ssf = smem_sf + st * kMoePSf;
-                    mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB + kMoePSf);
+                    mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB);
                     tma_load_2d_pair(smem_a + st * kMxPA, &ra.tmA, full_leader, kb * MX_BK, tl.row0);
                     if (B_MN)
                         tma_load_3d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, n_mine, kb * MX_BK, tl.le);
                     else
                         tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, kb * MX_BK, tl.le * p.Nw + n_mine);
-                    tma_load_2d_pair(ssf, &ra.tmSfa, full_leader, 0, sfa_atom0 + kb);
-                    tma_load_2d_pair(ssf + 512, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb);
-                    tma_load_2d_pair(ssf + 1024, &ra.tmSfb, full_leader, 0, sfb_atom1 + kb);
                 }
             }
             if (!ok) {
@@ -226,12 +229,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + st * kMxPA);
                     const uint32_t b_addr = smem_u32(smem_b + st * kMxPB);
-                    const uint32_t sf_addr = smem_u32(smem_sf + st * kMoePSf);
-                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * 16u;
+                    const uint32_t tmem_sfa = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols;
                     const uint32_t tmem_sfb = tmem_sfa + 4;
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));
 #pragma unroll
                     for (int k = 0; k < MX_BK / 32; ++k) {
                         const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
@@ -256,9 +255,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 }
             }
         }
-    } else if (warp < 6) {
+    } else if (warp < 10) {
         // ---------------------------------------------------------------- epilogue ----
+        // Eight warps: warp w drains TMEM lane quarter w % 4 (32 rows) and column half (w - 2) / 4 of the
+        // accumulator, so a row's epilogue arithmetic is shared by two warps on different schedulers.
         const int q = warp & 3;
+        const int ch = (warp - 2) >> 2;
         const int row_in_tile = q * 32 + lane;
         uint32_t tcount = 0;
         bool ok = true;
@@ -271,29 +273,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             tc_fence_after();
             const bool row_ok = row_in_tile < tl.rows;
             const int row = tl.row0 + row_in_tile;
+            const uint32_t lane_field = static_cast<uint32_t>(q * 32) << 16;
             if (MODE == 1) {
-                // Both halves leave TMEM at once, rounded to bf16 as the golden rounds the up projection, and the
-                // accumulator is handed back before any of the SwiGLU / quantisation arithmetic: that arithmetic
-                // (about as long as a tile's main loop on one warp per scheduler) then overlaps the next tile.
-                uint32_t act[64], gate[64];
+                // This warp's 64 act columns and the 64 gate columns that go with them leave TMEM at once, rounded
+                // to bf16 as the golden rounds the up projection, and the accumulator is handed back before any of
+                // the SwiGLU / quantisation arithmetic, which then overlaps the next tile's main loop.
+                uint32_t act[32], gate[32];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                    const int col = (c < 2) ? ch * 64 + c * 32 : 128 + ch * 64 + (c - 2) * 32;
+                    tmem_ld_32x32(tmem_base + col + lane_field, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint32_t pk2 = Pack2<__nv_bfloat16>::pack(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                        if (c < 4) act[c * 16 + i] = pk2; else gate[(c - 4) * 16 + i] = pk2;
+                        if (c < 2) act[c * 16 + i] = pk2; else gate[(c - 2) * 16 + i] = pk2;
                     }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
-                uint32_t scale_word = 0;
+                uint32_t scale_half = 0;
                 const int half_n = p.Nw / 2;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 2; ++c) {
                     uint32_t ypk[16];            // y rounded to bf16, two per word
                     uint32_t am = 0;
 #pragma unroll
@@ -314,7 +318,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         sb = e8 - 8u;
                         inv = __uint_as_float((262u - e8) << 23);
                     }
-                    scale_word |= sb << (8 * c);
+                    scale_half |= sb << (8 * c);
                     uint32_t code[8];
                     if (am <= 0x7F80u) {
                         // no NaN in the chunk: two values per conversion
@@ -343,26 +347,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         }
                     }
                     if (row_ok) {
-                        uint8_t *dst = ra.act_codes + static_cast<size_t>(row) * half_n + tl.ni * 128 + c * 32;
+                        uint8_t *dst = ra.act_codes + static_cast<size_t>(row) * half_n + tl.ni * 128 + ch * 64 + c * 32;
                         *reinterpret_cast<uint4 *>(dst) = make_uint4(code[0], code[1], code[2], code[3]);
                         *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(code[4], code[5], code[6], code[7]);
                     }
                 }
-                // the tile's 128 output columns are 4 k-blocks of the down projection = one atom column group;
-                // rows past the expert's count get the neutral scale so that stale bytes never reach the MMA.
-                // An empty half beyond the expert's last 128-row tile belongs to the next expert: left alone.
+                // the tile's 128 output columns are 4 k-blocks of the down projection = one 4-byte atom entry per row,
+                // of which this warp owns two bytes; rows past the expert's count get the neutral scale so that stale
+                // bytes never reach the MMA.  An empty half beyond the expert's last 128-row tile is left alone.
                 if (tl.rows > 0) {
                     const int kb4_2 = (half_n + 127) / 128;
                     uint8_t *sfdst = ra.act_sf + (static_cast<size_t>(row >> 7) * kb4_2 + tl.ni) * 512 + (row & 31) * 16 +
-                                     ((row >> 5) & 3) * 4;
-                    *reinterpret_cast<uint32_t *>(sfdst) = row_ok ? scale_word : 0x7F7F7F7Fu;
+                                     ((row >> 5) & 3) * 4 + ch * 2;
+                    *reinterpret_cast<uint16_t *>(sfdst) = static_cast<uint16_t>(row_ok ? scale_half : 0x7F7Fu);
                 }
             } else {
-                uint32_t pk[BN / 2];
+                // this warp's 128 columns, packed to the output type; then the accumulator goes back
+                uint32_t pk[64];
 #pragma unroll
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
+                    tmem_ld_32x32(tmem_base + ch * 128 + c * 32 + lane_field, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
@@ -371,14 +376,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->tmem_empty), 0));
-                const int col0 = tl.ni * BN;
+                const int col0 = tl.ni * BN + ch * 128;
                 const int w = tl.mi * BM + row_in_tile;              // row inside the expert
                 if (MODE == 3) {
                     // receive order without padding: rows of the experts before this one, then w
                     if (row_ok) {
                         TOut *dst = static_cast<TOut *>(ra.out) + static_cast<size_t>(sh->uprefix[tl.le] + w) * p.Nw + col0;
 #pragma unroll
-                        for (int g = 0; g < BN / 8; ++g)
+                        for (int g = 0; g < 16; ++g)
                             if (col0 + g * 8 < p.Nw)
                                 *reinterpret_cast<uint4 *>(dst + g * 8) =
                                     make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
@@ -393,9 +398,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         const int drow = meta->prefix_all[src][e] + (w - meta->cum_src[src][tl.le]);
                         dst = reinterpret_cast<TOut *>(p.heap_base[src] + p.combine_off) + static_cast<size_t>(drow) * p.Nw + col0;
                     }
-                    uint8_t *my_row = smem_side + row_in_tile * 128;
+                    // 128-byte pieces of the row through this thread's own staging slot (one per column half)
+                    uint8_t *my_row = smem_side + (ch * BM + row_in_tile) * 128;
 #pragma unroll
-                    for (int h = 0; h < 4; ++h) {
+                    for (int h = 0; h < 2; ++h) {
                         bulk_wait_read<0>();
 #pragma unroll
                         for (int g = 0; g < 8; ++g)
@@ -417,16 +423,77 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             bulk_wait<0>();
             fence_proxy_async_global();
         }
-    } else if (warp == 6) {
-        // -------------------------------------------------------------- tile queue ----
-        if (cr == 0 && lane == 0) {
-            int *const counters = meta->tile_queue[p.counter_slot & 1];
-            bool ok = true;
-            for (uint32_t seq = 0; ok; ++seq) {
-                uint32_t tq;
-                if (!(ok = tq_claim(&sh->tq, seq, pair, pairs, num_tiles, counters, ctl, tq)) || tq == kTileEnd) break;
+    } else {
+        // ---------------------------------------------------------- scale factors ----
+        // Warps 10-13 own TMEM lane quarters 2, 3, 0, 1 (a warp reaches the quarter warp % 4).  Per pipeline stage every lane reads its 16-byte row of the
+        // activation atom and of the two weight atoms from global memory (512 contiguous bytes per atom: one
+        // coalesced request per warp) and stores them into the stage's scale columns with tcgen05.st; the
+        // stage's "full" barrier in the leader counts these eight warps of the pair next to the operand loads.
+        const uint32_t lane_field = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint8_t *sfa_all = reinterpret_cast<const uint8_t *>(ra.sfa), *sfb_all = reinterpret_cast<const uint8_t *>(ra.sfb);
+        uint32_t it = 0;
+        bool ok = true;
+        int le_hint = 0;
+        for (uint32_t seq = 0; ok; ++seq) {
+            uint32_t tq = 0;
+            if (lane == 0) ok = tq_get(&sh->tq, seq, tq, ctl);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            tq = __shfl_sync(0xffffffffu, tq, 0);
+            if (!ok || tq == kTileEnd) break;
+            const MoePairTile tl = decode(static_cast<int>(tq), le_hint);
+            int n0, n1;
+            if (MODE == 1) {
+                n0 = tl.ni * 128;
+                n1 = n0 + p.Nw / 2;
+            } else {
+                n0 = tl.ni * BN;
+                n1 = n0 + 128;
             }
-            if (!ok) tq_publish_end(&sh->tq);
+            const uint8_t *sfa = sfa_all + static_cast<size_t>(tl.row0 >> 7) * kblocks * 512 + lane * 16;
+            const uint8_t *sfb0 = sfb_all + static_cast<size_t>(tl.le * nb128 + (n0 >> 7)) * kblocks * 512 + lane * 16;
+            const uint8_t *sfb1 = (n1 < p.Nw) ? sfb_all + static_cast<size_t>(tl.le * nb128 + (n1 >> 7)) * kblocks * 512 + lane * 16 : sfb0;
+            // an empty half past the receive buffer has no atoms of its own: any valid ones do (rows are masked)
+            if (tl.row0 >= p.rows_cap) sfa = sfa_all + lane * 16;
+            // the atoms of the next kSfAhead K-steps are kept in flight (an L2 round trip is longer than a K-step)
+            constexpr int kSfAhead = 4;
+            uint4 va[kSfAhead], vb0[kSfAhead], vb1[kSfAhead];
+#pragma unroll
+            for (int d = 0; d < kSfAhead; ++d) {
+                const int kk = d < kblocks ? d : kblocks - 1;
+                va[d] = *reinterpret_cast<const uint4 *>(sfa + static_cast<size_t>(kk) * 512);
+                vb0[d] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + static_cast<size_t>(kk) * 512));
+                vb1[d] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + static_cast<size_t>(kk) * 512));
+            }
+            for (int kb0 = 0; kb0 < kblocks && ok; kb0 += kSfAhead) {
+#pragma unroll
+                for (int d = 0; d < kSfAhead; ++d) {
+                    const int kb = kb0 + d;
+                    if (kb >= kblocks) break;
+                    const int st = it % kMoePStages;
+                    const uint32_t ph = (it / kMoePStages) & 1;
+                    ++it;
+                    const uint4 a = va[d], b0 = vb0[d], b1 = vb1[d];
+                    {
+                        const int kk = kb + kSfAhead < kblocks ? kb + kSfAhead : kblocks - 1;
+                        va[d] = *reinterpret_cast<const uint4 *>(sfa + static_cast<size_t>(kk) * 512);
+                        vb0[d] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + static_cast<size_t>(kk) * 512));
+                        vb1[d] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + static_cast<size_t>(kk) * 512));
+                    }
+                    // the MMAs that read this stage's scale columns one round ago have finished
+                    if (lane == 0) ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols + lane_field;
+                    tmem_st_32x4(col, a);
+                    tmem_st_32x4(col + 4, b0);
+                    tmem_st_32x4(col + 8, b1);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->full[st]), 0));
+                }
+            }
         }
     }
 

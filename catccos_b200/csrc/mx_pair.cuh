@@ -282,25 +282,45 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
             const uint8_t *sfb0 = ra.sfb + static_cast<size_t>(ni * 2) * kb4 * 512 + lane * 16;
             const bool second_b_atom = (ni * BN + 128) < p.N;
             const uint8_t *sfb1 = second_b_atom ? sfb0 + static_cast<size_t>(kb4) * 512 : sfb0;
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                const int st = it % kMxPStages;
-                const uint32_t ph = (it / kMxPStages) & 1;
-                const uint4 va = __ldg(reinterpret_cast<const uint4 *>(sfa + static_cast<size_t>(kb) * 512));
-                const uint4 vb0 = __ldg(reinterpret_cast<const uint4 *>(sfb0 + static_cast<size_t>(kb) * 512));
-                const uint4 vb1 = __ldg(reinterpret_cast<const uint4 *>(sfb1 + static_cast<size_t>(kb) * 512));
-                // the MMAs that read this stage's scale columns six K-steps ago have finished
-                if (lane == 0) ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols + lane_field;
-                tmem_st_32x4(col, va);
-                tmem_st_32x4(col + 4, vb0);
-                tmem_st_32x4(col + 8, vb1);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->full[st]), 0));
+            // the atoms of the next kSfAhead K-steps are kept in flight (an L2 round trip is longer than a K-step)
+            constexpr int kSfAhead = 4;
+            uint4 va[kSfAhead], vb0[kSfAhead], vb1[kSfAhead];
+#pragma unroll
+            for (int d = 0; d < kSfAhead; ++d) {
+                const int kk = d < kblocks ? d : kblocks - 1;
+                va[d] = __ldg(reinterpret_cast<const uint4 *>(sfa + static_cast<size_t>(kk) * 512));
+                vb0[d] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + static_cast<size_t>(kk) * 512));
+                vb1[d] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + static_cast<size_t>(kk) * 512));
+            }
+            for (int kb0 = 0; kb0 < kblocks && ok; kb0 += kSfAhead) {
+#pragma unroll
+                for (int d = 0; d < kSfAhead; ++d) {
+                    const int kb = kb0 + d;
+                    if (kb >= kblocks) break;
+                    const int st = it % kMxPStages;
+                    const uint32_t ph = (it / kMxPStages) & 1;
+                    ++it;
+                    const uint4 a = va[d], b0 = vb0[d], b1 = vb1[d];
+                    {
+                        const int kk = kb + kSfAhead < kblocks ? kb + kSfAhead : kblocks - 1;
+                        va[d] = __ldg(reinterpret_cast<const uint4 *>(sfa + static_cast<size_t>(kk) * 512));
+                        vb0[d] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + static_cast<size_t>(kk) * 512));
+                        vb1[d] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + static_cast<size_t>(kk) * 512));
+                    }
+                    // the MMAs that read this stage's scale columns one round ago have finished
+                    if (lane == 0) ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols + lane_field;
+                    tmem_st_32x4(col, a);
+                    tmem_st_32x4(col + 4, b0);
+                    tmem_st_32x4(col + 8, b1);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->full[st]), 0));
+                }
             }
         }
     } else {
