@@ -169,6 +169,39 @@ int launch_moe_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params,
                                            static_cast<int>(tiling->expertNum));
 }
 
+// Standalone MXFP8 AllToAllV-GroupedMatmul (op 0) / GroupedMatmul-AllToAllV (op 1): KernelParams as set by the
+// examples' operator classes (examples/ascend950_fp8_mx_alltoallv_grouped_matmul/..._host.h:118):
+// SetKernelParams(a, b, c, aScale, bScale, localTokensPerExpert, globalTokensPerLocalExpert).
+int launch_a2av_abi(int op, int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
+                    uint8_t **workspaces, uint8_t *symmetric, CocTilingParams *tiling) {
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    Team *t = team();
+    const int want = t->emulated ? t->n_pes : 1;
+    if (!params || n_params != want || !workspaces) {
+        set_error("all-to-all-v grouped matmul: one parameter block and one workspace per local PE are required");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (tiling->epSize != 0 && static_cast<int>(tiling->epSize) != t->n_pes) {
+        set_error("tiling.epSize (%u) must equal the number of PEs (%d): tensor-parallel groups inside an expert group are "
+                  "not supported", tiling->epSize, t->n_pes);
+        return CATCCOS_ERR_INVALID;
+    }
+    A2avArgs args[kMaxRanks];
+    for (int i = 0; i < n_params; ++i) {
+        if (params[i].customCount < 3 || !params[i].customPtrs) {
+            set_error("all-to-all-v grouped matmul expects customPtrs = {aScale, bScale, localTokensPerExpert, "
+                      "globalTokensPerLocalExpert}");
+            return CATCCOS_ERR_INVALID;
+        }
+        uint8_t **c = params[i].customPtrs;
+        args[i] = {params[i].ptrA, params[i].ptrB, params[i].ptrC, c[0], c[1], reinterpret_cast<const int *>(c[2]),
+                   workspaces[i]};
+    }
+    return launch_a2av(op, dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric, static_cast<int>(tiling->m),
+                       static_cast<int>(tiling->n), static_cast<int>(tiling->k), static_cast<int>(tiling->expertNum));
+}
+
 int launch_mxq_ag_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params, uint8_t *symmetric,
                       CocTilingParams *tiling) {
     int rc = check_tiling(tiling);
@@ -498,6 +531,11 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
                                      static_cast<int>(tiling->k));
     if (commType == CATCCOS_MX_QUANT_ALLGATHER)
         return mxq_allgather_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n));
+    if ((commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
+         commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && tiling->expertNum > 0)
+        return a2av_symmetric_bytes(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, world,
+                                    static_cast<int>(tiling->m), static_cast<int>(tiling->n), static_cast<int>(tiling->k),
+                                    static_cast<int>(tiling->expertNum));
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0)
         return moe_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->k),
                                    static_cast<int>(tiling->n), static_cast<int>(tiling->topK),
@@ -510,6 +548,13 @@ size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTili
                    commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER))
         return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
+    if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
+                   commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && tiling->expertNum > 0) {
+        const int world = tiling->rankSize ? static_cast<int>(tiling->rankSize) : (team() ? team()->n_pes : 1);
+        return a2av_workspace_bytes(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, world,
+                                    static_cast<int>(tiling->m), static_cast<int>(tiling->n), static_cast<int>(tiling->k),
+                                    static_cast<int>(tiling->expertNum));
+    }
     if (tiling && commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0) {
         const int world = tiling->rankSize ? static_cast<int>(tiling->rankSize) : (team() ? team()->n_pes : 1);
         return moe_workspace_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->k),
@@ -557,6 +602,19 @@ MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterBF16, CATCCOS_BF16, 1)
 MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterFP16, CATCCOS_FP16, 0)
 MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterBF16, CATCCOS_BF16, 0)
 
+#define A2AV_LAUNCH(name, op, dtype)                                                                           \
+    int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
+             uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
+        (void)fftsAddr;                                                                                          \
+        (void)transA;                                                                                            \
+        (void)transB;                                                                                            \
+        return launch_a2av_abi(op, dtype, stream, blockNum, params, 1, &workspace, symmetric, tiling);           \
+    }
+A2AV_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulFP16, 0, CATCCOS_FP16)
+A2AV_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulBF16, 0, CATCCOS_BF16)
+A2AV_LAUNCH(LaunchAscend950Fp8MxGroupedMatmulAllToAllVFP16, 1, CATCCOS_FP16)
+A2AV_LAUNCH(LaunchAscend950Fp8MxGroupedMatmulAllToAllVBF16, 1, CATCCOS_BF16)
+
 int LaunchAscend950BF16QuantAllGatherFP8E4M3FN(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params,
                                                uint8_t *workspace, uint8_t *symmetric, CocTilingParams *tiling,
                                                uint32_t transA, uint32_t transB) {
@@ -591,6 +649,10 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
         return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
         return launch_mxq_ag_abi(stream, blockNum, params, 1, symmetric, tiling);
+    if ((commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
+         commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_a2av_abi(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, dataType, stream, blockNum,
+                               params, 1, &workspace, symmetric, tiling);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }
@@ -616,6 +678,10 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
         return launch_moe_abi(stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
         return launch_mxq_ag_abi(stream, blockNum, params, t->n_pes, symmetric, tiling);
+    if ((commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
+         commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_a2av_abi(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, dataType, stream, blockNum,
+                               params, t->n_pes, workspaces, symmetric, tiling);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }

@@ -381,6 +381,130 @@ __global__ void __launch_bounds__(256) moe_unpermute_kernel(const MoeParams p) {
     }
 }
 
+// ---------------------------------------------- standalone all-to-all-v operators ----
+// AllToAllV-GroupedMatmul and GroupedMatmul-AllToAllV take rows that are already MXFP8 and already
+// sorted by expert, with the counts given (include/catccos/dgemm/kernel/mx_alltoallv_group_matmul.hpp:37-496,
+// grouped_matmul_alltoallv_mx.hpp:34-409).  They reuse the routing kernel (count exchange, offset
+// tables) by handing it an expert id per row, synthesised from the counts.
+
+// idx[i] = expert of row i for i < sum(counts), -1 (no row) beyond; one CTA per local rank
+__global__ void a2av_expert_idx_kernel(const MoeParams p, A2avPtrs ptrs) {
+    __shared__ int prefix[kMoeMaxExperts + 1];
+    const int lrank = blockIdx.x;
+    const int *counts = ptrs.local_tokens[lrank];
+    int *idx = const_cast<int *>(p.ranks[lrank].expert_idx);
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < p.experts; ++e) {
+            prefix[e] = run;
+            run += max(counts[e], 0);
+        }
+        prefix[p.experts] = run;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.m; i += blockDim.x) {
+        int lo = 0, hi = p.experts;                  // largest e with prefix[e] <= i
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (prefix[mid] <= i) lo = mid; else hi = mid;
+        }
+        idx[i] = i < prefix[p.experts] ? lo : -1;
+    }
+}
+
+// One warp per row: copies the row's codes and scale bytes into a receive buffer.
+//   mode 0 (dispatch): my row i (global-expert order) -> its expert owner's receive rows;
+//   mode 1 (re-layout): my row u (owner order: local expert major, source rank minor, no padding) -> my own
+//                       receive rows, whose expert segments start on multiples of 128.
+__global__ void __launch_bounds__(256) a2av_move_rows_kernel(const MoeParams p, A2avPtrs ptrs, int mode) {
+    __shared__ int abort_flag;
+    const int lrank = blockIdx.x / p.ctas_per_rank;
+    const int cta = blockIdx.x - lrank * p.ctas_per_rank;
+    const int rank = p.rank_base + lrank;
+    const int R = p.world;
+    const MoeRankArgs &ra = p.ranks[lrank];
+    const MoeMeta *meta = ra.meta;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) abort_flag = 0;
+    __syncthreads();
+    WaitCtl ctl;
+    ctl.abort_smem = &abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+    // every rank must have entered this epoch before its symmetric rows are overwritten
+    if (threadIdx.x < R && threadIdx.x != rank)
+        wait_flag_ge(mflag(p, rank, kFlagEntered + threadIdx.x), p.epoch, ctl, W_ENTERED, threadIdx.x);
+    __syncthreads();
+    const bool skip = abort_flag || meta->overflow;
+    const int K = p.K, EL = p.experts_per_rank, sld = p.lay.scale_ld;
+    const int src_sld = ptrs.scale_ld;
+    const uint8_t *codes = ptrs.codes[lrank], *scales = ptrs.scales[lrank];
+    const int rows = mode == 0 ? p.m : meta->total_rows;
+    if (!skip) {
+        for (int i = cta * 8 + warp; i < rows; i += p.ctas_per_rank * 8) {
+            int o, row;
+            if (mode == 0) {
+                const int e = ra.expert_idx[i];
+                if (e < 0) continue;
+                row = meta->dest_base[e] + (ra.expanded_row_idx[i] - meta->prefix_all[rank][e]);
+                o = e / EL;
+            } else {
+                int le = 0, before = 0;
+                while (le + 1 < EL && i >= before + meta->seg_rows[le]) before += meta->seg_rows[le++];
+                row = meta->seg_base[le] + (i - before);
+                o = rank;
+            }
+            uint8_t *dc = p.heap_base[o] + p.lay.recv_codes_off + static_cast<size_t>(row) * K;
+            uint8_t *ds = p.heap_base[o] + p.lay.recv_scale_off + static_cast<size_t>(row) * sld;
+            const uint4 *sc = reinterpret_cast<const uint4 *>(codes + static_cast<size_t>(i) * K);
+            for (int v = lane; v < K / 16; v += 32) reinterpret_cast<uint4 *>(dc)[v] = __ldg(sc + v);
+            for (int v = lane; v < sld; v += 32) ds[v] = v < src_sld ? scales[static_cast<size_t>(i) * src_sld + v] : 127;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const unsigned prev = atomicAdd(&ra.meta->done_counter[0], 1u);
+        if (prev == static_cast<unsigned>(p.ctas_per_rank) - 1u) {
+            fence_sys();
+            if (mode == 0) {
+                for (int o = 0; o < R; ++o) st_release_sys(mflag(p, o, kMoeFlagDispatch + rank), p.epoch);
+            } else {
+                st_release_sys(mflag(p, rank, kMoeFlagDispatch + rank), p.epoch);
+            }
+        }
+    }
+}
+
+// GroupedMatmul-AllToAllV, last step: my rows have come back into my combine buffer (16-bit, in my
+// expert-sorted order); copy them to the caller's output once every owner has flagged completion.
+__global__ void __launch_bounds__(256) a2av_copy_out_kernel(const MoeParams p, int n_cols) {
+    __shared__ int abort_flag;
+    const int lrank = blockIdx.x / p.ctas_per_rank;
+    const int cta = blockIdx.x - lrank * p.ctas_per_rank;
+    const int rank = p.rank_base + lrank;
+    const MoeRankArgs &ra = p.ranks[lrank];
+    if (threadIdx.x == 0) abort_flag = 0;
+    __syncthreads();
+    WaitCtl ctl;
+    ctl.abort_smem = &abort_flag;
+    ctl.status = p.status;
+    ctl.deadline_ns = globaltimer_ns() + p.timeout_ns;
+    ctl.rank = rank;
+    if (threadIdx.x < p.world)
+        wait_flag_ge(mflag(p, rank, kMoeFlagCombine + threadIdx.x), p.epoch, ctl, W_MOE_COMBINE, threadIdx.x);
+    __syncthreads();
+    if (abort_flag || ra.meta->overflow) return;
+    int mine = 0;
+    for (int e = 0; e < p.experts; ++e) mine += ra.meta->counts_all[rank][e];
+    const size_t vecs = static_cast<size_t>(mine) * n_cols / 8;
+    const uint4 *src = reinterpret_cast<const uint4 *>(p.heap_base[rank] + p.lay.combine_off);
+    uint4 *dst = reinterpret_cast<uint4 *>(ra.out);
+    for (size_t v = static_cast<size_t>(cta) * blockDim.x + threadIdx.x; v < vecs; v += static_cast<size_t>(p.ctas_per_rank) * blockDim.x)
+        dst[v] = src[v];
+}
+
 // One CTA per rank: returns once every rank's dispatch rows have landed in my receive buffer.
 __global__ void moe_wait_dispatch_kernel(const MoeParams p) {
     __shared__ int abort_flag;
@@ -456,6 +580,37 @@ static int launch_wide(K kern, const MoeParams &p, int threads, int ctas_per_sm,
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_error("%s launch failed: %s", name, cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+int a2av_launch_expert_idx(const MoeParams &p, const A2avPtrs &ptrs, cudaStream_t stream) {
+    a2av_expert_idx_kernel<<<p.n_local, 256, 0, stream>>>(p, ptrs);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("a2av_expert_idx_kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+int a2av_launch_move_rows(const MoeParams &p, const A2avPtrs &ptrs, int mode, cudaStream_t stream) {
+    MoeParams q = p;
+    q.ctas_per_rank = p.ctas_per_rank * 4;
+    a2av_move_rows_kernel<<<q.ctas_per_rank * q.n_local, 256, 0, stream>>>(q, ptrs, mode);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("a2av_move_rows_kernel launch failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+int a2av_launch_copy_out(const MoeParams &p, int n_cols, cudaStream_t stream) {
+    MoeParams q = p;
+    q.ctas_per_rank = p.ctas_per_rank * 4;
+    a2av_copy_out_kernel<<<q.ctas_per_rank * q.n_local, 256, 0, stream>>>(q, n_cols);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("a2av_copy_out_kernel launch failed: %s", cudaGetErrorString(e));
         return CATCCOS_ERR_CUDA;
     }
     return CATCCOS_OK;

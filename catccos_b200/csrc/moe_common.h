@@ -55,6 +55,14 @@ struct MoeLayout {
     int scale_ld;              // even(K/32)
 };
 
+// Inputs of the standalone all-to-all-v operators, per local rank: rows that are already MXFP8.
+struct A2avPtrs {
+    const uint8_t *codes[kMaxRanks];      // e4m3 [m, K]
+    const uint8_t *scales[kMaxRanks];     // E8M0 [m, scale_ld]
+    const int *local_tokens[kMaxRanks];   // int32 [experts]: rows this rank holds per global expert
+    int scale_ld;
+};
+
 struct MoeParams {
     MoeRankArgs ranks[kMaxRanks];
     uint8_t *heap_base[kMaxRanks];

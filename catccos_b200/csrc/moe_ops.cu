@@ -312,4 +312,217 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
     return moe_launch_unpermute(p, stream);
 }
 
+// ------------------------------------------------ standalone all-to-all-v operators ----
+struct A2avSizes {
+    int rows_cap, sld, nb128;
+    size_t counts, recv_codes, recv_scale, combine;                       // symmetric
+    size_t idx, eri, meta, recv_atoms, w_atoms;                           // workspace
+};
+
+static A2avSizes a2av_sizes(int op, int world, int m, int n, int k, int experts) {
+    A2avSizes z;
+    const int el = experts / world;
+    // op 0: a rank can receive every row of every rank; op 1: the rows are already here
+    z.rows_cap = static_cast<int>(up(static_cast<size_t>(op == 0 ? world : 1) * m + static_cast<size_t>(el) * 128, 128));
+    z.sld = (k / 32 + 1) / 2 * 2;
+    z.nb128 = (n + 127) / 128;
+    z.counts = up(static_cast<size_t>(world) * experts * 4, 1024);
+    z.recv_codes = up(static_cast<size_t>(z.rows_cap) * k, 1024);
+    z.recv_scale = up(static_cast<size_t>(z.rows_cap) * z.sld, 1024);
+    // op 1: a rank gets back one row for every row it contributed, on whichever owner: up to world * m rows
+    const size_t out_rows = static_cast<size_t>(op == 1 ? world : 1) * m;
+    z.combine = op == 1 ? up(out_rows * n * 2, 1024) : 0;
+    z.idx = up(out_rows * 4, 1024);
+    z.eri = z.idx;
+    z.meta = up(sizeof(MoeMeta), 1024);
+    z.recv_atoms = up(sf_atoms_bytes(z.rows_cap, k), 1024);
+    z.w_atoms = up(static_cast<size_t>(el) * sf_atoms_bytes(z.nb128 * 128, k), 1024);
+    return z;
+}
+
+size_t a2av_symmetric_bytes(int op, int world, int m, int n, int k, int experts) {
+    if (world < 1 || experts < world || experts % world) return 0;
+    const A2avSizes z = a2av_sizes(op, world, m, n, k, experts);
+    return z.counts + z.recv_codes + z.recv_scale + z.combine;
+}
+size_t a2av_workspace_bytes(int op, int world, int m, int n, int k, int experts) {
+    if (world < 1 || experts < world || experts % world) return 0;
+    const A2avSizes z = a2av_sizes(op, world, m, n, k, experts);
+    return z.idx + z.eri + z.meta + z.recv_atoms + z.w_atoms;
+}
+
+// weights [E_local][k][n] bytes as a 3-D tensor {n, k, expert}, box {128, 128, 1}: a tile that runs past an
+// expert's k rows or n columns is zero-filled
+static int encode_b3(const DriverApi *api, CUtensorMap *tm, const void *base, uint64_t n, uint64_t k, uint64_t el) {
+    cuuint64_t dims[3] = {n, k, el};
+    cuuint64_t strides[2] = {n, n * k};
+    cuuint32_t box[3] = {128, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = api->TensorMapEncodeTiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides,
+                                           box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (grouped weights) failed: %d", static_cast<int>(r));
+        return CATCCOS_ERR_CUDA;
+    }
+    return CATCCOS_OK;
+}
+
+int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, const A2avArgs *args, void *symmetric,
+                int m, int n, int k, int experts) {
+    Team *t = team();
+    if (!t) {
+        set_error("symmetric heap not initialised (call catccos_shmem_init first)");
+        return CATCCOS_ERR_NOT_INIT;
+    }
+    std::string why;
+    const DriverApi *api = driver_api(&why);
+    if (!api) {
+        set_error("CUDA driver unavailable: %s", why.c_str());
+        return CATCCOS_ERR_CUDA;
+    }
+    const int R = t->n_pes;
+    if ((op != 0 && op != 1) || (out_dtype != CATCCOS_FP16 && out_dtype != CATCCOS_BF16)) {
+        set_error("all-to-all-v grouped matmul: op %d / output type %d not supported (FP16 or BF16)", op, out_dtype);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (m <= 0 || n <= 0 || k <= 0 || (k % 64) != 0 || (n % 16) != 0) {
+        set_error("all-to-all-v grouped matmul requires k %% 64 == 0 and n %% 16 == 0 (m=%d n=%d k=%d)", m, n, k);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (experts <= 0 || experts % R != 0 || experts > kMoeMaxExperts || experts / R > kMoeMaxLocalExperts) {
+        set_error("unsupported expert setup: experts=%d (max %d, divisible by world %d, at most %d per rank)", experts,
+                  kMoeMaxExperts, R, kMoeMaxLocalExperts);
+        return CATCCOS_ERR_INVALID;
+    }
+    const int el = experts / R;
+    const int n_local = t->emulated ? R : 1;
+    const A2avSizes z = a2av_sizes(op, R, m, n, k, experts);
+    const size_t need = z.counts + z.recv_codes + z.recv_scale + z.combine;
+    uint8_t *sp = static_cast<uint8_t *>(symmetric);
+    uint8_t *hb = t->base[t->my_pe];
+    if (sp == nullptr || sp < hb + kFlagBytes || sp + need > hb + t->heap_bytes || ((sp - hb) % 1024) != 0) {
+        set_error("symmetric buffer %p (+%zu bytes) is not a 1024-aligned range of the symmetric heap", symmetric, need);
+        return CATCCOS_ERR_INVALID;
+    }
+    const uint64_t off0 = static_cast<uint64_t>(sp - hb);
+    int per_rank = t->num_sms / n_local;
+    if (block_num > 0 && static_cast<int>(block_num) < per_rank) per_rank = static_cast<int>(block_num);
+    if (per_rank < 2) {
+        set_error("all-to-all-v grouped matmul needs at least 2 CTAs per rank");
+        return CATCCOS_ERR_INVALID;
+    }
+
+    MoeParams p;
+    memset(&p, 0, sizeof(p));
+    p.lay.counts_off = off0;
+    p.lay.recv_codes_off = off0 + z.counts;
+    p.lay.recv_scale_off = p.lay.recv_codes_off + z.recv_codes;
+    p.lay.combine_off = p.lay.recv_scale_off + z.recv_scale;
+    p.lay.rows_cap = z.rows_cap;
+    p.lay.scale_ld = z.sld;
+    for (int pe = 0; pe < R; ++pe) p.heap_base[pe] = t->base[pe];
+    p.world = R;
+    p.rank_base = t->emulated ? 0 : t->my_pe;
+    p.n_local = n_local;
+    p.ctas_per_rank = per_rank;
+    p.m = op == 1 ? R * m : m;            // rows the routing kernel walks: this rank's row list
+    p.K = k;
+    p.N = n;
+    p.top_k = 1;
+    p.experts = experts;
+    p.experts_per_rank = el;
+    p.epoch = ++t->epoch;
+    p.timeout_ns = t->timeout_ns;
+    p.status = t->status_dev;
+
+    static thread_local MoePairParams q;
+    memset(&q, 0, sizeof(q));
+    for (int pe = 0; pe < R; ++pe) q.heap_base[pe] = t->base[pe];
+    q.combine_off = p.lay.combine_off;
+    q.world = R;
+    q.rank_base = p.rank_base;
+    q.n_local = n_local;
+    q.ctas_per_rank = per_rank & ~1;
+    q.rows_cap = z.rows_cap;
+    q.experts = experts;
+    q.experts_per_rank = el;
+    q.epoch = p.epoch;
+    q.timeout_ns = p.timeout_ns;
+    q.status = p.status;
+    q.Kin = k;
+    q.Nw = n;
+    q.counter_slot = 2;
+
+    A2avPtrs ptrs;
+    memset(&ptrs, 0, sizeof(ptrs));
+    ptrs.scale_ld = k / 32;
+    uint8_t *w_atoms[kMaxRanks], *recv_atoms[kMaxRanks];
+    for (int l = 0; l < n_local; ++l) {
+        const A2avArgs &a = args[l];
+        if (!a.a || !a.b || !a.c || !a.a_scale || !a.b_scale || !a.local_tokens || !a.workspace ||
+            (reinterpret_cast<uintptr_t>(a.a) & 15) || (reinterpret_cast<uintptr_t>(a.b) & 15) ||
+            (reinterpret_cast<uintptr_t>(a.c) & 15) || (reinterpret_cast<uintptr_t>(a.workspace) & 255)) {
+            set_error("all-to-all-v grouped matmul: every operand must be non-null; tensors 16-byte, workspace 256-byte aligned");
+            return CATCCOS_ERR_INVALID;
+        }
+        uint8_t *w = a.workspace;
+        MoeRankArgs &ra = p.ranks[l];
+        ra.expert_idx = reinterpret_cast<int *>(w);
+        w += z.idx;
+        ra.expanded_row_idx = reinterpret_cast<int *>(w);
+        w += z.eri;
+        ra.meta = reinterpret_cast<MoeMeta *>(w);
+        w += z.meta;
+        recv_atoms[l] = w;
+        w += z.recv_atoms;
+        w_atoms[l] = w;
+        ra.out = a.c;
+        ptrs.codes[l] = a.a;
+        ptrs.scales[l] = a.a_scale;
+        ptrs.local_tokens[l] = a.local_tokens;
+        const int pe = t->emulated ? l : t->my_pe;
+        MoePairRankArgs &r = q.ranks[l];
+        int rc;
+        if ((rc = encode_u8(api, &r.tmA, t->base[pe] + p.lay.recv_codes_off, k, z.rows_cap))) return rc;
+        if ((rc = encode_b3(api, &r.tmB, a.b, n, k, el))) return rc;
+        r.sfa = recv_atoms[l];
+        r.sfb = w_atoms[l];
+        r.out = a.c;
+        r.meta = ra.meta;
+    }
+
+    int rc;
+    if ((rc = a2av_launch_expert_idx(p, ptrs, stream))) return rc;
+    if ((rc = moe_launch_route(p, stream))) return rc;
+    if ((rc = a2av_launch_move_rows(p, ptrs, op, stream))) return rc;
+    // weight scales [k/64, n, 2] of every local expert -> atoms, each expert padded to whole 128-row atoms
+    const size_t expert_atoms = sf_atoms_bytes(z.nb128 * 128, k);
+    for (int l = 0; l < n_local; ++l)
+        for (int e = 0; e < el; ++e)
+            if ((rc = sf_to_atoms_launch(stream, args[l].b_scale + static_cast<size_t>(e) * (k / 64) * n * 2, 1, n, k / 32, 0,
+                                         w_atoms[l] + e * expert_atoms)))
+                return rc;
+    if (op == 0 && (rc = moe_launch_wait_dispatch(p, stream))) return rc;
+    for (int l = 0; l < n_local; ++l) {
+        const int pe = t->emulated ? l : t->my_pe;
+        if ((rc = sf_to_atoms_launch(stream, t->base[pe] + p.lay.recv_scale_off, 0, z.rows_cap, k / 32, z.sld, recv_atoms[l])))
+            return rc;
+        {
+            // the output has room for world * m rows (as the reference's buffer); rows beyond the real count are zero
+            cudaError_t e = cudaMemsetAsync(args[l].c, 0, static_cast<size_t>(R) * m * n * 2, stream);
+            if (e != cudaSuccess) {
+                set_error("cudaMemsetAsync failed: %s", cudaGetErrorString(e));
+                return CATCCOS_ERR_CUDA;
+            }
+        }
+    }
+    const bool bf16 = out_dtype == CATCCOS_BF16;
+    if (op == 0)
+        return bf16 ? launch_pair_gemm<3, __nv_bfloat16, true>(q, stream) : launch_pair_gemm<3, __half, true>(q, stream);
+    rc = bf16 ? launch_pair_gemm<2, __nv_bfloat16, true>(q, stream) : launch_pair_gemm<2, __half, true>(q, stream);
+    if (rc) return rc;
+    return a2av_launch_copy_out(p, n, stream);
+}
+
 }  // namespace cb

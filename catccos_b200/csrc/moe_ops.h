@@ -24,7 +24,26 @@ size_t moe_workspace_bytes(int world, int m, int k, int n, int top_k, int expert
 int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, const MoeArgs *args, void *symmetric,
                                     int m, int k, int n, int top_k, int experts);
 
+// Standalone MXFP8 AllToAllV-GroupedMatmul (op 0) and GroupedMatmul-AllToAllV (op 1): rows already quantised and
+// sorted by expert, weights [E_local, k, n] with scales [E_local, k/64, n, 2], 16-bit output.
+struct A2avArgs {
+    const uint8_t *a;            // e4m3 [m, k]: op 0 rows in global-expert order, op 1 rows in owner order
+    const uint8_t *b;            // e4m3 [E_local, k, n]
+    void *c;                     // [world*m, n]: op 0 received rows (owner order), op 1 returned rows (expert order); rest zero
+    const uint8_t *a_scale;      // E8M0 [m, k/64, 2]
+    const uint8_t *b_scale;      // E8M0 [E_local, k/64, n, 2]
+    const int *local_tokens;     // int32 [experts]
+    uint8_t *workspace;          // a2av_workspace_bytes()
+};
+size_t a2av_symmetric_bytes(int op, int world, int m, int n, int k, int experts);
+size_t a2av_workspace_bytes(int op, int world, int m, int n, int k, int experts);
+int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, const A2avArgs *args, void *symmetric,
+                int m, int n, int k, int experts);
+
 // kernels in moe_aux.cu
+int a2av_launch_expert_idx(const MoeParams &p, const A2avPtrs &ptrs, cudaStream_t stream);
+int a2av_launch_move_rows(const MoeParams &p, const A2avPtrs &ptrs, int mode, cudaStream_t stream);
+int a2av_launch_copy_out(const MoeParams &p, int n_cols, cudaStream_t stream);
 int moe_launch_route(const MoeParams &p, cudaStream_t stream);
 int moe_launch_dispatch(const MoeParams &p, cudaStream_t stream);
 int moe_launch_unpermute(const MoeParams &p, cudaStream_t stream);

@@ -14,6 +14,8 @@ MATMUL_REDUCE_SCATTER = 3
 MXFP8_MATMUL_REDUCE_SCATTER = 18
 FP8_MX_ALLGATHER_MATMUL = 22
 MX_QUANT_ALLGATHER = 24
+FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25
+FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27
 DISPATCH_FFN_COMBINE = 32
 FP16, BF16, FP8E4M3FN = 1, 27, 36
 

@@ -215,6 +215,25 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterBF16);
  * E8M0 scales [rankSize*m, even(n/32)], ptrC = gathered e4m3 codes [rankSize*m, n]; tiling m, n (n % 32 == 0). */
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950BF16QuantAllGatherFP8E4M3FN);
 
+/* Standalone MXFP8 AllToAllV-GroupedMatmul (include/catccos/dgemm/kernel/mx_alltoallv_group_matmul.hpp:37-496; operator
+ * "Ascend950Fp8MxAllToAllVGroupedMatmul", examples/ascend950_fp8_mx_alltoallv_grouped_matmul/..._host.h:14-156) and
+ * GroupedMatmul-AllToAllV (include/catccos/dgemm/kernel/grouped_matmul_alltoallv_mx.hpp:34-409; operator
+ * "Ascend950Fp8MxGroupedMatmulAllToAllV").  KernelParams as the operator classes set them: ptrA = float8_e4m3fn rows
+ * [m, k], ptrB = weights [expertNum/epSize, k, n], ptrC = 16-bit output with room for [rankSize*m, n],
+ * customPtrs = {aScale [m, k/64, 2], bScale [expertNum/epSize, k/64, n, 2], localTokensPerExpert int32 [expertNum],
+ * globalTokensPerLocalExpert int32 [rankSize, expertNum/epSize] (not read: the counts are exchanged on the device)}.
+ *   AllToAllV-GroupedMatmul: this rank's rows are grouped by global expert with localTokensPerExpert rows each;
+ *     every row goes to its expert's owner, which multiplies it with that expert's weight; ptrC receives the
+ *     owner's rows in receive order (local expert major, source rank minor), the rest of ptrC is zero.
+ *   GroupedMatmul-AllToAllV: ptrA holds the rows of this rank's experts in that receive order; every product row
+ *     goes back to the rank it came from, whose ptrC ends up with its rows in global-expert order.
+ * tiling: m, n, k (k % 64 == 0, n % 16 == 0), expertNum, epSize = rankSize.  `workspace` =
+ * catccos_workspace_bytes() bytes (256-byte aligned), `symmetric` = catccos_symmetric_bytes() bytes. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulBF16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxGroupedMatmulAllToAllVFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxGroupedMatmulAllToAllVBF16);
+
 /* The MoE operator: DispatchFFNCombine<...>(fftsAddr, gmA, gmB, gmBScale, gmB2, gmB2Scale, gmD, gmExpertIdx,
  * gmProbs, gmWorkSpace, gmSymmetric, CocTilingParams, ...) (examples/ascend950_dispatch_ffn_combine/
  * ascend950_dispatch_ffn_combine_device.h:617-718), with the operands in the operator class's KernelParams

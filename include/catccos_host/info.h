@@ -29,6 +29,8 @@ enum CocCommType {
     ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER,
     ASCEND950_FP8_MX_ALLGATHER_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL,
     MX_QUANT_ALLGATHER = CATCCOS_MX_QUANT_ALLGATHER,
+    ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV,
+    ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL,
     ASCEND950_DISPATCH_FFN_COMBINE = CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE,
     UNKNOWN = 36
 };
@@ -85,6 +87,8 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
         {"a5moe", ASCEND950_DISPATCH_FFN_COMBINE},
         {"mxqtag", MX_QUANT_ALLGATHER},
+        {"a5fp8gmmata", ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV},
+        {"a5fp8mxatavgmm", ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL},
     };
     return m;
 }
@@ -104,6 +108,8 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
         {ASCEND950_DISPATCH_FFN_COMBINE, "Ascend950DispatchFFNCombine"},
         {MX_QUANT_ALLGATHER, "MxQuantAllGather"},
+        {ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV, "Ascend950Fp8MxGroupedMatmulAllToAllV"},
+        {ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL, "Ascend950Fp8MxAllToAllVGroupedMatmul"},
     };
     return m;
 }

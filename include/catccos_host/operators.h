@@ -263,4 +263,52 @@ public:
 };
 REGISTER_OPERATOR("MxQuantAllGather", MxQuantAllGatherOperator);
 
+// Standalone MXFP8 AllToAllV-GroupedMatmul (examples/ascend950_fp8_mx_alltoallv_grouped_matmul/..._host.h:14-156) and
+// GroupedMatmul-AllToAllV (examples/ascend950_fp8_mx_grouped_matmul_alltoallv/..._host.h): customPtrs = {aScale,
+// bScale, localTokensPerExpert, globalTokensPerLocalExpert}; output_<rank>.bin holds [rankSize*m, n] 16-bit rows.
+class Ascend950Fp8MxAllToAllVGroupedMatmulOperator : public CatccosOperator {
+public:
+    virtual const char *AName() const { return "input_a_"; }
+    virtual const char *BName() const { return "input_b_"; }
+    virtual const char *AScaleName() const { return "input_a_scale_"; }
+    virtual const char *BScaleName() const { return "input_b_scale_"; }
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t el = t.expertNum / (t.epSize ? t.epSize : t.rankSize);
+        const size_t kb = static_cast<size_t>(t.k) / 32;
+        const size_t sizeA = static_cast<size_t>(t.m) * t.k, sizeB = el * t.k * t.n;
+        const size_t sizeC = static_cast<size_t>(t.m) * t.rankSize * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, AName(), rankId), sizeA),
+                               DeviceBufferFromFile(RankFile(dataFile, BName(), rankId), sizeB), DeviceZeros(sizeC),
+                               DeviceBufferFromFile(RankFile(dataFile, AScaleName(), rankId), t.m * kb, 127),
+                               DeviceBufferFromFile(RankFile(dataFile, BScaleName(), rankId), el * kb * t.n, 127),
+                               DeviceBufferFromFile(RankFile(dataFile, "local_tokens_per_expert_", rankId), t.expertNum * 4),
+                               DeviceBufferFromFile(RankFile(dataFile, "global_tokens_per_local_expert_", rankId),
+                                                    static_cast<size_t>(t.rankSize) * el * 4));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_" + std::to_string(rankId) + ".bin", params.ptrC,
+                                        static_cast<size_t>(t.m) * t.rankSize * t.n * 2);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &t) override { return catccos_workspace_bytes(GetActualKernelType(t), FP16, &t); }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return t.m > 0 && t.k % 64 == 0 && t.n % 16 == 0 && t.expertNum > 0 && t.expertNum % rankSize == 0 &&
+               (t.epSize == 0 || t.epSize == rankSize) && rankSize <= MAX_RANK_SIZE &&
+               catccos_symmetric_bytes(GetActualKernelType(t), FP16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950Fp8MxAllToAllVGroupedMatmul", Ascend950Fp8MxAllToAllVGroupedMatmulOperator);
+class Ascend950Fp8MxGroupedMatmulAllToAllVOperator : public Ascend950Fp8MxAllToAllVGroupedMatmulOperator {
+public:
+    const char *AName() const override { return "a_gm_"; }
+    const char *BName() const override { return "b_gm_"; }
+    const char *AScaleName() const override { return "a_scale_"; }
+    const char *BScaleName() const override { return "b_scale_"; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV; }
+};
+REGISTER_OPERATOR("Ascend950Fp8MxGroupedMatmulAllToAllV", Ascend950Fp8MxGroupedMatmulAllToAllVOperator);
+
 #endif  // CATCCOS_HOST_OPERATORS_H

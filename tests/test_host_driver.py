@@ -21,7 +21,8 @@ def test_registry_lists_every_operator_on_the_path(driver):
     out = subprocess.run([driver, "--list"], capture_output=True, text=True, check=True).stdout.split()
     assert set(out) == {"MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend950AllGatherMatmul",
                         "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
-                        "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather"}
+                        "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather",
+                        "Ascend950Fp8MxAllToAllVGroupedMatmul", "Ascend950Fp8MxGroupedMatmulAllToAllV"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
