@@ -99,6 +99,9 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
+CPU_BASELINE_SECONDS = 10.0        # timed CPU work of the cpu_baseline leg
+
+
 def workload(op, world):
     if op == "agmm":
         m_local = M_TOTAL // world
@@ -310,6 +313,18 @@ def parity_moe(wl, rank, world, x, idx_dev, probs, expert_weights, c_dev, torch)
     return _rel_err(got, gold, torch), int(toks.numel())
 
 
+def repeat_for(seconds, fn):
+    """Runs fn() (which returns (rate, cores, secs, ...)) until `seconds` of timed CPU work have accumulated;
+    returns the median rate, the cores, the total timed seconds and the number of runs."""
+    rates, total, cores, last = [], 0.0, 1, None
+    while total < seconds and len(rates) < 200:
+        last = fn()
+        rates.append(last[0])
+        cores = last[1]
+        total += last[2]
+    return statistics.median(rates), cores, total, len(rates), last
+
+
 def cpu_golden_rate(wl, sample_rows, torch):
     """Times the CPU golden (oracle port of the reference's torch fp32 matmul) on a bounded sample:
     `sample_rows` rows of the (gathered / full) A against one rank's B."""
@@ -329,6 +344,51 @@ def cpu_golden_rate(wl, sample_rows, torch):
     return flops / dt_s / 1e12, cores, dt_s
 
 
+_MX_SAMPLE = {}
+
+
+def cpu_golden_rate_mx(wl, op, torch):
+    """CPU golden of the block-scaled operators on a bounded sample: MX-dequantise the operands, fp32 matmul
+    (the reference's host golden does exactly that: gen_data_fp8_mx_allgather_matmul.py, gen_data_moe.py:546-588);
+    for the MoE one expert's up projection, SwiGLU, re-quantisation and down projection on 1024 rows."""
+    import numpy as np
+    from oracle import dense, moe, mxquant          # checker, used here only as the timed CPU baseline
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    rows, k, n = 1024, wl["k"], wl["n"]
+    key = (op, k, n)
+    if key not in _MX_SAMPLE:                      # seeded operands, quantised once (set-up, not timed)
+        rng = np.random.default_rng(5)
+        x = rng.standard_normal((rows, k)).astype(np.float32)
+        xq, xs, _ = mxquant.quantize_mx_e4m3(x, "rne")
+        w1 = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+        w1q, w1s, _ = mxquant.quantize_mx_e4m3(w1, "rne")
+        w2q = w2s = None
+        if op == "moe":
+            w2 = (rng.standard_normal((k, n // 2)) * 0.02).astype(np.float32)
+            w2q, w2s, _ = mxquant.quantize_mx_e4m3(w2, "rne")
+        _MX_SAMPLE[key] = (x, w1, xq, xs, w1q, w1s, w2q, w2s)
+    x, w1, xq, xs, w1q, w1s, w2q, w2s = _MX_SAMPLE[key]
+    dense.matmul_fp32(torch.from_numpy(x[:64]), torch.from_numpy(w1.T.copy()))       # warm the thread pool
+    t0 = time.perf_counter()
+    tn = torch.from_numpy
+    a = _dequant_e4m3_fast(tn(xq), tn(xs), torch)
+    b = _dequant_e4m3_fast(tn(w1q), tn(w1s), torch)
+    c1 = torch.matmul(a, b.t())
+    flops = 2.0 * rows * k * n
+    what = f"{rows} of {wl['c_shape'][0]} rows: MX dequantise + fp32 matmul against the full weight"
+    if op == "moe":
+        c1 = c1.to(torch.bfloat16).to(torch.float32).numpy()
+        glu = moe.swiglu_bf16(c1)
+        _, _, g_deq = mxquant.quantize_mx_e4m3(glu, "rne")
+        b2 = _dequant_e4m3_fast(tn(w2q), tn(w2s), torch)
+        torch.matmul(torch.from_numpy(g_deq), b2.t()).to(torch.bfloat16)
+        flops += 2.0 * rows * (n // 2) * k
+        what = f"{rows} of {wl['m'] * wl['top_k']} routed rows through one expert: dequantise, up projection, SwiGLU, MX quantise, down projection (fp32 matmuls)"
+    dt_s = time.perf_counter() - t0
+    return flops / dt_s / 1e12, cores, dt_s, what
+
+
 def run_reference(args, rank, world):
     """`--impl reference`: the reference's own implementation of the path is its CPU host golden
     (its device code targets Ascend NPUs and cannot be built here); rank 0 times the oracle port of
@@ -337,17 +397,31 @@ def run_reference(args, rank, world):
         return
     import torch
     wl = workload(args.op, max(world, 1))
+    if args.op in ("quant", "fp4"):
+        print(json.dumps({"impl": "reference", "unavailable": f"no reference-arm leg for --op {args.op}: the reference has "
+                          "no host golden timed for it (use --op agmm|mmrs|mmar|mxag|moe)"}), flush=True)
+        return
     rows = 1024 if args.op != "mmar" else AR_M
     vals = []
-    for _ in range(args.warmup):
-        cpu_golden_rate(wl, min(rows, 256), torch)
     cores = os.cpu_count() or 1
-    for _ in range(args.steps):
-        v, cores, _ = cpu_golden_rate(wl, rows, torch)
-        vals.append(v)
-    value = statistics.median(vals)
-    sample = f"{rows} of {wl['c_shape'][0] if args.op == 'agmm' else wl['m']} rows of A x full B, fp32 matmul, {args.steps} runs, median"
-    ms = (2.0 * rows * wl["b_shape"][0] * wl["b_shape"][1]) / (value * 1e12) * 1e3
+    if args.op in ("mxag", "moe"):
+        for _ in range(min(args.warmup, 1)):
+            cpu_golden_rate_mx(wl, args.op, torch)
+        for _ in range(args.steps):
+            v, cores, secs, sample = cpu_golden_rate_mx(wl, args.op, torch)
+            vals.append(v)
+        value = statistics.median(vals)
+        ms = secs * 1e3
+        sample += f", {args.steps} runs, median"
+    else:
+        for _ in range(args.warmup):
+            cpu_golden_rate(wl, min(rows, 256), torch)
+        for _ in range(args.steps):
+            v, cores, _ = cpu_golden_rate(wl, rows, torch)
+            vals.append(v)
+        value = statistics.median(vals)
+        sample = f"{rows} of {wl['c_shape'][0] if args.op == 'agmm' else wl['m']} rows of A x full B, fp32 matmul, {args.steps} runs, median"
+        ms = (2.0 * rows * wl["b_shape"][0] * wl["b_shape"][1]) / (value * 1e12) * 1e3
     line = {
         "impl": "reference", "metric": "fused-op TFLOP/s (whole job)", "value": value, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -464,7 +538,7 @@ def main():
             comm = rt.FP8_MX_ALLGATHER_MATMUL
             til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
             need = rt.symmetric_bytes(comm, rt.BF16, til)
-            rt.shmem_init(rank, world, max(need, 1 << 20) + (8 << 20), f"tcp://{addr}:{port}")
+            rt.shmem_init(rank, world, 2 * max(need, 1 << 20) + (8 << 20), f"tcp://{addr}:{port}")
             symm = rt.shmem_malloc(max(need, 1024))
             act = torch.randn((wl["m"], wl["k"]), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
             w = (torch.randn((wl["k"], wl["n"]), generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
@@ -494,7 +568,7 @@ def main():
             el = experts // world
             til = rt.tiling(m, k, n, world, topK=top_k, expertNum=experts, epSize=world)
             need = rt.symmetric_bytes(comm, rt.BF16, til)
-            rt.shmem_init(rank, world, need + (8 << 20), f"tcp://{addr}:{port}")
+            rt.shmem_init(rank, world, 2 * need + (8 << 20), f"tcp://{addr}:{port}")
             symm = rt.shmem_malloc(need)
             x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
             w1q = torch.empty((el, n, k), dtype=torch.uint8, device="cuda")
@@ -599,17 +673,37 @@ def main():
         barrier()
         exposed = max(0.0, (ms_per_step - compute_only_ms) / ms_per_step)
 
-    # end to end through the host-buffer entry point: H2D of A and B, fused launch, D2H of C, every step
+    # end to end through the host-buffer entry point: H2D of the step's inputs, fused launch, D2H of the result,
+    # every step.  Dense operators copy A and B; the block-scaled GEMM and the MoE keep their weights (and weight
+    # scales) resident after the first call and copy activations / routing every step.
     e2e = None
-    if not args.no_e2e and dense_op:
+    if not args.no_e2e and args.op in ("agmm", "mmrs", "mmar", "mxag", "moe"):
         numa_node = bind_to_gpu_numa_node(local_rank, torch)
-        a_p, b_p = a_h.pin_memory(), b_h.pin_memory()
-        c_p = torch.empty(wl["c_shape"], dtype=dt).pin_memory()
+        pin = lambda t_: t_.cpu().pin_memory()
+        if dense_op:
+            ins, cust, mask, e2e_dtype = [a_h.pin_memory(), b_h.pin_memory()], [], 0, dtype_code
+            per_step = [0, 1]
+            c_p = torch.empty(wl["c_shape"], dtype=dt).pin_memory()
+            resident_note = None
+        elif args.op == "mxag":
+            ins, cust, mask, e2e_dtype = [pin(a_codes), pin(b_codes)], [pin(a_scale), pin(b_scale)], (1 << 1) | (1 << 4), rt.BF16
+            per_step = [0, 2]
+            c_p = torch.empty(wl["c_shape"], dtype=torch.bfloat16).pin_memory()
+            resident_note = "weights and weight scales resident after the first call"
+        else:
+            ins, cust = [pin(x), pin(w1q)], [pin(w2q), pin(idx), pin(probs), pin(w1s), pin(w2s)]
+            mask, e2e_dtype = (1 << 1) | (1 << 3) | (1 << 6) | (1 << 7), rt.BF16
+            per_step = [0, 3, 4]
+            c_p = torch.empty(wl["c_shape"], dtype=torch.bfloat16).pin_memory()
+            resident_note = "expert weights and weight scales resident after the first call"
+        every = ins + cust
+        h2d_bytes = sum(every[i].numel() * every[i].element_size() for i in per_step)
+        cust_arr = (ctypes.c_void_p * max(len(cust), 1))(*[c_.data_ptr() for c_ in cust])
 
         def e2e_step():
-            check(lib().catccos_run_host(comm, dtype_code, 0, ctypes.c_void_p(a_p.data_ptr()),
-                                         ctypes.c_void_p(b_p.data_ptr()), ctypes.c_void_p(c_p.data_ptr()), None, 0,
-                                         ctypes.byref(til), 0, 0))
+            check(lib().catccos_run_host_resident(comm, e2e_dtype, 0, ctypes.c_void_p(ins[0].data_ptr()),
+                                                  ctypes.c_void_p(ins[1].data_ptr()), ctypes.c_void_p(c_p.data_ptr()),
+                                                  cust_arr if cust else None, len(cust), ctypes.byref(til), 0, 0, mask))
         for _ in range(3):
             e2e_step()
         barrier()
@@ -619,8 +713,10 @@ def main():
         barrier()
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         e2e = {"value": world * wl["flops"] * args.steps / e2e_s / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": a_p.numel() * 2 + b_p.numel() * 2, "d2h_bytes_per_step": c_p.numel() * 2,
+               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": c_p.numel() * 2,
                "ms_per_step": e2e_s / args.steps * 1e3, "host_numa_node": numa_node}
+        if resident_note:
+            e2e["resident"] = resident_note
         # the copy that came back must be the device result (guards against a stale host buffer)
         if not torch.equal(c_p[:64], c_d[:64].cpu()):
             raise SystemExit("end-to-end result differs from the device-resident result")
@@ -722,9 +818,14 @@ def main():
                 line["config"]["activation_quantisation"] = "inside every step" if args.mx_quant_in_step else \
                     "at set-up (operands reach the operator as MXFP8, as in the reference)"
             if world == 1 and not args.no_cpu_baseline and dense_op:
-                v, cores, secs = cpu_golden_rate(wl, 1024, torch)
+                rows_s = min(2048, wl["a_shape"][0])
+                v, cores, secs, runs, _ = repeat_for(CPU_BASELINE_SECONDS, lambda: cpu_golden_rate(wl, rows_s, torch))
                 line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                        "sample": f"1024 rows of A x full B fp32 matmul ({secs:.2f} s)"}
+                                        "sample": f"{rows_s} rows of A x full B fp32 matmul, {runs} runs, median ({secs:.1f} s of CPU work)"}
+            elif world == 1 and not args.no_cpu_baseline and args.op in ("mxag", "moe"):
+                v, cores, secs, runs, last = repeat_for(CPU_BASELINE_SECONDS, lambda: cpu_golden_rate_mx(wl, args.op, torch))
+                line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                        "sample": f"{last[3]}, {runs} runs, median ({secs:.1f} s of CPU work)"}
             print(json.dumps(line), flush=True)
 
     rt.shmem_finalize()

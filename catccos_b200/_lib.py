@@ -73,6 +73,10 @@ SIGNATURES = {
                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
                                         ctypes.c_uint32, ctypes.POINTER(CocTilingParams), ctypes.c_uint32,
                                         ctypes.c_uint32]),
+    "catccos_run_host_resident": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int32, ctypes.c_uint32, ctypes.c_void_p,
+                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                                 ctypes.c_uint32, ctypes.POINTER(CocTilingParams), ctypes.c_uint32,
+                                                 ctypes.c_uint32, ctypes.c_uint32]),
     "catccos_mx_quant": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32]),
     "catccos_sf_atoms_bytes": (ctypes.c_size_t, [ctypes.c_uint32, ctypes.c_uint32]),

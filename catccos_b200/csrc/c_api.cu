@@ -238,6 +238,13 @@ struct HostRunCache {
     cudaEvent_t landed[kHostRunChunks + 1] = {};                  // B, then every chunk of A
     cudaEvent_t done[kHostRunChunks] = {};                        // a chunk's rows of C are complete
     bool ready = false;
+    // operands of the block-scaled and MoE operators: device copy, its capacity, and what it holds
+    struct Operand {
+        void *dev = nullptr;
+        size_t cap = 0;
+        const void *host = nullptr;      // host buffer a resident copy came from
+        size_t bytes = 0;
+    } opnd[3 + 8], work;
 } g_hr;
 
 int ensure(void **p, size_t *have, size_t want) {
@@ -273,6 +280,9 @@ void release_host_run_cache() {
     if (g_hr.dA) cudaFree(g_hr.dA);
     if (g_hr.dB) cudaFree(g_hr.dB);
     if (g_hr.dC) cudaFree(g_hr.dC);
+    for (auto &o : g_hr.opnd)
+        if (o.dev) cudaFree(o.dev);
+    if (g_hr.work.dev) cudaFree(g_hr.work.dev);
     if (g_hr.in) cudaStreamDestroy(g_hr.in);
     if (g_hr.run) cudaStreamDestroy(g_hr.run);
     if (g_hr.out) cudaStreamDestroy(g_hr.out);
@@ -686,11 +696,121 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
     return CATCCOS_ERR_INVALID;
 }
 
+// Operand sizes (bytes) of the operators the host-buffer form serves beyond the dense ones; slot 0/1/2 = A/B/C,
+// 3.. = customPtrs in the operator's order.  Returns the number of custom operands, or -1.
+static int host_operand_bytes(int32_t commType, const CocTilingParams *t, size_t R, size_t *bytes) {
+    const size_t m = t->m, n = t->n, k = t->k;
+    if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER) {
+        const bool ag = commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL;
+        bytes[0] = m * k;
+        bytes[1] = k * n;
+        bytes[2] = (ag ? R * m : m / R) * n * 2;
+        bytes[3] = m * (k / 64) * 2;
+        bytes[4] = (k / 64) * n * 2;
+        return 2;
+    }
+    if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && t->expertNum > 0 && t->topK > 0) {
+        const size_t el = t->expertNum / R, tk = t->topK;
+        bytes[0] = m * k * 2;
+        bytes[1] = el * n * k;
+        bytes[2] = m * k * 2;
+        bytes[3] = el * k * (n / 2);
+        bytes[4] = m * tk * 4;
+        bytes[5] = m * tk * 4;
+        bytes[6] = el * n * (k / 32);
+        bytes[7] = el * k * (n / 64);
+        return 5;
+    }
+    return -1;
+}
+
+static int run_host_general(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
+                            void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
+                            uint32_t transA, uint32_t transB, uint32_t residentMask) {
+    Team *t = team();
+    const size_t R = t->n_pes;
+    size_t bytes[3 + 8] = {};
+    const int nc = host_operand_bytes(commType, tiling, R, bytes);
+    if (nc < 0) {
+        set_error("catccos_run_host: no host-buffer path for commType=%d dataType=%d", commType, dataType);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (!hostA || !hostB || !hostC || customCount < static_cast<uint32_t>(nc) || !hostCustom) {
+        set_error("host buffers must not be NULL (this operator takes %d custom operands)", nc);
+        return CATCCOS_ERR_INVALID;
+    }
+    int rc = ensure_host_run_streams();
+    if (rc) return rc;
+    const void *src[3 + 8] = {hostA, hostB, nullptr};
+    for (int i = 0; i < nc; ++i) {
+        if (!hostCustom[i]) {
+            set_error("custom host buffer %d is NULL", i);
+            return CATCCOS_ERR_INVALID;
+        }
+        src[3 + i] = hostCustom[i];
+    }
+    // inputs: a resident operand (bit i of the mask; bit 0 = A, 1 = B, 3.. = custom) is copied when its host buffer
+    // or size is new, every other input on every call
+    for (int i = 0; i < 3 + nc; ++i) {
+        auto &o = g_hr.opnd[i];
+        if ((rc = ensure(&o.dev, &o.cap, std::max<size_t>(bytes[i], 256)))) return rc;
+        if (i == 2) continue;
+        const bool resident = (residentMask >> i) & 1u;
+        if (resident && o.host == src[i] && o.bytes == bytes[i]) continue;
+        cudaMemcpyAsync(o.dev, src[i], bytes[i], cudaMemcpyHostToDevice, g_hr.run);
+        o.host = resident ? src[i] : nullptr;
+        o.bytes = bytes[i];
+    }
+    const size_t wbytes = catccos_workspace_bytes(commType, dataType, tiling);
+    if (wbytes > g_hr.work.cap) {
+        if ((rc = ensure(&g_hr.work.dev, &g_hr.work.cap, wbytes))) return rc;
+        cudaMemsetAsync(g_hr.work.dev, 0, wbytes, g_hr.run);
+    }
+    CocTilingParams til = *tiling;
+    til.rankSize = static_cast<uint32_t>(R);
+    const size_t need = catccos_symmetric_bytes(commType, dataType, &til);
+    void *symm = nullptr;
+    if (need > 0 && !(symm = team_top_region(need))) return CATCCOS_ERR_NOMEM;
+    uint8_t *custom[8];
+    for (int i = 0; i < nc; ++i) custom[i] = static_cast<uint8_t *>(g_hr.opnd[3 + i].dev);
+    CatccosKernelParams kp{static_cast<uint8_t *>(g_hr.opnd[0].dev), static_cast<uint8_t *>(g_hr.opnd[1].dev),
+                           static_cast<uint8_t *>(g_hr.opnd[2].dev), custom, static_cast<uint32_t>(nc)};
+    rc = catccos_launch(commType, dataType, g_hr.run, blockNum, 0, &kp, static_cast<uint8_t *>(g_hr.work.dev),
+                        static_cast<uint8_t *>(symm), tiling, transA, transB);
+    if (!rc) cudaMemcpyAsync(hostC, g_hr.opnd[2].dev, bytes[2], cudaMemcpyDeviceToHost, g_hr.run);
+    cudaError_t e = cudaStreamSynchronize(g_hr.run);
+    if (e != cudaSuccess) {
+        set_error("host-buffer run failed: %s", cudaGetErrorString(e));
+        return CATCCOS_ERR_CUDA;
+    }
+    if (rc) return rc;
+    return host_run_status();
+}
+
+int catccos_run_host_resident(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
+                              void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
+                              uint32_t transA, uint32_t transB, uint32_t residentMask) {
+    int rc = check_tiling(tiling);
+    if (rc) return rc;
+    if (team()->emulated) {
+        set_error("catccos_run_host needs one process per PE (catccos_shmem_init)");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (dense_op_of(commType) >= 0) {
+        if (residentMask) {
+            set_error("catccos_run_host_resident: the dense operators copy every operand on every call (mask must be 0)");
+            return CATCCOS_ERR_INVALID;
+        }
+        return catccos_run_host(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA,
+                                transB);
+    }
+    return run_host_general(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA,
+                            transB, residentMask);
+}
+
 int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
                      void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
                      uint32_t transA, uint32_t transB) {
-    (void)hostCustom;
-    (void)customCount;
     int rc = check_tiling(tiling);
     if (rc) return rc;
     Team *t = team();
@@ -699,7 +819,10 @@ int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, cons
         return CATCCOS_ERR_INVALID;
     }
     const int op = dense_op_of(commType);
-    if (op < 0 || (dataType != CATCCOS_FP16 && dataType != CATCCOS_BF16)) {
+    if (op < 0)
+        return run_host_general(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA,
+                                transB, 0);
+    if (dataType != CATCCOS_FP16 && dataType != CATCCOS_BF16) {
         set_error("catccos_run_host: no host-buffer path for commType=%d dataType=%d", commType, dataType);
         return CATCCOS_ERR_INVALID;
     }

@@ -3,9 +3,10 @@
 // A pair computes a 256-row x 256-column tile of ONE local expert: CTA c of the pair takes the
 // expert's 128-row tile 2 * j + c (an expert's rows start on a multiple of 128 in the receive
 // buffer; the second half of an expert's last pair tile may be empty and is then masked), its half
-// of the expert's weight tile, and both weight scale atoms.  Per K-step an SM pulls 33.5 KiB from
-// L2 instead of the 49.5 KiB of the one-CTA kernel (moe_gemm.cuh), which was bound by exactly that
-// feed, and there is room for six pipeline stages.  Tiles are handed out dynamically (tile_queue.cuh)
+// of the expert's weight tile; four helper warps read the scale atoms of both operands from global
+// memory and write them into TMEM with tcgen05.st, so they never enter shared memory or the MMA
+// queue.  Per K-step an SM pulls 32 KiB from L2 instead of the 49.5 KiB of the one-CTA kernel
+// (moe_gemm.cuh), and there is room for six pipeline stages.  Tiles are handed out dynamically (tile_queue.cuh)
 // in expert order, so an expert with many rows is shared by all pairs and the pairs that finish
 // early take what is left.
 //   MODE 1 (up projection): the pair's B tile is 128 "act" rows (CTA 0) + 128 "gate" rows (CTA 1) of

@@ -35,7 +35,7 @@ enum class CostModelStatus { SUCCESS, UNSUPPORTED, INVALID_ARGUMENT, NO_VALID_CA
 
 struct CostModelHardwareConfig {
     uint32_t smCount = 148;
-    double tensorTflops = 1424.4;        // sustained cuBLAS bf16 on this pool (fp8: x2)
+    double tensorTflops = 1424.4;        // sustained cuBLAS bf16 of a B200 under its 1 kW power cap (fp8: x2); override with measured figures
     double nvlinkGBs = 770.0;            // peer copy, one direction
     double pairEfficiency = 0.86;        // main loop of the CTA-pair kernels against tensorTflops (long K)
     double oneCtaEfficiency = 0.78;      // ... of the one-CTA kernels (L2 feed: 48 instead of 32 KiB per K-step)

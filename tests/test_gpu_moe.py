@@ -60,12 +60,14 @@ def _run(world, m, k, n, top_k, experts, xs, idxs, probs, w1q, w1s, w2q, w2s):
             w = ws[r].cpu().numpy()
             eri = w[:m * top_k * 4].view(np.int32).copy()
             counts = w[idx_bytes:idx_bytes + 8 * 512 * 4].view(np.int32).reshape(8, 512)[:world, :experts].copy()
-            nbytes = counts_bytes + _up(rows_cap * k, 1024) + _up(rows_cap * sld, 1024)
+            combine_off = counts_bytes + _up(rows_cap * k, 1024) + _up(rows_cap * sld, 1024)
+            nbytes = combine_off + m * top_k * k * 2
             h = np.empty(nbytes, dtype=np.uint8)
             assert lib().catccos_shmem_get_host(h.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(symm), r, nbytes) == 0
             codes = h[counts_bytes:counts_bytes + rows_cap * k].reshape(rows_cap, k)
             sc = h[counts_bytes + _up(rows_cap * k, 1024):][:rows_cap * sld].reshape(rows_cap, sld)
-            internals.append((eri, counts, codes, sc))
+            combine = h[combine_off:combine_off + m * top_k * k * 2].view(np.uint16).reshape(m * top_k, k).copy()
+            internals.append((eri, counts, codes, sc, combine))
         return outs, internals
 
 
@@ -76,7 +78,7 @@ def _oracle(world, epr, xs, idxs, probs, w1q, w1s, w2q, w2s):
 def _check_bit_exact_parts(world, epr, top_k, inter, internals):
     counts_all = inter["counts"]
     for r in range(world):
-        eri, counts, codes, sc = internals[r]
+        eri, counts, codes, sc, _ = internals[r]
         assert np.array_equal(counts, counts_all), "tokens per expert (all-gathered) differ"
         assert np.array_equal(eri, moe.expanded_row_idx_src_to_dst(inter["sorted_src"][r])), "expandedRowIdx differs"
         # dispatched rows: golden receive order, every local expert's segment starting on a multiple of 128
@@ -138,3 +140,15 @@ def test_moe_zipf_routing(world, m, k, n, top_k, experts):
     for r in range(world):
         err = verify.max_rel_err(torch.from_numpy(outs[r]), torch.from_numpy(gold[r]))
         assert err <= TOL_MX, f"rank {r}: {err}"
+    _check_unpermute_bit_exact(world, probs, outs, internals)
+
+
+def _check_unpermute_bit_exact(world, probs, outs, internals):
+    """The un-permute kernel alone: the rows the combine stage left in this rank's buffer, weighted and summed by
+    the oracle in the kernel's order of operations (fp32 multiply, fp32 add, top-k order, one bf16 rounding),
+    must give the operator's output bit for bit."""
+    for r in range(world):
+        eri, _, _, _, combine = internals[r]
+        rows = mxquant.bf16_bits_to_f32(combine)
+        want = moe.unpermute_fp32(rows, eri, np.asarray(probs[r], dtype=np.float32))
+        assert np.array_equal(want.view(np.uint32), outs[r].view(np.uint32)), f"rank {r}: un-permute differs from the oracle"
