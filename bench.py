@@ -441,6 +441,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar", "mxag", "moe", "quant", "fp4"])
+    ap.add_argument("--variant", default="push", choices=["push", "remote_read", "gather_result"],
+                    help="--op agmm only: data flow of the all-gather (push = AllGatherMatmul, the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -484,6 +486,8 @@ def main():
     a_h = b_h = None
     if dense_op:
         comm = {"agmm": rt.ALLGATHER_MATMUL, "mmrs": rt.MATMUL_REDUCE_SCATTER, "mmar": rt.MATMUL_ALLREDUCE}[args.op]
+        if args.op == "agmm" and args.variant != "push":
+            comm = rt.ALLGATHER_MATMUL_REMOTE_READ if args.variant == "remote_read" else rt.ALLGATHER_MATMUL_WITH_GATHER_RESULT
         a_h, b_h, dt = host_inputs(wl, rank, torch)
         til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
         dtype_code = rt.FP16 if wl["dtype"] == "fp16" else rt.BF16
@@ -493,8 +497,12 @@ def main():
         a_d, b_d = a_h.cuda(), b_h.cuda()
         c_d = torch.empty(wl["c_shape"], dtype=dt, device="cuda")
 
+        gathered = None
+        if comm == rt.ALLGATHER_MATMUL_WITH_GATHER_RESULT:
+            gathered = torch.empty((world * wl["m"], wl["k"]), dtype=dt, device="cuda")
+
         def step():
-            rt.launch(comm, a_d, b_d, c_d, symm, til, stream=stream)
+            rt.launch(comm, a_d, b_d, c_d, symm, til, stream=stream, custom=[gathered] if gathered is not None else None)
         launches_per_step = 1
     else:
         gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
@@ -677,7 +685,7 @@ def main():
     # every step.  Dense operators copy A and B; the block-scaled GEMM and the MoE keep their weights (and weight
     # scales) resident after the first call and copy activations / routing every step.
     e2e = None
-    if not args.no_e2e and args.op in ("agmm", "mmrs", "mmar", "mxag", "moe"):
+    if not args.no_e2e and args.op in ("agmm", "mmrs", "mmar", "mxag", "moe") and args.variant == "push":
         numa_node = bind_to_gpu_numa_node(local_rank, torch)
         pin = lambda t_: t_.cpu().pin_memory()
         if dense_op:
@@ -812,6 +820,8 @@ def main():
                 "exposed_comm_frac": exposed, "compute_only_ms_per_step": compute_only_ms,
                 "e2e": e2e, "gpu_launches": args.steps * launches_per_step, "clocks": clocks, "parity": parity,
             }
+            if args.op == "agmm" and args.variant != "push":
+                line["config"]["variant"] = args.variant
             if args.op == "moe":
                 line["config"]["hottest_rank_rows_over_mean"] = moe_imbalance
             if args.op == "mxag":

@@ -32,11 +32,17 @@ int dense_op_of(int32_t commType) {
     switch (commType) {
         case CATCCOS_MATMUL_ALLREDUCE: return OP_MMAR;
         case CATCCOS_ALLGATHER_MATMUL:
-        case CATCCOS_ASCEND950_ALLGATHER_MATMUL: return OP_AGMM;
+        case CATCCOS_ASCEND950_ALLGATHER_MATMUL:
+        case CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT:
+        case CATCCOS_ALLGATHER_MATMUL_REMOTE_READ: return OP_AGMM;
         case CATCCOS_MATMUL_REDUCE_SCATTER:
         case CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER: return OP_MMRS;
         default: return -1;
     }
+}
+
+int dense_flow_of(int32_t commType) {
+    return commType == CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT ? 1 : commType == CATCCOS_ALLGATHER_MATMUL_REMOTE_READ ? 2 : 0;
 }
 
 int check_tiling(const CocTilingParams *tiling) {
@@ -56,8 +62,11 @@ int check_tiling(const CocTilingParams *tiling) {
     return CATCCOS_OK;
 }
 
+// `flow`: 0 = the operator as such; 1 = AllGather-Matmul that also returns the gathered A in customPtrs[0]
+// (examples/allgather_matmul_with_gather_result/allgather_matmul_with_gather_result_host.h:54); 2 = remote-read
+// AllGather-Matmul (examples/allgather_matmul_remote_read).
 int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
-                     uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {
+                     uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB, int flow = 0) {
     int rc = check_tiling(tiling);
     if (rc) return rc;
     if (!params) {
@@ -72,10 +81,19 @@ int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, Catccos
         return CATCCOS_ERR_INVALID;
     }
     DenseArgs args[kMaxRanks];
-    for (int i = 0; i < n_params; ++i) args[i] = {params[i].ptrA, params[i].ptrB, params[i].ptrC};
+    for (int i = 0; i < n_params; ++i) {
+        args[i] = {params[i].ptrA, params[i].ptrB, params[i].ptrC};
+        if (flow == 1) {
+            if (params[i].customCount < 1 || !params[i].customPtrs || !params[i].customPtrs[0]) {
+                set_error("AllGatherMatmulWithGatherResult expects customPtrs = {gatherA [rankSize*m, k]}");
+                return CATCCOS_ERR_INVALID;
+            }
+            args[i].gather_out = params[i].customPtrs[0];
+        }
+    }
     return launch_dense(op, dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric,
                         static_cast<int>(tiling->m), static_cast<int>(tiling->n), static_cast<int>(tiling->k),
-                        static_cast<int>(transA), static_cast<int>(transB));
+                        static_cast<int>(transA), static_cast<int>(transB), flow == 2 ? AG_REMOTE_READ : AG_PUSH);
 }
 
 int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
@@ -581,6 +599,17 @@ size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTili
         (void)workspace;                                                                                         \
         return launch_dense_abi(op, dtype, stream, blockNum, params, 1, symmetric, tiling, transA, transB);      \
     }
+#define DENSE_FLOW_LAUNCH(name, flow, dtype)                                                                     \
+    int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
+             uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
+        (void)fftsAddr;                                                                                          \
+        (void)workspace;                                                                                         \
+        return launch_dense_abi(OP_AGMM, dtype, stream, blockNum, params, 1, symmetric, tiling, transA, transB, flow); \
+    }
+DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulWithGatherResultFP16, 1, CATCCOS_FP16)
+DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulWithGatherResultBF16, 1, CATCCOS_BF16)
+DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulRemoteReadFP16, 2, CATCCOS_FP16)
+DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulRemoteReadBF16, 2, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchMatmulAllReduceFP16, OP_MMAR, CATCCOS_FP16)
 DENSE_LAUNCH(LaunchMatmulAllReduceBF16, OP_MMAR, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchAllGatherMatmulFP16, OP_AGMM, CATCCOS_FP16)
@@ -650,7 +679,8 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
     (void)fftsAddr;
     const int op = dense_op_of(commType);
     if (op >= 0 && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
-        return launch_dense_abi(op, dataType, stream, blockNum, params, 1, symmetric, tiling, transA, transB);
+        return launch_dense_abi(op, dataType, stream, blockNum, params, 1, symmetric, tiling, transA, transB,
+                                dense_flow_of(commType));
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
@@ -677,7 +707,8 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
     }
     const int op = dense_op_of(commType);
     if (op >= 0 && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
-        return launch_dense_abi(op, dataType, stream, blockNum, params, t->n_pes, symmetric, tiling, transA, transB);
+        return launch_dense_abi(op, dataType, stream, blockNum, params, t->n_pes, symmetric, tiling, transA, transB,
+                                dense_flow_of(commType));
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
                                 transB);

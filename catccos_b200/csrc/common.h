@@ -43,6 +43,7 @@ struct alignas(64) RankArgs {
     CUtensorMap tmB;    // transB=1: [N, K] box {BK, BN};  transB=0: [K, N] box {64 (n), BK (k)}
     const void *A;      // raw pointers of the same operands
     void *C;
+    void *gather_out;   // AG-MM with gather result: [R*m, K] copy of the gathered A for the caller (nullptr: none)
 };
 
 struct FusedParams {
@@ -63,6 +64,8 @@ struct FusedParams {
     int rs_fp16;                      // reduce family: partial tiles cross the link as fp16 (11-bit mantissa) whatever
                                       // the output type; 0: in the output type
     int ag_group;                     // 256-row tiles per L2 group of the AllGather-Matmul tile order (sched.h)
+    int ag_pull;                      // AG-MM data flow: 0 = every rank pushes its rows into the peers' gathered regions;
+                                      // 1 = remote read: every rank stages its rows in its own region and the peers fetch them
     unsigned long long *trace;        // optional: kTraceSlots %globaltimer stamps per CTA (nullptr = off)
 };
 

@@ -182,7 +182,7 @@ size_t dense_symmetric_bytes(int op, int world, int m, int n, int k) {
 }
 
 int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, const DenseArgs *args, void *symmetric,
-                 int m, int n, int k, int trans_a, int trans_b) {
+                 int m, int n, int k, int trans_a, int trans_b, int variant) {
     Team *t = team();
     if (!t) {
         set_error("symmetric heap not initialised (call catccos_shmem_init first)");
@@ -204,6 +204,10 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     }
     if (trans_a != 0) {
         set_error("transA=1 is not supported");
+        return CATCCOS_ERR_INVALID;
+    }
+    if ((variant != AG_PUSH && variant != AG_REMOTE_READ) || (variant != AG_PUSH && op != OP_AGMM)) {
+        set_error("data-flow variant %d does not exist for operator %d", variant, op);
         return CATCCOS_ERR_INVALID;
     }
     if (m <= 0 || n <= 0 || k <= 0 || (k % 8) != 0 || (n % 8) != 0) {
@@ -232,7 +236,8 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
             return CATCCOS_ERR_INVALID;
         }
         size_t flags = 0;
-        if (op == OP_AGMM) flags = static_cast<size_t>(R) * ((m + BM - 1) / BM) * kAgSubChunks;
+        if (op == OP_AGMM)      // arrival flags; remote read adds one "staged" flag per unit and source
+            flags = static_cast<size_t>(R) * ((m + BM - 1) / BM) * kAgSubChunks * (variant == AG_REMOTE_READ ? 2 : 1);
         if (op == OP_MMRS) flags = static_cast<size_t>(R) * ((m / R + BM - 1) / BM) * nt;
         if (op == OP_MMAR) flags = 2 * static_cast<size_t>(R) * (((m + R - 1) / R + BM - 1) / BM) * nt;
         if (kFlagOpBase + flags > kFlagWords) {
@@ -249,12 +254,24 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     sig = slot_sig(sig, static_cast<uint64_t>(n));
     sig = slot_sig(sig, static_cast<uint64_t>(k));
     sig = slot_sig(sig, symm_off);
+    sig = slot_sig(sig, static_cast<uint64_t>(variant));
     const LaunchSlot slot = peek_slot(t, sig, epoch);
     if (R > 1) symm_off += static_cast<uint64_t>(slot.half) * dense_half_bytes(op, R, m, n, k);
 
     // the operators run on CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
     bool use_pair = true;
     if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = atoi(e) != 0;
+    bool wants_gather = false;
+    for (int l = 0; l < n_local; ++l) wants_gather = wants_gather || args[l].gather_out != nullptr;
+    if (!use_pair && (variant != AG_PUSH || wants_gather)) {
+        set_error("the remote-read and gather-result variants of AllGather-Matmul exist in the CTA-pair kernel only "
+                  "(unset CATCCOS_TWO_CTA=0)");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (wants_gather && op != OP_AGMM) {
+        set_error("only AllGather-Matmul returns the gathered A");
+        return CATCCOS_ERR_INVALID;
+    }
     FusedParams p;
     memset(&p, 0, sizeof(p));
     const CUtensorMapDataType dt = dtype == 27 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -285,6 +302,11 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         }
         ra.A = a.A;
         ra.C = a.C;
+        ra.gather_out = a.gather_out;
+        if (a.gather_out && (reinterpret_cast<uintptr_t>(a.gather_out) & 15)) {
+            set_error("the gathered-A output must be 16-byte aligned");
+            return CATCCOS_ERR_INVALID;
+        }
     }
     for (int pe = 0; pe < R; ++pe) p.heap_base[pe] = t->base[pe];
     p.symm_off = symm_off;
@@ -317,6 +339,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
     p.rs_fp16 = rs_exchange_fp16();
+    p.ag_pull = variant == AG_REMOTE_READ ? 1 : 0;
     p.sched = t->sched_dev;
     p.trace = t->trace_dev;
 

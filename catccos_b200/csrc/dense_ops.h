@@ -9,6 +9,13 @@ struct DenseArgs {
     const void *A;   // [m, k] row-major
     const void *B;   // transB=0: [k, n] row-major;  transB=1: [n, k] row-major
     void *C;         // AG-MM: [R*m, n];  MM-RS: [m/R, n];  MM-AR: [m, n]
+    void *gather_out = nullptr;   // AG-MM with gather result: receives the gathered A [R*m, k]
+};
+
+// Data-flow variants of AllGather-Matmul (launch_dense's `variant`): same product, different movement of A.
+enum AgVariant : int {
+    AG_PUSH = 0,          // every rank writes its rows into the peers' gathered regions (default)
+    AG_REMOTE_READ = 1,   // every rank stages its rows in its own symmetric region; the peers read them from there
 };
 
 // Bytes of the caller's symmetric buffer the operator uses (0 for a single rank).
@@ -18,7 +25,7 @@ size_t dense_symmetric_bytes(int op, int world, int m, int n, int k);
 // m, n, k carry the reference's meaning per operator (AG-MM: m = rows held by one rank; MM-RS and
 // MM-AR: m = rows of the full product).  Asynchronous on `stream`.
 int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, const DenseArgs *args, void *symmetric,
-                 int m, int n, int k, int trans_a, int trans_b);
+                 int m, int n, int k, int trans_a, int trans_b, int variant = AG_PUSH);
 
 // 1: the reduce family exchanges its partial tiles as fp16 (default), 0: in the output type (CATCCOS_RS_EXCHANGE=native)
 int rs_exchange_fp16();

@@ -298,67 +298,140 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             tq_retire(next_tile, pairs);
         }
     } else {
-        // ------------------------------------------------------ all-gather push ----
-        // warps 6..9: one push lane per warp
+        // ------------------------------------------------- all-gather data movement ----
+        // warps 6..9: one copy lane per warp.  Default: this rank's rows are pushed into every peer's gathered
+        // region.  Remote read (p.ag_pull): this rank stages its rows in its own region, tells the peers, and
+        // fetches the peers' staged rows into its own region.  Either way a unit's arrival flag in this rank's
+        // flag region tells the scout that the rows are in local memory.  With a gather-result output the lanes
+        // finally copy every unit (own rows from A, the others from the gathered region) to the caller's buffer.
         const int ctid = warp - 6;
-        if (R > 1 && !p.compute_only) {
+        const bool moves = R > 1 && !p.compute_only;
+        if (moves) {
             if (warp == 6 && cta == 0 && lane < R && lane != rank) {
                 fence_sys();
                 st_release_sys(flag_ptr(p, lane, kFlagEntered + rank), p.epoch);
             }
             __syncwarp();
-            if (lane == 0 && ctid < kPushLanesShared) {
-                // same units, order and flags as the one-CTA kernel: destination rank-1 first, units of
-                // BM/kAgSubChunks rows, one flag per unit, every lane owns whole units
-                const int units_per_dest = mt_ag * kAgSubChunks;
+        }
+        if (lane == 0 && ctid < kPushLanesShared && (moves || (ra.gather_out && !p.compute_only))) {
+            // units of BM/kAgSubChunks rows, one flag per unit, every lane owns whole units
+            const int units_per_dest = mt_ag * kAgSubChunks;
+            const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
+            const int lane_id = cta * kPushLanesShared + ctid;
+            const int n_lanes = p.ctas_per_rank * kPushLanesShared;
+            uint8_t *buf = smem_push + ctid * kPushPieceBytes;
+            uint64_t *bar = &sh->push_bar[ctid];
+            bool ok = true;
+            uint32_t entered_ok = 0;
+            uint32_t piece = 0;
+            uint64_t entered_wait_ns = 0;
+            const uint32_t staged_base = kFlagOpBase + static_cast<uint32_t>(R * mt_ag * kAgSubChunks);
+            auto unit_rows = [&](int cu, int &r0, int &r1) {
+                const int chunk = cu / kAgSubChunks, sub = cu % kAgSubChunks;
+                r0 = chunk * BM + sub * (BM / kAgSubChunks);
+                r1 = min(p.M, r0 + BM / kAgSubChunks);
+            };
+            auto unit_flag = [&](int src, int cu) { return kFlagOpBase + static_cast<uint32_t>(src * units_per_dest + cu); };
+            // bytes from src to dst through this lane's 8 KiB staging piece (async proxy both ways)
+            auto copy_rows = [&](const uint8_t *src, uint8_t *dst, size_t bytes) {
+                for (size_t off = 0; off < bytes && ok; off += kPushPieceBytes, ++piece) {
+                    const uint32_t len = static_cast<uint32_t>(min(static_cast<size_t>(kPushPieceBytes), bytes - off));
+                    bulk_wait_read<0>();
+                    mbar_expect_tx(bar, len);
+                    bulk_load(buf, src + off, len, bar);
+                    if (!(ok = mbar_wait(bar, piece & 1, ctl, W_DRAIN))) break;
+                    bulk_store(dst + off, buf, len);
+                    bulk_commit();
+                }
+            };
+            auto wait_entered = [&](int d) {
+                if ((entered_ok >> d) & 1) return;
+                const uint64_t te0 = p.trace ? globaltimer_ns() : 0;
+                ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d);
+                if (p.trace) entered_wait_ns += globaltimer_ns() - te0;
+                entered_ok |= 1u << d;
+            };
+            if (ctid == 0) CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
+            if (moves && !p.ag_pull) {
+                // push: same units, order and flags as the one-CTA kernel, destination rank-1 first
                 const int total = (R - 1) * units_per_dest;
-                const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
-                const int lane_id = cta * kPushLanesShared + ctid;
-                const int n_lanes = p.ctas_per_rank * kPushLanesShared;
-                uint8_t *buf = smem_push + ctid * kPushPieceBytes;
-                uint64_t *bar = &sh->push_bar[ctid];
-                bool ok = true;
-                uint32_t entered_ok = 0;
-                uint32_t piece = 0;
-                uint64_t entered_wait_ns = 0;
-                if (ctid == 0) CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
                 for (int u = lane_id; u < total && ok; u += n_lanes) {
-                    int d, cu;
+                    int d, cu, r0, r1;
                     ag_push_decode(R, units_per_dest, rank, u, d, cu);
-                    const int chunk = cu / kAgSubChunks, sub = cu % kAgSubChunks;
-                    const int r0 = chunk * BM + sub * (BM / kAgSubChunks);
-                    const int r1 = min(p.M, r0 + BM / kAgSubChunks);
-                    if (!((entered_ok >> d) & 1)) {
-                        const uint64_t te0 = p.trace ? globaltimer_ns() : 0;
-                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + d), p.entered_need, ctl, W_ENTERED, d))) break;
-                        if (p.trace) entered_wait_ns += globaltimer_ns() - te0;
-                        entered_ok |= 1u << d;
-                    }
-                    if (r1 > r0) {
-                        const uint8_t *src = static_cast<const uint8_t *>(ra.A) + r0 * row_bytes;
-                        uint8_t *dst = p.heap_base[d] + p.symm_off + (static_cast<size_t>(rank) * p.M + r0) * row_bytes;
-                        const size_t bytes = (r1 - r0) * row_bytes;
-                        for (size_t off = 0; off < bytes && ok; off += kPushPieceBytes, ++piece) {
-                            const uint32_t len = static_cast<uint32_t>(min(static_cast<size_t>(kPushPieceBytes), bytes - off));
-                            bulk_wait_read<0>();
-                            mbar_expect_tx(bar, len);
-                            bulk_load(buf, src + off, len, bar);
-                            if (!(ok = mbar_wait(bar, piece & 1, ctl, W_DRAIN))) break;
-                            bulk_store(dst + off, buf, len);
-                            bulk_commit();
-                        }
-                    }
+                    unit_rows(cu, r0, r1);
+                    wait_entered(d);
+                    if (!ok) break;
+                    if (r1 > r0)
+                        copy_rows(static_cast<const uint8_t *>(ra.A) + r0 * row_bytes,
+                                  p.heap_base[d] + p.symm_off + (static_cast<size_t>(rank) * p.M + r0) * row_bytes,
+                                  (r1 - r0) * row_bytes);
                     if (!ok) break;
                     bulk_wait<0>();
                     fence_proxy_async_global();
                     fence_sys();
-                    st_release_sys(flag_ptr(p, d, kFlagOpBase + (rank * mt_ag + chunk) * kAgSubChunks + sub), p.epoch);
+                    st_release_sys(flag_ptr(p, d, unit_flag(rank, cu)), p.epoch);
                 }
-                bulk_wait<0>();
-                if (ctid == 0) {
-                    CB_TRACE(TR_PUSH_END, globaltimer_ns());
-                    CB_TRACE(TR_EPI_WAIT_NS, entered_wait_ns);     // time this lane waited for peers to enter
+            } else if (moves) {
+                // remote read, stage: my rows into my own region once no peer reads what an earlier launch left
+                // there, then one "staged" flag per unit in every peer's flag region
+                uint8_t *mine = p.heap_base[rank] + p.symm_off;
+                for (int cu = lane_id; cu < units_per_dest && ok; cu += n_lanes) {
+                    int r0, r1;
+                    unit_rows(cu, r0, r1);
+                    for (int j = 1; j < R && ok; ++j) wait_entered((rank + j) % R);
+                    if (!ok) break;
+                    if (r1 > r0)
+                        copy_rows(static_cast<const uint8_t *>(ra.A) + r0 * row_bytes,
+                                  mine + (static_cast<size_t>(rank) * p.M + r0) * row_bytes, (r1 - r0) * row_bytes);
+                    if (!ok) break;
+                    bulk_wait<0>();
+                    fence_proxy_async_global();
+                    fence_sys();
+                    for (int j = 1; j < R; ++j)
+                        st_release_sys(flag_ptr(p, (rank + R - j) % R, staged_base + rank * units_per_dest + cu), p.epoch);
                 }
+                // fetch: source rank+1 first (the order the tiles need them), unit by unit
+                const int total = (R - 1) * units_per_dest;
+                for (int u = lane_id; u < total && ok; u += n_lanes) {
+                    const int s = (rank + 1 + u / units_per_dest) % R;
+                    const int cu = u % units_per_dest;
+                    int r0, r1;
+                    unit_rows(cu, r0, r1);
+                    if (!(ok = wait_flag_ge(flag_ptr(p, rank, staged_base + s * units_per_dest + cu), p.epoch, ctl, W_AG_CHUNK, s)))
+                        break;
+                    fence_proxy_async_global();
+                    const size_t off = (static_cast<size_t>(s) * p.M + r0) * row_bytes;
+                    if (r1 > r0) copy_rows(p.heap_base[s] + p.symm_off + off, mine + off, (r1 - r0) * row_bytes);
+                    if (!ok) break;
+                    bulk_wait<0>();
+                    fence_proxy_async_global();
+                    fence_sys();
+                    st_release_sys(flag_ptr(p, rank, unit_flag(s, cu)), p.epoch);
+                }
+            }
+            if (ra.gather_out && ok) {
+                // gather result: own rows first, then the sources in the order their rows arrive
+                const int total = R * units_per_dest;
+                for (int u = lane_id; u < total && ok; u += n_lanes) {
+                    const int s = (rank + u / units_per_dest) % R;
+                    const int cu = u % units_per_dest;
+                    int r0, r1;
+                    unit_rows(cu, r0, r1);
+                    if (r1 <= r0) continue;
+                    const size_t off = (static_cast<size_t>(s) * p.M + r0) * row_bytes;
+                    const uint8_t *src = static_cast<const uint8_t *>(ra.A) + r0 * row_bytes;
+                    if (s != rank) {
+                        if (!(ok = wait_flag_ge(flag_ptr(p, rank, unit_flag(s, cu)), p.epoch, ctl, W_AG_CHUNK, s))) break;
+                        fence_proxy_async_global();
+                        src = p.heap_base[rank] + p.symm_off + off;
+                    }
+                    copy_rows(src, static_cast<uint8_t *>(ra.gather_out) + off, (r1 - r0) * row_bytes);
+                }
+            }
+            bulk_wait<0>();
+            if (ctid == 0) {
+                CB_TRACE(TR_PUSH_END, globaltimer_ns());
+                CB_TRACE(TR_EPI_WAIT_NS, entered_wait_ns);     // time this lane waited for peers to enter
             }
         }
     }

@@ -11,6 +11,8 @@ from ._lib import CocTilingParams, KernelParams, check, lib
 MATMUL_ALLREDUCE = 0
 ALLGATHER_MATMUL = 1
 MATMUL_REDUCE_SCATTER = 3
+ALLGATHER_MATMUL_WITH_GATHER_RESULT = 5
+ALLGATHER_MATMUL_REMOTE_READ = 20
 MXFP8_MATMUL_REDUCE_SCATTER = 18
 FP8_MX_ALLGATHER_MATMUL = 22
 MX_QUANT_ALLGATHER = 24

@@ -65,7 +65,9 @@ enum {
     CATCCOS_ASCEND950_ALLGATHER_MATMUL = 2,
     CATCCOS_MATMUL_REDUCE_SCATTER = 3,
     CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER = 4,
+    CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT = 5,
     CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = 18,
+    CATCCOS_ALLGATHER_MATMUL_REMOTE_READ = 20,
     CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL = 22,
     CATCCOS_MX_QUANT_ALLGATHER = 24,
     CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25,
@@ -187,6 +189,19 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllGatherMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllGatherMatmulBF16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16);
+
+/* Data-flow variants of AllGather-Matmul: same operands, tiling meaning and product as LaunchAllGatherMatmul*.
+ * WithGatherResult (tests/dynamic_tiling/impl/kernel_bf16.cpp:286, include/catccos/dgemm/kernel/
+ * allgather_matmul_with_gather_result.hpp): customPtrs = {gatherA}, a [rankSize*m, k] buffer that receives every
+ * rank's A in rank order (examples/allgather_matmul_with_gather_result/..._host.h:51-54,75-79), written by the
+ * kernel's copy warps as the rows arrive.
+ * RemoteRead (kernel_bf16.cpp:170, include/catccos/dgemm/kernel/allgather_matmul_with_remote_read_local_mm_opt.hpp):
+ * every rank stages its A in its own symmetric region and the peers fetch it from there (reads over NVLink,
+ * arrival flags stay local) instead of every rank writing into its peers' regions. */
+CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulWithGatherResultFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulWithGatherResultBF16);
+CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulRemoteReadFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulRemoteReadBF16);
 
 /* tests/dynamic_tiling/impl/kernel_fp16_ascend950.cpp:274 (MxAllGatherMatmulTla,
  * include/catccos/dgemm/kernel/mx_allgather_matmul.hpp:27-428): ptrA/ptrB = e4m3 operands,

@@ -26,6 +26,8 @@ enum CocCommType {
     ASCEND950_ALLGATHER_MATMUL = CATCCOS_ASCEND950_ALLGATHER_MATMUL,
     MATMUL_REDUCE_SCATTER = CATCCOS_MATMUL_REDUCE_SCATTER,
     ASCEND950_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER,
+    ALLGATHER_MATMUL_WITH_GATHER_RESULT = CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT,
+    ALLGATHER_MATMUL_REMOTE_READ = CATCCOS_ALLGATHER_MATMUL_REMOTE_READ,
     ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER,
     ASCEND950_FP8_MX_ALLGATHER_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL,
     MX_QUANT_ALLGATHER = CATCCOS_MX_QUANT_ALLGATHER,
@@ -83,6 +85,8 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"a5agmm", ASCEND950_ALLGATHER_MATMUL},
         {"mmrs", MATMUL_REDUCE_SCATTER},
         {"a5mmrs", ASCEND950_MATMUL_REDUCE_SCATTER},
+        {"agmmwg", ALLGATHER_MATMUL_WITH_GATHER_RESULT},
+        {"agmmrr", ALLGATHER_MATMUL_REMOTE_READ},
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
         {"a5moe", ASCEND950_DISPATCH_FFN_COMBINE},
@@ -104,6 +108,8 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ASCEND950_ALLGATHER_MATMUL, "Ascend950AllGatherMatmul"},
         {MATMUL_REDUCE_SCATTER, "MatmulReduceScatter"},
         {ASCEND950_MATMUL_REDUCE_SCATTER, "Ascend950MatmulReduceScatter"},
+        {ALLGATHER_MATMUL_WITH_GATHER_RESULT, "AllGatherMatmulWithGatherResult"},
+        {ALLGATHER_MATMUL_REMOTE_READ, "AllGatherMatmulRemoteRead"},
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
         {ASCEND950_DISPATCH_FFN_COMBINE, "Ascend950DispatchFFNCombine"},

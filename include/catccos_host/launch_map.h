@@ -26,6 +26,10 @@ private:
             {Hash(MATMUL_ALLREDUCE, BF16), &LaunchMatmulAllReduceBF16},
             {Hash(ALLGATHER_MATMUL, FP16), &LaunchAllGatherMatmulFP16},
             {Hash(ALLGATHER_MATMUL, BF16), &LaunchAllGatherMatmulBF16},
+            {Hash(ALLGATHER_MATMUL_WITH_GATHER_RESULT, FP16), &LaunchAllGatherMatmulWithGatherResultFP16},
+            {Hash(ALLGATHER_MATMUL_WITH_GATHER_RESULT, BF16), &LaunchAllGatherMatmulWithGatherResultBF16},
+            {Hash(ALLGATHER_MATMUL_REMOTE_READ, FP16), &LaunchAllGatherMatmulRemoteReadFP16},
+            {Hash(ALLGATHER_MATMUL_REMOTE_READ, BF16), &LaunchAllGatherMatmulRemoteReadBF16},
             {Hash(MATMUL_REDUCE_SCATTER, FP16), &LaunchMatmulReduceScatterFP16},
             {Hash(MATMUL_REDUCE_SCATTER, BF16), &LaunchMatmulReduceScatterBF16},
             {Hash(ASCEND950_ALLGATHER_MATMUL, FP16), &LaunchAscend950AllGatherMatmulFP16},

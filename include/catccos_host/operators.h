@@ -95,6 +95,33 @@ public:
     CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_ALLGATHER_MATMUL; }
 };
 REGISTER_OPERATOR("Ascend950AllGatherMatmul", Ascend950AllGatherMatmulOperator);
+// The same product plus the gathered A [rankSize*m, k] in customPtrs[0], written to output_gather_a.bin
+// (examples/allgather_matmul_with_gather_result/allgather_matmul_with_gather_result_host.h:17-84).
+class AllGatherMatmulWithGatherResultOperator : public AllGatherMatmulOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t aSize = static_cast<size_t>(t.m) * t.k * 2, bSize = static_cast<size_t>(t.k) * t.n * 2;
+        const size_t cSize = static_cast<size_t>(t.m) * t.rankSize * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), aSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), bSize), DeviceZeros(cSize),
+                               DeviceZeros(aSize * t.rankSize));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        AllGatherMatmulOperator::WriteResultFile(params, t, rankId, dataFile);
+        const size_t gSize = static_cast<size_t>(t.m) * t.rankSize * t.k * 2;
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_gather_a_" + std::to_string(rankId) + ".bin", params.customPtrs[0], gSize);
+        if (rankId == 0) catccos_host::WriteDeviceBuffer(dataFile + "/output_gather_a.bin", params.customPtrs[0], gSize);
+    }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ALLGATHER_MATMUL_WITH_GATHER_RESULT; }
+};
+REGISTER_OPERATOR("AllGatherMatmulWithGatherResult", AllGatherMatmulWithGatherResultOperator);
+// Remote-read data flow (examples/allgather_matmul_remote_read/allgather_matmul_remote_read_host.h): same files.
+class AllGatherMatmulRemoteReadOperator : public AllGatherMatmulOperator {
+public:
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ALLGATHER_MATMUL_REMOTE_READ; }
+};
+REGISTER_OPERATOR("AllGatherMatmulRemoteRead", AllGatherMatmulRemoteReadOperator);
 
 // D_r = rows r of sum_s A_s * B_s (examples/matmul_reduce_scatter/matmul_reduce_scatter_host.h); m = total rows.
 class MatmulReduceScatterOperator : public CatccosOperator {

@@ -22,7 +22,8 @@ def test_registry_lists_every_operator_on_the_path(driver):
     assert set(out) == {"MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend950AllGatherMatmul",
                         "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
                         "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather",
-                        "Ascend950Fp8MxAllToAllVGroupedMatmul", "Ascend950Fp8MxGroupedMatmulAllToAllV"}
+                        "Ascend950Fp8MxAllToAllVGroupedMatmul", "Ascend950Fp8MxGroupedMatmulAllToAllV",
+                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
