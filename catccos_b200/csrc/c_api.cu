@@ -98,7 +98,7 @@ int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, Catccos
 
 int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
                      uint8_t **workspaces, uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA,
-                     uint32_t transB) {
+                     uint32_t transB, int fmt = 0) {
     int rc = check_tiling(tiling);
     if (rc) return rc;
     Team *t = team();
@@ -122,7 +122,7 @@ int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelPa
     }
     return launch_mx_allgather_matmul(dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric,
                                       static_cast<int>(tiling->m), static_cast<int>(tiling->n),
-                                      static_cast<int>(tiling->k), static_cast<int>(transB));
+                                      static_cast<int>(tiling->k), static_cast<int>(transB), fmt);
 }
 
 // MXFP8 Matmul-ReduceScatter: KernelParams as set by the example's operator class
@@ -551,9 +551,9 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     if (op >= 0)
         return dense_symmetric_bytes(op, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
-    if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL)
+    if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL)
         return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
-                                     static_cast<int>(tiling->k));
+                                     static_cast<int>(tiling->k), commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL ? 1 : 0);
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER)
         return dense_symmetric_bytes(OP_MMRS, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
@@ -572,7 +572,7 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
 }
 size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
     (void)dataType;
-    if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL ||
+    if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL ||
                    commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER))
         return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
@@ -621,14 +621,16 @@ DENSE_LAUNCH(LaunchAscend950AllGatherMatmulBF16, OP_AGMM, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterFP16, OP_MMRS, CATCCOS_FP16)
 DENSE_LAUNCH(LaunchAscend950MatmulReduceScatterBF16, OP_MMRS, CATCCOS_BF16)
 
-#define MXAG_LAUNCH(name, dtype)                                                                               \
+#define MXAG_LAUNCH(name, dtype, fmt)                                                                          \
     int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
              uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
         (void)fftsAddr;                                                                                          \
-        return launch_mx_ag_abi(dtype, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB); \
+        return launch_mx_ag_abi(dtype, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB, fmt); \
     }
-MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16, CATCCOS_FP16)
-MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16, CATCCOS_BF16)
+MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16, CATCCOS_FP16, 0)
+MXAG_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16, CATCCOS_BF16, 0)
+MXAG_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulFP16, CATCCOS_FP16, 1)
+MXAG_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulBF16, CATCCOS_BF16, 1)
 
 #define MXRS_LAUNCH(name, dtype, fmt)                                                                          \
     int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
@@ -683,6 +685,8 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
                                 dense_flow_of(commType));
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
+    if (commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB, 1);
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_rs_abi(dataType, 1, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
@@ -712,6 +716,9 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_ag_abi(dataType, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
                                 transB);
+    if (commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_ag_abi(dataType, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
+                                transB, 1);
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_rs_abi(dataType, 1, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
                                 transB);

@@ -29,6 +29,23 @@ constexpr int kMxPushLanes = kMxSideBytes / kPushPieceBytes;
 constexpr int kMxSmemBytes = kMxStages * kMxStageBytes + kMxSideBytes + 1024 + 512;
 constexpr int kMxFlagsPerChunk = kAgSubChunks + 1;   // data units + one scale-factor unit
 
+// Operand format of the one-CTA kernel.  MXFP4 (e2m1, two codes per byte, K-major operands only): a stage holds
+// 128 bytes = 256 elements of K per row, i.e. two scale atoms per operand tile instead of one, and is consumed by
+// four tcgen05.mma.kind::mxf4nvf4 (scale_vec::2X) of K = 64.
+enum MxFormat : int { MX_FP8 = 0, MX_FP4 = 1 };
+template <int FMT>
+struct MxCfg {
+    static constexpr int kAtoms = FMT == MX_FP4 ? 2 : 1;                 // scale atoms per operand tile and stage
+    static constexpr int kSfStage = FMT == MX_FP4 ? 3072 : 2048;         // A atoms + 2 x B atoms
+    static constexpr int kStageBytes = kMxAStage + kMxBStage + kSfStage;
+    static constexpr int kSideBytes = FMT == MX_FP4 ? 16 * 1024 : kMxSideBytes;
+    static constexpr int kPushLanes = kSideBytes / kPushPieceBytes;
+    static constexpr int kSmemBytes = kMxStages * kStageBytes + kSideBytes + 1024 + 512;
+    static constexpr int kSfCols = 12 * kAtoms;                          // TMEM columns of one stage's scales
+    static_assert(kSmemBytes <= 232448, "shared memory budget");
+    static_assert(kPushLanes <= kMxPushLanes, "push barriers");
+};
+
 struct alignas(64) MxRankArgs {
     CUtensorMap tmA;        // local activations  [m, K] bytes, box {128, BM}
     CUtensorMap tmAg;       // gathered activations [R*m, K] bytes in this PE's symmetric region
@@ -73,12 +90,17 @@ struct MxSmem {
         if (p.trace) p.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + (slot)] = (value); \
     } while (0)
 
-template <typename TOut, bool B_MN>
+template <typename TOut, bool B_MN, int FMT = MX_FP8>
 __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(const __grid_constant__ MxParams p) {
+    using Cfg = MxCfg<FMT>;
+    static_assert(!(FMT == MX_FP4 && B_MN), "4-bit operands are K-major");
+    constexpr int kMxStageBytes = Cfg::kStageBytes;       // shadows the MXFP8 constants of the same names
+    constexpr int kMxPushLanes = Cfg::kPushLanes;
+    constexpr int kAtoms = Cfg::kAtoms;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_push = smem + kMxStages * kMxStageBytes;
-    MxSmem *sh = reinterpret_cast<MxSmem *>(smem_push + kMxSideBytes);
+    MxSmem *sh = reinterpret_cast<MxSmem *>(smem_push + Cfg::kSideBytes);
     static_assert(sizeof(MxSmem) <= 512, "barrier block outgrew its budget");
 
     const int warp = threadIdx.x >> 5;
@@ -92,8 +114,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
     const int nt = (p.N + BN - 1) / BN;
     const int per_src = mt * nt;
     const int num_tiles = R * per_src;
-    const int kblocks = (p.K + MX_BK - 1) / MX_BK;
-    const int kb4 = kblocks;                        // scale atoms per row tile
+    const int Kb = FMT == MX_FP4 ? p.K / 2 : p.K;  // bytes of one operand row
+    const int kblocks = (Kb + MX_BK - 1) / MX_BK;   // pipeline stages per tile
+    const int kb4 = (p.K + 127) / 128;              // scale atoms per row tile (one per 128 elements of K)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMxStages; ++s) {
@@ -170,7 +193,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
                     uint8_t *sa = smem + st * kMxStageBytes;
                     uint8_t *sb = sa + kMxAStage;
                     uint8_t *ssf = sb + kMxBStage;
-                    mbar_expect_tx(&sh->full[st], kMxAStage + kMxBStage + 512 + (second_b_atom ? 1024 : 512));
+                    // scale atoms of this stage (the last stage of an MXFP4 tile may hold one instead of two)
+                    const int atoms = min(kAtoms, kb4 - kb * kAtoms);
+                    const uint32_t sfb_bytes = static_cast<uint32_t>(atoms) * 512;
+                    mbar_expect_tx(&sh->full[st], kMxAStage + kMxBStage + sfb_bytes * (second_b_atom ? 3 : 2));
                     tma_load_2d(sa, tma, &sh->full[st], kb * MX_BK, a_row);
                     if (B_MN) {
 #pragma unroll
@@ -179,10 +205,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
                     } else {
                         tma_load_2d(sb, &ra.tmB, &sh->full[st], kb * MX_BK, ni * BN);
                     }
-                    bulk_load(ssf, sfa + static_cast<size_t>(kb) * 512, 512, &sh->full[st]);
-                    bulk_load(ssf + 512, sfb + static_cast<size_t>(kb) * 512, 512, &sh->full[st]);
+                    bulk_load(ssf, sfa + static_cast<size_t>(kb) * kAtoms * 512, sfb_bytes, &sh->full[st]);
+                    bulk_load(ssf + kAtoms * 512, sfb + static_cast<size_t>(kb) * kAtoms * 512, sfb_bytes, &sh->full[st]);
                     if (second_b_atom)
-                        bulk_load(ssf + 1024, sfb + (static_cast<size_t>(kb4) + kb) * 512, 512, &sh->full[st]);
+                        bulk_load(ssf + 2 * kAtoms * 512, sfb + (static_cast<size_t>(kb4) + kb * kAtoms) * 512, sfb_bytes,
+                                  &sh->full[st]);
                 }
             }
             if (!ok) {
@@ -211,20 +238,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
                     const uint32_t b_addr = a_addr + kMxAStage;
                     const uint32_t sf_addr = b_addr + kMxBStage;
                     // scale atoms: 32 rows x 16 B, 8-row groups 128 B apart, no swizzle
-                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * 16u;
-                    const uint32_t tmem_sfb = tmem_sfa + 4;
-                    tmem_cp_32x128b_warpx4(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
-                    tmem_cp_32x128b_warpx4(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
-                    tmem_cp_32x128b_warpx4(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));
+                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * (FMT == MX_FP4 ? 24u : 16u);
+                    if constexpr (FMT == MX_FP4) {
+                        const uint32_t tmem_sfb = tmem_sfa + 4 * kAtoms;     // per atom: 4 columns (n 0-127) + 4 (n 128-255)
+                        const int mmas = min(4, p.K / 64 - kb * 4);
+                        const int atoms = (mmas + 1) / 2;
+                        for (int a = 0; a < atoms; ++a) {
+                            tmem_cp_32x128b_warpx4(tmem_sfa + a * 4, make_smem_desc_noswizzle(sf_addr + a * 512, 16, 128));
+                            tmem_cp_32x128b_warpx4(tmem_sfb + a * 8,
+                                                   make_smem_desc_noswizzle(sf_addr + kAtoms * 512 + a * 512, 16, 128));
+                            tmem_cp_32x128b_warpx4(tmem_sfb + a * 8 + 4,
+                                                   make_smem_desc_noswizzle(sf_addr + 2 * kAtoms * 512 + a * 512, 16, 128));
+                        }
+                        for (int k = 0; k < mmas; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);   // 64 e2m1 = 32 bytes of a row
+                            const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t sf_id = static_cast<uint32_t>(k & 1) * 2u;
+                            umma_fp4<false>(tmem_base, ad, bd, make_idesc_fp4(BM, BN, sf_id, sf_id, 1u), tmem_sfa + (k >> 1) * 4,
+                                            tmem_sfb + (k >> 1) * 8, (kb | k) != 0);
+                        }
+                    } else {
+                        const uint32_t tmem_sfb = tmem_sfa + 4;
+                        tmem_cp_32x128b_warpx4(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
+                        tmem_cp_32x128b_warpx4(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
+                        tmem_cp_32x128b_warpx4(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));
 #pragma unroll
-                    for (int k = 0; k < MX_BK / 32; ++k) {
-                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
-                        // B MN-major (8-bit): 128-column chunks 128*MX_BK B apart, 8-row (K) groups 1024 B
-                        // apart, 32 K-rows = 4096 B
-                        const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
-                                                 : make_smem_desc(b_addr + k * 32, 16, 1024);
-                        const uint32_t idesc = make_idesc_mxf8(BM, BN, k, k) | (B_MN ? (1u << 16) : 0u);
-                        umma_mxf8(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        for (int k = 0; k < MX_BK / 32; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                            // B MN-major (8-bit): 128-column chunks 128*MX_BK B apart, 8-row (K) groups 1024 B
+                            // apart, 32 K-rows = 4096 B
+                            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
+                                                     : make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t idesc = make_idesc_mxf8(BM, BN, k, k) | (B_MN ? (1u << 16) : 0u);
+                            umma_mxf8(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        }
                     }
                     umma_commit(&sh->empty[st]);
                 }
@@ -292,7 +339,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) mx_allgather_gemm_kernel(cons
                 // one unit with the chunk's scale atoms; destination rank-1 first
                 const int units_per_dest = mt * kMxFlagsPerChunk;
                 const int total = (R - 1) * units_per_dest;
-                const size_t row_bytes = static_cast<size_t>(p.K);
+                const size_t row_bytes = static_cast<size_t>(Kb);
                 const int lane_id = cta * kMxPushLanes + ctid;
                 const int n_lanes = p.ctas_per_rank * kMxPushLanes;
                 uint8_t *buf = smem_push + ctid * kPushPieceBytes;

@@ -48,16 +48,17 @@ static int encode_atoms(const DriverApi *api, CUtensorMap *tm, const void *base,
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// one half of the (double-buffered) gathered region: codes, then scale atoms
-static size_t mx_ag_half_bytes(int world, int m, int k) {
-    const size_t data = align_up(static_cast<size_t>(world) * m * k, 1024);
+// one half of the (double-buffered) gathered region: codes (k bytes per row; k/2 for 4-bit codes), then scale atoms
+static size_t mx_ag_half_bytes(int world, int m, int k, int fmt = MX_FP8) {
+    const size_t row = fmt == MX_FP4 ? k / 2 : k;
+    const size_t data = align_up(static_cast<size_t>(world) * m * row, 1024);
     return align_up(data + static_cast<size_t>(world) * sf_atoms_bytes(m, k), 1024);
 }
 
-size_t mx_ag_symmetric_bytes(int world, int m, int n, int k) {
+size_t mx_ag_symmetric_bytes(int world, int m, int n, int k, int fmt) {
     (void)n;
     if (world <= 1) return 0;
-    return 2 * mx_ag_half_bytes(world, m, k);
+    return 2 * mx_ag_half_bytes(world, m, k, fmt);
 }
 
 size_t mx_ag_workspace_bytes(int m, int n, int k) {
@@ -85,17 +86,18 @@ static int launch_pair_k(const MxParams &p, int grid, bool coop, cudaStream_t st
     return CATCCOS_OK;
 }
 
-template <typename TOut, bool B_MN>
+template <typename TOut, bool B_MN, int FMT = MX_FP8>
 static int launch_k(const MxParams &p, int grid, bool coop, cudaStream_t stream) {
-    auto kern = mx_allgather_gemm_kernel<TOut, B_MN>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxSmemBytes);
+    auto kern = mx_allgather_gemm_kernel<TOut, B_MN, FMT>;
+    constexpr int kSmem = MxCfg<FMT>::kSmemBytes;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e == cudaSuccess) {
         if (coop) {
             void *args[] = {const_cast<MxParams *>(&p)};
             e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
-                                            kMxSmemBytes, stream);
+                                            kSmem, stream);
         } else {
-            kern<<<grid, kGemmThreads, kMxSmemBytes, stream>>>(p);
+            kern<<<grid, kGemmThreads, kSmem, stream>>>(p);
             e = cudaGetLastError();
         }
     }
@@ -107,7 +109,7 @@ static int launch_k(const MxParams &p, int grid, bool coop, cudaStream_t stream)
 }
 
 int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t block_num, const MxAgArgs *args,
-                               void *symmetric, int m, int n, int k, int trans_b) {
+                               void *symmetric, int m, int n, int k, int trans_b, int fmt) {
     Team *t = team();
     if (!t) {
         set_error("symmetric heap not initialised (call catccos_shmem_init first)");
@@ -127,10 +129,19 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
         set_error("unsupported shape m=%d n=%d k=%d (k multiple of 32, n multiple of 16)", m, n, k);
         return CATCCOS_ERR_INVALID;
     }
+    if (fmt != MX_FP8 && fmt != MX_FP4) {
+        set_error("unknown block-scaled format %d", fmt);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (fmt == MX_FP4 && (!trans_b || (k % 64) != 0)) {
+        set_error("MXFP4 AllGather-Matmul needs K-major operands (transB = 1) and k a multiple of 64 (k=%d transB=%d)", k, trans_b);
+        return CATCCOS_ERR_INVALID;
+    }
+    const int kbytes = fmt == MX_FP4 ? k / 2 : k;      // bytes of one operand row
     const int R = t->n_pes;
     const int n_local = t->emulated ? R : 1;
     const int mt = (m + BM - 1) / BM;
-    const size_t need = mx_ag_symmetric_bytes(R, m, n, k);
+    const size_t need = mx_ag_symmetric_bytes(R, m, n, k, fmt);
     uint64_t symm_off = 0, sf_off = 0;
     const uint32_t epoch = t->epoch + 1;
     LaunchSlot slot{0, epoch};
@@ -143,13 +154,13 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
             return CATCCOS_ERR_INVALID;
         }
         symm_off = static_cast<uint64_t>(sp - b);
-        sig = slot_sig(0x4D584147ull, static_cast<uint64_t>(m));
+        sig = slot_sig(0x4D584147ull + static_cast<uint64_t>(fmt), static_cast<uint64_t>(m));
         sig = slot_sig(sig, static_cast<uint64_t>(n));
         sig = slot_sig(sig, static_cast<uint64_t>(k));
         sig = slot_sig(sig, symm_off);
         slot = peek_slot(t, sig, epoch);      // which half of the region this launch uses
-        symm_off += static_cast<uint64_t>(slot.half) * mx_ag_half_bytes(R, m, k);
-        sf_off = symm_off + align_up(static_cast<size_t>(R) * m * k, 1024);
+        symm_off += static_cast<uint64_t>(slot.half) * mx_ag_half_bytes(R, m, k, fmt);
+        sf_off = symm_off + align_up(static_cast<size_t>(R) * m * kbytes, 1024);
         if (kFlagOpBase + static_cast<size_t>(R) * mt * kMxFlagsPerChunk > kFlagWords) {
             set_error("shape needs more flags than the flag region holds");
             return CATCCOS_ERR_INVALID;
@@ -157,6 +168,7 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
     }
     bool use_pair = true;      // CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
     if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = atoi(e) != 0;
+    if (fmt == MX_FP4) use_pair = false;      // the 4-bit format exists in the one-CTA kernel
     const int kb4 = (k + 127) / 128;
     MxParams p;
     memset(&p, 0, sizeof(p));
@@ -178,8 +190,8 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
                      : sf_to_atoms_launch(stream, a.b_scale, 1, n, kblocks, 0, sfb);
         if (rc) return rc;
         MxRankArgs &ra = p.ranks[l];
-        if ((rc = encode_u8(api, &ra.tmA, a.A, k, m, MX_BK, BM))) return rc;
-        rc = trans_b ? encode_u8(api, &ra.tmB, a.B, k, n, MX_BK, use_pair ? 128 : BN)
+        if ((rc = encode_u8(api, &ra.tmA, a.A, kbytes, m, MX_BK, BM))) return rc;
+        rc = trans_b ? encode_u8(api, &ra.tmB, a.B, kbytes, n, MX_BK, use_pair ? 128 : BN)
                      : encode_u8(api, &ra.tmB, a.B, n, k, 128, MX_BK);
         if (rc) return rc;
         if (use_pair) {
@@ -194,7 +206,7 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
         }
         if (R > 1) {
             const int pe = t->emulated ? l : t->my_pe;
-            if ((rc = encode_u8(api, &ra.tmAg, t->base[pe] + symm_off, k, static_cast<uint64_t>(R) * m, MX_BK, BM)))
+            if ((rc = encode_u8(api, &ra.tmAg, t->base[pe] + symm_off, kbytes, static_cast<uint64_t>(R) * m, MX_BK, BM)))
                 return rc;
         } else {
             ra.tmAg = ra.tmA;
@@ -234,6 +246,9 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
         return b_mn ? launch_pair_k<__half, true>(p, g2, coop, stream) : launch_pair_k<__half, false>(p, g2, coop, stream);
     }
     const int grid = per_rank * n_local;
+    if (fmt == MX_FP4)
+        return out_dtype == 27 ? launch_k<__nv_bfloat16, false, MX_FP4>(p, grid, coop, stream)
+                               : launch_k<__half, false, MX_FP4>(p, grid, coop, stream);
     if (out_dtype == 27)
         return b_mn ? launch_k<__nv_bfloat16, true>(p, grid, coop, stream) : launch_k<__nv_bfloat16, false>(p, grid, coop, stream);
     return b_mn ? launch_k<__half, true>(p, grid, coop, stream) : launch_k<__half, false>(p, grid, coop, stream);

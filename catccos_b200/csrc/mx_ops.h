@@ -14,12 +14,13 @@ struct MxAgArgs {
     uint8_t *workspace;      // mx_ag_workspace_bytes() bytes of device memory
 };
 
-size_t mx_ag_symmetric_bytes(int world, int m, int n, int k);
+// fmt: 0 = MXFP8 (e4m3 codes, k bytes per row), 1 = MXFP4 (e2m1 codes, two per byte, K-major operands only)
+size_t mx_ag_symmetric_bytes(int world, int m, int n, int k, int fmt = 0);
 size_t mx_ag_workspace_bytes(int m, int n, int k);
 
 // AllGather-Matmul on MXFP8 operands; out_dtype 1 = fp16, 27 = bf16.  m = rows held by one rank.
 int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t block_num, const MxAgArgs *args,
-                               void *symmetric, int m, int n, int k, int trans_b);
+                               void *symmetric, int m, int n, int k, int trans_b, int fmt = 0);
 
 // Matmul-ReduceScatter on MXFP8 operands (codes `code_format` 0 = e4m3, 1 = e5m2; E8M0 scales per 32 along k):
 // D_r = rows r*m/R .. of sum_s A_s B_s.  m = rows of the full product, k = this rank's share of the

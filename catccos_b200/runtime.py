@@ -15,6 +15,7 @@ ALLGATHER_MATMUL_WITH_GATHER_RESULT = 5
 ALLGATHER_MATMUL_REMOTE_READ = 20
 MXFP8_MATMUL_REDUCE_SCATTER = 18
 FP8_MX_ALLGATHER_MATMUL = 22
+FP4_MX_ALLGATHER_MATMUL = 23
 MX_QUANT_ALLGATHER = 24
 FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25
 FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27

@@ -69,6 +69,7 @@ enum {
     CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = 18,
     CATCCOS_ALLGATHER_MATMUL_REMOTE_READ = 20,
     CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL = 22,
+    CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL = 23,
     CATCCOS_MX_QUANT_ALLGATHER = 24,
     CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25,
     CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27,
@@ -210,6 +211,15 @@ CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulRemoteReadBF16);
  * reference writes fp16, examples/ascend950_fp8_mx_allgather_matmul/..._host.h:33; BF16 is added). */
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16);
+
+/* tests/dynamic_tiling/include/launch_map.h:95 (Ascend950Fp4MxAllGatherMatmul; operator class
+ * examples/ascend950_fp4_mx_allgather_matmul/ascend950_fp4_mx_allgather_matmul_host.h:88): MXFP4 operands --
+ * ptrA = e2m1 codes [m, k/2] (two per byte, low nibble first), ptrB = [n, k/2] (transB = 1 only: 4-bit operands
+ * are K-major on tcgen05), customPtrs = {aScale [m, k/64, 2], bScale [n, k/64, 2]} E8M0 bytes, one per 32 values
+ * along k; k % 64 == 0.  ptrC = 16-bit [rankSize*m, n]; `workspace` = catccos_workspace_bytes() bytes.  One-CTA
+ * tcgen05.mma.kind::mxf4nvf4 kernel with the all-gather of codes and scale atoms fused in. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulBF16);
 
 /* MXFP8 Matmul-ReduceScatter (MatmulReduceScatterMxTla, include/catccos/dgemm/kernel/matmul_reduce_scatter_mx_tla.hpp:39;
  * operator "Ascend950MxFp8MatmulReduceScatter", examples/ascend950_mxfp8_matmul_reduce_scatter/main.cpp:32-141 and

@@ -30,6 +30,7 @@ enum CocCommType {
     ALLGATHER_MATMUL_REMOTE_READ = CATCCOS_ALLGATHER_MATMUL_REMOTE_READ,
     ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER,
     ASCEND950_FP8_MX_ALLGATHER_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL,
+    ASCEND950_FP4_MX_ALLGATHER_MATMUL = CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL,
     MX_QUANT_ALLGATHER = CATCCOS_MX_QUANT_ALLGATHER,
     ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV,
     ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL,
@@ -88,6 +89,7 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"agmmwg", ALLGATHER_MATMUL_WITH_GATHER_RESULT},
         {"agmmrr", ALLGATHER_MATMUL_REMOTE_READ},
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
+        {"a5fp4mxagmm", ASCEND950_FP4_MX_ALLGATHER_MATMUL},
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
         {"a5moe", ASCEND950_DISPATCH_FFN_COMBINE},
         {"mxqtag", MX_QUANT_ALLGATHER},
@@ -111,6 +113,7 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ALLGATHER_MATMUL_WITH_GATHER_RESULT, "AllGatherMatmulWithGatherResult"},
         {ALLGATHER_MATMUL_REMOTE_READ, "AllGatherMatmulRemoteRead"},
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
+        {ASCEND950_FP4_MX_ALLGATHER_MATMUL, "Ascend950Fp4MxAllGatherMatmul"},
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
         {ASCEND950_DISPATCH_FFN_COMBINE, "Ascend950DispatchFFNCombine"},
         {MX_QUANT_ALLGATHER, "MxQuantAllGather"},

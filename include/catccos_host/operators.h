@@ -184,6 +184,37 @@ public:
 };
 REGISTER_OPERATOR("Ascend950Fp8MxAllGatherMatmul", Ascend950Fp8MxAllGatherMatmulOperator);
 
+// MXFP4 AllGather-Matmul (examples/ascend950_fp4_mx_allgather_matmul/ascend950_fp4_mx_allgather_matmul_host.h:17-140):
+// e2m1 codes packed two per byte, A [m, k/2], B^T [n, k/2] (run with transB = 1), E8M0 scales per 32 along k.
+class Ascend950Fp4MxAllGatherMatmulOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t sizeA = static_cast<size_t>(t.m) * t.k / 2, sizeB = static_cast<size_t>(t.k) / 2 * t.n;
+        const size_t kb = (static_cast<size_t>(t.k) / 32 + 1) / 2 * 2;
+        const size_t sizeC = static_cast<size_t>(t.m) * t.rankSize * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "input_a_", rankId), sizeA),
+                               DeviceBufferFromFile(RankFile(dataFile, "input_b_", rankId), sizeB), DeviceZeros(sizeC),
+                               DeviceBufferFromFile(RankFile(dataFile, "input_a_scale_", rankId), t.m * kb, 127),
+                               DeviceBufferFromFile(RankFile(dataFile, "input_b_scale_", rankId), t.n * kb, 127));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_" + std::to_string(rankId) + ".bin", params.ptrC,
+                                        static_cast<size_t>(t.m) * t.rankSize * t.n * 2);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &t) override {
+        return catccos_workspace_bytes(ASCEND950_FP4_MX_ALLGATHER_MATMUL, FP16, &t);
+    }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP4_MX_ALLGATHER_MATMUL; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return t.m > 0 && t.k % 64 == 0 && t.n % 16 == 0 && rankSize <= MAX_RANK_SIZE &&
+               catccos_symmetric_bytes(ASCEND950_FP4_MX_ALLGATHER_MATMUL, FP16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950Fp4MxAllGatherMatmul", Ascend950Fp4MxAllGatherMatmulOperator);
+
 // MXFP8 Matmul-ReduceScatter (examples/ascend950_mxfp8_matmul_reduce_scatter/ascend950_mxfp8_matmul_reduce_scatter_host.h):
 // float8_e5m2 operands, customPtrs = {aScale, bScale}, rank r's rows written at offset r*size of output.bin.
 class Ascend950MxFp8MatmulReduceScatterOperator : public CatccosOperator {

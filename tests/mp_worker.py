@@ -59,6 +59,27 @@ def main():
         rc, words = rt.last_status()
         assert rc == 0, words
         check(f"mmar#{rep}", e, gold)
+    # AllGather-Matmul data-flow variants: remote read (twice, so the region is reused) and gather result
+    m, k, n = 384, 512, 768
+    a, b = inputs.allgather_matmul_inputs(world, m, k, n, torch.bfloat16)
+    gold = dense.golden_allgather_matmul(a, b)[rank]
+    for rep in range(2):
+        c = torch.full((world * m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        rt.launch(rt.ALLGATHER_MATMUL_REMOTE_READ, a[rank].cuda(), b[rank].cuda(), c, symm, rt.tiling(m, k, n, world))
+        rc, words = rt.last_status()
+        assert rc == 0, words
+        check(f"agmm_remote_read#{rep}", c, gold)
+    c = torch.full((world * m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    g = torch.full((world * m, k), float("nan"), dtype=torch.bfloat16, device="cuda")
+    rt.launch(rt.ALLGATHER_MATMUL_WITH_GATHER_RESULT, a[rank].cuda(), b[rank].cuda(), c, symm, rt.tiling(m, k, n, world),
+              custom=[g])
+    rc, words = rt.last_status()
+    assert rc == 0, words
+    check("agmm_gather_result", c, gold)
+    same = torch.equal(g.cpu().view(torch.int16), torch.cat(a, dim=0).view(torch.int16))
+    print(f"[rank {rank}] agmm_gather_result: gathered A bit-exact {same}", flush=True)
+    if not same:
+        failures.append(("agmm_gather_result gathered A", 1.0))
     # MXFP8 AllGather-Matmul (scale atoms and data pushed to the peers)
     from oracle import mxquant, moe
     import numpy as np
