@@ -681,6 +681,26 @@ def main():
         barrier()
         exposed = max(0.0, (ms_per_step - compute_only_ms) / ms_per_step)
 
+    # MoE: one more step with CUDA events between its stages (outside the timed region); every stage's time as the
+    # max over ranks, plus the times of the rank that receives the most rows
+    moe_stage_ms = None
+    if args.op == "moe":
+        check(lib().catccos_debug_set_flags(2))
+        step()
+        barrier()
+        check(lib().catccos_debug_set_flags(0))
+        buf = (ctypes.c_float * 12)()
+        n_st = lib().catccos_debug_moe_stage_ms(buf, 12)
+        names = ["route", "quant_dispatch", "weight_scale_atoms", "wait_dispatch", "recv_scale_atoms", "gemm1_swiglu_quant",
+                 "gemm2_combine", "unpermute"]
+        if n_st == len(names):
+            mine = torch.tensor([buf[i] for i in range(n_st)], dtype=torch.float64, device="cuda")
+            worst = mine.clone()
+            if world > 1:
+                dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            moe_stage_ms = {"max_over_ranks": {nm: round(float(v), 4) for nm, v in zip(names, worst.tolist())},
+                            "rank0": {nm: round(float(v), 4) for nm, v in zip(names, mine.tolist())}}
+
     # end to end through the host-buffer entry point: H2D of the step's inputs, fused launch, D2H of the result,
     # every step.  Dense operators copy A and B; the block-scaled GEMM and the MoE keep their weights (and weight
     # scales) resident after the first call and copy activations / routing every step.
@@ -824,6 +844,7 @@ def main():
                 line["config"]["variant"] = args.variant
             if args.op == "moe":
                 line["config"]["hottest_rank_rows_over_mean"] = moe_imbalance
+                line["stage_ms"] = moe_stage_ms
             if args.op == "mxag":
                 line["config"]["activation_quantisation"] = "inside every step" if args.mx_quant_in_step else \
                     "at set-up (operands reach the operator as MXFP8, as in the reference)"

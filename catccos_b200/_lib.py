@@ -77,6 +77,7 @@ SIGNATURES = {
                                                  ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
                                                  ctypes.c_uint32, ctypes.POINTER(CocTilingParams), ctypes.c_uint32,
                                                  ctypes.c_uint32, ctypes.c_uint32]),
+    "catccos_debug_moe_stage_ms": (ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.c_int32]),
     "catccos_mx_quant": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32]),
     "catccos_sf_atoms_bytes": (ctypes.c_size_t, [ctypes.c_uint32, ctypes.c_uint32]),
@@ -100,6 +101,7 @@ for _dt in ("FP16", "BF16"):
 for _dt in ("FP16", "BF16"):
     SIGNATURES[f"LaunchAllGatherMatmulWithGatherResult{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
     SIGNATURES[f"LaunchAllGatherMatmulRemoteRead{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
+    SIGNATURES[f"LaunchAscend950AllToAllMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
 SIGNATURES["LaunchAscend950DispatchFFNCombineBF16"] = (ctypes.c_int, LAUNCH_ARGS)
 SIGNATURES["LaunchAscend950BF16QuantAllGatherFP8E4M3FN"] = (ctypes.c_int, LAUNCH_ARGS)
 for _dt in ("FP16", "BF16"):

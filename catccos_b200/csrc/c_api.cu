@@ -34,7 +34,8 @@ int dense_op_of(int32_t commType) {
         case CATCCOS_ALLGATHER_MATMUL:
         case CATCCOS_ASCEND950_ALLGATHER_MATMUL:
         case CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT:
-        case CATCCOS_ALLGATHER_MATMUL_REMOTE_READ: return OP_AGMM;
+        case CATCCOS_ALLGATHER_MATMUL_REMOTE_READ:
+        case CATCCOS_ASCEND950_ALLTOALL_MATMUL: return OP_AGMM;
         case CATCCOS_MATMUL_REDUCE_SCATTER:
         case CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER: return OP_MMRS;
         default: return -1;
@@ -42,7 +43,10 @@ int dense_op_of(int32_t commType) {
 }
 
 int dense_flow_of(int32_t commType) {
-    return commType == CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT ? 1 : commType == CATCCOS_ALLGATHER_MATMUL_REMOTE_READ ? 2 : 0;
+    return commType == CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT ? 1
+           : commType == CATCCOS_ALLGATHER_MATMUL_REMOTE_READ      ? 2
+           : commType == CATCCOS_ASCEND950_ALLTOALL_MATMUL         ? 3
+                                                                    : 0;
 }
 
 int check_tiling(const CocTilingParams *tiling) {
@@ -64,7 +68,8 @@ int check_tiling(const CocTilingParams *tiling) {
 
 // `flow`: 0 = the operator as such; 1 = AllGather-Matmul that also returns the gathered A in customPtrs[0]
 // (examples/allgather_matmul_with_gather_result/allgather_matmul_with_gather_result_host.h:54); 2 = remote-read
-// AllGather-Matmul (examples/allgather_matmul_remote_read).
+// AllGather-Matmul (examples/allgather_matmul_remote_read); 3 = AllToAll-Matmul (examples/ascend950_alltoall_matmul:
+// tiling.m = rows of every rank's A, block d of which goes to rank d).
 int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
                      uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB, int flow = 0) {
     int rc = check_tiling(tiling);
@@ -91,9 +96,17 @@ int launch_dense_abi(int op, int dtype, void *stream, uint32_t blockNum, Catccos
             args[i].gather_out = params[i].customPtrs[0];
         }
     }
-    return launch_dense(op, dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric,
-                        static_cast<int>(tiling->m), static_cast<int>(tiling->n), static_cast<int>(tiling->k),
-                        static_cast<int>(transA), static_cast<int>(transB), flow == 2 ? AG_REMOTE_READ : AG_PUSH);
+    int m = static_cast<int>(tiling->m);
+    if (flow == 3) {
+        if (m % t->n_pes != 0) {
+            set_error("AllToAll-Matmul needs m (%d) divisible by the world size (%d)", m, t->n_pes);
+            return CATCCOS_ERR_INVALID;
+        }
+        m /= t->n_pes;
+    }
+    return launch_dense(op, dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric, m,
+                        static_cast<int>(tiling->n), static_cast<int>(tiling->k), static_cast<int>(transA),
+                        static_cast<int>(transB), flow == 2 ? AG_REMOTE_READ : flow == 3 ? AG_ALLTOALL : AG_PUSH);
 }
 
 int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
@@ -447,6 +460,14 @@ int catccos_debug_set_flags(uint32_t flags) {
     return CATCCOS_OK;
 }
 
+int catccos_debug_moe_stage_ms(float *ms, int32_t capacity) {
+    if (!ms || capacity < 1) {
+        set_error("catccos_debug_moe_stage_ms: bad arguments");
+        return -1;
+    }
+    return moe_stage_ms(ms, capacity);
+}
+
 int catccos_debug_set_trace(void *device_buf) {
     if (!team()) {
         set_error("symmetric heap not initialised");
@@ -549,8 +570,8 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     const int world = tiling->rankSize ? static_cast<int>(tiling->rankSize) : (team() ? team()->n_pes : 1);
     const int op = dense_op_of(commType);
     if (op >= 0)
-        return dense_symmetric_bytes(op, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
-                                     static_cast<int>(tiling->k));
+        return dense_symmetric_bytes(op, world, static_cast<int>(tiling->m) / (dense_flow_of(commType) == 3 ? world : 1),
+                                     static_cast<int>(tiling->n), static_cast<int>(tiling->k));
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL)
         return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k), commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL ? 1 : 0);
@@ -610,6 +631,8 @@ DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulWithGatherResultFP16, 1, CATCCOS_FP16)
 DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulWithGatherResultBF16, 1, CATCCOS_BF16)
 DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulRemoteReadFP16, 2, CATCCOS_FP16)
 DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulRemoteReadBF16, 2, CATCCOS_BF16)
+DENSE_FLOW_LAUNCH(LaunchAscend950AllToAllMatmulFP16, 3, CATCCOS_FP16)
+DENSE_FLOW_LAUNCH(LaunchAscend950AllToAllMatmulBF16, 3, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchMatmulAllReduceFP16, OP_MMAR, CATCCOS_FP16)
 DENSE_LAUNCH(LaunchMatmulAllReduceBF16, OP_MMAR, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchAllGatherMatmulFP16, OP_AGMM, CATCCOS_FP16)

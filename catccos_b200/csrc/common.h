@@ -64,6 +64,7 @@ struct FusedParams {
     int rs_fp16;                      // reduce family: partial tiles cross the link as fp16 (11-bit mantissa) whatever
                                       // the output type; 0: in the output type
     int ag_group;                     // 256-row tiles per L2 group of the AllGather-Matmul tile order (sched.h)
+    int ag_a2a;                       // AllToAll-Matmul: A holds world * M rows; block d goes to rank d (block `rank` stays)
     int ag_pull;                      // AG-MM data flow: 0 = every rank pushes its rows into the peers' gathered regions;
                                       // 1 = remote read: every rank stages its rows in its own region and the peers fetch them
     unsigned long long *trace;        // optional: kTraceSlots %globaltimer stamps per CTA (nullptr = off)

@@ -206,7 +206,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         set_error("transA=1 is not supported");
         return CATCCOS_ERR_INVALID;
     }
-    if ((variant != AG_PUSH && variant != AG_REMOTE_READ) || (variant != AG_PUSH && op != OP_AGMM)) {
+    if ((variant != AG_PUSH && variant != AG_REMOTE_READ && variant != AG_ALLTOALL) || (variant != AG_PUSH && op != OP_AGMM)) {
         set_error("data-flow variant %d does not exist for operator %d", variant, op);
         return CATCCOS_ERR_INVALID;
     }
@@ -268,14 +268,14 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
                   "(unset CATCCOS_TWO_CTA=0)");
         return CATCCOS_ERR_INVALID;
     }
-    if (wants_gather && op != OP_AGMM) {
+    if (wants_gather && (op != OP_AGMM || variant == AG_ALLTOALL)) {
         set_error("only AllGather-Matmul returns the gathered A");
         return CATCCOS_ERR_INVALID;
     }
     FusedParams p;
     memset(&p, 0, sizeof(p));
     const CUtensorMapDataType dt = dtype == 27 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const int a_rows = m;   // rows of the caller's A in every operator
+    const int a_rows = variant == AG_ALLTOALL ? R * m : m;   // rows of the caller's A
     for (int l = 0; l < n_local; ++l) {
         const DenseArgs &a = args[l];
         if (!a.A || !a.B || !a.C || (reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
@@ -340,6 +340,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.status = t->status_dev;
     p.rs_fp16 = rs_exchange_fp16();
     p.ag_pull = variant == AG_REMOTE_READ ? 1 : 0;
+    p.ag_a2a = variant == AG_ALLTOALL ? 1 : 0;
     p.sched = t->sched_dev;
     p.trace = t->trace_dev;
 

@@ -16,6 +16,8 @@ struct DenseArgs {
 enum AgVariant : int {
     AG_PUSH = 0,          // every rank writes its rows into the peers' gathered regions (default)
     AG_REMOTE_READ = 1,   // every rank stages its rows in its own symmetric region; the peers read them from there
+    AG_ALLTOALL = 2,      // AllToAll-Matmul: A is [R*m, k]; block d is pushed to rank d, which multiplies the R blocks it
+                          // holds afterwards (block s from rank s) by its B -> C [R*m, n]
 };
 
 // Bytes of the caller's symmetric buffer the operator uses (0 for a single rank).

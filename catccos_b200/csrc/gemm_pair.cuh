@@ -134,7 +134,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                     }
                 }
                 const CUtensorMap *tma = gathered ? &ra.tmAg : &ra.tmA;
-                const int a_row = (gathered ? s * p.M : 0) + row_in_src;
+                const int a_row = (gathered ? s * p.M : (p.ag_a2a ? rank * p.M : 0)) + row_in_src;
                 const int n_half = ni * BN + static_cast<int>(cr) * 128;         // this CTA's 128 columns of B
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int st = it % kPStages;
@@ -361,8 +361,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
                     unit_rows(cu, r0, r1);
                     wait_entered(d);
                     if (!ok) break;
-                    if (r1 > r0)
-                        copy_rows(static_cast<const uint8_t *>(ra.A) + r0 * row_bytes,
+                    if (r1 > r0)      // AllToAll-Matmul sends block d of A, AllGather-Matmul the whole A
+                        copy_rows(static_cast<const uint8_t *>(ra.A) + (static_cast<size_t>(p.ag_a2a ? d * p.M : 0) + r0) * row_bytes,
                                   p.heap_base[d] + p.symm_off + (static_cast<size_t>(rank) * p.M + r0) * row_bytes,
                                   (r1 - r0) * row_bytes);
                     if (!ok) break;

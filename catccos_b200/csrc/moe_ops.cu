@@ -10,6 +10,10 @@
 
 namespace cb {
 
+static cudaEvent_t g_stage_ev[12] = {};     // debug flag 2: events between the stages of the last MoE launch
+static int g_stage_count = 0;
+
+
 static size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 int moe_rows_cap(int world, int m, int top_k, int experts_per_rank) {
@@ -286,30 +290,64 @@ int launch_moe_dispatch_ffn_combine(cudaStream_t stream, uint32_t block_num, con
         }
     }
 
+    // debug flag 2: CUDA events between the stages of this launch (read back with moe_stage_ms)
+    const bool timed = (t->debug_flags & 2u) != 0;
+    int stage = 0;
+    auto mark = [&]() {
+        if (!timed) return;
+        if (!g_stage_ev[stage]) cudaEventCreate(&g_stage_ev[stage]);
+        cudaEventRecord(g_stage_ev[stage], stream);
+        ++stage;
+    };
     int rc;
+    mark();
     if ((rc = moe_launch_route(p, stream))) return rc;
+    mark();
     if ((rc = moe_launch_dispatch(p, stream))) return rc;
+    mark();
     // weight scales -> atoms (independent of the exchange)
     for (int l = 0; l < n_local; ++l) {
         if ((rc = sf_to_atoms_launch(stream, args[l].w1_scale, 0, el * n, k / 32, k / 32, ws[l].w1_atoms))) return rc;
         if ((rc = sf_to_atoms_launch(stream, args[l].w2_scale, 0, el * k, (n / 2) / 32, (n / 2) / 32, ws[l].w2_atoms)))
             return rc;
     }
+    mark();
     if ((rc = moe_launch_wait_dispatch(p, stream))) return rc;
+    mark();
     for (int l = 0; l < n_local; ++l) {
         const int pe = t->emulated ? l : t->my_pe;
         if ((rc = sf_to_atoms_launch(stream, t->base[pe] + p.lay.recv_scale_off, 0, z.rows_cap, k / 32, z.sld1,
                                      ws[l].recv_atoms)))
             return rc;
     }
+    mark();
     if (use_pair) {
         if ((rc = launch_pair_gemm<1, __nv_bfloat16, false>(q1, stream))) return rc;
+        mark();
         if ((rc = launch_pair_gemm<2, __nv_bfloat16, false>(q2, stream))) return rc;
     } else {
         if ((rc = launch_gemm<1>(g1, stream))) return rc;
+        mark();
         if ((rc = launch_gemm<2>(g2, stream))) return rc;
     }
-    return moe_launch_unpermute(p, stream);
+    mark();
+    rc = moe_launch_unpermute(p, stream);
+    mark();
+    g_stage_count = timed ? stage : 0;
+    return rc;
+}
+
+// Milliseconds of the stages of the last MoE launch made with debug flag 2 set (after the stream has drained):
+// route, quant-dispatch, weight scale atoms, wait for the dispatch, received scale atoms, GEMM1, GEMM2, un-permute.
+int moe_stage_ms(float *ms, int capacity) {
+    int n = 0;
+    for (int i = 0; i + 1 < g_stage_count && n < capacity; ++i, ++n) {
+        if (cudaEventElapsedTime(&ms[n], g_stage_ev[i], g_stage_ev[i + 1]) != cudaSuccess) {
+            set_error("stage events are not complete (synchronise the stream first)");
+            return -1;
+        }
+    }
+    return n;
 }
 
 // ------------------------------------------------ standalone all-to-all-v operators ----

@@ -47,6 +47,8 @@ int a2av_launch_copy_out(const MoeParams &p, int n_cols, cudaStream_t stream);
 int moe_launch_route(const MoeParams &p, cudaStream_t stream);
 int moe_launch_dispatch(const MoeParams &p, cudaStream_t stream);
 int moe_launch_unpermute(const MoeParams &p, cudaStream_t stream);
+// stage times of the last dispatch-FFN-combine launch made with debug flag 2 set; returns the number of stages
+int moe_stage_ms(float *ms, int capacity);
 int moe_launch_wait_dispatch(const MoeParams &p, cudaStream_t stream);
 
 }  // namespace cb

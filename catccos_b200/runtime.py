@@ -20,6 +20,7 @@ MX_QUANT_ALLGATHER = 24
 FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25
 FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27
 DISPATCH_FFN_COMBINE = 32
+ALLTOALL_MATMUL = 101
 FP16, BF16, FP8E4M3FN = 1, 27, 36
 
 _DTYPE = {torch.float16: FP16, torch.bfloat16: BF16}

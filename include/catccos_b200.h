@@ -73,7 +73,10 @@ enum {
     CATCCOS_MX_QUANT_ALLGATHER = 24,
     CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25,
     CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27,
-    CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE = 32
+    CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE = 32,
+    /* not in the reference's enum (its example instantiates the device template directly,
+     * examples/ascend950_alltoall_matmul/main.cpp): a value of this library's own */
+    CATCCOS_ASCEND950_ALLTOALL_MATMUL = 101
 };
 enum { CATCCOS_FP16 = 1, CATCCOS_INT8 = 2, CATCCOS_BF16 = 27, CATCCOS_FP8E4M3FN = 36 };
 
@@ -133,6 +136,11 @@ CATCCOS_API int catccos_debug_set_flags(uint32_t flags);
  * 16 * 8 bytes per CTA of the largest grid, zeroed by the caller) receives per-CTA %globaltimer
  * stamps and accumulated wait times of later launches; NULL switches tracing off. */
 CATCCOS_API int catccos_debug_set_trace(void *device_buf);
+/* With bit 1 of catccos_debug_set_flags set, a dispatch-FFN-combine launch records CUDA events between its
+ * stages; after the stream has drained this returns their count and fills `ms` with the stage times in order:
+ * route, quant-dispatch, weight scale atoms, wait for the dispatch, received scale atoms, GEMM1, GEMM2,
+ * un-permute.  -1 on error. */
+CATCCOS_API int catccos_debug_moe_stage_ms(float *ms, int32_t capacity);
 
 /* The work orders of the CTA-pair kernels, computed on the host by the very functions the kernels use
  * (no device needed; no reference counterpart of their own — the reference's orders are CommSwizzle::GetCoord,
@@ -203,6 +211,13 @@ CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulWithGatherResultFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulWithGatherResultBF16);
 CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulRemoteReadFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulRemoteReadBF16);
+
+/* AllToAll-Matmul (examples/ascend950_alltoall_matmul, include/catccos/dgemm/kernel/ascend950_alltoall_matmul.hpp;
+ * golden examples/ascend950_alltoall_matmul/scripts/gen_data.py:19-86): every rank holds A [m, k] with m divisible
+ * by rankSize; rows [j*m/R, (j+1)*m/R) go to rank j, which multiplies the R blocks it holds afterwards (block i from
+ * rank i) by its B [k, n]: ptrC = [m, n].  The AllGather-Matmul kernel with a per-destination source block. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllToAllMatmulFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllToAllMatmulBF16);
 
 /* tests/dynamic_tiling/impl/kernel_fp16_ascend950.cpp:274 (MxAllGatherMatmulTla,
  * include/catccos/dgemm/kernel/mx_allgather_matmul.hpp:27-428): ptrA/ptrB = e4m3 operands,

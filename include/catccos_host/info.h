@@ -35,7 +35,8 @@ enum CocCommType {
     ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV,
     ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL,
     ASCEND950_DISPATCH_FFN_COMBINE = CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE,
-    UNKNOWN = 36
+    UNKNOWN = 36,
+    ASCEND950_ALLTOALL_MATMUL = CATCCOS_ASCEND950_ALLTOALL_MATMUL      // no counterpart in the reference's enum
 };
 
 enum CocDataType { FP16 = CATCCOS_FP16, INT8 = CATCCOS_INT8, BF16 = CATCCOS_BF16, FP8E4M3FN = CATCCOS_FP8E4M3FN };
@@ -88,6 +89,7 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"a5mmrs", ASCEND950_MATMUL_REDUCE_SCATTER},
         {"agmmwg", ALLGATHER_MATMUL_WITH_GATHER_RESULT},
         {"agmmrr", ALLGATHER_MATMUL_REMOTE_READ},
+        {"a5atamm", ASCEND950_ALLTOALL_MATMUL},
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
         {"a5fp4mxagmm", ASCEND950_FP4_MX_ALLGATHER_MATMUL},
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
@@ -112,6 +114,7 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ASCEND950_MATMUL_REDUCE_SCATTER, "Ascend950MatmulReduceScatter"},
         {ALLGATHER_MATMUL_WITH_GATHER_RESULT, "AllGatherMatmulWithGatherResult"},
         {ALLGATHER_MATMUL_REMOTE_READ, "AllGatherMatmulRemoteRead"},
+        {ASCEND950_ALLTOALL_MATMUL, "Ascend950AllToAllMatmul"},
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
         {ASCEND950_FP4_MX_ALLGATHER_MATMUL, "Ascend950Fp4MxAllGatherMatmul"},
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},

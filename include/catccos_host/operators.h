@@ -122,6 +122,31 @@ public:
     CocCommType GetActualKernelType(const CocTilingParams &) override { return ALLGATHER_MATMUL_REMOTE_READ; }
 };
 REGISTER_OPERATOR("AllGatherMatmulRemoteRead", AllGatherMatmulRemoteReadOperator);
+// AllToAll-Matmul (examples/ascend950_alltoall_matmul/ascend950_alltoall_matmul_host.h:17-109): A [m, k] per rank, block j
+// of its rows goes to rank j; C [m, n] per rank, written to output_<rank>.bin.
+class Ascend950AllToAllMatmulOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t aSize = static_cast<size_t>(t.m) * t.k * 2, bSize = static_cast<size_t>(t.k) * t.n * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), aSize),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), bSize),
+                               DeviceZeros(static_cast<size_t>(t.m) * t.n * 2));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_" + std::to_string(rankId) + ".bin", params.ptrC,
+                                        static_cast<size_t>(t.m) * t.n * 2);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &) override { return 0; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_ALLTOALL_MATMUL; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return catccos_host::DenseShapeOk(t) && rankSize >= 1 && rankSize <= MAX_RANK_SIZE && t.m % rankSize == 0 &&
+               catccos_symmetric_bytes(ASCEND950_ALLTOALL_MATMUL, BF16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950AllToAllMatmul", Ascend950AllToAllMatmulOperator);
 
 // D_r = rows r of sum_s A_s * B_s (examples/matmul_reduce_scatter/matmul_reduce_scatter_host.h); m = total rows.
 class MatmulReduceScatterOperator : public CatccosOperator {

@@ -64,3 +64,30 @@ def test_variants_need_the_pair_kernel(monkeypatch):
     a, b = inputs.allgather_matmul_inputs(2, 128, 64, 256, torch.bfloat16)
     with pytest.raises(CatccosError, match="CTA-pair kernel"):
         _run(rt.ALLGATHER_MATMUL_REMOTE_READ, 2, a, b, 128, 64, 256, 0, torch.bfloat16, False)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("chunk,n,k,trans_b,dtype", [(128, 256, 128, 0, torch.bfloat16), (320, 520, 192, 1, torch.float16),
+                                                      (100, 256, 64, 0, torch.bfloat16)])
+def test_alltoall_matmul(world, chunk, n, k, trans_b, dtype):
+    """AllToAll-Matmul: rank j ends up with block j of every rank's A (in rank order) times its own B
+    (examples/ascend950_alltoall_matmul/scripts/gen_data.py:19-86)."""
+    from catccos_b200 import runtime as rt
+    m = chunk * world
+    a, b = inputs.allgather_matmul_inputs(world, m, k, n, dtype)          # every rank: A [m, k], B [k, n]
+    til = rt.tiling(m, k, n, world)
+    need = rt.symmetric_bytes(rt.ALLTOALL_MATMUL, rt.BF16, til)
+    with rt.emulated_team(world, max(need, 1 << 20)):
+        symm = rt.shmem_malloc(max(need, 1024))
+        a_d = [dev(x) for x in a]
+        b_d = [dev(x.t() if trans_b else x) for x in b]
+        c_d = [torch.full((m, n), float("nan"), dtype=dtype, device="cuda") for _ in range(world)]
+        for _ in range(2):
+            rt.launch_emulated(rt.ALLTOALL_MATMUL, a_d, b_d, c_d, symm, til, trans_b=1 if trans_b else 0)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+        outs = [c.cpu() for c in c_d]
+    for j in range(world):
+        assembled = torch.cat([a[i][j * chunk:(j + 1) * chunk] for i in range(world)], dim=0)
+        gold = dense.matmul_fp32(assembled, b[j])
+        assert_close_to_golden(outs[j], gold, k, TOL, f"alltoall-matmul rank {j}")
