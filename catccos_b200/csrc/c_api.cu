@@ -38,6 +38,7 @@ int dense_op_of(int32_t commType) {
         case CATCCOS_ASCEND950_ALLTOALL_MATMUL: return OP_AGMM;
         case CATCCOS_MATMUL_REDUCE_SCATTER:
         case CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER: return OP_MMRS;
+        case CATCCOS_ASCEND950_MATMUL_ALLTOALL: return OP_MMA2A;
         default: return -1;
     }
 }
@@ -633,6 +634,8 @@ DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulRemoteReadFP16, 2, CATCCOS_FP16)
 DENSE_FLOW_LAUNCH(LaunchAllGatherMatmulRemoteReadBF16, 2, CATCCOS_BF16)
 DENSE_FLOW_LAUNCH(LaunchAscend950AllToAllMatmulFP16, 3, CATCCOS_FP16)
 DENSE_FLOW_LAUNCH(LaunchAscend950AllToAllMatmulBF16, 3, CATCCOS_BF16)
+DENSE_LAUNCH(LaunchAscend950MatmulAllToAllFP16, OP_MMA2A, CATCCOS_FP16)
+DENSE_LAUNCH(LaunchAscend950MatmulAllToAllBF16, OP_MMA2A, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchMatmulAllReduceFP16, OP_MMAR, CATCCOS_FP16)
 DENSE_LAUNCH(LaunchMatmulAllReduceBF16, OP_MMAR, CATCCOS_BF16)
 DENSE_LAUNCH(LaunchAllGatherMatmulFP16, OP_AGMM, CATCCOS_FP16)

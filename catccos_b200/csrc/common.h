@@ -17,7 +17,7 @@ constexpr uint32_t kFlagEntered = 0;      // entered[src PE]            (kMaxRan
 constexpr uint32_t kFlagBarrier = 16;     // host-visible barrier words (kMaxRanks words)
 constexpr uint32_t kFlagOpBase = 64;      // per-operator flags start here
 
-enum FusedOp : int { OP_AGMM = 0, OP_MMRS = 1, OP_MMAR = 2 };
+enum FusedOp : int { OP_AGMM = 0, OP_MMRS = 1, OP_MMAR = 2, OP_MMA2A = 3 /* Matmul-AllToAll: MM-RS's data flow without the sum */ };
 
 // GEMM tile of the dense (f16/bf16) kernel.
 constexpr int BM = 128, BN = 256, BK = 64;

@@ -104,6 +104,7 @@ static int launch_pair(int op, const FusedParams &p, const RsMapsAll &maps, int 
     switch (op) {
         case OP_AGMM: return launch_pair_kernel(pair_agmm_kernel<T, B_MN>, kPairAgThreads, p, grid, coop, stream);
         case OP_MMRS: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMRS, T, B_MN>, p, maps, grid, coop, stream);
+        case OP_MMA2A: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMA2A, T, B_MN>, p, maps, grid, coop, stream);
         default: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMAR, T, B_MN>, p, maps, grid, coop, stream);
     }
 }
@@ -117,9 +118,11 @@ static int launch_t(const FusedParams &p, int grid, bool coop, cudaStream_t s, b
     return bf16 ? launch_b<OP, __nv_bfloat16>(p, grid, coop, s, b_mn) : launch_b<OP, __half>(p, grid, coop, s, b_mn);
 }
 
-int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, bool allreduce, CUtensorMapDataType dt,
+int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, int op, CUtensorMapDataType dt,
                    void *const *outputs, int n_local, int m, int n, uint64_t symm_off, bool compute_only) {
     const int R = t->n_pes;
+    const bool allreduce = op == OP_MMAR;
+    const bool full_output = op == OP_MMAR || op == OP_MMA2A;      // the output holds all m rows; own rows at pe * mr
     const int mr = allreduce ? (m + R - 1) / R : m / R;
     auto rows_valid = [&](int d) { return std::min(m, (d + 1) * mr) - d * mr; };
     const size_t row_b = static_cast<size_t>(n) * 2;
@@ -130,7 +133,7 @@ int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, bool allreduc
             const int rv_d = rows_valid(d), rv_me = rows_valid(pe);
             if (d == pe) {
                 if (rv_me <= 0) continue;
-                uint8_t *base = static_cast<uint8_t *>(outputs[l]) + (allreduce ? static_cast<size_t>(pe) * mr * row_b : 0);
+                uint8_t *base = static_cast<uint8_t *>(outputs[l]) + (full_output ? static_cast<size_t>(pe) * mr * row_b : 0);
                 int rc = encode_2d(api, &mp.out[d], dt, base, n, rv_me, row_b, 64, 32);
                 if (rc) return rc;
                 continue;
@@ -166,7 +169,8 @@ static size_t dense_half_bytes(int op, int world, int m, int n, int k) {
     size_t b = 0;
     switch (op) {
         case OP_AGMM: b = static_cast<size_t>(world) * m * k * es; break;
-        case OP_MMRS: b = static_cast<size_t>(m) * n * es; break;
+        case OP_MMRS:
+        case OP_MMA2A: b = static_cast<size_t>(m) * n * es; break;
         case OP_MMAR: {
             const size_t mr = (m + world - 1) / world;
             b = 2 * static_cast<size_t>(world) * mr * n * es;
@@ -194,7 +198,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         set_error("CUDA driver unavailable: %s", why.c_str());
         return CATCCOS_ERR_CUDA;
     }
-    if (op != OP_AGMM && op != OP_MMRS && op != OP_MMAR) {
+    if (op != OP_AGMM && op != OP_MMRS && op != OP_MMAR && op != OP_MMA2A) {
         set_error("unknown dense operator %d", op);
         return CATCCOS_ERR_INVALID;
     }
@@ -215,8 +219,8 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         return CATCCOS_ERR_INVALID;
     }
     const int R = t->n_pes;
-    if (op == OP_MMRS && (m % R) != 0) {
-        set_error("matmul_reduce_scatter needs m (%d) divisible by the world size (%d)", m, R);
+    if ((op == OP_MMRS || op == OP_MMA2A) && (m % R) != 0) {
+        set_error("matmul_reduce_scatter / matmul_alltoall need m (%d) divisible by the world size (%d)", m, R);
         return CATCCOS_ERR_INVALID;
     }
     const int n_local = t->emulated ? R : 1;
@@ -238,7 +242,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
         size_t flags = 0;
         if (op == OP_AGMM)      // arrival flags; remote read adds one "staged" flag per unit and source
             flags = static_cast<size_t>(R) * ((m + BM - 1) / BM) * kAgSubChunks * (variant == AG_REMOTE_READ ? 2 : 1);
-        if (op == OP_MMRS) flags = static_cast<size_t>(R) * ((m / R + BM - 1) / BM) * nt;
+        if (op == OP_MMRS || op == OP_MMA2A) flags = static_cast<size_t>(R) * ((m / R + BM - 1) / BM) * nt;
         if (op == OP_MMAR) flags = 2 * static_cast<size_t>(R) * (((m + R - 1) / R + BM - 1) / BM) * nt;
         if (kFlagOpBase + flags > kFlagWords) {
             set_error("shape needs %zu flags, the flag region holds %u", flags, kFlagWords - kFlagOpBase);
@@ -266,6 +270,10 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     if (!use_pair && (variant != AG_PUSH || wants_gather)) {
         set_error("the remote-read and gather-result variants of AllGather-Matmul exist in the CTA-pair kernel only "
                   "(unset CATCCOS_TWO_CTA=0)");
+        return CATCCOS_ERR_INVALID;
+    }
+    if (!use_pair && op == OP_MMA2A) {
+        set_error("Matmul-AllToAll exists in the CTA-pair kernel only (unset CATCCOS_TWO_CTA=0)");
         return CATCCOS_ERR_INVALID;
     }
     if (wants_gather && (op != OP_AGMM || variant == AG_ALLTOALL)) {
@@ -338,7 +346,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.compute_only = (t->debug_flags & 1u) ? 1 : 0;
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
-    p.rs_fp16 = rs_exchange_fp16();
+    p.rs_fp16 = op == OP_MMA2A ? 0 : rs_exchange_fp16();      // rows that are only moved keep the output type
     p.ag_pull = variant == AG_REMOTE_READ ? 1 : 0;
     p.ag_a2a = variant == AG_ALLTOALL ? 1 : 0;
     p.sched = t->sched_dev;
@@ -356,7 +364,7 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     if (use_pair && op != OP_AGMM) {
         void *outs[kMaxRanks];
         for (int l = 0; l < n_local; ++l) outs[l] = args[l].C;
-        int rc = encode_rs_maps(api, t, &maps, op == OP_MMAR, dt, outs, n_local, m, n, symm_off, p.compute_only != 0);
+        int rc = encode_rs_maps(api, t, &maps, op, dt, outs, n_local, m, n, symm_off, p.compute_only != 0);
         if (rc) return rc;
     }
     commit_slot(t, sig, epoch, slot);

@@ -33,9 +33,9 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
 int rs_exchange_fp16();
 
 // Output tensor maps of a pair reduce-scatter kernel for every local rank (see RsMaps): `outputs[l]` is local
-// rank l's output (reduce-scatter: [m/R, n]; all-reduce: [m, n]), 16-bit elements of type `dt`; `symm_off` the
+// rank l's output (reduce-scatter: [m/R, n]; all-reduce and all-to-all: [m, n]), 16-bit elements of type `dt`; `symm_off` the
 // offset of the launch's half of the staging region.
-int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, bool allreduce, CUtensorMapDataType dt,
+int encode_rs_maps(const DriverApi *api, Team *t, RsMapsAll *maps, int op, CUtensorMapDataType dt,
                    void *const *outputs, int n_local, int m, int n, uint64_t symm_off, bool compute_only);
 
 }  // namespace cb

@@ -33,7 +33,10 @@ struct PairRsSmem {
 template <int OP, typename T, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     pair_rs_kernel(const __grid_constant__ FusedParams p, const __grid_constant__ RsMapsAll maps) {
-    static_assert(OP == OP_MMRS || OP == OP_MMAR, "reduce-scatter family only");
+    static_assert(OP == OP_MMRS || OP == OP_MMAR || OP == OP_MMA2A, "reduce-scatter family only");
+    // OP_MMA2A (Matmul-AllToAll): the same movement of row blocks to their owners, without the sum -- a block is
+    // stored in the output type into the owner's staging slot, the owner copies the R - 1 slots it received into
+    // its output behind its own block (examples/ascend950_matmul_alltoall/scripts/gen_data.py:19-89).
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
@@ -260,7 +263,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             const bool remote = d != rank;
             const bool comm = R > 1 && !p.compute_only && half_ok;
 
-            if (comm && (remote ? !((entered_ok >> d) & 1) : true)) {
+            if (comm && (remote ? !((entered_ok >> d) & 1) : OP != OP_MMA2A)) {
                 // This half-tile depends on peers: the owner must have entered (remote rows), or every
                 // peer's partial must be in (own rows).  Warp 2 looks once without blocking, lane s for
                 // rank s; only if something is missing is the pending flag raised first (which costs a
@@ -320,7 +323,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         uint32_t v[32];
                         tmem_ld_32x32(tmem_base + acc * BN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
                         const int col = n0 + c * 32;
-                        const bool reduce = !remote && R > 1 && row_ok && col < p.N;
+                        const bool reduce = OP != OP_MMA2A && !remote && R > 1 && row_ok && col < p.N;
                         uint4 part[kMaxRanks][4];
                         if (reduce) {
 #pragma unroll
@@ -430,6 +433,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const int cc = c0 + (i % vec_per_row) * 8;
                     const size_t off = static_cast<size_t>(rr) * p.N + cc;
                     *reinterpret_cast<uint4 *>(C + off) = *reinterpret_cast<const uint4 *>(fin + off);
+                }
+            }
+        }
+        if (OP == OP_MMA2A && R > 1 && ok && !p.compute_only) {
+            // second phase: the blocks the peers stored into my staging slots go into D behind my own block
+            const int total = (R - 1) * per;
+            for (int u = cta; u < total && ok; u += p.ctas_per_rank) {
+                const int s = (rank + 1 + u / per) % R;
+                const int tip = u % per;
+                const int mi = tip / nt, ni = tip % nt;
+                const int r0 = mi * BM;                                   // row inside the block
+                const int r1 = min(mr, r0 + BM);
+                if (r0 >= r1) continue;
+                const uint32_t w = kFlagOpBase + s * per + tip;
+                if (!(ok = wait_flag_ge(flag_ptr(p, rank, w), p.epoch, ctl, W_RS_PARTIAL, w))) break;
+                const int c0 = ni * BN;
+                const int c1 = min(p.N, c0 + BN);
+                const int vec_per_row = (c1 - c0) / 8;
+                const T *src = my_stage + static_cast<size_t>(s) * mr * p.N;
+                T *dst = C + static_cast<size_t>(s) * mr * p.N;
+                for (int i = etid; i < (r1 - r0) * vec_per_row; i += 128) {
+                    const size_t off = static_cast<size_t>(r0 + i / vec_per_row) * p.N + c0 + (i % vec_per_row) * 8;
+                    *reinterpret_cast<uint4 *>(dst + off) = *reinterpret_cast<const uint4 *>(src + off);
                 }
             }
         }

@@ -374,7 +374,7 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
     const bool compute_only = (t->debug_flags & 1u) != 0;
     static thread_local RsMapsAll maps;
     const CUtensorMapDataType dt = out_dtype == 27 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    int rc = encode_rs_maps(api, t, &maps, false, dt, outs, n_local, m, n, symm_off, compute_only);
+    int rc = encode_rs_maps(api, t, &maps, OP_MMRS, dt, outs, n_local, m, n, symm_off, compute_only);
     if (rc) return rc;
     for (int pe = 0; pe < R; ++pe) p.heap_base[pe] = t->base[pe];
     p.symm_off = symm_off;

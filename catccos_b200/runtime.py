@@ -21,6 +21,7 @@ FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25
 FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27
 DISPATCH_FFN_COMBINE = 32
 ALLTOALL_MATMUL = 101
+MATMUL_ALLTOALL = 102
 FP16, BF16, FP8E4M3FN = 1, 27, 36
 
 _DTYPE = {torch.float16: FP16, torch.bfloat16: BF16}

@@ -76,7 +76,8 @@ enum {
     CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE = 32,
     /* not in the reference's enum (its example instantiates the device template directly,
      * examples/ascend950_alltoall_matmul/main.cpp): a value of this library's own */
-    CATCCOS_ASCEND950_ALLTOALL_MATMUL = 101
+    CATCCOS_ASCEND950_ALLTOALL_MATMUL = 101,
+    CATCCOS_ASCEND950_MATMUL_ALLTOALL = 102      /* likewise (examples/ascend950_matmul_alltoall/main.cpp) */
 };
 enum { CATCCOS_FP16 = 1, CATCCOS_INT8 = 2, CATCCOS_BF16 = 27, CATCCOS_FP8E4M3FN = 36 };
 
@@ -218,6 +219,13 @@ CATCCOS_DECLARE_LAUNCH(LaunchAllGatherMatmulRemoteReadBF16);
  * rank i) by its B [k, n]: ptrC = [m, n].  The AllGather-Matmul kernel with a per-destination source block. */
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllToAllMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllToAllMatmulBF16);
+
+/* Matmul-AllToAll (examples/ascend950_matmul_alltoall, include/catccos/dgemm/kernel/ascend950_matmul_alltoall.hpp;
+ * golden examples/ascend950_matmul_alltoall/scripts/gen_data.py:19-89): C_i = A_i [m, k] x B_i [k, n] on every rank,
+ * then rows [j*m/R, (j+1)*m/R) of C_i go to rank j: ptrC = [m, n] with block i from rank i.  The Matmul-ReduceScatter
+ * kernel without the sum; the symmetric region is that operator's. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulAllToAllFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulAllToAllBF16);
 
 /* tests/dynamic_tiling/impl/kernel_fp16_ascend950.cpp:274 (MxAllGatherMatmulTla,
  * include/catccos/dgemm/kernel/mx_allgather_matmul.hpp:27-428): ptrA/ptrB = e4m3 operands,

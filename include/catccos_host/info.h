@@ -36,7 +36,8 @@ enum CocCommType {
     ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL,
     ASCEND950_DISPATCH_FFN_COMBINE = CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE,
     UNKNOWN = 36,
-    ASCEND950_ALLTOALL_MATMUL = CATCCOS_ASCEND950_ALLTOALL_MATMUL      // no counterpart in the reference's enum
+    ASCEND950_ALLTOALL_MATMUL = CATCCOS_ASCEND950_ALLTOALL_MATMUL,     // no counterparts in the reference's enum
+    ASCEND950_MATMUL_ALLTOALL = CATCCOS_ASCEND950_MATMUL_ALLTOALL
 };
 
 enum CocDataType { FP16 = CATCCOS_FP16, INT8 = CATCCOS_INT8, BF16 = CATCCOS_BF16, FP8E4M3FN = CATCCOS_FP8E4M3FN };
@@ -90,6 +91,7 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"agmmwg", ALLGATHER_MATMUL_WITH_GATHER_RESULT},
         {"agmmrr", ALLGATHER_MATMUL_REMOTE_READ},
         {"a5atamm", ASCEND950_ALLTOALL_MATMUL},
+        {"a5mmata", ASCEND950_MATMUL_ALLTOALL},
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
         {"a5fp4mxagmm", ASCEND950_FP4_MX_ALLGATHER_MATMUL},
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
@@ -115,6 +117,7 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ALLGATHER_MATMUL_WITH_GATHER_RESULT, "AllGatherMatmulWithGatherResult"},
         {ALLGATHER_MATMUL_REMOTE_READ, "AllGatherMatmulRemoteRead"},
         {ASCEND950_ALLTOALL_MATMUL, "Ascend950AllToAllMatmul"},
+        {ASCEND950_MATMUL_ALLTOALL, "Ascend950MatmulAllToAll"},
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
         {ASCEND950_FP4_MX_ALLGATHER_MATMUL, "Ascend950Fp4MxAllGatherMatmul"},
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},

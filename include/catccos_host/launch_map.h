@@ -30,6 +30,8 @@ private:
             {Hash(ALLGATHER_MATMUL_WITH_GATHER_RESULT, BF16), &LaunchAllGatherMatmulWithGatherResultBF16},
             {Hash(ALLGATHER_MATMUL_REMOTE_READ, FP16), &LaunchAllGatherMatmulRemoteReadFP16},
             {Hash(ALLGATHER_MATMUL_REMOTE_READ, BF16), &LaunchAllGatherMatmulRemoteReadBF16},
+            {Hash(ASCEND950_MATMUL_ALLTOALL, FP16), &LaunchAscend950MatmulAllToAllFP16},
+            {Hash(ASCEND950_MATMUL_ALLTOALL, BF16), &LaunchAscend950MatmulAllToAllBF16},
             {Hash(ASCEND950_ALLTOALL_MATMUL, FP16), &LaunchAscend950AllToAllMatmulFP16},
             {Hash(ASCEND950_ALLTOALL_MATMUL, BF16), &LaunchAscend950AllToAllMatmulBF16},
             {Hash(MATMUL_REDUCE_SCATTER, FP16), &LaunchMatmulReduceScatterFP16},

@@ -147,6 +147,19 @@ public:
     }
 };
 REGISTER_OPERATOR("Ascend950AllToAllMatmul", Ascend950AllToAllMatmulOperator);
+// Matmul-AllToAll (examples/ascend950_matmul_alltoall/ascend950_matmul_alltoall_host.h:17-100): C_i = A_i x B_i, then row
+// block j of every C_i goes to rank j; same files and sizes as AllToAll-Matmul.
+class Ascend950MatmulAllToAllOperator : public Ascend950AllToAllMatmulOperator {
+public:
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_MATMUL_ALLTOALL; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return catccos_host::DenseShapeOk(t) && rankSize >= 1 && rankSize <= MAX_RANK_SIZE && t.m % rankSize == 0 &&
+               catccos_symmetric_bytes(ASCEND950_MATMUL_ALLTOALL, BF16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950MatmulAllToAll", Ascend950MatmulAllToAllOperator);
 
 // D_r = rows r of sum_s A_s * B_s (examples/matmul_reduce_scatter/matmul_reduce_scatter_host.h); m = total rows.
 class MatmulReduceScatterOperator : public CatccosOperator {

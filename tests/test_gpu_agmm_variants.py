@@ -91,3 +91,30 @@ def test_alltoall_matmul(world, chunk, n, k, trans_b, dtype):
         assembled = torch.cat([a[i][j * chunk:(j + 1) * chunk] for i in range(world)], dim=0)
         gold = dense.matmul_fp32(assembled, b[j])
         assert_close_to_golden(outs[j], gold, k, TOL, f"alltoall-matmul rank {j}")
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("chunk,n,k,trans_b,dtype", [(128, 256, 128, 0, torch.bfloat16), (320, 520, 192, 1, torch.float16),
+                                                      (100, 264, 64, 0, torch.bfloat16)])
+def test_matmul_alltoall(world, chunk, n, k, trans_b, dtype):
+    """Matmul-AllToAll: C_i = A_i x B_i on every rank, then rank j holds row block j of every C_i in rank order
+    (examples/ascend950_matmul_alltoall/scripts/gen_data.py:19-89)."""
+    from catccos_b200 import runtime as rt
+    m = chunk * world
+    a, b = inputs.matmul_reduce_scatter_inputs(world, m, k, n, dtype)       # every rank: A [m, k], B [k, n]
+    til = rt.tiling(m, k, n, world)
+    need = rt.symmetric_bytes(rt.MATMUL_ALLTOALL, rt.BF16, til)
+    with rt.emulated_team(world, max(need, 1 << 20)):
+        symm = rt.shmem_malloc(max(need, 1024))
+        a_d = [dev(x) for x in a]
+        b_d = [dev(x.t() if trans_b else x) for x in b]
+        c_d = [torch.full((m, n), float("nan"), dtype=dtype, device="cuda") for _ in range(world)]
+        for _ in range(2):
+            rt.launch_emulated(rt.MATMUL_ALLTOALL, a_d, b_d, c_d, symm, til, trans_b=1 if trans_b else 0)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+        outs = [c.cpu() for c in c_d]
+    full = [dense.matmul_fp32(x, y) for x, y in zip(a, b)]
+    for j in range(world):
+        gold = torch.cat([full[i][j * chunk:(j + 1) * chunk] for i in range(world)], dim=0)
+        assert_close_to_golden(outs[j], gold, k, TOL, f"matmul-alltoall rank {j}")

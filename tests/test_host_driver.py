@@ -23,7 +23,7 @@ def test_registry_lists_every_operator_on_the_path(driver):
                         "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
                         "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather",
                         "Ascend950Fp8MxAllToAllVGroupedMatmul", "Ascend950Fp8MxGroupedMatmulAllToAllV",
-                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul"}
+                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul", "Ascend950MatmulAllToAll"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
