@@ -103,6 +103,7 @@ for _dt in ("FP16", "BF16"):
     SIGNATURES[f"LaunchAllGatherMatmulRemoteRead{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
     SIGNATURES[f"LaunchAscend950AllToAllMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
     SIGNATURES[f"LaunchAscend950MatmulAllToAll{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
+    SIGNATURES[f"LaunchAscend950MxFp8MatmulAllToAll{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
 SIGNATURES["LaunchAscend950DispatchFFNCombineBF16"] = (ctypes.c_int, LAUNCH_ARGS)
 SIGNATURES["LaunchAscend950BF16QuantAllGatherFP8E4M3FN"] = (ctypes.c_int, LAUNCH_ARGS)
 for _dt in ("FP16", "BF16"):

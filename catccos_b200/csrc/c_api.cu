@@ -144,7 +144,7 @@ int launch_mx_ag_abi(int dtype, void *stream, uint32_t blockNum, CatccosKernelPa
 // SetKernelParams(a, b, c, aScale, bScale)).
 int launch_mx_rs_abi(int dtype, int code_format, void *stream, uint32_t blockNum, CatccosKernelParams *params,
                      int n_params, uint8_t **workspaces, uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA,
-                     uint32_t transB) {
+                     uint32_t transB, int alltoall = 0) {
     int rc = check_tiling(tiling);
     if (rc) return rc;
     Team *t = team();
@@ -168,7 +168,7 @@ int launch_mx_rs_abi(int dtype, int code_format, void *stream, uint32_t blockNum
     }
     return launch_mx_matmul_reduce_scatter(dtype, code_format, static_cast<cudaStream_t>(stream), blockNum, args,
                                            symmetric, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
-                                           static_cast<int>(tiling->k), static_cast<int>(transB));
+                                           static_cast<int>(tiling->k), static_cast<int>(transB), alltoall);
 }
 
 int launch_moe_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params, uint8_t **workspaces,
@@ -576,7 +576,7 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL)
         return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k), commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL ? 1 : 0);
-    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER)
+    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER || commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL)
         return dense_symmetric_bytes(OP_MMRS, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
     if (commType == CATCCOS_MX_QUANT_ALLGATHER)
@@ -595,7 +595,8 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
 size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTilingParams *tiling) {
     (void)dataType;
     if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL ||
-                   commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER))
+                   commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER ||
+                   commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL))
         return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
     if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
@@ -664,6 +665,14 @@ MXAG_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulBF16, CATCCOS_BF16, 1)
         (void)fftsAddr;                                                                                          \
         return launch_mx_rs_abi(dtype, fmt, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB); \
     }
+#define MXA2A_LAUNCH(name, dtype)                                                                              \
+    int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
+             uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
+        (void)fftsAddr;                                                                                          \
+        return launch_mx_rs_abi(dtype, 0, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB, 1); \
+    }
+MXA2A_LAUNCH(LaunchAscend950MxFp8MatmulAllToAllFP16, CATCCOS_FP16)
+MXA2A_LAUNCH(LaunchAscend950MxFp8MatmulAllToAllBF16, CATCCOS_BF16)
 MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterFP16, CATCCOS_FP16, 1)
 MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterBF16, CATCCOS_BF16, 1)
 MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterFP16, CATCCOS_FP16, 0)
@@ -715,6 +724,8 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
         return launch_mx_ag_abi(dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB, 1);
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_rs_abi(dataType, 1, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
+    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_rs_abi(dataType, 0, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB, 1);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
@@ -748,6 +759,9 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_rs_abi(dataType, 1, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
                                 transB);
+    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_rs_abi(dataType, 0, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
+                                transB, 1);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)

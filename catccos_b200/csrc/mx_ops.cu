@@ -276,7 +276,7 @@ static int launch_rs_k(const MxRsParams &p, const RsMapsAll &maps, int grid, boo
 }
 
 int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t stream, uint32_t block_num,
-                                    const MxAgArgs *args, void *symmetric, int m, int n, int k, int trans_b) {
+                                    const MxAgArgs *args, void *symmetric, int m, int n, int k, int trans_b, int alltoall) {
     Team *t = team();
     if (!t) {
         set_error("symmetric heap not initialised (call catccos_shmem_init first)");
@@ -374,7 +374,7 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
     const bool compute_only = (t->debug_flags & 1u) != 0;
     static thread_local RsMapsAll maps;
     const CUtensorMapDataType dt = out_dtype == 27 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    int rc = encode_rs_maps(api, t, &maps, OP_MMRS, dt, outs, n_local, m, n, symm_off, compute_only);
+    int rc = encode_rs_maps(api, t, &maps, alltoall ? OP_MMA2A : OP_MMRS, dt, outs, n_local, m, n, symm_off, compute_only);
     if (rc) return rc;
     for (int pe = 0; pe < R; ++pe) p.heap_base[pe] = t->base[pe];
     p.symm_off = symm_off;
@@ -386,6 +386,7 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
     p.N = n;
     p.K = k;
     p.fmt_bits = code_format == 1 ? ((1u << 7) | (1u << 10)) : 0u;
+    p.a2a = alltoall ? 1 : 0;
     p.epoch = epoch;
     p.entered_need = slot.entered_need;
     p.compute_only = compute_only ? 1 : 0;

@@ -26,7 +26,9 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
 // D_r = rows r*m/R .. of sum_s A_s B_s.  m = rows of the full product, k = this rank's share of the
 // contraction; m/R must be a multiple of 128.  MxAgArgs as above with C = [m/R, n]; the symmetric region is that
 // of the f16/bf16 Matmul-ReduceScatter (dense_symmetric_bytes), the workspace mx_ag_workspace_bytes(m, n, k).
+// alltoall = 1: Matmul-AllToAll -- the same movement of row blocks without the sum, C = [m, n] with block s from rank s.
 int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t stream, uint32_t block_num,
-                                    const MxAgArgs *args, void *symmetric, int m, int n, int k, int trans_b);
+                                    const MxAgArgs *args, void *symmetric, int m, int n, int k, int trans_b,
+                                    int alltoall = 0);
 
 }  // namespace cb

@@ -28,6 +28,7 @@ struct MxRsParams {
     uint32_t entered_need;
     int compute_only;
     int rs_fp16;                     // partial tiles cross the link as fp16 (0: in the output type)
+    int a2a;                         // Matmul-AllToAll: row blocks go to their owners without the sum; C is [M, N]
     uint64_t timeout_ns;
     int *status;
     unsigned long long *trace;
@@ -260,7 +261,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             const bool remote = d != rank;
             const bool comm = R > 1 && !p.compute_only && half_ok;
 
-            if (comm && (remote ? !((entered_ok >> d) & 1) : true)) {
+            if (comm && (remote ? !((entered_ok >> d) & 1) : !p.a2a)) {
                 // look once without blocking (lane s for rank s); only if something is missing raise the
                 // pending flag first and wait
                 volatile int *verdict = &sh->epi_ok[check_no & 1];
@@ -314,7 +315,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         uint32_t v[32];
                         tmem_ld_32x32(tmem_base + c * 32 + (static_cast<uint32_t>(q * 32) << 16), v);
                         const int col = n0 + c * 32;
-                        const bool reduce = !remote && R > 1 && row_ok && col < p.N;
+                        const bool reduce = !p.a2a && !remote && R > 1 && row_ok && col < p.N;
                         uint4 part[kMaxRanks][4];
                         if (reduce) {
 #pragma unroll
@@ -390,6 +391,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (ok) ok = publish(true);
         if (!(amax_sent <= 65504.0f)) report_partial_range(p.status, rank, static_cast<int>(tcount));
         if (lane == 0) bulk_wait<0>();
+        if (p.a2a && R > 1 && ok && !p.compute_only) {
+            // Matmul-AllToAll, second phase: the blocks the peers stored into my staging slots go into C behind my own
+            TOut *const C = reinterpret_cast<TOut *>(ra.C);
+            const int total = (R - 1) * per;
+            for (int u = cta; u < total && ok; u += p.ctas_per_rank) {
+                const int s = (rank + 1 + u / per) % R;
+                const int tip = u % per;
+                const int mi = tip / nt, ni = tip % nt;
+                const int r0 = mi * BM;
+                const int r1 = min(mr, r0 + BM);
+                if (r0 >= r1) continue;
+                const uint32_t w = kFlagOpBase + s * per + tip;
+                if (!(ok = wait_flag_ge(flagp(rank, w), p.epoch, ctl, W_RS_PARTIAL, w))) break;
+                const int c0 = ni * BN;
+                const int c1 = min(p.N, c0 + BN);
+                const int vec_per_row = (c1 - c0) / 8;
+                const TOut *src = my_stage + static_cast<size_t>(s) * mr * p.N;
+                TOut *dst = C + static_cast<size_t>(s) * mr * p.N;
+                for (int i = etid; i < (r1 - r0) * vec_per_row; i += 128) {
+                    const size_t off = static_cast<size_t>(r0 + i / vec_per_row) * p.N + c0 + (i % vec_per_row) * 8;
+                    *reinterpret_cast<uint4 *>(dst + off) = *reinterpret_cast<const uint4 *>(src + off);
+                }
+            }
+        }
     } else if (warp == 6) {
         // tell every peer that this rank has entered the epoch: its staging rows may be overwritten
         if (R > 1 && !p.compute_only && cta == 0 && lane < R && lane != rank) {

@@ -14,6 +14,7 @@ MATMUL_REDUCE_SCATTER = 3
 ALLGATHER_MATMUL_WITH_GATHER_RESULT = 5
 ALLGATHER_MATMUL_REMOTE_READ = 20
 MXFP8_MATMUL_REDUCE_SCATTER = 18
+MXFP8_MATMUL_ALLTOALL = 19
 FP8_MX_ALLGATHER_MATMUL = 22
 FP4_MX_ALLGATHER_MATMUL = 23
 MX_QUANT_ALLGATHER = 24

@@ -67,6 +67,7 @@ enum {
     CATCCOS_ASCEND950_MATMUL_REDUCE_SCATTER = 4,
     CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT = 5,
     CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = 18,
+    CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL = 19,
     CATCCOS_ALLGATHER_MATMUL_REMOTE_READ = 20,
     CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL = 22,
     CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL = 23,
@@ -226,6 +227,11 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950AllToAllMatmulBF16);
  * kernel without the sum; the symmetric region is that operator's. */
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulAllToAllFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950MatmulAllToAllBF16);
+/* The same on MXFP8 operands (tests/dynamic_tiling/include/launch_map.h:104, examples/ascend950_mxfp8_matmul_alltoall,
+ * row-block form of scripts/gen_data_slice_m.py): e4m3 codes, customPtrs = {aScale, bScale} as
+ * LaunchAscend950MxFp8MatmulReduceScatter*, `workspace` = catccos_workspace_bytes() bytes. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8MatmulAllToAllFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950MxFp8MatmulAllToAllBF16);
 
 /* tests/dynamic_tiling/impl/kernel_fp16_ascend950.cpp:274 (MxAllGatherMatmulTla,
  * include/catccos/dgemm/kernel/mx_allgather_matmul.hpp:27-428): ptrA/ptrB = e4m3 operands,

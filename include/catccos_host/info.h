@@ -29,6 +29,7 @@ enum CocCommType {
     ALLGATHER_MATMUL_WITH_GATHER_RESULT = CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT,
     ALLGATHER_MATMUL_REMOTE_READ = CATCCOS_ALLGATHER_MATMUL_REMOTE_READ,
     ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER,
+    ASCEND950_MXFP8_MATMUL_ALLTOALL = CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL,
     ASCEND950_FP8_MX_ALLGATHER_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL,
     ASCEND950_FP4_MX_ALLGATHER_MATMUL = CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL,
     MX_QUANT_ALLGATHER = CATCCOS_MX_QUANT_ALLGATHER,
@@ -95,6 +96,7 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
         {"a5fp4mxagmm", ASCEND950_FP4_MX_ALLGATHER_MATMUL},
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
+        {"a5mxfp8mmata", ASCEND950_MXFP8_MATMUL_ALLTOALL},
         {"a5moe", ASCEND950_DISPATCH_FFN_COMBINE},
         {"mxqtag", MX_QUANT_ALLGATHER},
         {"a5fp8gmmata", ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV},
@@ -121,6 +123,7 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
         {ASCEND950_FP4_MX_ALLGATHER_MATMUL, "Ascend950Fp4MxAllGatherMatmul"},
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
+        {ASCEND950_MXFP8_MATMUL_ALLTOALL, "Ascend950MxFp8MatmulAllToAll"},
         {ASCEND950_DISPATCH_FFN_COMBINE, "Ascend950DispatchFFNCombine"},
         {MX_QUANT_ALLGATHER, "MxQuantAllGather"},
         {ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV, "Ascend950Fp8MxGroupedMatmulAllToAllV"},

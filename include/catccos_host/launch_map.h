@@ -44,6 +44,8 @@ private:
             {Hash(ASCEND950_FP8_MX_ALLGATHER_MATMUL, BF16), &LaunchAscend950Fp8MxAllGatherMatmulBF16},
             {Hash(ASCEND950_FP4_MX_ALLGATHER_MATMUL, FP16), &LaunchAscend950Fp4MxAllGatherMatmulFP16},
             {Hash(ASCEND950_FP4_MX_ALLGATHER_MATMUL, BF16), &LaunchAscend950Fp4MxAllGatherMatmulBF16},
+            {Hash(ASCEND950_MXFP8_MATMUL_ALLTOALL, FP16), &LaunchAscend950MxFp8MatmulAllToAllFP16},
+            {Hash(ASCEND950_MXFP8_MATMUL_ALLTOALL, BF16), &LaunchAscend950MxFp8MatmulAllToAllBF16},
             {Hash(ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, FP16), &LaunchAscend950MxFp8MatmulReduceScatterFP16},
             {Hash(ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, BF16), &LaunchAscend950MxFp8MatmulReduceScatterBF16},
             {Hash(ASCEND950_DISPATCH_FFN_COMBINE, BF16), &LaunchAscend950DispatchFFNCombineBF16},

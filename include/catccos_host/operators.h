@@ -284,6 +284,30 @@ public:
     }
 };
 REGISTER_OPERATOR("Ascend950MxFp8MatmulReduceScatter", Ascend950MxFp8MatmulReduceScatterOperator);
+// MXFP8 Matmul-AllToAll (examples/ascend950_mxfp8_matmul_alltoall/ascend950_mxfp8_matmul_alltoall_host.h:17-120, row-block
+// form): e4m3 operands and scales in the files of the operator above, C [m, n] written to output_<rank>.bin.
+class Ascend950MxFp8MatmulAllToAllOperator : public Ascend950MxFp8MatmulReduceScatterOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t sizeA = static_cast<size_t>(t.m) * t.k, sizeB = static_cast<size_t>(t.k) * t.n;
+        const size_t kb = (static_cast<size_t>(t.k) + 63) / 64 * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), sizeA, 56),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), sizeB, 56),
+                               DeviceZeros(static_cast<size_t>(t.m) * t.n * 2),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a_scale"), t.m * kb, 121),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b_scale"), t.n * kb, 121));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        catccos_host::WriteDeviceBuffer(dataFile + "/output_" + std::to_string(rankId) + ".bin", params.ptrC,
+                                        static_cast<size_t>(t.m) * t.n * 2);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &t) override {
+        return catccos_workspace_bytes(ASCEND950_MXFP8_MATMUL_ALLTOALL, BF16, &t);
+    }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_MXFP8_MATMUL_ALLTOALL; }
+};
+REGISTER_OPERATOR("Ascend950MxFp8MatmulAllToAll", Ascend950MxFp8MatmulAllToAllOperator);
 
 // MoE dispatch -> FFN -> combine (examples/ascend950_dispatch_ffn_combine/ascend950_dispatch_ffn_combine_host.h):
 // customPtrs = {b2, expertIdx, probs, bScale, b2Scale}.

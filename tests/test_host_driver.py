@@ -23,7 +23,7 @@ def test_registry_lists_every_operator_on_the_path(driver):
                         "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
                         "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather",
                         "Ascend950Fp8MxAllToAllVGroupedMatmul", "Ascend950Fp8MxGroupedMatmulAllToAllV",
-                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul", "Ascend950MatmulAllToAll"}
+                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul", "Ascend950MatmulAllToAll", "Ascend950MxFp8MatmulAllToAll"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
@@ -116,6 +116,15 @@ def _check(driver, *args):
     ("a5moe", 8, 4096, 4096, 7168, 8, 256),            # 5 (n = 2 x intermediate)
     ("a5mxfp8mmrs", 8, 8192, 8192, 2048),
     ("a5agmm", 1, 8, 8, 8),
+    ("agmmwg", 8, 1024, 4096, 8192),                   # data-flow variants and further operators on configuration-sized shapes
+    ("agmmrr", 8, 1024, 4096, 8192),
+    ("a5atamm", 8, 8192, 4096, 8192),
+    ("a5mmata", 8, 8192, 8192, 2048),
+    ("a5mxfp8mmata", 8, 8192, 8192, 2048),
+    ("a5fp4mxagmm", 8, 2048, 4096, 7168),
+    ("mxqtag", 8, 2048, 7168, 0),
+    ("a5fp8mxatavgmm", 8, 4096, 4096, 7168, 1, 256),
+    ("a5fp8gmmata", 8, 4096, 7168, 2048, 1, 256),
 ])
 def test_operator_classes_accept_the_benchmark_configurations(driver, args):
     """CheckCocTilingParams of every operator class, and the buffers fit the reference's 1004 MiB symmetric buffer."""
@@ -133,6 +142,10 @@ def test_operator_classes_accept_the_benchmark_configurations(driver, args):
     ("a5moe", 8, 4096, 4096, 7000, 8, 256),            # k % 256, as the reference operator demands
     ("a5moe", 8, 4096, 4096, 7168, 8, 250),            # experts not divisible by the ranks
     ("mmar", 0, 512, 2048, 1024),                      # no ranks
+    ("a5atamm", 8, 8190, 4096, 8192),                  # rows not divisible by the ranks
+    ("a5mmata", 8, 8190, 8192, 2048),
+    ("a5fp4mxagmm", 8, 2048, 4096, 7200),              # k not a multiple of 64
+    ("a5fp8mxatavgmm", 8, 4096, 4096, 7168, 1, 250),   # experts not divisible by the ranks
 ])
 def test_operator_classes_reject_unusable_tilings(driver, args):
     rc, out = _check(driver, *args)
