@@ -65,14 +65,25 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
     const int begin = warp * chunk;
     const int end = min(total, begin + chunk);
     // a negative expert id marks a row that takes no part (the all-to-all-v operators pad their row lists with them)
-    for (int base = begin; base < end; base += 32) {
-        const int i = base + lane;
-        const int raw = i < end ? ra.expert_idx[i] : -1;
-        const bool valid = raw >= 0;
-        const int key = valid ? raw : -1 - lane;
-        const unsigned mask = __match_any_sync(0xffffffffu, key);
-        if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
-        __syncwarp();
+    // the ids are read eight steps at a time, so that their load latencies overlap
+    constexpr int kBatch = 8;
+    for (int base = begin; base < end; base += 32 * kBatch) {
+        int raws[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int i = base + j * 32 + lane;
+            raws[j] = i < end ? ra.expert_idx[i] : -1;
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            if (base + j * 32 >= end) break;
+            const int raw = raws[j];
+            const bool valid = raw >= 0;
+            const int key = valid ? raw : -1 - lane;
+            const unsigned mask = __match_any_sync(0xffffffffu, key);
+            if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
+            __syncwarp();
+        }
     }
     __syncthreads();
     if (tid < E) {
@@ -102,20 +113,31 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
         my_count = run - scan[tid];
     }
     __syncthreads();
-    for (int base = begin; base < end; base += 32) {
-        const int i = base + lane;
-        const int raw = i < end ? ra.expert_idx[i] : -1;
-        const bool valid = raw >= 0;
-        const int key = valid ? raw : -1 - lane;
-        const unsigned mask = __match_any_sync(0xffffffffu, key);
-        const int rnk = __popc(mask & ((1u << lane) - 1u));
-        int dst = -1;
-        if (valid) dst = cnt[warp * E + key] + rnk;
-        __syncwarp();
-        if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
-        __syncwarp();
-        if (i < end) ra.expanded_row_idx[i] = dst;
+    for (int base = begin; base < end; base += 32 * kBatch) {
+        int raws[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            const int i = base + j * 32 + lane;
+            raws[j] = i < end ? ra.expert_idx[i] : -1;
+        }
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+            if (base + j * 32 >= end) break;
+            const int i = base + j * 32 + lane;
+            const int raw = raws[j];
+            const bool valid = raw >= 0;
+            const int key = valid ? raw : -1 - lane;
+            const unsigned mask = __match_any_sync(0xffffffffu, key);
+            const int rnk = __popc(mask & ((1u << lane) - 1u));
+            int dst = -1;
+            if (valid) dst = cnt[warp * E + key] + rnk;
+            __syncwarp();
+            if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
+            __syncwarp();
+            if (i < end) ra.expanded_row_idx[i] = dst;
+        }
     }
+    __syncthreads();      // the warp counters are dead from here on: their space holds the gathered counts below
 
     // ---- tokens-per-expert to every rank (the count all-gather), then the offset tables ----
     if (tid < E) {
@@ -138,8 +160,17 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
     __syncthreads();
     if (abort_flag) return;
 
-    const int *counts = reinterpret_cast<const int *>(p.heap_base[rank] + p.lay.counts_off);
-    for (int i = tid; i < R * E; i += blockDim.x) meta->counts_all[i / E][i % E] = counts[i];
+    // the all-gathered [R][E] table goes into shared memory once; the serial loops below read it from there
+    int *counts = cnt;
+    {
+        const int *counts_g = reinterpret_cast<const int *>(p.heap_base[rank] + p.lay.counts_off);
+        for (int i = tid; i < R * E; i += blockDim.x) {
+            const int c = counts_g[i];
+            counts[i] = c;
+            meta->counts_all[i / E][i % E] = c;
+        }
+    }
+    __syncthreads();
     if (tid < R) {
         int run = 0;
         for (int e = 0; e < E; ++e) {
@@ -355,7 +386,7 @@ __global__ void __launch_bounds__(256) moe_unpermute_kernel(const MoeParams p) {
 #pragma unroll
             for (int k = 0; k < kMaxTopK; ++k)
                 if (k < topk)
-                    x[k] = *reinterpret_cast<const uint4 *>(comb + static_cast<size_t>(s_row[k]) * K + v * 8);
+                    x[k] = __ldcs(reinterpret_cast<const uint4 *>(comb + static_cast<size_t>(s_row[k]) * K + v * 8));
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -619,7 +650,10 @@ int moe_launch_dispatch(const MoeParams &p, cudaStream_t stream) {
     return launch_wide(moe_quant_dispatch_kernel, p, kDispWarps * 32, 4, stream, "moe_quant_dispatch_kernel");
 }
 int moe_launch_unpermute(const MoeParams &p, cudaStream_t stream) {
-    return launch_wide(moe_unpermute_kernel, p, 256, 6, stream, "moe_unpermute_kernel");
+    // a thread count that divides the 16-byte pieces of a row leaves no thread idle in the last pass over a token
+    const int vecs = p.K / 8;
+    const int threads = vecs % 256 == 0 ? 256 : vecs % 224 == 0 ? 224 : vecs % 192 == 0 ? 192 : 256;
+    return launch_wide(moe_unpermute_kernel, p, threads, 6, stream, "moe_unpermute_kernel");
 }
 
 }  // namespace cb
