@@ -59,15 +59,16 @@ static int launch_kernel(const FusedParams &p, int grid, bool cooperative, cudaS
 
 // CTA-pair (cta_group::2) kernels
 template <typename K>
-static int launch_pair_kernel(K kern, int threads, const FusedParams &p, int grid, bool cooperative, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+static int launch_pair_kernel(K kern, int threads, const FusedParams &p, int grid, bool cooperative, cudaStream_t stream,
+                              int smem_bytes = kPairSmemBytes) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (e == cudaSuccess) {
         if (cooperative) {
             void *args[] = {const_cast<FusedParams *>(&p)};
             e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(threads), args,
-                                            kPairSmemBytes, stream);
+                                            smem_bytes, stream);
         } else {
-            kern<<<grid, threads, kPairSmemBytes, stream>>>(p);
+            kern<<<grid, threads, smem_bytes, stream>>>(p);
             e = cudaGetLastError();
         }
     }
@@ -102,7 +103,12 @@ static int launch_pair_rs_kernel(K kern, const FusedParams &p, const RsMapsAll &
 template <typename T, bool B_MN>
 static int launch_pair(int op, const FusedParams &p, const RsMapsAll &maps, int grid, bool coop, cudaStream_t stream) {
     switch (op) {
-        case OP_AGMM: return launch_pair_kernel(pair_agmm_kernel<T, B_MN>, kPairAgThreads, p, grid, coop, stream);
+        case OP_AGMM:
+            // a single rank without a gather-result output moves nothing: the copy lanes' staging becomes a seventh stage
+            if (p.world == 1 && !p.ranks[0].gather_out && !getenv("CATCCOS_AG_SIX_STAGES"))
+                return launch_pair_kernel(pair_agmm_kernel<T, B_MN, kPStagesSolo>, kPairAgThreads, p, grid, coop, stream,
+                                          kPairSoloSmemBytes);
+            return launch_pair_kernel(pair_agmm_kernel<T, B_MN>, kPairAgThreads, p, grid, coop, stream);
         case OP_MMRS: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMRS, T, B_MN>, p, maps, grid, coop, stream);
         case OP_MMA2A: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMA2A, T, B_MN>, p, maps, grid, coop, stream);
         default: return launch_pair_rs_kernel(pair_rs_kernel<OP_MMAR, T, B_MN>, p, maps, grid, coop, stream);

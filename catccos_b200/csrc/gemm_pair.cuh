@@ -21,14 +21,17 @@
 namespace cb {
 
 constexpr int kPStages = 6;
+constexpr int kPStagesSolo = 7;     // AllGather-Matmul of a single rank: no copy lanes, their staging is a seventh stage
 constexpr int kPAStage = BM * BK * 2;          // 128 rows of A      : 16 KiB
 constexpr int kPBStage = 128 * BK * 2;         // 128 columns of B   : 16 KiB
 constexpr int kPairSmemBytes = kPStages * (kPAStage + kPBStage) + kSideSmemBytes + 1024 + 512;
+constexpr int kPairSoloSmemBytes = kPStagesSolo * (kPAStage + kPBStage) + 1024 + 512;
+static_assert(kPairSoloSmemBytes <= 232448, "shared memory budget");
 constexpr int BM2 = 2 * BM;                    // rows of a pair's tile
 
 struct PairSmem {
-    uint64_t full[kPStages];        // used in the leader: both CTAs' loads of a stage have landed
-    uint64_t empty[kPStages];       // per CTA: the pair's MMAs have finished reading this stage
+    uint64_t full[kPStagesSolo];    // used in the leader: both CTAs' loads of a stage have landed
+    uint64_t empty[kPStagesSolo];   // per CTA: the pair's MMAs have finished reading this stage
     uint64_t tmem_full[2];          // per CTA: accumulator complete
     uint64_t tmem_empty[2];         // used in the leader: both CTAs' epilogues have drained the accumulator
     uint64_t drain;
@@ -39,15 +42,18 @@ struct PairSmem {
     TileQueue tq;                   // claimed tiles (written by the leader's warp 10)
 };
 
-template <typename T, bool B_MN>
+template <typename T, bool B_MN, int STAGES = kPStages>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
     pair_agmm_kernel(const __grid_constant__ FusedParams p) {
+    static_assert(STAGES == kPStages || STAGES == kPStagesSolo, "pipeline depth");
+    constexpr int kPStages = STAGES;                 // shadows the default depth inside this kernel
+    constexpr bool kHasSide = STAGES == cb::kPStages;   // the seven-stage form has no copy lanes (world size 1, no gather result)
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
     uint8_t *smem_b = smem + kPStages * kPAStage;
     uint8_t *smem_push = smem + kPStages * (kPAStage + kPBStage);
-    PairSmem *sh = reinterpret_cast<PairSmem *>(smem_push + kSideSmemBytes);
+    PairSmem *sh = reinterpret_cast<PairSmem *>(smem_push + (kHasSide ? kSideSmemBytes : 0));
     static_assert(sizeof(PairSmem) <= 512, "barrier block outgrew its budget");
 
     const int warp = threadIdx.x >> 5;
@@ -313,7 +319,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             }
             __syncwarp();
         }
-        if (lane == 0 && ctid < kPushLanesShared && (moves || (ra.gather_out && !p.compute_only))) {
+        if (kHasSide && lane == 0 && ctid < kPushLanesShared && (moves || (ra.gather_out && !p.compute_only))) {
             // units of BM/kAgSubChunks rows, one flag per unit, every lane owns whole units
             const int units_per_dest = mt_ag * kAgSubChunks;
             const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
