@@ -50,6 +50,7 @@ struct FusedParams {
     RankArgs ranks[kMaxRanks];        // indexed by LOCAL rank (1 entry per process; R entries when emulating)
     uint8_t *heap_base[kMaxRanks];    // VA (in this process) of every PE's symmetric heap
     uint64_t symm_off;                // byte offset of the operator's data region inside the heap
+    uint8_t *mc_base;                 // multicast view of all heaps (a store lands in every heap), or nullptr
     int world, rank_base, n_local, ctas_per_rank;
     int push_ctas;                    // AG-MM: > 0: the last push_ctas CTAs of a rank only move all-gather traffic;
                                       // 0: every CTA pushes from its comm warp next to its GEMM tiles

@@ -353,6 +353,8 @@ int launch_dense(int op, int dtype, cudaStream_t stream, uint32_t block_num, con
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
     p.rs_fp16 = op == OP_MMA2A ? 0 : rs_exchange_fp16();      // rows that are only moved keep the output type
+    // all-gather through the NVSwitch multicast view when the team has one (plain AllGather-Matmul only)
+    p.mc_base = (op == OP_AGMM && variant == AG_PUSH && !wants_gather && R > 1 && !t->emulated) ? t->mc_base : nullptr;
     p.ag_pull = variant == AG_REMOTE_READ ? 1 : 0;
     p.ag_a2a = variant == AG_ALLTOALL ? 1 : 0;
     p.sched = t->sched_dev;

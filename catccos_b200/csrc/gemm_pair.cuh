@@ -319,7 +319,51 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairAgThreads, 1)
             }
             __syncwarp();
         }
-        if (kHasSide && lane == 0 && ctid < kPushLanesShared && (moves || (ra.gather_out && !p.compute_only))) {
+        if (kHasSide && moves && !p.ag_pull && p.mc_base != nullptr) {
+            // push through the multicast view: every unit is read once and stored once, the switch delivers it to
+            // all ranks (this one included).  The whole warp moves a unit, 16 bytes per lane and step; the flags
+            // stay unicast, one release store per peer by lanes 1..R-1 after their own system fence.
+            if (ctid < kPushLanesShared) {
+                const int units = mt_ag * kAgSubChunks;
+                const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);
+                const int lane_id = cta * kPushLanesShared + ctid;
+                const int n_lanes = p.ctas_per_rank * kPushLanesShared;
+                if (ctid == 0 && lane == 0) CB_TRACE(TR_PUSH_BEGIN, globaltimer_ns());
+                // nobody's region may be written before its owner has entered
+                bool ok = true;
+                if (lane < R && lane != rank)
+                    ok = wait_flag_ge(flag_ptr(p, rank, kFlagEntered + lane), p.entered_need, ctl, W_ENTERED, lane);
+                ok = __all_sync(0xffffffffu, ok);
+                uint8_t *mc_slot = p.mc_base + p.symm_off + static_cast<size_t>(rank) * p.M * row_bytes;
+                for (int cu = lane_id; cu < units && ok; cu += n_lanes) {
+                    const int chunk = cu / kAgSubChunks, sub = cu % kAgSubChunks;
+                    const int r0 = chunk * BM + sub * (BM / kAgSubChunks);
+                    const int r1 = min(p.M, r0 + BM / kAgSubChunks);
+                    if (r1 > r0) {
+                        const size_t bytes = (r1 - r0) * row_bytes;            // a multiple of 16
+                        const uint8_t *src = static_cast<const uint8_t *>(ra.A) + r0 * row_bytes;
+                        uint8_t *dst = mc_slot + r0 * row_bytes;
+                        constexpr int kInFlight = 8;
+                        for (size_t off = static_cast<size_t>(lane) * 16; off < bytes; off += 32 * 16 * kInFlight) {
+                            uint4 v[kInFlight];
+#pragma unroll
+                            for (int j = 0; j < kInFlight; ++j)
+                                if (off + j * 512 < bytes) v[j] = ld_nc_v4(src + off + j * 512);
+#pragma unroll
+                            for (int j = 0; j < kInFlight; ++j)
+                                if (off + j * 512 < bytes) multimem_st_v4(dst + off + j * 512, v[j]);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane >= 1 && lane < R) {
+                        fence_sys();
+                        st_release_sys(flag_ptr(p, (rank + lane) % R, kFlagOpBase + rank * units + cu), p.epoch);
+                    }
+                    __syncwarp();
+                }
+                if (ctid == 0 && lane == 0) CB_TRACE(TR_PUSH_END, globaltimer_ns());
+            }
+        } else if (kHasSide && lane == 0 && ctid < kPushLanesShared && (moves || (ra.gather_out && !p.compute_only))) {
             // units of BM/kAgSubChunks rows, one flag per unit, every lane owns whole units
             const int units_per_dest = mt_ag * kAgSubChunks;
             const size_t row_bytes = static_cast<size_t>(p.K) * sizeof(T);

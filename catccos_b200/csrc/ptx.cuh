@@ -221,6 +221,20 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                  : "memory");
 }
 
+// 16-byte store to a multicast address: the NVSwitch writes the value at the same offset of every bound heap.
+// Only for addresses inside a multicast mapping (Team::mc_base); such addresses are never loaded from.
+__device__ __forceinline__ void multimem_st_v4(void *mc_addr, const uint4 &v) {
+    asm volatile("multimem.st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ld_nc_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
 // ----------------------------------------------------- CTA pairs (cta_group::2) ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

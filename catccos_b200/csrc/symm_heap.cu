@@ -59,6 +59,15 @@ const DriverApi *driver_api(std::string *why) {
                   resolve(g_api.TensorMapEncodeTiled, "cuTensorMapEncodeTiled") &&
                   resolve(g_api.GetErrorString, "cuGetErrorString");
         g_api.loaded = ok;
+        if (ok) {      // optional entry points: all or nothing
+            const bool mc = resolve(g_api.DeviceGet, "cuDeviceGet") && resolve(g_api.DeviceGetAttribute, "cuDeviceGetAttribute") &&
+                            resolve(g_api.MulticastCreate, "cuMulticastCreate") &&
+                            resolve(g_api.MulticastAddDevice, "cuMulticastAddDevice") &&
+                            resolve(g_api.MulticastBindMem, "cuMulticastBindMem") &&
+                            resolve(g_api.MulticastUnbind, "cuMulticastUnbind") &&
+                            resolve(g_api.MulticastGetGranularity, "cuMulticastGetGranularity");
+            if (!mc) g_api.MulticastCreate = nullptr;
+        }
     });
     if (!g_api.loaded) {
         if (why) *why = g_api_why;
@@ -89,6 +98,11 @@ static const char *cu_err(const DriverApi *api, CUresult r) {
             return CATCCOS_ERR_CUDA;                                                          \
         }                                                                                     \
     } while (0)
+
+static bool multicast_requested() {
+    const char *e = getenv("CATCCOS_MULTICAST");
+    return e && atoi(e) != 0;
+}
 
 // ------------------------------------------------------------------- the team ----
 static Team *g_team = nullptr;
@@ -286,6 +300,16 @@ static int common_setup(Team *t, uint64_t local_mem_size, const DriverApi **api_
     CU_TRY(api->MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED));
     if (gran == 0) gran = 2u << 20;
     const size_t want = static_cast<size_t>(local_mem_size) + kFlagBytes;
+    if (multicast_requested() && api->MulticastCreate && t->n_pes > 1) {
+        // the whole heap is bound to the multicast object: its size has to be a multiple of that granularity too
+        CUmulticastObjectProp mp;
+        memset(&mp, 0, sizeof(mp));
+        mp.numDevices = static_cast<unsigned>(t->n_pes);
+        mp.size = (want + gran - 1) / gran * gran;
+        mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+        size_t mg = 0;
+        if (api->MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && mg > gran) gran = mg;
+    }
     t->heap_bytes = (want + gran - 1) / gran * gran;
     // status words followed by the tile-queue counters of the fused kernels (two per local rank)
     RT_TRY(cudaMalloc(&t->status_dev, (ST_WORDS + 2 * kMaxRanks) * sizeof(int)));
@@ -297,6 +321,99 @@ static int common_setup(Team *t, uint64_t local_mem_size, const DriverApi **api_
     }
     *api_out = api;
     return CATCCOS_OK;
+}
+
+// Releases this PE's part of the multicast object: the mapping, then the binding of its heap.  No host barrier:
+// also runs from the exit handler of a process that leaves without catccos_shmem_finalize.
+static void release_multicast(const DriverApi *api, Team *t) {
+    if (!t->mc_handle) return;
+    cudaDeviceSynchronize();
+    if (t->mc_base) {
+        api->MemUnmap(reinterpret_cast<CUdeviceptr>(t->mc_base), t->heap_bytes);
+        api->MemAddressFree(reinterpret_cast<CUdeviceptr>(t->mc_base), t->heap_bytes);
+        t->mc_base = nullptr;
+    }
+    CUdevice dev;
+    if (api->DeviceGet(&dev, t->device) == CUDA_SUCCESS) api->MulticastUnbind(t->mc_handle, dev, 0, t->heap_bytes);
+    api->MemRelease(t->mc_handle);
+    t->mc_handle = 0;
+}
+static void multicast_exit_handler() {
+    if (g_team && g_team->mc_handle) {
+        const DriverApi *api = driver_api();
+        if (api) release_multicast(api, g_team);
+    }
+}
+
+// One multicast object over all PEs' heaps (PE 0 creates it, the others import it), every PE binds its heap at
+// offset 0 and maps the object: t->mc_base.  Collective; needs g_team for the host barrier.
+static int setup_multicast(const DriverApi *api, Team *t) {
+    if (!api->MulticastCreate) {
+        set_error("CATCCOS_MULTICAST=1: the driver has no multicast objects");
+        return CATCCOS_ERR_CUDA;
+    }
+    CUdevice dev;
+    CU_TRY(api->DeviceGet(&dev, t->device));
+    int supported = 0;
+    CU_TRY(api->DeviceGetAttribute(&supported, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, dev));
+    if (!supported) {
+        set_error("CATCCOS_MULTICAST=1: device %d does not support multicast objects", t->device);
+        return CATCCOS_ERR_CUDA;
+    }
+    CUmulticastObjectProp mp;
+    memset(&mp, 0, sizeof(mp));
+    mp.numDevices = static_cast<unsigned>(t->n_pes);
+    mp.size = t->heap_bytes;
+    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    int fd = -1;
+    if (t->my_pe == 0) {
+        CU_TRY(api->MulticastCreate(&t->mc_handle, &mp));
+        CU_TRY(api->MemExportToShareableHandle(&fd, t->mc_handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0));
+    }
+    // every PE sends a type-3 message to every peer; PE 0's carries the object's descriptor
+    Msg m{kMagic, 3, t->my_pe, 0};
+    for (int pe = 0; pe < t->n_pes; ++pe) {
+        if (pe == t->my_pe) continue;
+        int rc = send_msg(t, pe, m, fd);
+        if (rc) return rc;
+    }
+    int fds[kMaxRanks];
+    for (int i = 0; i < kMaxRanks; ++i) fds[i] = -1;
+    int rc = recv_all(t, 3, 0, fds);
+    if (rc) return rc;
+    if (fd >= 0) close(fd);
+    if (t->my_pe != 0) {
+        if (fds[0] < 0) {
+            set_error("PE 0 sent no multicast handle");
+            return CATCCOS_ERR_BOOTSTRAP;
+        }
+        CU_TRY(api->MemImportFromShareableHandle(&t->mc_handle, reinterpret_cast<void *>(static_cast<intptr_t>(fds[0])),
+                                                 CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+    }
+    for (int pe = 0; pe < t->n_pes; ++pe)
+        if (fds[pe] >= 0) close(fds[pe]);
+    CU_TRY(api->MulticastAddDevice(t->mc_handle, dev));
+    if ((rc = team_host_barrier())) return rc;          // every device is in before anyone binds
+    CU_TRY(api->MulticastBindMem(t->mc_handle, 0, t->handles[t->my_pe], 0, t->heap_bytes, 0));
+    if ((rc = team_host_barrier())) return rc;
+    size_t mg = 0;
+    CU_TRY(api->MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED));
+    CUdeviceptr ptr = 0;
+    CU_TRY(api->MemAddressReserve(&ptr, t->heap_bytes, mg, 0, 0));
+    CU_TRY(api->MemMap(ptr, t->heap_bytes, 0, t->mc_handle, 0));
+    CUmemAccessDesc acc;
+    memset(&acc, 0, sizeof(acc));
+    acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    acc.location.id = t->device;
+    acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    CU_TRY(api->MemSetAccess(ptr, t->heap_bytes, &acc, 1));
+    t->mc_base = reinterpret_cast<uint8_t *>(ptr);
+    static bool registered = false;
+    if (!registered) {
+        registered = true;
+        atexit(multicast_exit_handler);
+    }
+    return team_host_barrier();
 }
 
 int team_init_emulated(int n_pes, uint64_t local_mem_size) {
@@ -400,7 +517,9 @@ int team_init(int my_pe, int n_pes, uint64_t local_mem_size, const char *ip_port
     }
     g_team = t;
     // nobody may touch a peer's flags before that peer has zeroed them
-    return team_host_barrier();
+    rc = team_host_barrier();
+    if (!rc && n_pes > 1 && multicast_requested()) rc = setup_multicast(api, t);
+    return rc;
 }
 
 int team_finalize() {
@@ -409,6 +528,10 @@ int team_finalize() {
     const DriverApi *api = driver_api();
     cudaDeviceSynchronize();
     team_host_barrier();   // peers may still be reading this PE's memory
+    if (api && t->mc_handle) {
+        release_multicast(api, t);
+        team_host_barrier();   // every PE has unbound its heap before any heap is released
+    }
     if (api) {
         for (int pe = 0; pe < t->n_pes; ++pe) {
             if (t->base[pe]) {

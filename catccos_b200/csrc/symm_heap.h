@@ -36,6 +36,15 @@ struct DriverApi {
                                      CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                      CUtensorMapFloatOOBfill);
     CUresult (*GetErrorString)(CUresult, const char **);
+    // NVSwitch multicast objects (optional: null when the driver has none)
+    CUresult (*DeviceGet)(CUdevice *, int) = nullptr;
+    CUresult (*DeviceGetAttribute)(int *, CUdevice_attribute, CUdevice) = nullptr;
+    CUresult (*MulticastCreate)(CUmemGenericAllocationHandle *, const CUmulticastObjectProp *) = nullptr;
+    CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice) = nullptr;
+    CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t,
+                                 unsigned long long) = nullptr;
+    CUresult (*MulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t) = nullptr;
+    CUresult (*MulticastGetGranularity)(size_t *, const CUmulticastObjectProp *, CUmulticastGranularity_flags) = nullptr;
     bool loaded = false;
 };
 // Returns nullptr (and sets *why) when no driver is available.
@@ -54,6 +63,10 @@ struct Team {
     size_t top_reserved = 0;       // bytes at the end of the heap held by team_top_region (not part of the stack)
     uint8_t *base[kMaxRanks] = {};
     CUmemGenericAllocationHandle handles[kMaxRanks] = {};
+    // NVSwitch multicast view of all heaps (CATCCOS_MULTICAST=1, one process per PE): a store to mc_base + offset
+    // lands at that offset of EVERY PE's heap.  Written with multimem.st only, never read.
+    uint8_t *mc_base = nullptr;
+    CUmemGenericAllocationHandle mc_handle = 0;
     uint32_t epoch = 0;            // launches so far; identical on all PEs by collective-call order
     int *status_dev = nullptr;     // StatusWord[ST_WORDS]
     int *sched_dev = nullptr;      // tile-queue counters: {next tile, pairs finished} per local rank, zero between launches
