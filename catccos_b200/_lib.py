@@ -96,6 +96,7 @@ for _op in ("MatmulAllReduce", "AllGatherMatmul", "MatmulReduceScatter", "Ascend
 for _dt in ("FP16", "BF16"):
     SIGNATURES[f"LaunchAscend950Fp8MxAllGatherMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
     SIGNATURES[f"LaunchAscend950Fp4MxAllGatherMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
+    SIGNATURES[f"LaunchAscend950Fp4MxMatmulReduceScatter{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
 
 
 for _dt in ("FP16", "BF16"):

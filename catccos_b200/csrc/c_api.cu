@@ -576,7 +576,8 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
     if (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL)
         return mx_ag_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k), commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL ? 1 : 0);
-    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER || commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL)
+    if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER || commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL ||
+        commType == CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER)
         return dense_symmetric_bytes(OP_MMRS, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
     if (commType == CATCCOS_MX_QUANT_ALLGATHER)
@@ -596,7 +597,8 @@ size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTili
     (void)dataType;
     if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLGATHER_MATMUL || commType == CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL ||
                    commType == CATCCOS_ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER ||
-                   commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL))
+                   commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL ||
+                   commType == CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER))
         return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
     if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
@@ -673,6 +675,8 @@ MXAG_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulBF16, CATCCOS_BF16, 1)
     }
 MXA2A_LAUNCH(LaunchAscend950MxFp8MatmulAllToAllFP16, CATCCOS_FP16)
 MXA2A_LAUNCH(LaunchAscend950MxFp8MatmulAllToAllBF16, CATCCOS_BF16)
+MXRS_LAUNCH(LaunchAscend950Fp4MxMatmulReduceScatterFP16, CATCCOS_FP16, 2)
+MXRS_LAUNCH(LaunchAscend950Fp4MxMatmulReduceScatterBF16, CATCCOS_BF16, 2)
 MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterFP16, CATCCOS_FP16, 1)
 MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterBF16, CATCCOS_BF16, 1)
 MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterFP16, CATCCOS_FP16, 0)
@@ -726,6 +730,8 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
         return launch_mx_rs_abi(dataType, 1, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_rs_abi(dataType, 0, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB, 1);
+    if (commType == CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_rs_abi(dataType, 2, stream, blockNum, params, 1, &workspace, symmetric, tiling, transA, transB);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
@@ -762,6 +768,9 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
     if (commType == CATCCOS_ASCEND950_MXFP8_MATMUL_ALLTOALL && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
         return launch_mx_rs_abi(dataType, 0, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
                                 transB, 1);
+    if (commType == CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_mx_rs_abi(dataType, 2, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, transA,
+                                transB);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && dataType == CATCCOS_BF16)
         return launch_moe_abi(stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)

@@ -254,17 +254,18 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
     return b_mn ? launch_k<__half, true>(p, grid, coop, stream) : launch_k<__half, false>(p, grid, coop, stream);
 }
 
-template <typename TOut, bool B_MN>
+template <typename TOut, bool B_MN, int FMT = MX_FP8>
 static int launch_rs_k(const MxRsParams &p, const RsMapsAll &maps, int grid, bool coop, cudaStream_t stream) {
-    auto kern = mx_pair_rs_kernel<TOut, B_MN>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxRsSmemBytes);
+    auto kern = mx_pair_rs_kernel<TOut, B_MN, FMT>;
+    constexpr int kSmem = FMT == MX_FP4 ? kMxRsSmemBytesFp4 : kMxRsSmemBytes;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e == cudaSuccess) {
         if (coop) {
             void *args[] = {const_cast<MxRsParams *>(&p), const_cast<RsMapsAll *>(&maps)};
             e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(kern), dim3(grid), dim3(kGemmThreads), args,
-                                            kMxRsSmemBytes, stream);
+                                            kSmem, stream);
         } else {
-            kern<<<grid, kGemmThreads, kMxRsSmemBytes, stream>>>(p, maps);
+            kern<<<grid, kGemmThreads, kSmem, stream>>>(p, maps);
             e = cudaGetLastError();
         }
     }
@@ -292,10 +293,16 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
         set_error("MXFP8 Matmul-ReduceScatter writes FP16 (1) or BF16 (27), got %d", out_dtype);
         return CATCCOS_ERR_INVALID;
     }
-    if (code_format != 0 && code_format != 1) {
-        set_error("code format must be 0 (e4m3) or 1 (e5m2), got %d", code_format);
+    if (code_format != 0 && code_format != 1 && code_format != 2) {
+        set_error("code format must be 0 (e4m3), 1 (e5m2) or 2 (e2m1, MXFP4), got %d", code_format);
         return CATCCOS_ERR_INVALID;
     }
+    const bool fp4 = code_format == 2;
+    if (fp4 && (!trans_b || (k % 64) != 0)) {
+        set_error("MXFP4 operands are K-major (transB = 1) with k a multiple of 64 (k=%d transB=%d)", k, trans_b);
+        return CATCCOS_ERR_INVALID;
+    }
+    const int kbytes = fp4 ? k / 2 : k;
     const int R = t->n_pes;
     if (m <= 0 || n <= 0 || k <= 0 || (k % 32) != 0 || (n % 16) != 0 || (m % R) != 0 || ((m / R) % BM) != 0) {
         set_error("unsupported shape m=%d n=%d k=%d for %d ranks (k multiple of 32, n multiple of 16, m/ranks multiple of %d)",
@@ -321,7 +328,7 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
             set_error("shape needs more flags than the flag region holds");
             return CATCCOS_ERR_INVALID;
         }
-        sig = slot_sig(0x4D585253ull, static_cast<uint64_t>(m));
+        sig = slot_sig(0x4D585253ull + static_cast<uint64_t>(code_format) * 16 + (alltoall ? 1 : 0), static_cast<uint64_t>(m));
         sig = slot_sig(sig, static_cast<uint64_t>(n));
         sig = slot_sig(sig, static_cast<uint64_t>(k));
         sig = slot_sig(sig, symm_off);
@@ -358,8 +365,8 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
                      : sf_to_atoms_launch(stream, a.b_scale, 1, n, kblocks, 0, sfb);
         if (rc) return rc;
         MxRankArgs &ra = p.ranks[l];
-        if ((rc = encode_u8(api, &ra.tmA, a.A, k, m, MX_BK, BM))) return rc;
-        rc = trans_b ? encode_u8(api, &ra.tmB, a.B, k, n, MX_BK, 128) : encode_u8(api, &ra.tmB, a.B, n, k, 128, MX_BK);
+        if ((rc = encode_u8(api, &ra.tmA, a.A, kbytes, m, MX_BK, BM))) return rc;
+        rc = trans_b ? encode_u8(api, &ra.tmB, a.B, kbytes, n, MX_BK, 128) : encode_u8(api, &ra.tmB, a.B, n, k, 128, MX_BK);
         if (rc) return rc;
         if ((rc = encode_atoms(api, &ra.tmSfa, sfa, static_cast<uint64_t>(mt) * kb4))) return rc;
         if ((rc = encode_atoms(api, &ra.tmSfb, sfb, static_cast<uint64_t>((n + 127) / 128) * kb4))) return rc;
@@ -390,7 +397,7 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
     p.epoch = epoch;
     p.entered_need = slot.entered_need;
     p.compute_only = compute_only ? 1 : 0;
-    p.rs_fp16 = rs_exchange_fp16();
+    p.rs_fp16 = alltoall ? 0 : rs_exchange_fp16();      // rows that are only moved keep the output type
     p.timeout_ns = t->timeout_ns;
     p.status = t->status_dev;
     p.trace = t->trace_dev;
@@ -398,6 +405,9 @@ int launch_mx_matmul_reduce_scatter(int out_dtype, int code_format, cudaStream_t
     const bool coop = n_local > 1;
     const bool b_mn = trans_b == 0;
     const int grid = per_rank * n_local;
+    if (fp4)
+        return out_dtype == 27 ? launch_rs_k<__nv_bfloat16, false, MX_FP4>(p, maps, grid, coop, stream)
+                               : launch_rs_k<__half, false, MX_FP4>(p, maps, grid, coop, stream);
     if (out_dtype == 27)
         return b_mn ? launch_rs_k<__nv_bfloat16, true>(p, maps, grid, coop, stream)
                     : launch_rs_k<__nv_bfloat16, false>(p, maps, grid, coop, stream);

@@ -16,6 +16,10 @@ namespace cb {
 constexpr int kMxRsStages = 5;                  // 5 x 33.5 KiB + 32 KiB of epilogue staging
 constexpr int kMxRsSmemBytes = kMxRsStages * (kMxPA + kMxPB + kMxPSf) + kSideSmemBytes + 1024 + 512;
 static_assert(kMxRsSmemBytes <= 232448, "shared memory budget");
+// MXFP4 operands (e2m1, K-major only): a stage of 128 bytes per row holds 256 elements = two scale atoms per operand tile
+constexpr int kMxRsSfFp4 = 3072;
+constexpr int kMxRsSmemBytesFp4 = kMxRsStages * (kMxPA + kMxPB + kMxRsSfFp4) + kSideSmemBytes + 1024 + 512;
+static_assert(kMxRsSmemBytesFp4 <= 232448, "shared memory budget");
 
 struct MxRsParams {
     MxRankArgs ranks[kMaxRanks];     // tmA [M, K], tmB, tmSfa / tmSfb scale atoms, C; the gathered maps are unused
@@ -46,9 +50,12 @@ struct MxRsSmem {
     int epi_ok[2];
 };
 
-template <typename TOut, bool B_MN>
+template <typename TOut, bool B_MN, int FMT = MX_FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     mx_pair_rs_kernel(const __grid_constant__ MxRsParams p, const __grid_constant__ RsMapsAll maps) {
+    static_assert(!(FMT == MX_FP4 && B_MN), "4-bit operands are K-major");
+    constexpr int kMxPSf = FMT == MX_FP4 ? kMxRsSfFp4 : cb::kMxPSf;     // shadows the MXFP8 constant
+    constexpr int kAtoms = FMT == MX_FP4 ? 2 : 1;                        // scale atoms per operand tile and stage
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
@@ -75,8 +82,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     const int mt2 = (mr + BM2 - 1) / BM2;
     const int per = ((mr + BM - 1) / BM) * nt;                  // flag index space: 128-row tiles per owner
     const int num_tiles = R * mt2 * nt;
-    const int kblocks = (p.K + MX_BK - 1) / MX_BK;
-    const int kb4 = kblocks;
+    const int Kb = FMT == MX_FP4 ? p.K / 2 : p.K;               // bytes of one operand row
+    const int kblocks = (Kb + MX_BK - 1) / MX_BK;               // pipeline stages per tile
+    const int kb4 = (p.K + 127) / 128;                          // scale atoms per row tile
     const int a_atoms_rows = (p.M + BM - 1) / BM;               // atom rows of A's scales
 
     if (threadIdx.x == 0) {
@@ -144,15 +152,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     if (!(ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY))) break;
                     const uint32_t full_leader = mapa_cluster(smem_u32(&sh->full[st]), 0);
                     uint8_t *ssf = smem_sf + st * kMxPSf;
-                    mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB + 1024 + (second_b_atom ? 512 : 0));
+                    const int atoms = min(kAtoms, kb4 - kb * kAtoms);      // the last MXFP4 stage may hold one atom
+                    mbar_expect_tx_cluster(full_leader, kMxPA + kMxPB + atoms * 512 * (second_b_atom ? 3 : 2));
                     tma_load_2d_pair(smem_a + st * kMxPA, &ra.tmA, full_leader, kb * MX_BK, a_row);
                     if (B_MN)
                         tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, n_half, kb * MX_BK);
                     else
                         tma_load_2d_pair(smem_b + st * kMxPB, &ra.tmB, full_leader, kb * MX_BK, n_half);
-                    tma_load_2d_pair(ssf, &ra.tmSfa, full_leader, 0, sfa_atom0 + kb);
-                    tma_load_2d_pair(ssf + 512, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb);
-                    if (second_b_atom) tma_load_2d_pair(ssf + 1024, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb4 + kb);
+                    for (int a = 0; a < atoms; ++a) {
+                        const int ka = kb * kAtoms + a;
+                        tma_load_2d_pair(ssf + a * 512, &ra.tmSfa, full_leader, 0, sfa_atom0 + ka);
+                        tma_load_2d_pair(ssf + (kAtoms + a) * 512, &ra.tmSfb, full_leader, 0, sfb_atom0 + ka);
+                        if (second_b_atom)
+                            tma_load_2d_pair(ssf + (2 * kAtoms + a) * 512, &ra.tmSfb, full_leader, 0, sfb_atom0 + kb4 + ka);
+                    }
                 }
             }
             if (!ok) {
@@ -180,18 +193,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const uint32_t a_addr = smem_u32(smem_a + st * kMxPA);
                     const uint32_t b_addr = smem_u32(smem_b + st * kMxPB);
                     const uint32_t sf_addr = smem_u32(smem_sf + st * kMxPSf);
-                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * 16u;
-                    const uint32_t tmem_sfb = tmem_sfa + 4;
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
-                    tmem_cp_32x128b_warpx4_pair(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));
+                    const uint32_t tmem_sfa = tmem_sf0 + (it & 3u) * (FMT == MX_FP4 ? 24u : 16u);
+                    if constexpr (FMT == MX_FP4) {
+                        const uint32_t tmem_sfb = tmem_sfa + 4 * kAtoms;     // per atom: 4 columns (n 0-127) + 4 (n 128-255)
+                        const int mmas = min(4, p.K / 64 - kb * 4);
+                        const int atoms = (mmas + 1) / 2;
+                        for (int a = 0; a < atoms; ++a) {
+                            tmem_cp_32x128b_warpx4_pair(tmem_sfa + a * 4, make_smem_desc_noswizzle(sf_addr + a * 512, 16, 128));
+                            tmem_cp_32x128b_warpx4_pair(tmem_sfb + a * 8,
+                                                        make_smem_desc_noswizzle(sf_addr + (kAtoms + a) * 512, 16, 128));
+                            tmem_cp_32x128b_warpx4_pair(tmem_sfb + a * 8 + 4,
+                                                        make_smem_desc_noswizzle(sf_addr + (2 * kAtoms + a) * 512, 16, 128));
+                        }
+                        for (int k = 0; k < mmas; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);   // 64 e2m1 = 32 bytes of a row
+                            const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t sf_id = static_cast<uint32_t>(k & 1) * 2u;
+                            umma_mxfp4_pair(tmem_base, ad, bd, make_idesc_fp4(2 * BM, BN, sf_id, sf_id, 1u), tmem_sfa + (k >> 1) * 4,
+                                            tmem_sfb + (k >> 1) * 8, (kb | k) != 0);
+                        }
+                    } else {
+                        const uint32_t tmem_sfb = tmem_sfa + 4;
+                        tmem_cp_32x128b_warpx4_pair(tmem_sfa, make_smem_desc_noswizzle(sf_addr, 16, 128));
+                        tmem_cp_32x128b_warpx4_pair(tmem_sfb, make_smem_desc_noswizzle(sf_addr + 512, 16, 128));
+                        tmem_cp_32x128b_warpx4_pair(tmem_sfb + 4, make_smem_desc_noswizzle(sf_addr + 1024, 16, 128));
 #pragma unroll
-                    for (int k = 0; k < MX_BK / 32; ++k) {
-                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
-                        const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
-                                                 : make_smem_desc(b_addr + k * 32, 16, 1024);
-                        const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, k, k) | p.fmt_bits | (B_MN ? (1u << 16) : 0u);
-                        umma_mxf8_pair(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        for (int k = 0; k < MX_BK / 32; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
+                                                     : make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, k, k) | p.fmt_bits | (B_MN ? (1u << 16) : 0u);
+                            umma_mxf8_pair(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        }
                     }
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 0));
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 1));

@@ -20,6 +20,7 @@ FP4_MX_ALLGATHER_MATMUL = 23
 MX_QUANT_ALLGATHER = 24
 FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25
 FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27
+FP4_MX_MATMUL_REDUCE_SCATTER = 30
 DISPATCH_FFN_COMBINE = 32
 ALLTOALL_MATMUL = 101
 MATMUL_ALLTOALL = 102

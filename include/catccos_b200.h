@@ -74,6 +74,7 @@ enum {
     CATCCOS_MX_QUANT_ALLGATHER = 24,
     CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25,
     CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27,
+    CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER = 30,
     CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE = 32,
     /* not in the reference's enum (its example instantiates the device template directly,
      * examples/ascend950_alltoall_matmul/main.cpp): a value of this library's own */
@@ -249,6 +250,13 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllGatherMatmulBF16);
  * tcgen05.mma.kind::mxf4nvf4 kernel with the all-gather of codes and scale atoms fused in. */
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxAllGatherMatmulBF16);
+/* tests/dynamic_tiling/impl/kernel_fp16_ascend950.cpp:211 (Ascend950Fp4MxMatmulReduceScatter; operator class
+ * examples/ascend950_fp4_mx_matmul_reduce_scatter/..._host.h:84): MXFP4 Matmul-ReduceScatter -- operands and scales as
+ * LaunchAscend950Fp4MxAllGatherMatmul* (K-major, transB = 1 only; the reference's example runs transB = 0, whose
+ * N-packed 4-bit B has no tcgen05 form), m = rows of the full product, ptrC = this rank's [m/rankSize, n] rows;
+ * the MXFP8 reduce-scatter pair kernel with tcgen05.mma.kind::mxf4nvf4 on CTA pairs. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxMatmulReduceScatterFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxMatmulReduceScatterBF16);
 
 /* MXFP8 Matmul-ReduceScatter (MatmulReduceScatterMxTla, include/catccos/dgemm/kernel/matmul_reduce_scatter_mx_tla.hpp:39;
  * operator "Ascend950MxFp8MatmulReduceScatter", examples/ascend950_mxfp8_matmul_reduce_scatter/main.cpp:32-141 and

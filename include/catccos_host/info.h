@@ -35,6 +35,7 @@ enum CocCommType {
     MX_QUANT_ALLGATHER = CATCCOS_MX_QUANT_ALLGATHER,
     ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV,
     ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL,
+    ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER,
     ASCEND950_DISPATCH_FFN_COMBINE = CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE,
     UNKNOWN = 36,
     ASCEND950_ALLTOALL_MATMUL = CATCCOS_ASCEND950_ALLTOALL_MATMUL,     // no counterparts in the reference's enum
@@ -95,6 +96,7 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"a5mmata", ASCEND950_MATMUL_ALLTOALL},
         {"a5fp8mxagmm", ASCEND950_FP8_MX_ALLGATHER_MATMUL},
         {"a5fp4mxagmm", ASCEND950_FP4_MX_ALLGATHER_MATMUL},
+        {"a5fp4mmrs", ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER},
         {"a5mxfp8mmrs", ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER},
         {"a5mxfp8mmata", ASCEND950_MXFP8_MATMUL_ALLTOALL},
         {"a5moe", ASCEND950_DISPATCH_FFN_COMBINE},
@@ -122,6 +124,7 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {ASCEND950_MATMUL_ALLTOALL, "Ascend950MatmulAllToAll"},
         {ASCEND950_FP8_MX_ALLGATHER_MATMUL, "Ascend950Fp8MxAllGatherMatmul"},
         {ASCEND950_FP4_MX_ALLGATHER_MATMUL, "Ascend950Fp4MxAllGatherMatmul"},
+        {ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER, "Ascend950Fp4MxMatmulReduceScatter"},
         {ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, "Ascend950MxFp8MatmulReduceScatter"},
         {ASCEND950_MXFP8_MATMUL_ALLTOALL, "Ascend950MxFp8MatmulAllToAll"},
         {ASCEND950_DISPATCH_FFN_COMBINE, "Ascend950DispatchFFNCombine"},

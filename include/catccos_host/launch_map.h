@@ -42,6 +42,8 @@ private:
             {Hash(ASCEND950_MATMUL_REDUCE_SCATTER, BF16), &LaunchAscend950MatmulReduceScatterBF16},
             {Hash(ASCEND950_FP8_MX_ALLGATHER_MATMUL, FP16), &LaunchAscend950Fp8MxAllGatherMatmulFP16},
             {Hash(ASCEND950_FP8_MX_ALLGATHER_MATMUL, BF16), &LaunchAscend950Fp8MxAllGatherMatmulBF16},
+            {Hash(ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER, FP16), &LaunchAscend950Fp4MxMatmulReduceScatterFP16},
+            {Hash(ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER, BF16), &LaunchAscend950Fp4MxMatmulReduceScatterBF16},
             {Hash(ASCEND950_FP4_MX_ALLGATHER_MATMUL, FP16), &LaunchAscend950Fp4MxAllGatherMatmulFP16},
             {Hash(ASCEND950_FP4_MX_ALLGATHER_MATMUL, BF16), &LaunchAscend950Fp4MxAllGatherMatmulBF16},
             {Hash(ASCEND950_MXFP8_MATMUL_ALLTOALL, FP16), &LaunchAscend950MxFp8MatmulAllToAllFP16},

@@ -253,6 +253,38 @@ public:
 };
 REGISTER_OPERATOR("Ascend950Fp4MxAllGatherMatmul", Ascend950Fp4MxAllGatherMatmulOperator);
 
+// MXFP4 Matmul-ReduceScatter (examples/ascend950_fp4_mx_matmul_reduce_scatter/ascend950_fp4_mx_matmul_reduce_scatter_host.h:17-110):
+// rank_<i>_{a,b}[_scale].bin, rank r's rows at offset r*size of output.bin.  B as B^T [n, k/2] (run with transB = 1).
+class Ascend950Fp4MxMatmulReduceScatterOperator : public CatccosOperator {
+public:
+    void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        using namespace catccos_host;
+        const size_t sizeA = static_cast<size_t>(t.m) * t.k / 2, sizeB = static_cast<size_t>(t.k) / 2 * t.n;
+        const size_t kb = (static_cast<size_t>(t.k) + 63) / 64 * 2;
+        const size_t sizeC = static_cast<size_t>(t.m) * t.n / t.rankSize * 2;
+        params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a"), sizeA),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b"), sizeB), DeviceZeros(sizeC),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_a_scale"), t.m * kb, 127),
+                               DeviceBufferFromFile(RankFile(dataFile, "rank_", rankId, "_b_scale"), t.n * kb, 127));
+    }
+    void WriteResultFile(const KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
+        const size_t cSize = static_cast<size_t>(t.m) * t.n / t.rankSize * 2;
+        catccos_host::WriteDeviceBuffer(dataFile + "/output.bin", params.ptrC, cSize, rankId * cSize);
+    }
+    size_t GetWorkspaceSize(const CocTilingParams &t) override {
+        return catccos_workspace_bytes(ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER, BF16, &t);
+    }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        CocTilingParams c = t;
+        c.rankSize = rankSize;
+        return t.m > 0 && t.k % 64 == 0 && t.n % 16 == 0 && rankSize >= 1 && rankSize <= MAX_RANK_SIZE &&
+               t.m % rankSize == 0 && (t.m / rankSize) % 128 == 0 &&
+               catccos_symmetric_bytes(ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER, BF16, &c) <= SHMEM_BUFF_BYTES;
+    }
+};
+REGISTER_OPERATOR("Ascend950Fp4MxMatmulReduceScatter", Ascend950Fp4MxMatmulReduceScatterOperator);
+
 // MXFP8 Matmul-ReduceScatter (examples/ascend950_mxfp8_matmul_reduce_scatter/ascend950_mxfp8_matmul_reduce_scatter_host.h):
 // float8_e5m2 operands, customPtrs = {aScale, bScale}, rank r's rows written at offset r*size of output.bin.
 class Ascend950MxFp8MatmulReduceScatterOperator : public CatccosOperator {

@@ -23,7 +23,7 @@ def test_registry_lists_every_operator_on_the_path(driver):
                         "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
                         "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather",
                         "Ascend950Fp8MxAllToAllVGroupedMatmul", "Ascend950Fp8MxGroupedMatmulAllToAllV",
-                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul", "Ascend950MatmulAllToAll", "Ascend950MxFp8MatmulAllToAll"}
+                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul", "Ascend950MatmulAllToAll", "Ascend950MxFp8MatmulAllToAll", "Ascend950Fp4MxMatmulReduceScatter"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
@@ -122,6 +122,7 @@ def _check(driver, *args):
     ("a5mmata", 8, 8192, 8192, 2048),
     ("a5mxfp8mmata", 8, 8192, 8192, 2048),
     ("a5fp4mxagmm", 8, 2048, 4096, 7168),
+    ("a5fp4mmrs", 8, 8192, 8192, 2048),
     ("mxqtag", 8, 2048, 7168, 0),
     ("a5fp8mxatavgmm", 8, 4096, 4096, 7168, 1, 256),
     ("a5fp8gmmata", 8, 4096, 7168, 2048, 1, 256),
