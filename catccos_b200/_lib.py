@@ -109,6 +109,8 @@ SIGNATURES["LaunchAscend950DispatchFFNCombineBF16"] = (ctypes.c_int, LAUNCH_ARGS
 SIGNATURES["LaunchAscend950BF16QuantAllGatherFP8E4M3FN"] = (ctypes.c_int, LAUNCH_ARGS)
 for _dt in ("FP16", "BF16"):
     SIGNATURES[f"LaunchAscend950Fp8MxAllToAllVGroupedMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
+    SIGNATURES[f"LaunchAscend950Fp4MxAllToAllVGroupedMatmul{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
+    SIGNATURES[f"LaunchAscend950Fp4MxGroupedMatmulAllToAllV{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
     SIGNATURES[f"LaunchAscend950Fp8MxGroupedMatmulAllToAllV{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)
 for _dt in ("FP16", "BF16"):
     SIGNATURES[f"LaunchAscend950MxFp8MatmulReduceScatter{_dt}"] = (ctypes.c_int, LAUNCH_ARGS)

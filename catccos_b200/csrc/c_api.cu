@@ -43,6 +43,17 @@ int dense_op_of(int32_t commType) {
     }
 }
 
+// all-to-all-v grouped matmul family: returns 1 and sets op (0 dispatch-GMM, 1 GMM-combine) and fmt (0 MXFP8, 1 MXFP4)
+int a2av_kind_of(int32_t commType, int *op, int *fmt) {
+    switch (commType) {
+        case CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL: *op = 0; *fmt = 0; return 1;
+        case CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV: *op = 1; *fmt = 0; return 1;
+        case CATCCOS_ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL: *op = 0; *fmt = 1; return 1;
+        case CATCCOS_ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV: *op = 1; *fmt = 1; return 1;
+        default: return 0;
+    }
+}
+
 int dense_flow_of(int32_t commType) {
     return commType == CATCCOS_ALLGATHER_MATMUL_WITH_GATHER_RESULT ? 1
            : commType == CATCCOS_ALLGATHER_MATMUL_REMOTE_READ      ? 2
@@ -205,7 +216,7 @@ int launch_moe_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params,
 // examples' operator classes (examples/ascend950_fp8_mx_alltoallv_grouped_matmul/..._host.h:118):
 // SetKernelParams(a, b, c, aScale, bScale, localTokensPerExpert, globalTokensPerLocalExpert).
 int launch_a2av_abi(int op, int dtype, void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params,
-                    uint8_t **workspaces, uint8_t *symmetric, CocTilingParams *tiling) {
+                    uint8_t **workspaces, uint8_t *symmetric, CocTilingParams *tiling, int fmt = 0) {
     int rc = check_tiling(tiling);
     if (rc) return rc;
     Team *t = team();
@@ -231,7 +242,7 @@ int launch_a2av_abi(int op, int dtype, void *stream, uint32_t blockNum, CatccosK
                    workspaces[i]};
     }
     return launch_a2av(op, dtype, static_cast<cudaStream_t>(stream), blockNum, args, symmetric, static_cast<int>(tiling->m),
-                       static_cast<int>(tiling->n), static_cast<int>(tiling->k), static_cast<int>(tiling->expertNum));
+                       static_cast<int>(tiling->n), static_cast<int>(tiling->k), static_cast<int>(tiling->expertNum), fmt);
 }
 
 int launch_mxq_ag_abi(void *stream, uint32_t blockNum, CatccosKernelParams *params, int n_params, uint8_t *symmetric,
@@ -582,11 +593,10 @@ size_t catccos_symmetric_bytes(int32_t commType, int32_t dataType, const CocTili
                                      static_cast<int>(tiling->k));
     if (commType == CATCCOS_MX_QUANT_ALLGATHER)
         return mxq_allgather_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->n));
-    if ((commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
-         commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && tiling->expertNum > 0)
-        return a2av_symmetric_bytes(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, world,
-                                    static_cast<int>(tiling->m), static_cast<int>(tiling->n), static_cast<int>(tiling->k),
-                                    static_cast<int>(tiling->expertNum));
+    int a2_op = 0, a2_fmt = 0;
+    if (a2av_kind_of(commType, &a2_op, &a2_fmt) && tiling->expertNum > 0)
+        return a2av_symmetric_bytes(a2_op, world, static_cast<int>(tiling->m), static_cast<int>(tiling->n),
+                                    static_cast<int>(tiling->k), static_cast<int>(tiling->expertNum), a2_fmt);
     if (commType == CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE && tiling->expertNum > 0)
         return moe_symmetric_bytes(world, static_cast<int>(tiling->m), static_cast<int>(tiling->k),
                                    static_cast<int>(tiling->n), static_cast<int>(tiling->topK),
@@ -601,10 +611,10 @@ size_t catccos_workspace_bytes(int32_t commType, int32_t dataType, const CocTili
                    commType == CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER))
         return mx_ag_workspace_bytes(static_cast<int>(tiling->m), static_cast<int>(tiling->n),
                                      static_cast<int>(tiling->k));
-    if (tiling && (commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
-                   commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && tiling->expertNum > 0) {
+    int a2_op = 0, a2_fmt = 0;
+    if (tiling && a2av_kind_of(commType, &a2_op, &a2_fmt) && tiling->expertNum > 0) {
         const int world = tiling->rankSize ? static_cast<int>(tiling->rankSize) : (team() ? team()->n_pes : 1);
-        return a2av_workspace_bytes(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, world,
+        return a2av_workspace_bytes(a2_op, world,
                                     static_cast<int>(tiling->m), static_cast<int>(tiling->n), static_cast<int>(tiling->k),
                                     static_cast<int>(tiling->expertNum));
     }
@@ -682,14 +692,19 @@ MXRS_LAUNCH(LaunchAscend950MxFp8MatmulReduceScatterBF16, CATCCOS_BF16, 1)
 MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterFP16, CATCCOS_FP16, 0)
 MXRS_LAUNCH(LaunchAscend950MxFp8E4M3MatmulReduceScatterBF16, CATCCOS_BF16, 0)
 
-#define A2AV_LAUNCH(name, op, dtype)                                                                           \
+#define A2AV_LAUNCH(name, op, dtype) A2AV_LAUNCH_F(name, op, dtype, 0)
+#define A2AV_LAUNCH_F(name, op, dtype, fmt)                                                                    \
     int name(void *stream, uint32_t blockNum, uint64_t fftsAddr, CatccosKernelParams *params, uint8_t *workspace, \
              uint8_t *symmetric, CocTilingParams *tiling, uint32_t transA, uint32_t transB) {                    \
         (void)fftsAddr;                                                                                          \
         (void)transA;                                                                                            \
         (void)transB;                                                                                            \
-        return launch_a2av_abi(op, dtype, stream, blockNum, params, 1, &workspace, symmetric, tiling);           \
+        return launch_a2av_abi(op, dtype, stream, blockNum, params, 1, &workspace, symmetric, tiling, fmt);      \
     }
+A2AV_LAUNCH_F(LaunchAscend950Fp4MxAllToAllVGroupedMatmulFP16, 0, CATCCOS_FP16, 1)
+A2AV_LAUNCH_F(LaunchAscend950Fp4MxAllToAllVGroupedMatmulBF16, 0, CATCCOS_BF16, 1)
+A2AV_LAUNCH_F(LaunchAscend950Fp4MxGroupedMatmulAllToAllVFP16, 1, CATCCOS_FP16, 1)
+A2AV_LAUNCH_F(LaunchAscend950Fp4MxGroupedMatmulAllToAllVBF16, 1, CATCCOS_BF16, 1)
 A2AV_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulFP16, 0, CATCCOS_FP16)
 A2AV_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulBF16, 0, CATCCOS_BF16)
 A2AV_LAUNCH(LaunchAscend950Fp8MxGroupedMatmulAllToAllVFP16, 1, CATCCOS_FP16)
@@ -736,10 +751,9 @@ int catccos_launch(int32_t commType, int32_t dataType, void *stream, uint32_t bl
         return launch_moe_abi(stream, blockNum, params, 1, &workspace, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
         return launch_mxq_ag_abi(stream, blockNum, params, 1, symmetric, tiling);
-    if ((commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
-         commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
-        return launch_a2av_abi(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, dataType, stream, blockNum,
-                               params, 1, &workspace, symmetric, tiling);
+    int a2_op = 0, a2_fmt = 0;
+    if (a2av_kind_of(commType, &a2_op, &a2_fmt) && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_a2av_abi(a2_op, dataType, stream, blockNum, params, 1, &workspace, symmetric, tiling, a2_fmt);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }
@@ -775,10 +789,9 @@ int catccos_launch_emulated(int32_t commType, int32_t dataType, void *stream, ui
         return launch_moe_abi(stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling);
     if (commType == CATCCOS_MX_QUANT_ALLGATHER && dataType == CATCCOS_FP8E4M3FN)
         return launch_mxq_ag_abi(stream, blockNum, params, t->n_pes, symmetric, tiling);
-    if ((commType == CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL ||
-         commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV) && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
-        return launch_a2av_abi(commType == CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV ? 1 : 0, dataType, stream, blockNum,
-                               params, t->n_pes, workspaces, symmetric, tiling);
+    int a2_op = 0, a2_fmt = 0;
+    if (a2av_kind_of(commType, &a2_op, &a2_fmt) && (dataType == CATCCOS_FP16 || dataType == CATCCOS_BF16))
+        return launch_a2av_abi(a2_op, dataType, stream, blockNum, params, t->n_pes, workspaces, symmetric, tiling, a2_fmt);
     set_error("no kernel registered for commType=%d dataType=%d", commType, dataType);
     return CATCCOS_ERR_INVALID;
 }

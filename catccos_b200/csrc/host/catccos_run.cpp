@@ -6,7 +6,7 @@
 //
 //   catccos_run <kernel> <dtype> <rank_size> <rank_id> <ip_port> <m> <n> <k> <data_dir>
 //               [transA transB [topK expertNum [device_id [warmup timed]]]]
-//   kernel: mmar | agmm | a5agmm | mmrs | a5mmrs | a5fp8mxagmm | a5mxfp8mmrs | a5moe | mxqtag | a5fp8mxatavgmm | a5fp8gmmata | agmmwg | agmmrr | a5fp4mxagmm | a5atamm | a5mmata | a5mxfp8mmata | a5fp4mmrs
+//   kernel: mmar | agmm | a5agmm | mmrs | a5mmrs | a5fp8mxagmm | a5mxfp8mmrs | a5moe | mxqtag | a5fp8mxatavgmm | a5fp8gmmata | agmmwg | agmmrr | a5fp4mxagmm | a5atamm | a5mmata | a5mxfp8mmata | a5fp4mmrs | a5fp4mxatavgmm | a5fp4gmmata
 //   dtype: 1 (fp16) | 27 (bf16) | 36 (float8_e4m3fn, mxqtag)
 //   catccos_run --list        prints the registered operator names
 //   catccos_run --check <kernel> <rank_size> <m> <n> <k> [topK expertNum]

@@ -357,7 +357,7 @@ struct A2avSizes {
     size_t idx, eri, meta, recv_atoms, w_atoms;                           // workspace
 };
 
-static A2avSizes a2av_sizes(int op, int world, int m, int n, int k, int experts) {
+static A2avSizes a2av_sizes(int op, int world, int m, int n, int k, int experts, int fmt = 0) {
     A2avSizes z;
     const int el = experts / world;
     // op 0: a rank can receive every row of every rank; op 1: the rows are already here
@@ -365,7 +365,7 @@ static A2avSizes a2av_sizes(int op, int world, int m, int n, int k, int experts)
     z.sld = (k / 32 + 1) / 2 * 2;
     z.nb128 = (n + 127) / 128;
     z.counts = up(static_cast<size_t>(world) * experts * 4, 1024);
-    z.recv_codes = up(static_cast<size_t>(z.rows_cap) * k, 1024);
+    z.recv_codes = up(static_cast<size_t>(z.rows_cap) * (fmt ? k / 2 : k), 1024);      // MXFP4: two codes per byte
     z.recv_scale = up(static_cast<size_t>(z.rows_cap) * z.sld, 1024);
     // op 1: a rank gets back one row for every row it contributed, on whichever owner: up to world * m rows
     const size_t out_rows = static_cast<size_t>(op == 1 ? world : 1) * m;
@@ -378,9 +378,9 @@ static A2avSizes a2av_sizes(int op, int world, int m, int n, int k, int experts)
     return z;
 }
 
-size_t a2av_symmetric_bytes(int op, int world, int m, int n, int k, int experts) {
+size_t a2av_symmetric_bytes(int op, int world, int m, int n, int k, int experts, int fmt) {
     if (world < 1 || experts < world || experts % world) return 0;
-    const A2avSizes z = a2av_sizes(op, world, m, n, k, experts);
+    const A2avSizes z = a2av_sizes(op, world, m, n, k, experts, fmt);
     return z.counts + z.recv_codes + z.recv_scale + z.combine;
 }
 size_t a2av_workspace_bytes(int op, int world, int m, int n, int k, int experts) {
@@ -407,7 +407,7 @@ static int encode_b3(const DriverApi *api, CUtensorMap *tm, const void *base, ui
 }
 
 int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, const A2avArgs *args, void *symmetric,
-                int m, int n, int k, int experts) {
+                int m, int n, int k, int experts, int fmt) {
     Team *t = team();
     if (!t) {
         set_error("symmetric heap not initialised (call catccos_shmem_init first)");
@@ -428,6 +428,15 @@ int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, 
         set_error("all-to-all-v grouped matmul requires k %% 64 == 0 and n %% 16 == 0 (m=%d n=%d k=%d)", m, n, k);
         return CATCCOS_ERR_INVALID;
     }
+    if (fmt != 0 && fmt != 1) {
+        set_error("unknown operand format %d (0 = MXFP8, 1 = MXFP4)", fmt);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (fmt == 1 && (k % 256) != 0) {
+        set_error("the MXFP4 all-to-all-v operators require k %% 256 == 0 (k=%d)", k);
+        return CATCCOS_ERR_INVALID;
+    }
+    const int kbytes = fmt ? k / 2 : k;      // bytes of one operand row
     if (experts <= 0 || experts % R != 0 || experts > kMoeMaxExperts || experts / R > kMoeMaxLocalExperts) {
         set_error("unsupported expert setup: experts=%d (max %d, divisible by world %d, at most %d per rank)", experts,
                   kMoeMaxExperts, R, kMoeMaxLocalExperts);
@@ -435,7 +444,7 @@ int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, 
     }
     const int el = experts / R;
     const int n_local = t->emulated ? R : 1;
-    const A2avSizes z = a2av_sizes(op, R, m, n, k, experts);
+    const A2avSizes z = a2av_sizes(op, R, m, n, k, experts, fmt);
     const size_t need = z.counts + z.recv_codes + z.recv_scale + z.combine;
     uint8_t *sp = static_cast<uint8_t *>(symmetric);
     uint8_t *hb = t->base[t->my_pe];
@@ -465,7 +474,7 @@ int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, 
     p.n_local = n_local;
     p.ctas_per_rank = per_rank;
     p.m = op == 1 ? R * m : m;            // rows the routing kernel walks: this rank's row list
-    p.K = k;
+    p.K = kbytes;                         // the row-moving kernels count bytes
     p.N = n;
     p.top_k = 1;
     p.experts = experts;
@@ -488,7 +497,8 @@ int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, 
     q.epoch = p.epoch;
     q.timeout_ns = p.timeout_ns;
     q.status = p.status;
-    q.Kin = k;
+    q.Kin = kbytes;
+    q.fp4 = fmt;
     q.Nw = n;
     q.counter_slot = 2;
 
@@ -522,8 +532,10 @@ int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, 
         const int pe = t->emulated ? l : t->my_pe;
         MoePairRankArgs &r = q.ranks[l];
         int rc;
-        if ((rc = encode_u8(api, &r.tmA, t->base[pe] + p.lay.recv_codes_off, k, z.rows_cap))) return rc;
-        if ((rc = encode_b3(api, &r.tmB, a.b, n, k, el))) return rc;
+        if ((rc = encode_u8(api, &r.tmA, t->base[pe] + p.lay.recv_codes_off, kbytes, z.rows_cap))) return rc;
+        // MXFP8: weights [E_local][k][n] (transB = 0, as the reference's example); MXFP4: K-major [E_local][n][k/2]
+        rc = fmt ? encode_u8(api, &r.tmB, a.b, kbytes, static_cast<uint64_t>(el) * n) : encode_b3(api, &r.tmB, a.b, n, k, el);
+        if (rc) return rc;
         r.sfa = recv_atoms[l];
         r.sfb = w_atoms[l];
         r.out = a.c;
@@ -538,8 +550,10 @@ int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, 
     const size_t expert_atoms = sf_atoms_bytes(z.nb128 * 128, k);
     for (int l = 0; l < n_local; ++l)
         for (int e = 0; e < el; ++e)
-            if ((rc = sf_to_atoms_launch(stream, args[l].b_scale + static_cast<size_t>(e) * (k / 64) * n * 2, 1, n, k / 32, 0,
-                                         w_atoms[l] + e * expert_atoms)))
+            if ((rc = fmt ? sf_to_atoms_launch(stream, args[l].b_scale + static_cast<size_t>(e) * n * (k / 32), 0, n, k / 32, k / 32,
+                                               w_atoms[l] + e * expert_atoms)      // [n, k/64, 2] rows of the K-major weights
+                          : sf_to_atoms_launch(stream, args[l].b_scale + static_cast<size_t>(e) * (k / 64) * n * 2, 1, n, k / 32, 0,
+                                               w_atoms[l] + e * expert_atoms)))
                 return rc;
     if (op == 0 && (rc = moe_launch_wait_dispatch(p, stream))) return rc;
     for (int l = 0; l < n_local; ++l) {
@@ -556,6 +570,13 @@ int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, 
         }
     }
     const bool bf16 = out_dtype == CATCCOS_BF16;
+    if (fmt) {      // MXFP4: K-major weights
+        if (op == 0)
+            return bf16 ? launch_pair_gemm<3, __nv_bfloat16, false>(q, stream) : launch_pair_gemm<3, __half, false>(q, stream);
+        rc = bf16 ? launch_pair_gemm<2, __nv_bfloat16, false>(q, stream) : launch_pair_gemm<2, __half, false>(q, stream);
+        if (rc) return rc;
+        return a2av_launch_copy_out(p, n, stream);
+    }
     if (op == 0)
         return bf16 ? launch_pair_gemm<3, __nv_bfloat16, true>(q, stream) : launch_pair_gemm<3, __half, true>(q, stream);
     rc = bf16 ? launch_pair_gemm<2, __nv_bfloat16, true>(q, stream) : launch_pair_gemm<2, __half, true>(q, stream);

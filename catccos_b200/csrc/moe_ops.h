@@ -35,10 +35,11 @@ struct A2avArgs {
     const int *local_tokens;     // int32 [experts]
     uint8_t *workspace;          // a2av_workspace_bytes()
 };
-size_t a2av_symmetric_bytes(int op, int world, int m, int n, int k, int experts);
+// fmt: 0 = MXFP8 (weights [E_local, k, n]), 1 = MXFP4 (two e2m1 codes per byte, weights K-major [E_local, n, k/2], k % 256 == 0)
+size_t a2av_symmetric_bytes(int op, int world, int m, int n, int k, int experts, int fmt = 0);
 size_t a2av_workspace_bytes(int op, int world, int m, int n, int k, int experts);
 int launch_a2av(int op, int out_dtype, cudaStream_t stream, uint32_t block_num, const A2avArgs *args, void *symmetric,
-                int m, int n, int k, int experts);
+                int m, int n, int k, int experts, int fmt = 0);
 
 // kernels in moe_aux.cu
 int a2av_launch_expert_idx(const MoeParams &p, const A2avPtrs &ptrs, cudaStream_t stream);

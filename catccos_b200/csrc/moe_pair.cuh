@@ -53,7 +53,8 @@ struct MoePairParams {
     uint8_t *heap_base[kMaxRanks];
     uint64_t combine_off;      // MODE 2: bf16 [m*topK, Nw] combine buffer inside every heap
     int world, rank_base, n_local, ctas_per_rank;      // ctas_per_rank is even
-    int Kin, Nw;
+    int Kin, Nw;               // Kin: BYTES of one activation / weight row along the contraction
+    int fp4;                   // 1: MXFP4 operands (two e2m1 codes per byte, K-major weights, two scale atoms per stage)
     int rows_cap;              // rows of the activation buffer (a multiple of 128)
     int experts, experts_per_rank;
     int counter_slot;          // MoeMeta::done_counter / tile_queue slot of this launch
@@ -107,7 +108,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMoePairThreads, 1)
     MoeMeta *meta = ra.meta;
     const int n_tiles = (MODE == 1) ? (p.Nw / 2) / 128 : (p.Nw + BN - 1) / BN;
     const int nb128 = (p.Nw + 127) / 128;          // weight scale atoms (128 weight rows each) per expert
-    const int kblocks = (p.Kin + MX_BK - 1) / MX_BK;
+    const int kblocks = (p.Kin + MX_BK - 1) / MX_BK;          // pipeline stages per tile (128 bytes of K each)
+    const int katoms = p.fp4 ? 2 * kblocks : kblocks;          // scale atoms per 128-row tile (one per 128 elements of K)
+    constexpr uint32_t kSfCols = 24;                           // TMEM scale columns per stage: MXFP8 uses 12, MXFP4 24
     const bool skip_all = meta->overflow != 0;
 
     if (threadIdx.x == 0) {
@@ -230,15 +233,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMoePairThreads, 1)
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem_a + st * kMxPA);
                     const uint32_t b_addr = smem_u32(smem_b + st * kMxPB);
-                    const uint32_t tmem_sfa = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols;
-                    const uint32_t tmem_sfb = tmem_sfa + 4;
+                    const uint32_t tmem_sfa = tmem_sf0 + static_cast<uint32_t>(st) * kSfCols;
+                    if (!B_MN && p.fp4) {
+                        // MXFP4: four MMAs of K = 64; atom a = k / 2 of the stage: A at +4a, B at +8 + 8a (two 128-column halves)
 #pragma unroll
-                    for (int k = 0; k < MX_BK / 32; ++k) {
-                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
-                        const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
-                                                 : make_smem_desc(b_addr + k * 32, 16, 1024);
-                        const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, k, k) | (B_MN ? (1u << 16) : 0u);
-                        umma_mxf8_pair(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                            const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t sf_id = static_cast<uint32_t>(k & 1) * 2u;
+                            umma_mxfp4_pair(tmem_base, ad, bd, make_idesc_fp4(2 * BM, BN, sf_id, sf_id, 1u), tmem_sfa + (k >> 1) * 4,
+                                            tmem_sfa + 8 + (k >> 1) * 8, (kb | k) != 0);
+                        }
+                    } else {
+                        const uint32_t tmem_sfb = tmem_sfa + 4;
+#pragma unroll
+                        for (int k = 0; k < MX_BK / 32; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
+                                                     : make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, k, k) | (B_MN ? (1u << 16) : 0u);
+                            umma_mxf8_pair(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        }
                     }
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 0));
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 1));
@@ -450,11 +465,49 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMoePairThreads, 1)
                 n0 = tl.ni * BN;
                 n1 = n0 + 128;
             }
-            const uint8_t *sfa = sfa_all + static_cast<size_t>(tl.row0 >> 7) * kblocks * 512 + lane * 16;
-            const uint8_t *sfb0 = sfb_all + static_cast<size_t>(tl.le * nb128 + (n0 >> 7)) * kblocks * 512 + lane * 16;
-            const uint8_t *sfb1 = (n1 < p.Nw) ? sfb_all + static_cast<size_t>(tl.le * nb128 + (n1 >> 7)) * kblocks * 512 + lane * 16 : sfb0;
+            const uint8_t *sfa = sfa_all + static_cast<size_t>(tl.row0 >> 7) * katoms * 512 + lane * 16;
+            const uint8_t *sfb0 = sfb_all + static_cast<size_t>(tl.le * nb128 + (n0 >> 7)) * katoms * 512 + lane * 16;
+            const uint8_t *sfb1 = (n1 < p.Nw) ? sfb_all + static_cast<size_t>(tl.le * nb128 + (n1 >> 7)) * katoms * 512 + lane * 16 : sfb0;
             // an empty half past the receive buffer has no atoms of its own: any valid ones do (rows are masked)
             if (tl.row0 >= p.rows_cap) sfa = sfa_all + lane * 16;
+            if (!B_MN && p.fp4) {
+                // MXFP4: two atoms per operand tile and stage; the next stage's six rows are in flight
+                uint4 cur[6], nxt[6];
+                auto load6 = [&](uint4 (&v)[6], int kb) {
+                    const size_t o = static_cast<size_t>(kb) * 1024;
+                    v[0] = *reinterpret_cast<const uint4 *>(sfa + o);
+                    v[1] = *reinterpret_cast<const uint4 *>(sfa + o + 512);
+                    v[2] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + o));
+                    v[3] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + o));
+                    v[4] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + o + 512));
+                    v[5] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + o + 512));
+                };
+                load6(nxt, 0);
+                for (int kb = 0; kb < kblocks && ok; ++kb) {
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) cur[j] = nxt[j];
+                    load6(nxt, kb + 1 < kblocks ? kb + 1 : kb);
+                    const int st = it % kMoePStages;
+                    const uint32_t ph = (it / kMoePStages) & 1;
+                    ++it;
+                    if (lane == 0) ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kSfCols + lane_field;
+                    tmem_st_32x4(col, cur[0]);            // A, atom 0 and 1
+                    tmem_st_32x4(col + 4, cur[1]);
+                    tmem_st_32x4(col + 8, cur[2]);        // B atom 0: columns 0-127, 128-255
+                    tmem_st_32x4(col + 12, cur[3]);
+                    tmem_st_32x4(col + 16, cur[4]);       // B atom 1
+                    tmem_st_32x4(col + 20, cur[5]);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->full[st]), 0));
+                }
+                continue;
+            }
             // the atoms of the next kSfAhead K-steps are kept in flight (an L2 round trip is longer than a K-step)
             constexpr int kSfAhead = 4;
             uint4 va[kSfAhead], vb0[kSfAhead], vb1[kSfAhead];
@@ -485,7 +538,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMoePairThreads, 1)
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols + lane_field;
+                    const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kSfCols + lane_field;
                     tmem_st_32x4(col, a);
                     tmem_st_32x4(col + 4, b0);
                     tmem_st_32x4(col + 8, b1);

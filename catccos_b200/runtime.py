@@ -19,7 +19,9 @@ FP8_MX_ALLGATHER_MATMUL = 22
 FP4_MX_ALLGATHER_MATMUL = 23
 MX_QUANT_ALLGATHER = 24
 FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25
+FP4_MX_GROUPED_MATMUL_ALLTOALLV = 26
 FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27
+FP4_MX_ALLTOALLV_GROUPED_MATMUL = 28
 FP4_MX_MATMUL_REDUCE_SCATTER = 30
 DISPATCH_FFN_COMBINE = 32
 ALLTOALL_MATMUL = 101

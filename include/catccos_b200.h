@@ -73,7 +73,9 @@ enum {
     CATCCOS_ASCEND950_FP4_MX_ALLGATHER_MATMUL = 23,
     CATCCOS_MX_QUANT_ALLGATHER = 24,
     CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = 25,
+    CATCCOS_ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV = 26,
     CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = 27,
+    CATCCOS_ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL = 28,
     CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER = 30,
     CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE = 32,
     /* not in the reference's enum (its example instantiates the device template directly,
@@ -295,6 +297,14 @@ CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxAllToAllVGroupedMatmulBF16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxGroupedMatmulAllToAllVFP16);
 CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp8MxGroupedMatmulAllToAllVBF16);
+/* The same two operators on MXFP4 operands (tests/dynamic_tiling/include/launch_map.h:99,101;
+ * examples/ascend950_fp4_mx_alltoallv_grouped_matmul, examples/ascend950_fp4_mx_grouped_matmul_alltoallv): ptrA = e2m1
+ * codes [rows, k/2], ptrB = K-major weights [expertNum/epSize, n, k/2] (the transB = 1 form; N-packed 4-bit
+ * weights have no tcgen05 form), bScale [expertNum/epSize, n, k/64, 2]; k % 256 == 0.  Everything else as above. */
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxAllToAllVGroupedMatmulFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxAllToAllVGroupedMatmulBF16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxGroupedMatmulAllToAllVFP16);
+CATCCOS_DECLARE_LAUNCH(LaunchAscend950Fp4MxGroupedMatmulAllToAllVBF16);
 
 /* The MoE operator: DispatchFFNCombine<...>(fftsAddr, gmA, gmB, gmBScale, gmB2, gmB2Scale, gmD, gmExpertIdx,
  * gmProbs, gmWorkSpace, gmSymmetric, CocTilingParams, ...) (examples/ascend950_dispatch_ffn_combine/

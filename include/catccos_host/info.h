@@ -35,6 +35,8 @@ enum CocCommType {
     MX_QUANT_ALLGATHER = CATCCOS_MX_QUANT_ALLGATHER,
     ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV = CATCCOS_ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV,
     ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL = CATCCOS_ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL,
+    ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV = CATCCOS_ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV,
+    ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL = CATCCOS_ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL,
     ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER = CATCCOS_ASCEND950_FP4_MX_MATMUL_REDUCE_SCATTER,
     ASCEND950_DISPATCH_FFN_COMBINE = CATCCOS_ASCEND950_DISPATCH_FFN_COMBINE,
     UNKNOWN = 36,
@@ -103,6 +105,8 @@ inline const std::map<std::string, CocCommType> &CommTypeMap() {
         {"mxqtag", MX_QUANT_ALLGATHER},
         {"a5fp8gmmata", ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV},
         {"a5fp8mxatavgmm", ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL},
+        {"a5fp4gmmata", ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV},
+        {"a5fp4mxatavgmm", ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL},
     };
     return m;
 }
@@ -131,6 +135,8 @@ inline const std::map<CocCommType, std::string> &CommTypeOpNameMap() {
         {MX_QUANT_ALLGATHER, "MxQuantAllGather"},
         {ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV, "Ascend950Fp8MxGroupedMatmulAllToAllV"},
         {ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL, "Ascend950Fp8MxAllToAllVGroupedMatmul"},
+        {ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV, "Ascend950Fp4MxGroupedMatmulAllToAllV"},
+        {ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL, "Ascend950Fp4MxAllToAllVGroupedMatmul"},
     };
     return m;
 }

@@ -52,6 +52,10 @@ private:
             {Hash(ASCEND950_MXFP8_MATMUL_REDUCE_SCATTER, BF16), &LaunchAscend950MxFp8MatmulReduceScatterBF16},
             {Hash(ASCEND950_DISPATCH_FFN_COMBINE, BF16), &LaunchAscend950DispatchFFNCombineBF16},
             {Hash(MX_QUANT_ALLGATHER, FP8E4M3FN), &LaunchAscend950BF16QuantAllGatherFP8E4M3FN},
+            {Hash(ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL, FP16), &LaunchAscend950Fp4MxAllToAllVGroupedMatmulFP16},
+            {Hash(ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL, BF16), &LaunchAscend950Fp4MxAllToAllVGroupedMatmulBF16},
+            {Hash(ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV, FP16), &LaunchAscend950Fp4MxGroupedMatmulAllToAllVFP16},
+            {Hash(ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV, BF16), &LaunchAscend950Fp4MxGroupedMatmulAllToAllVBF16},
             {Hash(ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL, FP16), &LaunchAscend950Fp8MxAllToAllVGroupedMatmulFP16},
             {Hash(ASCEND950_FP8_MX_ALLTOALLV_GROUPED_MATMUL, BF16), &LaunchAscend950Fp8MxAllToAllVGroupedMatmulBF16},
             {Hash(ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV, FP16), &LaunchAscend950Fp8MxGroupedMatmulAllToAllVFP16},

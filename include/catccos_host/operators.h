@@ -424,11 +424,12 @@ public:
     virtual const char *BName() const { return "input_b_"; }
     virtual const char *AScaleName() const { return "input_a_scale_"; }
     virtual const char *BScaleName() const { return "input_b_scale_"; }
+    virtual size_t CodesPerByte() const { return 1; }      // 2 for the MXFP4 operators
     void AllocateDeviceSpace(KernelParams &params, const CocTilingParams &t, uint32_t rankId, std::string dataFile) override {
         using namespace catccos_host;
         const size_t el = t.expertNum / (t.epSize ? t.epSize : t.rankSize);
         const size_t kb = static_cast<size_t>(t.k) / 32;
-        const size_t sizeA = static_cast<size_t>(t.m) * t.k, sizeB = el * t.k * t.n;
+        const size_t sizeA = static_cast<size_t>(t.m) * t.k / CodesPerByte(), sizeB = el * t.k * t.n / CodesPerByte();
         const size_t sizeC = static_cast<size_t>(t.m) * t.rankSize * t.n * 2;
         params.SetKernelParams(DeviceBufferFromFile(RankFile(dataFile, AName(), rankId), sizeA),
                                DeviceBufferFromFile(RankFile(dataFile, BName(), rankId), sizeB), DeviceZeros(sizeC),
@@ -462,5 +463,25 @@ public:
     CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP8_MX_GROUPED_MATMUL_ALLTOALLV; }
 };
 REGISTER_OPERATOR("Ascend950Fp8MxGroupedMatmulAllToAllV", Ascend950Fp8MxGroupedMatmulAllToAllVOperator);
+// The MXFP4 forms (examples/ascend950_fp4_mx_alltoallv_grouped_matmul, examples/ascend950_fp4_mx_grouped_matmul_alltoallv):
+// the same files with two e2m1 codes per byte; weights K-major (generated with transB = 1), k % 256 == 0.
+class Ascend950Fp4MxAllToAllVGroupedMatmulOperator : public Ascend950Fp8MxAllToAllVGroupedMatmulOperator {
+public:
+    size_t CodesPerByte() const override { return 2; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP4_MX_ALLTOALLV_GROUPED_MATMUL; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        return t.k % 256 == 0 && Ascend950Fp8MxAllToAllVGroupedMatmulOperator::CheckCocTilingParams(rankSize, t);
+    }
+};
+REGISTER_OPERATOR("Ascend950Fp4MxAllToAllVGroupedMatmul", Ascend950Fp4MxAllToAllVGroupedMatmulOperator);
+class Ascend950Fp4MxGroupedMatmulAllToAllVOperator : public Ascend950Fp8MxGroupedMatmulAllToAllVOperator {
+public:
+    size_t CodesPerByte() const override { return 2; }
+    CocCommType GetActualKernelType(const CocTilingParams &) override { return ASCEND950_FP4_MX_GROUPED_MATMUL_ALLTOALLV; }
+    bool CheckCocTilingParams(uint32_t rankSize, const CocTilingParams &t) override {
+        return t.k % 256 == 0 && Ascend950Fp8MxGroupedMatmulAllToAllVOperator::CheckCocTilingParams(rankSize, t);
+    }
+};
+REGISTER_OPERATOR("Ascend950Fp4MxGroupedMatmulAllToAllV", Ascend950Fp4MxGroupedMatmulAllToAllVOperator);
 
 #endif  // CATCCOS_HOST_OPERATORS_H

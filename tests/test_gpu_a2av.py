@@ -146,3 +146,79 @@ def test_argument_errors():
     with pytest.raises(CatccosError, match="k % 64"):
         _run(rt.FP8_MX_ALLTOALLV_GROUPED_MATMUL, world, m, n, k, experts, [z(m, k)] * 2, [z(m, k // 32)] * 2,
              [z(2, k, n)] * 2, [z(2, 2, n, 2)] * 2, [np.zeros(experts, np.int32)] * 2)
+
+
+# ---- MXFP4 forms (Ascend950Fp4MxAllToAllVGroupedMatmul / Ascend950Fp4MxGroupedMatmulAllToAllV), tolerance 5e-2 ----
+TOL_FP4 = 5e-2
+
+
+def _fp4_case(world, rows, n, k, experts, seed):
+    rng = np.random.default_rng(seed)
+    epr = experts // world
+    counts = np.zeros((world, experts), dtype=np.int32)
+    for r in range(world):
+        w = rng.dirichlet(np.full(experts, 0.6))
+        c = np.floor(w * rows).astype(np.int32)
+        c[rng.integers(0, experts)] += rows - int(c.sum()) - int(rng.integers(0, 3))
+        counts[r] = np.maximum(c, 0)
+    b_codes, b_scales, w_deq = [], [], []
+    for r in range(world):
+        cs, ss, ds = [], [], []
+        for le in range(epr):
+            wt = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)          # K-major weights [n, k]
+            _, pk, sc, dq = mxquant.quantize_mx_e2m1(wt)
+            cs.append(pk); ss.append(sc[:, :k // 32].copy()); ds.append(np.ascontiguousarray(dq.T))
+        b_codes.append(np.stack(cs)); b_scales.append(np.stack(ss)); w_deq.append(ds)
+    return rng, counts, b_codes, b_scales, w_deq
+
+
+def _check_fp4(out, gold_rows, what):
+    rows = gold_rows.shape[0]
+    err = verify.max_rel_err(out[:rows], torch.from_numpy(np.ascontiguousarray(gold_rows)))
+    assert err <= TOL_FP4, f"{what}: max relative error {err}"
+    assert not out[rows:].any(), f"{what}: rows past the real count must stay zero"
+
+
+@pytest.mark.parametrize("world,m,n,k,experts,out", [(2, 300, 272, 256, 4, torch.bfloat16), (4, 520, 1024, 512, 8, torch.float16),
+                                                      (8, 200, 256, 768, 32, torch.bfloat16)])
+def test_fp4_alltoallv_grouped_matmul_random(world, m, n, k, experts, out):
+    from catccos_b200 import runtime as rt
+    rng, counts, b_codes, b_scales, w_deq = _fp4_case(world, m, n, k, experts, 311 + world)
+    a_codes, a_scales, a_deq = [], [], []
+    for r in range(world):
+        _, pk, sc, dq = mxquant.quantize_mx_e2m1(rng.standard_normal((m, k)).astype(np.float32))
+        a_codes.append(pk); a_scales.append(sc[:, :k // 32].copy()); a_deq.append(dq)
+    gold, blocks = moe.alltoallv_grouped_matmul(a_deq, w_deq, counts, world, experts // world)
+    outs = _run(rt.FP4_MX_ALLTOALLV_GROUPED_MATMUL, world, m, n, k, experts, a_codes, a_scales, b_codes, b_scales,
+                list(counts), out)
+    for r in range(world):
+        assert gold[r].shape[0] == sum(blocks[r])
+        _check_fp4(outs[r], gold[r], f"fp4 dispatch-GMM rank {r}")
+
+
+@pytest.mark.parametrize("world,m,n,k,experts,out", [(2, 300, 272, 256, 4, torch.float16), (4, 520, 1024, 512, 8, torch.bfloat16),
+                                                      (8, 200, 256, 768, 32, torch.float16)])
+def test_fp4_grouped_matmul_alltoallv_random(world, m, n, k, experts, out):
+    from catccos_b200 import runtime as rt
+    epr = experts // world
+    rng, counts, b_codes, b_scales, w_deq = _fp4_case(world, m // world, n, k, experts, 523 + world)
+    a_codes, a_scales, a_deq = [], [], []
+    for o in range(world):
+        assert int(counts[:, o * epr:(o + 1) * epr].sum()) <= m
+        _, pk, sc, dq = mxquant.quantize_mx_e2m1(rng.standard_normal((m, k)).astype(np.float32))
+        a_codes.append(pk); a_scales.append(sc[:, :k // 32].copy()); a_deq.append(dq)
+    gold = moe.grouped_matmul_alltoallv(a_deq, w_deq, counts, world, epr)
+    outs = _run(rt.FP4_MX_GROUPED_MATMUL_ALLTOALLV, world, m, n, k, experts, a_codes, a_scales, b_codes, b_scales,
+                list(counts), out)
+    for r in range(world):
+        assert gold[r].shape[0] == int(counts[r].sum())
+        _check_fp4(outs[r], gold[r], f"fp4 GMM-combine rank {r}")
+
+
+def test_fp4_needs_k_multiple_of_256():
+    from catccos_b200 import runtime as rt, CatccosError
+    world, m, n, k, experts = 2, 64, 64, 320, 4
+    z = lambda *s: np.zeros(s, dtype=np.uint8)
+    with pytest.raises(CatccosError, match="k % 256"):
+        _run(rt.FP4_MX_ALLTOALLV_GROUPED_MATMUL, world, m, n, k, experts, [z(m, k // 2)] * 2, [z(m, k // 32)] * 2,
+             [z(2, n, k // 2)] * 2, [z(2, n, k // 32)] * 2, [np.zeros(experts, np.int32)] * 2)

@@ -23,7 +23,8 @@ def test_registry_lists_every_operator_on_the_path(driver):
                         "Ascend950MatmulReduceScatter", "Ascend950Fp8MxAllGatherMatmul", "Ascend950DispatchFFNCombine",
                         "Ascend950MxFp8MatmulReduceScatter", "MxQuantAllGather",
                         "Ascend950Fp8MxAllToAllVGroupedMatmul", "Ascend950Fp8MxGroupedMatmulAllToAllV",
-                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul", "Ascend950MatmulAllToAll", "Ascend950MxFp8MatmulAllToAll", "Ascend950Fp4MxMatmulReduceScatter"}
+                        "AllGatherMatmulWithGatherResult", "AllGatherMatmulRemoteRead", "Ascend950Fp4MxAllGatherMatmul", "Ascend950AllToAllMatmul", "Ascend950MatmulAllToAll", "Ascend950MxFp8MatmulAllToAll", "Ascend950Fp4MxMatmulReduceScatter",
+                        "Ascend950Fp4MxAllToAllVGroupedMatmul", "Ascend950Fp4MxGroupedMatmulAllToAllV"}
 
 
 def test_argument_and_init_errors_return_nonzero(driver, tmp_path):
@@ -126,6 +127,8 @@ def _check(driver, *args):
     ("mxqtag", 8, 2048, 7168, 0),
     ("a5fp8mxatavgmm", 8, 4096, 4096, 7168, 1, 256),
     ("a5fp8gmmata", 8, 4096, 7168, 2048, 1, 256),
+    ("a5fp4mxatavgmm", 8, 4096, 4096, 7168, 1, 256),
+    ("a5fp4gmmata", 8, 4096, 7168, 2048, 1, 256),
 ])
 def test_operator_classes_accept_the_benchmark_configurations(driver, args):
     """CheckCocTilingParams of every operator class, and the buffers fit the reference's 1004 MiB symmetric buffer."""
