@@ -709,10 +709,10 @@ def main():
         numa_node = bind_to_gpu_numa_node(local_rank, torch)
         pin = lambda t_: t_.cpu().pin_memory()
         if dense_op:
-            ins, cust, mask, e2e_dtype = [a_h.pin_memory(), b_h.pin_memory()], [], 0, dtype_code
-            per_step = [0, 1]
+            ins, cust, mask, e2e_dtype = [a_h.pin_memory(), b_h.pin_memory()], [], 1 << 1, dtype_code
+            per_step = [0]
             c_p = torch.empty(wl["c_shape"], dtype=dt).pin_memory()
-            resident_note = None
+            resident_note = "B (this rank's weight shard) resident after the first call; A travels every step"
         elif args.op == "mxag":
             ins, cust, mask, e2e_dtype = [pin(a_codes), pin(b_codes)], [pin(a_scale), pin(b_scale)], (1 << 1) | (1 << 4), rt.BF16
             per_step = [0, 2]

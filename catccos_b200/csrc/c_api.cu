@@ -277,6 +277,9 @@ constexpr int kHostRunChunks = 8;
 struct HostRunCache {
     void *dA = nullptr, *dB = nullptr, *dC = nullptr;
     size_t bytesA = 0, bytesB = 0, bytesC = 0;
+    const void *b_host = nullptr;                                // dense operators: the host buffer a resident B came from
+    size_t b_bytes = 0;
+    void *b_dev = nullptr;
     cudaStream_t in = nullptr, run = nullptr, out = nullptr;     // host->device, kernels, device->host
     cudaEvent_t landed[kHostRunChunks + 1] = {};                  // B, then every chunk of A
     cudaEvent_t done[kHostRunChunks] = {};                        // a chunk's rows of C are complete
@@ -889,28 +892,11 @@ static int run_host_general(int32_t commType, int32_t dataType, uint32_t blockNu
 
 int catccos_run_host_resident(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
                               void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
-                              uint32_t transA, uint32_t transB, uint32_t residentMask) {
-    int rc = check_tiling(tiling);
-    if (rc) return rc;
-    if (team()->emulated) {
-        set_error("catccos_run_host needs one process per PE (catccos_shmem_init)");
-        return CATCCOS_ERR_INVALID;
-    }
-    if (dense_op_of(commType) >= 0) {
-        if (residentMask) {
-            set_error("catccos_run_host_resident: the dense operators copy every operand on every call (mask must be 0)");
-            return CATCCOS_ERR_INVALID;
-        }
-        return catccos_run_host(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA,
-                                transB);
-    }
-    return run_host_general(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA,
-                            transB, residentMask);
-}
+                              uint32_t transA, uint32_t transB, uint32_t residentMask);
 
-int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
-                     void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
-                     uint32_t transA, uint32_t transB) {
+static int run_host_any(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
+                        void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
+                        uint32_t transA, uint32_t transB, uint32_t residentMask) {
     int rc = check_tiling(tiling);
     if (rc) return rc;
     Team *t = team();
@@ -921,7 +907,15 @@ int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, cons
     const int op = dense_op_of(commType);
     if (op < 0)
         return run_host_general(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA,
-                                transB, 0);
+                                transB, residentMask);
+    if (dense_flow_of(commType) != 0 || op == OP_MMA2A) {
+        set_error("catccos_run_host: no host-buffer path for commType=%d (the data-flow variants take device buffers)", commType);
+        return CATCCOS_ERR_INVALID;
+    }
+    if (residentMask & ~2u) {
+        set_error("catccos_run_host_resident: of the dense operators' operands only B (bit 1) can stay resident");
+        return CATCCOS_ERR_INVALID;
+    }
     if (dataType != CATCCOS_FP16 && dataType != CATCCOS_BF16) {
         set_error("catccos_run_host: no host-buffer path for commType=%d dataType=%d", commType, dataType);
         return CATCCOS_ERR_INVALID;
@@ -938,6 +932,11 @@ int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, cons
     if ((rc = ensure(&g_hr.dA, &g_hr.bytesA, bytesA)) || (rc = ensure(&g_hr.dB, &g_hr.bytesB, bytesB)) ||
         (rc = ensure(&g_hr.dC, &g_hr.bytesC, bytesC)) || (rc = ensure_host_run_streams()))
         return rc;
+    // a resident B is copied when its host buffer, size or device copy is new
+    const bool copy_b = !((residentMask & 2u) && g_hr.b_host == hostB && g_hr.b_bytes == bytesB && g_hr.b_dev == g_hr.dB);
+    g_hr.b_host = (residentMask & 2u) ? hostB : nullptr;
+    g_hr.b_bytes = bytesB;
+    g_hr.b_dev = g_hr.dB;
     // the symmetric region of this path sits at the end of the heap, outside the stack that the
     // caller's catccos_shmem_malloc / catccos_shmem_free calls grow and shrink
     void *symm = nullptr;
@@ -948,7 +947,7 @@ int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, cons
         // overlap -- chunk i's rows of C travel to the host while chunk i+1 is multiplied and chunk
         // i+2 is still arriving.  B goes first (every chunk needs all of it).
         const size_t rows_per = (m / kHostRunChunks + 255) / 256 * 256;
-        cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.in);
+        if (copy_b) cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.in);
         cudaEventRecord(g_hr.landed[0], g_hr.in);
         cudaStreamWaitEvent(g_hr.run, g_hr.landed[0], 0);
         int chunk = 0;
@@ -974,7 +973,7 @@ int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, cons
     } else {
         // several PEs: the fused launch needs this rank's whole A and B; the copies are stream-ordered around it
         cudaMemcpyAsync(g_hr.dA, hostA, bytesA, cudaMemcpyHostToDevice, g_hr.run);
-        cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.run);
+        if (copy_b) cudaMemcpyAsync(g_hr.dB, hostB, bytesB, cudaMemcpyHostToDevice, g_hr.run);
         CatccosKernelParams kp{static_cast<uint8_t *>(g_hr.dA), static_cast<uint8_t *>(g_hr.dB),
                                static_cast<uint8_t *>(g_hr.dC), nullptr, 0};
         rc = launch_dense_abi(op, dataType, g_hr.run, blockNum, &kp, 1, static_cast<uint8_t *>(symm), tiling, transA,
@@ -988,6 +987,19 @@ int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, cons
     }
     if (rc) return rc;
     return host_run_status();
+}
+
+int catccos_run_host(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
+                     void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
+                     uint32_t transA, uint32_t transB) {
+    return run_host_any(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA, transB, 0);
+}
+
+int catccos_run_host_resident(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA, const void *hostB,
+                              void *hostC, const void *const *hostCustom, uint32_t customCount, CocTilingParams *tiling,
+                              uint32_t transA, uint32_t transB, uint32_t residentMask) {
+    return run_host_any(commType, dataType, blockNum, hostA, hostB, hostC, hostCustom, customCount, tiling, transA, transB,
+                        residentMask);
 }
 
 }  // extern "C"

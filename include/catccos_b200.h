@@ -356,8 +356,8 @@ CATCCOS_API int catccos_run_host(int32_t commType, int32_t dataType, uint32_t bl
  * bit 3 + j = hostCustom[j]) marks an operand as resident: it is copied when its host pointer or size differs
  * from the previous call's and skipped otherwise -- expert weights and weight scales of the MoE operator, the
  * weight matrix of the block-scaled GEMMs.  Serves Ascend950Fp8MxAllGatherMatmul, Ascend950MxFp8MatmulReduceScatter
- * and Ascend950DispatchFFNCombine (hostCustom in the operator's customPtrs order); the dense operators copy
- * everything on every call and accept a mask of 0 only.  catccos_run_host() is this call with a mask of 0. */
+ * and Ascend950DispatchFFNCombine (hostCustom in the operator's customPtrs order); of the dense operators'
+ * operands only B (bit 1) can be resident.  catccos_run_host() is this call with a mask of 0. */
 CATCCOS_API int catccos_run_host_resident(int32_t commType, int32_t dataType, uint32_t blockNum, const void *hostA,
                                           const void *hostB, void *hostC, const void *const *hostCustom,
                                           uint32_t customCount, CocTilingParams *tiling, uint32_t transA, uint32_t transB,
