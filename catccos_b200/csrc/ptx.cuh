@@ -320,6 +320,15 @@ __device__ __forceinline__ void umma_mxfp4_pair(uint32_t d_tmem, uint64_t adesc,
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
         : "memory");
 }
+// NVFP4 (e2m1, UE4M3 scale per 16, K = 64 per instruction, four scales per row and instruction) on a CTA pair
+__device__ __forceinline__ void umma_nvfp4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred P;\n setp.ne.b32 P, %6, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], P;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
 // each CTA of the pair copies 32 rows x 128 bit from its own shared memory (same offset) into its own TMEM
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
