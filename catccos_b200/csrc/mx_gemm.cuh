@@ -66,6 +66,7 @@ struct MxParams {
     uint64_t sf_off;          // byte offset (inside the heap) of the gathered scale atoms
     int world, rank_base, n_local, ctas_per_rank;
     int M, N, K;              // M = rows held by one rank
+    int fp4;                  // pair kernel: 1 = MXFP4 operands (the one-CTA kernel takes the format as a template argument)
     uint32_t epoch;
     uint32_t entered_need;     // a peer's data region may be written once it has entered this epoch
     int compute_only;

@@ -168,7 +168,6 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
     }
     bool use_pair = true;      // CTA pairs (cta_group::2) unless CATCCOS_TWO_CTA=0
     if (const char *e = getenv("CATCCOS_TWO_CTA")) use_pair = atoi(e) != 0;
-    if (fmt == MX_FP4) use_pair = false;      // the 4-bit format exists in the one-CTA kernel
     const int kb4 = (k + 127) / 128;
     MxParams p;
     memset(&p, 0, sizeof(p));
@@ -229,6 +228,7 @@ int launch_mx_allgather_matmul(int out_dtype, cudaStream_t stream, uint32_t bloc
     p.M = m;
     p.N = n;
     p.K = k;
+    p.fp4 = fmt == MX_FP4 ? 1 : 0;
     p.epoch = epoch;
     p.entered_need = slot.entered_need;
     p.compute_only = (t->debug_flags & 1u) ? 1 : 0;

@@ -18,7 +18,7 @@ constexpr int kMxPA = BM * MX_BK;               // 16 KiB
 constexpr int kMxPB = 128 * MX_BK;              // 16 KiB
 constexpr int kMxPairThreads = 480;             // warps 0-10 as the f16/bf16 pair kernel, warps 11-14 feed the scale factors
 constexpr int kMxPSf = 1536;                    // kernels that still stage scale atoms in shared memory: A atom + two B atoms
-constexpr int kMxSfCols = 16;                   // TMEM columns of one stage's scales: 4 (A) + 8 (B), padded
+constexpr int kMxSfCols = 24;                   // TMEM columns of one stage's scales: MXFP8 4 (A) + 8 (B); MXFP4 twice that
 constexpr int kMxPairSmemBytes = kMxPStages * (kMxPA + kMxPB) + kMxSideBytes + 1024 + 512;
 static_assert(kMxPairSmemBytes <= 232448, "shared memory budget");
 
@@ -59,8 +59,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
     const int nt = (p.N + BN - 1) / BN;
     const int per_src = mt2 * nt;
     const int num_tiles = R * per_src;
-    const int kblocks = (p.K + MX_BK - 1) / MX_BK;
-    const int kb4 = kblocks;
+    const bool fp4 = !B_MN && p.fp4 != 0;          // MXFP4: two codes per byte, K-major operands only
+    const int Kb = fp4 ? p.K / 2 : p.K;           // bytes of one operand row
+    const int kblocks = (Kb + MX_BK - 1) / MX_BK;  // pipeline stages per tile
+    const int kb4 = (p.K + 127) / 128;             // scale atoms per row tile (one per 128 elements of K)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMxPStages; ++s) {
@@ -163,14 +165,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
                     const uint32_t a_addr = smem_u32(smem_a + st * kMxPA);
                     const uint32_t b_addr = smem_u32(smem_b + st * kMxPB);
                     const uint32_t tmem_sfa = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols;   // written by warps 11-14
-                    const uint32_t tmem_sfb = tmem_sfa + 4;
+                    if (fp4) {
+                        // four MMAs of K = 64 (fewer in a ragged last stage); atom a = k / 2: A at +4a, B at +8 + 8a
+                        const int mmas = min(4, p.K / 64 - kb * 4);
+                        for (int k = 0; k < mmas; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                            const uint64_t bd = make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t sf_id = static_cast<uint32_t>(k & 1) * 2u;
+                            umma_mxfp4_pair(tmem_base, ad, bd, make_idesc_fp4(2 * BM, BN, sf_id, sf_id, 1u), tmem_sfa + (k >> 1) * 4,
+                                            tmem_sfa + 8 + (k >> 1) * 8, (kb | k) != 0);
+                        }
+                    } else {
+                        const uint32_t tmem_sfb = tmem_sfa + 4;
 #pragma unroll
-                    for (int k = 0; k < MX_BK / 32; ++k) {
-                        const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
-                        const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
-                                                 : make_smem_desc(b_addr + k * 32, 16, 1024);
-                        const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, k, k) | (B_MN ? (1u << 16) : 0u);
-                        umma_mxf8_pair(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        for (int k = 0; k < MX_BK / 32; ++k) {
+                            const uint64_t ad = make_smem_desc(a_addr + k * 32, 16, 1024);
+                            const uint64_t bd = B_MN ? make_smem_desc(b_addr + k * 4096, 128 * MX_BK, 1024)
+                                                     : make_smem_desc(b_addr + k * 32, 16, 1024);
+                            const uint32_t idesc = make_idesc_mxf8(2 * BM, BN, k, k) | (B_MN ? (1u << 16) : 0u);
+                            umma_mxf8_pair(tmem_base, ad, bd, idesc, tmem_sfa, tmem_sfb, (kb | k) != 0);
+                        }
                     }
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 0));
                     umma_commit_pair(mapa_cluster(smem_u32(&sh->empty[st]), 1));
@@ -282,6 +296,44 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
             const uint8_t *sfb0 = ra.sfb + static_cast<size_t>(ni * 2) * kb4 * 512 + lane * 16;
             const bool second_b_atom = (ni * BN + 128) < p.N;
             const uint8_t *sfb1 = second_b_atom ? sfb0 + static_cast<size_t>(kb4) * 512 : sfb0;
+            if (fp4) {
+                // MXFP4: two atoms per operand tile and stage (one in a ragged last stage: the second index is clamped)
+                uint4 cur[6], nxt[6];
+                auto load6 = [&](uint4 (&v)[6], int kb) {
+                    const size_t o0 = static_cast<size_t>(min(2 * kb, kb4 - 1)) * 512, o1 = static_cast<size_t>(min(2 * kb + 1, kb4 - 1)) * 512;
+                    v[0] = *reinterpret_cast<const uint4 *>(sfa + o0);
+                    v[1] = *reinterpret_cast<const uint4 *>(sfa + o1);
+                    v[2] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + o0));
+                    v[3] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + o0));
+                    v[4] = __ldg(reinterpret_cast<const uint4 *>(sfb0 + o1));
+                    v[5] = __ldg(reinterpret_cast<const uint4 *>(sfb1 + o1));
+                };
+                load6(nxt, 0);
+                for (int kb = 0; kb < kblocks && ok; ++kb) {
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) cur[j] = nxt[j];
+                    load6(nxt, kb + 1 < kblocks ? kb + 1 : kb);
+                    const int st = it % kMxPStages;
+                    const uint32_t ph = (it / kMxPStages) & 1;
+                    ++it;
+                    if (lane == 0) ok = mbar_wait(&sh->empty[st], ph ^ 1, ctl, W_MBAR_EMPTY);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t col = tmem_sf0 + static_cast<uint32_t>(st) * kMxSfCols + lane_field;
+                    tmem_st_32x4(col, cur[0]);
+                    tmem_st_32x4(col + 4, cur[1]);
+                    tmem_st_32x4(col + 8, cur[2]);
+                    tmem_st_32x4(col + 12, cur[3]);
+                    tmem_st_32x4(col + 16, cur[4]);
+                    tmem_st_32x4(col + 20, cur[5]);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_cluster(smem_u32(&sh->full[st]), 0));
+                }
+                continue;
+            }
             // the atoms of the next kSfAhead K-steps are kept in flight (an L2 round trip is longer than a K-step)
             constexpr int kSfAhead = 4;
             uint4 va[kSfAhead], vb0[kSfAhead], vb1[kSfAhead];
@@ -336,7 +388,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kMxPairThreads, 1)
             if (lane == 0 && ctid < kMxPushLanes) {
                 const int units_per_dest = mt * kMxFlagsPerChunk;
                 const int total = (R - 1) * units_per_dest;
-                const size_t row_bytes = static_cast<size_t>(p.K);
+                const size_t row_bytes = static_cast<size_t>(Kb);
                 const int lane_id = cta * kMxPushLanes + ctid;
                 const int n_lanes = p.ctas_per_rank * kMxPushLanes;
                 uint8_t *buf = smem_push + ctid * kPushPieceBytes;
