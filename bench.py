@@ -128,6 +128,12 @@ def workload(op, world):
                     dtype="mxfp8", peak_scale=2.0,
                     desc=f"MXFP8 allgather_matmul: activations [{m_local},7168] per rank in e4m3 + E8M0/32 (quantised from "
                          f"bf16 normal(0,1) at set-up), gathered [16384,7168] x W[7168,4096] e4m3 -> bf16 [16384,4096]")
+    if op == "mxrs":
+        return dict(name="mxfp8_matmul_reduce_scatter", m=RS_M, k=RS_KLOCAL, n=RS_N, c_shape=(RS_M // world, RS_N),
+                    flops=2.0 * RS_M * RS_KLOCAL * RS_N, comm_bytes=(world - 1) * (RS_M // world) * RS_N * 2,
+                    dtype="mxfp8", peak_scale=2.0,
+                    desc=f"MXFP8 matmul_reduce_scatter: A[8192,2048] x B[2048,8192] per rank in e4m3 + E8M0/32 (quantised from "
+                         f"bf16 at set-up), summed over ranks, rows scattered -> bf16 D[{RS_M // world},8192]")
     if op == "moe":
         experts = 32 * world
         return dict(name="moe_dispatch_ffn_combine", m=MOE_M, k=MOE_K, n=MOE_N, top_k=MOE_TOPK, experts=experts,
@@ -440,7 +446,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar", "mxag", "moe", "quant", "fp4"])
+    ap.add_argument("--op", default="agmm", choices=["agmm", "mmrs", "mmar", "mxag", "mxrs", "moe", "quant", "fp4"])
     ap.add_argument("--variant", default="push", choices=["push", "remote_read", "gather_result"],
                     help="--op agmm only: data flow of the all-gather (push = AllGatherMatmul, the headline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -570,6 +576,35 @@ def main():
                 rt.launch(comm, a_codes, b_codes, c_d, symm, til, stream=stream, dtype=rt.BF16,
                           custom=[a_scale, b_scale], workspace=wsp)
             launches_per_step = 4 if args.mx_quant_in_step else 3
+        elif args.op == "mxrs":
+            comm = rt.MXFP8_MATMUL_REDUCE_SCATTER
+            til = rt.tiling(wl["m"], wl["k"], wl["n"], world)
+            need = rt.symmetric_bytes(comm, rt.BF16, til)
+            rt.shmem_init(rank, world, max(need, 1 << 20) + (8 << 20), f"tcp://{addr}:{port}")
+            symm = rt.shmem_malloc(max(need, 1024))
+
+            def mxrs_operands(r):
+                """MXFP8 operands of rank r, seeded by r so that every rank can rebuild its peers' for the parity check."""
+                gr = torch.Generator(device="cuda").manual_seed(8800 + r)
+                a_bf = torch.randn((wl["m"], wl["k"]), generator=gr, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+                w_bf = (torch.randn((wl["n"], wl["k"]), generator=gr, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16)
+                aq, asc = quant_rows(a_bf)
+                wq, wsc = quant_rows(w_bf)                    # K-major weights [n, k] (transB = 1)
+                return aq, asc, wq, wsc
+            a_codes, a_scale, wq_t, ws_t = mxrs_operands(rank)
+            c_d = torch.empty(wl["c_shape"], dtype=torch.bfloat16, device="cuda")
+            wsp = torch.zeros(lib().catccos_workspace_bytes(comm, rt.BF16, ctypes.byref(til)), dtype=torch.uint8, device="cuda")
+            kp_rs = rt.KernelParams()
+            kp_rs.ptrA, kp_rs.ptrB, kp_rs.ptrC = a_codes.data_ptr(), wq_t.data_ptr(), c_d.data_ptr()
+            cust_rs = (ctypes.c_void_p * 2)(a_scale.data_ptr(), ws_t.data_ptr())
+            kp_rs.customPtrs = ctypes.cast(cust_rs, ctypes.POINTER(ctypes.c_void_p))
+            kp_rs.customCount = 2
+
+            def step():      # the e4m3 form of the operator (the reference's example feeds e5m2 codes to the same kernel)
+                check(lib().LaunchAscend950MxFp8E4M3MatmulReduceScatterBF16(sptr, 0, 0, ctypes.byref(kp_rs),
+                                                                             ctypes.c_void_p(wsp.data_ptr()), ctypes.c_void_p(symm),
+                                                                             ctypes.byref(til), 0, 1))
+            launches_per_step = 3
         else:   # moe
             comm = rt.DISPATCH_FFN_COMBINE
             m, k, n, top_k, experts = wl["m"], wl["k"], wl["n"], wl["top_k"], wl["experts"]
@@ -674,7 +709,7 @@ def main():
     # pushes): exposed communication = (fused - compute-only) / fused
     exposed = None
     compute_only_ms = None
-    if world > 1 and args.op in ("agmm", "mmrs", "mmar", "mxag"):
+    if world > 1 and args.op in ("agmm", "mmrs", "mmar", "mxag", "mxrs"):
         check(lib().catccos_debug_set_flags(1))
         compute_only_ms, _ = timed_region(False)
         check(lib().catccos_debug_set_flags(0))
@@ -763,6 +798,17 @@ def main():
             err, rows = parity_dense(args.op, wl, rank, world, a_h, b_h, c_d, torch)
         elif args.op == "mxag":
             err, rows, bit_exact = parity_mxag(wl, rank, world, act, a_codes, a_scale, wq_t, ws_t, c_d, torch, dist)
+        elif args.op == "mxrs":
+            # rows of this rank's output block: sum over all ranks of dequant(A_s)[row] x dequant(B_s)
+            ridx = _sample_rows(wl["m"] // world, 48, 77, torch)
+            gold = None
+            for r_ in range(world):
+                aq_, as_, wq_, ws_ = (a_codes, a_scale, wq_t, ws_t) if r_ == rank else mxrs_operands(r_)
+                rows_g = (rank * (wl["m"] // world) + ridx).cuda()
+                part = torch.matmul(_dequant_e4m3_fast(aq_[rows_g].cpu(), as_[rows_g].cpu(), torch),
+                                    _dequant_e4m3_fast(wq_.cpu(), ws_.cpu(), torch).t())
+                gold = part if gold is None else gold + part
+            err, rows = _rel_err(c_d[ridx.cuda()].cpu(), gold, torch), int(ridx.numel())
         elif args.op == "moe":
             err, rows = parity_moe(wl, rank, world, x, idx, probs, expert_weights, c_d, torch)
         elif args.op == "fp4":
