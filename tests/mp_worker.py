@@ -187,6 +187,106 @@ def main():
         assert rc == 0, words
     check("moe", out, torch.from_numpy(gold), 2e-2)
 
+    # AllToAll-Matmul and Matmul-AllToAll (bf16)
+    chunk, k, n = 128, 256, 512
+    m = chunk * world
+    a, b = inputs.allgather_matmul_inputs(world, m, k, n, torch.bfloat16)
+    til = rt.tiling(m, k, n, world)
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for rep in range(2):
+        rt.launch(rt.ALLTOALL_MATMUL, a[rank].cuda(), b[rank].cuda(), c, symm, til)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    assembled = torch.cat([a[i][rank * chunk:(rank + 1) * chunk] for i in range(world)], dim=0)
+    check("alltoall_matmul", c, dense.matmul_fp32(assembled, b[rank]))
+    a, b = inputs.matmul_reduce_scatter_inputs(world, m, k, n, torch.bfloat16)
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for rep in range(2):
+        rt.launch(rt.MATMUL_ALLTOALL, a[rank].cuda(), b[rank].cuda(), c, symm, til)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    full = [dense.matmul_fp32(x_, y_) for x_, y_ in zip(a, b)]
+    check("matmul_alltoall", c, torch.cat([full[i][rank * chunk:(rank + 1) * chunk] for i in range(world)], dim=0))
+
+    # MXFP4 AllGather-Matmul and Matmul-ReduceScatter (K-major operands)
+    m, n, k = 128, 256, 256
+    rng = np.random.default_rng(4100)
+    fa, fsa, fda, fb, fsb, fdb = [], [], [], [], [], []
+    for r in range(world):
+        _, pa, sa, da = mxquant.quantize_mx_e2m1(rng.standard_normal((m * world, k)).astype(np.float32))
+        _, pb, sb, db = mxquant.quantize_mx_e2m1((rng.standard_normal((n, k)) * 0.05).astype(np.float32))
+        fa.append(pa); fsa.append(sa); fda.append(da); fb.append(pb); fsb.append(sb); fdb.append(db)
+    t = lambda a_: torch.from_numpy(np.ascontiguousarray(a_)).cuda()
+    til = rt.tiling(m, k, n, world)
+    wsp = torch.zeros(lib().catccos_workspace_bytes(rt.FP4_MX_ALLGATHER_MATMUL, rt.BF16, ctypes.byref(til)), dtype=torch.uint8, device="cuda")
+    c = torch.full((world * m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for rep in range(2):
+        rt.launch(rt.FP4_MX_ALLGATHER_MATMUL, t(fa[rank][:m]), t(fb[rank]), c, symm, til, trans_b=1, dtype=rt.BF16,
+                  custom=[t(fsa[rank][:m]), t(fsb[rank])], workspace=wsp)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    gathered = torch.from_numpy(np.concatenate([fda[r][:m] for r in range(world)]))
+    check("fp4_agmm", c, gathered @ torch.from_numpy(fdb[rank]).T, 5e-2)
+    til = rt.tiling(m * world, k, n, world)
+    wsp = torch.zeros(lib().catccos_workspace_bytes(rt.FP4_MX_MATMUL_REDUCE_SCATTER, rt.BF16, ctypes.byref(til)), dtype=torch.uint8, device="cuda")
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for rep in range(2):
+        rt.launch(rt.FP4_MX_MATMUL_REDUCE_SCATTER, t(fa[rank]), t(fb[rank]), d, symm, til, trans_b=1, dtype=rt.BF16,
+                  custom=[t(fsa[rank]), t(fsb[rank])], workspace=wsp)
+        rc, words = rt.last_status()
+        assert rc == 0, words
+    rows = slice(rank * m, (rank + 1) * m)
+    check("fp4_mmrs", d, sum(torch.from_numpy(fda[r][rows]) @ torch.from_numpy(fdb[r]).T for r in range(world)), 5e-2)
+
+    # standalone AllToAllV-GroupedMatmul and GroupedMatmul-AllToAllV, MXFP8 and MXFP4
+    for fmt, tol in (("fp8", 2e-2), ("fp4", 5e-2)):
+        m, n, k, experts = 96, 256, 256, 2 * world
+        epr = experts // world
+        rng = np.random.default_rng(5200)
+        counts = np.zeros((world, experts), dtype=np.int32)
+        for r in range(world):
+            w_ = rng.dirichlet(np.full(experts, 0.6))
+            c_ = np.floor(w_ * (m // world)).astype(np.int32)
+            counts[r] = np.maximum(c_, 0)
+        a_codes, a_scales, a_deq, b_codes, b_scales, w_deq = [], [], [], [], [], []
+        for r in range(world):
+            x_ = rng.standard_normal((m, k)).astype(np.float32)
+            if fmt == "fp8":
+                cc, ss, dd = mxquant.quantize_mx_e4m3(x_, "rne")
+            else:
+                _, cc, ss, dd = mxquant.quantize_mx_e2m1(x_)
+            a_codes.append(cc); a_scales.append(ss[:, :k // 32].copy()); a_deq.append(dd)
+            cs, sc_, ds = [], [], []
+            for le in range(epr):
+                if fmt == "fp8":
+                    w_ = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+                    cq, sq, dq = mxquant.quantize_mx_e4m3_axis0(w_, "rne")
+                    cs.append(cq); ds.append(dq)
+                    sc_.append(np.ascontiguousarray(sq[:k // 32].reshape(k // 64, 2, n).transpose(0, 2, 1)))
+                else:
+                    w_ = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+                    _, cq, sq, dq = mxquant.quantize_mx_e2m1(w_)
+                    cs.append(cq); ds.append(np.ascontiguousarray(dq.T)); sc_.append(sq[:, :k // 32].copy())
+            b_codes.append(np.stack(cs)); b_scales.append(np.stack(sc_)); w_deq.append(ds)
+        for comm, name in ((rt.FP8_MX_ALLTOALLV_GROUPED_MATMUL if fmt == "fp8" else rt.FP4_MX_ALLTOALLV_GROUPED_MATMUL, "atav_gmm"),
+                           (rt.FP8_MX_GROUPED_MATMUL_ALLTOALLV if fmt == "fp8" else rt.FP4_MX_GROUPED_MATMUL_ALLTOALLV, "gmm_atav")):
+            til = rt.tiling(m, k, n, world, expertNum=experts, epSize=world)
+            need = rt.symmetric_bytes(comm, rt.BF16, til)
+            assert need <= (200 << 20), need
+            wsp = torch.zeros(lib().catccos_workspace_bytes(comm, rt.BF16, ctypes.byref(til)), dtype=torch.uint8, device="cuda")
+            c = torch.full((world * m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            gt = torch.zeros(world * epr, dtype=torch.int32, device="cuda")
+            for rep in range(2):
+                rt.launch(comm, t(a_codes[rank]), t(b_codes[rank]), c, symm, til, dtype=rt.BF16,
+                          custom=[t(a_scales[rank]), t(b_scales[rank]), t(counts[rank]), gt], workspace=wsp)
+                rc, words = rt.last_status()
+                assert rc == 0, words
+            if name == "atav_gmm":
+                gold_rows = moe.alltoallv_grouped_matmul(a_deq, w_deq, counts, world, epr)[0][rank]
+            else:
+                gold_rows = moe.grouped_matmul_alltoallv(a_deq, w_deq, counts, world, epr)[rank]
+            check(f"{fmt}_{name}", c[:gold_rows.shape[0]], torch.from_numpy(np.ascontiguousarray(gold_rows)), tol)
+
     rt.shmem_finalize()
     if failures:
         print(f"[rank {rank}] FAILED {failures}", flush=True)
