@@ -31,15 +31,6 @@ __device__ __forceinline__ uint32_t *mflag(const MoeParams &p, int pe, uint32_t 
 // One CTA (1024 threads) per rank.  Stable counting sort with warp-private counters: warp w owns
 // the w-th contiguous slice of the flattened [m, topK] expert ids, walks it 32 ids at a time and
 // ranks equal ids inside a step with __match_any_sync, so equal experts keep their index order.
-// lanes of the warp that hold the same key as this one (what __match_any_sync returns), by 32 shuffles and
-// compares: on this architecture that is several times faster than the match instruction
-__device__ __forceinline__ unsigned same_key_mask(int key) {
-    unsigned mask = 0;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) mask |= (__shfl_sync(0xffffffffu, key, j) == key ? 1u : 0u) << j;
-    return mask;
-}
-
 __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
     extern __shared__ int smem_i[];
     const int E = p.experts;
@@ -91,7 +82,7 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
             const int raw = raws[j];
             const bool valid = raw >= 0;
             const int key = valid ? raw : -1 - lane;
-            const unsigned mask = p.route_match ? __match_any_sync(0xffffffffu, key) : same_key_mask(key);
+            const unsigned mask = __match_any_sync(0xffffffffu, key);
             if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
             __syncwarp();
         }
@@ -138,7 +129,7 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
             const int raw = raws[j];
             const bool valid = raw >= 0;
             const int key = valid ? raw : -1 - lane;
-            const unsigned mask = p.route_match ? __match_any_sync(0xffffffffu, key) : same_key_mask(key);
+            const unsigned mask = __match_any_sync(0xffffffffu, key);
             const int rnk = __popc(mask & ((1u << lane) - 1u));
             int dst = -1;
             if (valid) dst = cnt[warp * E + key] + rnk;
@@ -574,9 +565,7 @@ int moe_launch_wait_dispatch(const MoeParams &p, cudaStream_t stream) {
     return CATCCOS_OK;
 }
 
-int moe_launch_route(const MoeParams &p_in, cudaStream_t stream) {
-    MoeParams p = p_in;
-    if (const char *e = getenv("CATCCOS_ROUTE_MATCH")) p.route_match = atoi(e) != 0;
+int moe_launch_route(const MoeParams &p, cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(34) * p.experts * sizeof(int);
     cudaError_t e = cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e == cudaSuccess) {

@@ -69,7 +69,6 @@ struct MoeParams {
     MoeLayout lay;
     int world, rank_base, n_local, ctas_per_rank;
     int m, K, N, top_k, experts, experts_per_rank;
-    int route_match;            // routing kernel: 1 = __match_any_sync, 0 = shuffle-and-compare (CATCCOS_ROUTE_MATCH)
     uint32_t epoch;
     uint64_t timeout_ns;
     int *status;
