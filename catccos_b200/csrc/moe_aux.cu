@@ -31,6 +31,18 @@ __device__ __forceinline__ uint32_t *mflag(const MoeParams &p, int pe, uint32_t 
 // One CTA (1024 threads) per rank.  Stable counting sort with warp-private counters: warp w owns
 // the w-th contiguous slice of the flattened [m, topK] expert ids, walks it 32 ids at a time and
 // ranks equal ids inside a step with __match_any_sync, so equal experts keep their index order.
+// lanes of the warp whose key equals this lane's (what __match_any_sync returns), from one ballot per key bit:
+// keys are expert ids below 2^bits, or negative for lanes that take no part (they match nobody but themselves)
+__device__ __forceinline__ unsigned same_key_lanes(int key, int bits, int lane) {
+    const bool valid = key >= 0;
+    unsigned mask = __ballot_sync(0xffffffffu, valid);
+    for (int b = 0; b < bits; ++b) {
+        const unsigned has = __ballot_sync(0xffffffffu, valid && ((key >> b) & 1));
+        mask &= ((key >> b) & 1) ? has : ~has;
+    }
+    return valid ? mask : (1u << lane);
+}
+
 __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
     extern __shared__ int smem_i[];
     const int E = p.experts;
@@ -63,6 +75,10 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
     }
     __syncthreads();
 
+    // equal keys inside a step of 32 ids are found with one ballot per key bit (p.route_ballot; 0: the match instruction)
+    int key_bits = 0;
+    if (p.route_ballot)
+        while ((1 << key_bits) < E) ++key_bits;
     const int chunk = ((total + 31) / 32 + 31) / 32 * 32;
     const int begin = warp * chunk;
     const int end = min(total, begin + chunk);
@@ -82,7 +98,7 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
             const int raw = raws[j];
             const bool valid = raw >= 0;
             const int key = valid ? raw : -1 - lane;
-            const unsigned mask = __match_any_sync(0xffffffffu, key);
+            const unsigned mask = key_bits ? same_key_lanes(raw, key_bits, lane) : __match_any_sync(0xffffffffu, key);
             if (valid && lane == __ffs(mask) - 1) cnt[warp * E + key] += __popc(mask);
             __syncwarp();
         }
@@ -129,7 +145,7 @@ __global__ void __launch_bounds__(1024, 1) moe_route_kernel(const MoeParams p) {
             const int raw = raws[j];
             const bool valid = raw >= 0;
             const int key = valid ? raw : -1 - lane;
-            const unsigned mask = __match_any_sync(0xffffffffu, key);
+            const unsigned mask = key_bits ? same_key_lanes(raw, key_bits, lane) : __match_any_sync(0xffffffffu, key);
             const int rnk = __popc(mask & ((1u << lane) - 1u));
             int dst = -1;
             if (valid) dst = cnt[warp * E + key] + rnk;
@@ -565,7 +581,10 @@ int moe_launch_wait_dispatch(const MoeParams &p, cudaStream_t stream) {
     return CATCCOS_OK;
 }
 
-int moe_launch_route(const MoeParams &p, cudaStream_t stream) {
+int moe_launch_route(const MoeParams &p_in, cudaStream_t stream) {
+    MoeParams p = p_in;
+    p.route_ballot = 1;
+    if (const char *e = getenv("CATCCOS_ROUTE_BALLOT")) p.route_ballot = atoi(e) != 0;
     const size_t smem = static_cast<size_t>(34) * p.experts * sizeof(int);
     cudaError_t e = cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e == cudaSuccess) {

@@ -69,6 +69,7 @@ struct MoeParams {
     MoeLayout lay;
     int world, rank_base, n_local, ctas_per_rank;
     int m, K, N, top_k, experts, experts_per_rank;
+    int route_ballot;           // routing kernel: equal keys by ballots (1) or by the match instruction (0)
     uint32_t epoch;
     uint64_t timeout_ns;
     int *status;
