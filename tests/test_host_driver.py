@@ -84,6 +84,27 @@ def test_single_rank_driver_run(driver, tmp_path, kernel, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("kernel", ["agmmwg", "agmmrr", "a5atamm", "a5mmata"])
+def test_single_rank_driver_run_of_the_data_flow_variants(driver, tmp_path, kernel):
+    """The variants' operator classes through the driver at rank_size 1 (every one is then the plain product); the
+    gather-result operator also writes the gathered A, which must be the input bit for bit."""
+    from oracle import dense, inputs, verify
+    m, n, k = 384, 520, 256
+    a, b = inputs.allgather_matmul_inputs(1, m, k, n, torch.bfloat16)
+    _write_dense_files(str(tmp_path), 1, a, b)
+    r = subprocess.run([driver, kernel, "27", "1", "0", "tcp://127.0.0.1:8788", str(m), str(n), str(k), str(tmp_path),
+                        "0", "0", "1", "0", "0", "2", "3"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    raw = np.fromfile(os.path.join(tmp_path, "output_0.bin"), dtype=np.uint16)
+    out = torch.from_numpy(raw.reshape(m, n)).view(torch.bfloat16)
+    ok, precision, eb = verify.reference_check(out, dense.matmul_fp32(a[0], b[0]), k)
+    assert ok, (precision, eb)
+    if kernel == "agmmwg":
+        got = np.fromfile(os.path.join(tmp_path, "output_gather_a.bin"), dtype=np.uint16).reshape(m, k)
+        assert np.array_equal(got, a[0].view(torch.uint16).numpy())
+
+
+@pytest.mark.gpu
 def test_two_rank_driver_run(driver, tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
