@@ -98,3 +98,34 @@ def test_buffer_sizes_of_the_benchmark_configurations():
     assert 0 < s <= 1004 << 20 and w > 0
     assert symm(rt.MXFP8_MATMUL_REDUCE_SCATTER, rt.BF16, 8192, 2048, 8192, 8)[0] == 2 * 8192 * 8192 * 2
     assert L.catccos_fp4_gemm_workspace_bytes(1, 128, 256, 256) == 2048 + 4096 + 64    # atoms of A, of B, status words
+
+
+def test_buffer_sizes_of_the_variants_and_fp4_operators():
+    """The data-flow variants use the region of the operator they derive from; the MXFP4 operators gather half the
+    code bytes of their MXFP8 twins with the same scale atoms."""
+    import ctypes
+    from catccos_b200 import lib, runtime as rt
+    L = lib()
+
+    def symm(comm, m, k, n, ranks, **kw):
+        t = rt.tiling(m, k, n, ranks, **kw)
+        return L.catccos_symmetric_bytes(comm, rt.BF16, ctypes.byref(t)), L.catccos_workspace_bytes(comm, rt.BF16, ctypes.byref(t))
+
+    ag = symm(rt.ALLGATHER_MATMUL, 1024, 8192, 4096, 8)
+    assert symm(rt.ALLGATHER_MATMUL_WITH_GATHER_RESULT, 1024, 8192, 4096, 8) == ag
+    assert symm(rt.ALLGATHER_MATMUL_REMOTE_READ, 1024, 8192, 4096, 8) == ag
+    assert symm(rt.ALLTOALL_MATMUL, 8 * 1024, 8192, 4096, 8) == ag                     # m = rows of every rank's A
+    rs = symm(rt.MATMUL_REDUCE_SCATTER, 8192, 2048, 8192, 8)
+    assert symm(rt.MATMUL_ALLTOALL, 8192, 2048, 8192, 8) == rs
+    mxrs = symm(rt.MXFP8_MATMUL_REDUCE_SCATTER, 8192, 2048, 8192, 8)
+    assert symm(rt.MXFP8_MATMUL_ALLTOALL, 8192, 2048, 8192, 8) == mxrs
+    assert symm(rt.FP4_MX_MATMUL_REDUCE_SCATTER, 8192, 2048, 8192, 8) == mxrs          # partial tiles, not operands, are exchanged
+    s8, w8 = symm(rt.FP8_MX_ALLGATHER_MATMUL, 2048, 7168, 4096, 8)
+    s4, w4 = symm(rt.FP4_MX_ALLGATHER_MATMUL, 2048, 7168, 4096, 8)
+    assert w4 == w8 and s8 - s4 == 2 * 8 * 2048 * 7168 // 2                            # half the code bytes in both halves
+    kw = dict(expertNum=256, epSize=8)
+    for c8, c4 in ((rt.FP8_MX_ALLTOALLV_GROUPED_MATMUL, rt.FP4_MX_ALLTOALLV_GROUPED_MATMUL),
+                   (rt.FP8_MX_GROUPED_MATMUL_ALLTOALLV, rt.FP4_MX_GROUPED_MATMUL_ALLTOALLV)):
+        a8, b8 = symm(c8, 4096, 7168, 4096, 8, **kw)
+        a4, b4 = symm(c4, 4096, 7168, 4096, 8, **kw)
+        assert 0 < a4 < a8 <= 1004 << 20 and b4 == b8 > 0
