@@ -45,6 +45,10 @@ def _define():
     lib.define("allgather_matmul(Tensor a, Tensor b, int rank_size) -> Tensor")
     lib.define("matmul_reduce_scatter(Tensor a, Tensor b, int rank_size) -> Tensor")
     lib.define("matmul_allreduce(Tensor a, Tensor b, int rank_size) -> Tensor")
+    lib.define("allgather_matmul_remote_read(Tensor a, Tensor b, int rank_size) -> Tensor")
+    lib.define("allgather_matmul_with_gather_result(Tensor a, Tensor b, int rank_size) -> (Tensor, Tensor)")
+    lib.define("alltoall_matmul(Tensor a, Tensor b, int rank_size) -> Tensor")
+    lib.define("matmul_alltoall(Tensor a, Tensor b, int rank_size) -> Tensor")
     lib.define("finalize() -> int")
     lib.impl("init", _init, "CompositeExplicitAutograd")
     lib.impl("finalize", _finalize, "CompositeExplicitAutograd")
@@ -54,6 +58,13 @@ def _define():
     lib.impl("allgather_matmul", _allgather_matmul_meta, "Meta")
     lib.impl("matmul_reduce_scatter", _matmul_reduce_scatter_meta, "Meta")
     lib.impl("matmul_allreduce", _matmul_allreduce_meta, "Meta")
+    for name, cuda, meta in (("allgather_matmul_remote_read", _allgather_matmul_remote_read, _allgather_matmul_meta),
+                             ("allgather_matmul_with_gather_result", _allgather_matmul_with_gather_result,
+                              _allgather_matmul_with_gather_result_meta),
+                             ("alltoall_matmul", _alltoall_matmul, _matmul_allreduce_meta),
+                             ("matmul_alltoall", _matmul_alltoall, _matmul_allreduce_meta)):
+        lib.impl(name, cuda, "CUDA")
+        lib.impl(name, meta, "Meta")
     _LIB = lib
 
 
@@ -121,7 +132,7 @@ def _check_operands(a, b, rank_size):
     _check(b.size(0) == a.size(1), f"A/K shape mismatch, a.size(1)={a.size(1)}, b.size(0)={b.size(0)}")
 
 
-def _run(comm, a, b, out_rows, rank_size):
+def _run(comm, a, b, out_rows, rank_size, custom=None):
     _check_operands(a, b, rank_size)
     m, k, n = a.size(0), a.size(1), b.size(1)
     a_c, b_c = a.contiguous(), b.contiguous()
@@ -130,7 +141,7 @@ def _run(comm, a, b, out_rows, rank_size):
     need = rt.symmetric_bytes(comm, rt._DTYPE[a.dtype], til)
     with torch.cuda.device(a.device):
         symm = _symm(need) if rank_size > 1 else 0
-        rt.launch(comm, a_c, b_c, c, symm, til)
+        rt.launch(comm, a_c, b_c, c, symm, til, custom=custom)
     return c
 
 
@@ -149,6 +160,34 @@ def _matmul_reduce_scatter(a, b, rank_size):
 def _matmul_allreduce(a, b, rank_size):
     """D[m, n] = sum_r A_r @ B_r on every rank (examples/matmul_allreduce/matmul_allreduce_host.h:17-96)."""
     return _run(rt.MATMUL_ALLREDUCE, a, b, a.size(0), rank_size)
+
+
+def _allgather_matmul_remote_read(a, b, rank_size):
+    """The same product with the remote-read data flow (examples/allgather_matmul_remote_read)."""
+    return _run(rt.ALLGATHER_MATMUL_REMOTE_READ, a, b, a.size(0) * rank_size, rank_size)
+
+
+def _allgather_matmul_with_gather_result(a, b, rank_size):
+    """(C, gathered A [rank_size * m, k]) (examples/allgather_matmul_with_gather_result)."""
+    gathered = torch.empty((a.size(0) * rank_size, a.size(1)), dtype=a.dtype, device=a.device)
+    c = _run(rt.ALLGATHER_MATMUL_WITH_GATHER_RESULT, a, b, a.size(0) * rank_size, rank_size, custom=[gathered])
+    return c, gathered
+
+
+def _alltoall_matmul(a, b, rank_size):
+    """C[m, n]: block j of every rank's A (rank order) times this rank's B (examples/ascend950_alltoall_matmul)."""
+    _check(a.size(0) % rank_size == 0, f"m ({a.size(0)}) must be divisible by rank_size ({rank_size})")
+    return _run(rt.ALLTOALL_MATMUL, a, b, a.size(0), rank_size)
+
+
+def _matmul_alltoall(a, b, rank_size):
+    """C[m, n]: row block j of every rank's A_i @ B_i, in rank order (examples/ascend950_matmul_alltoall)."""
+    _check(a.size(0) % rank_size == 0, f"m ({a.size(0)}) must be divisible by rank_size ({rank_size})")
+    return _run(rt.MATMUL_ALLTOALL, a, b, a.size(0), rank_size)
+
+
+def _allgather_matmul_with_gather_result_meta(a, b, rank_size):
+    return a.new_empty((a.size(0) * rank_size, b.size(1))), a.new_empty((a.size(0) * rank_size, a.size(1)))
 
 
 def _allgather_matmul_meta(a, b, rank_size):

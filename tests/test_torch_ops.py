@@ -23,6 +23,11 @@ def test_meta_kernels_infer_shapes():
     assert torch.ops.catccos.matmul_reduce_scatter(a, b, 4).shape == (24, 40)
     assert torch.ops.catccos.matmul_allreduce(a, b, 4).shape == (96, 40)
     assert torch.ops.catccos.allgather_matmul(a, b, 4).dtype == torch.float16
+    assert torch.ops.catccos.allgather_matmul_remote_read(a, b, 4).shape == (384, 40)
+    c, g = torch.ops.catccos.allgather_matmul_with_gather_result(a, b, 4)
+    assert c.shape == (384, 40) and g.shape == (384, 64)
+    assert torch.ops.catccos.alltoall_matmul(a, b, 4).shape == (96, 40)
+    assert torch.ops.catccos.matmul_alltoall(a, b, 4).shape == (96, 40)
 
 
 def test_init_argument_checks_and_idle_finalize():
@@ -65,8 +70,12 @@ def test_single_rank_operators_on_cuda(dtype):
     gold = a.float() @ b.float()
     assert torch.ops.catccos.init(0, 1, 64 << 20, "tcp://127.0.0.1:8799") == 0
     try:
+        c, g = torch.ops.catccos.allgather_matmul_with_gather_result(a, b, 1)
+        torch.cuda.synchronize()
+        assert torch.equal(g, a) and ((c.float() - gold).abs() / gold.abs().clamp(min=1.0)).max().item() <= 1e-2
         for op in (torch.ops.catccos.allgather_matmul, torch.ops.catccos.matmul_reduce_scatter,
-                   torch.ops.catccos.matmul_allreduce):
+                   torch.ops.catccos.matmul_allreduce, torch.ops.catccos.allgather_matmul_remote_read,
+                   torch.ops.catccos.alltoall_matmul, torch.ops.catccos.matmul_alltoall):
             c = op(a, b, 1)
             torch.cuda.synchronize()
             assert c.shape == (m, n) and c.dtype == dtype
